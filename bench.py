@@ -1,0 +1,348 @@
+#!/usr/bin/env python
+"""Benchmark of the sparse-decode attention hot path (and, as extras, the other configurations).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload ...]
+
+Headline workload (N = 1): the batched DS-V4-shaped sparse decode step — batch 32,
+context ~ U[32K, 128K] per sequence, top-k 2048, bf16 queries over an int8 latent KV
+cache with per-token fp16 scales, FP8-E4M3 index keys, 64 heads x 576 (V = first 512),
+indexer 16 heads x 64, seed 1.  One "step" = indexer score -> top-k -> indexed sparse
+attention for the whole batch (one decoded token per sequence), so tokens/s = batch /
+step time.  With N > 1 every rank holds its own batch of 32 sequences (sequence
+sharding, no collective on the data path): weak scaling.
+
+Prints ONE JSON line on rank 0.  `value` is timed with the inputs resident in HBM;
+`e2e` goes through the public Python operator with the step's inputs in pinned host
+memory and the result read back to the host inside the timed region.  The latent KV
+and index-key tables are the decode cache (state that lives on the device between
+steps, like weights); the per-step inputs are the queries, indexer queries and
+head weights.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "sparse_decode_attn_tokens_per_s"
+UNIT = "tokens/s"
+WORKLOAD = "c3_batched_sparse_decode_b32_ctx32k-128k_topk2048_int8kv_fp8idx"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi samples during the timed region (read-only query)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows = []
+        self.proc = None
+        self.gpu = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); smax.append(float(r[2]))
+            except Exception:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- #
+# CPU arm (the oracle's float32 NumPy formulation, timed)
+# --------------------------------------------------------------------------- #
+
+def cpu_decode_batch(c, seqs) -> float:
+    """Seconds the NumPy formulation needs for the given sequences of workload `c`."""
+    from moespresso_b200 import synth
+    from oracle import ds4
+    t0 = time.perf_counter()
+    for b in seqs:
+        s, n = int(c["row_start"][b]), int(c["lens"][b])
+        keys = synth.e4m3_bits_to_f32(c["idx_key_bits"][s:s + n])
+        ds4.sparse_decode_step(c["q"][b], c["kv"][s:s + n], c["idx_q"][b], keys, c["idx_w"][b], k=c["k"],
+                               scale=c["scale"], d_v=c["d_v"], kv_scales=c["kv_scales"][s:s + n], dtype=np.float32)
+    return time.perf_counter() - t0
+
+
+def run_reference(args):
+    """The reference formulation of the path on the host cores (NumPy; MLX, which the
+    reference uses, has no Linux build here).  Rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    from moespresso_b200 import synth
+    cores = len(os.sched_getaffinity(0))
+    c = synth.config3(seed=1)
+    B = int(c["lens"].size)
+    sample = list(range(B))
+    for _ in range(args.warmup):
+        cpu_decode_batch(c, sample[:4])
+    t = 0.0
+    for _ in range(args.steps):
+        t += cpu_decode_batch(c, sample)
+    ms = t / args.steps * 1e3
+    val = B / (ms / 1e3)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "batch": B, "topk": int(c["k"]), "rows_total": int(c["lens"].sum())},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"all {B} sequences of the batch per step, NumPy float32 (BLAS threads = {cores})"},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------- #
+# GPU arm
+# --------------------------------------------------------------------------- #
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the secondary workloads (c1, c2)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--small", action="store_true", help="reduced sizes (for profiling captures only)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from moespresso_b200 import _abi, synth
+    from moespresso_b200.deepseek_v4.attention import topk_select
+    from moespresso_b200.deepseek_v4.decode_step import LatentCache
+    from moespresso_b200.deepseek_v4.indexed_attention_kernel import indexer_scores, sparse_attention
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path for the product kernels")
+    _abi.load()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    W = max(args.warmup, 3)
+    K = args.steps
+
+    if args.small:
+        c = synth.config3(seed=1 + rank, B=8, lo=16384, hi=32768)
+    else:
+        c = synth.config3(seed=1 + rank)
+    B = int(c["lens"].size)
+    total = int(c["lens"].sum())
+    kk, scale, d_v = int(c["k"]), float(c["scale"]), int(c["d_v"])
+    cache = LatentCache(
+        kv=torch.from_numpy(c["kv"]).to(dev), kv_scales=torch.from_numpy(c["kv_scales"]).to(dev),
+        idx_keys=torch.from_numpy(c["idx_key_bits"]).to(dev).view(torch.float8_e4m3fn),
+        row_start=torch.from_numpy(c["row_start"]).to(dev),
+        row_count=torch.from_numpy(c["lens"].astype(np.int32)).to(dev), max_rows=int(c["lens"].max()))
+    q_h = torch.from_numpy(c["q"]).to(torch.bfloat16).pin_memory()
+    iq_h = torch.from_numpy(c["idx_q"]).to(torch.bfloat16).pin_memory()
+    iw_h = torch.from_numpy(c["idx_w"]).pin_memory()
+    q_d, iq_d, iw_d = q_h.to(dev), iq_h.to(dev), iw_h.to(dev)
+    out_h = torch.empty((B, 64, d_v), dtype=torch.float32).pin_memory()
+
+    stage_events = []
+
+    def step(q, iq, iw, record=False):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if record else None
+        if record: ev[0].record()
+        scores = indexer_scores(iq[:, :, None, :], iw[:, None, :], cache.idx_keys, n_rows=cache.max_rows,
+                                row_start=cache.row_start, row_count=cache.row_count)
+        if record: ev[1].record()
+        ids = topk_select(scores, kk, valid=cache.row_count, row_start=cache.row_start, n=cache.max_rows)
+        if record: ev[2].record()
+        out = sparse_attention(q[:, :, None, :], cache.kv, ids[:, None, :], None, pos0=0, window=0, ratio=0,
+                               scale=scale, d_v=d_v, kv_scales=cache.kv_scales, comp_row_start=cache.row_start,
+                               comp_row_count=cache.row_count, n_comp=cache.max_rows)
+        if record:
+            ev[3].record()
+            stage_events.append(ev)
+        return out
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    sampler = ClockSampler(local)
+    for _ in range(W):
+        step(q_d, iq_d, iw_d)
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        step(q_d, iq_d, iw_d, record=True)
+    e1.record()
+    barrier()
+    ms_step = max_over_ranks(e0.elapsed_time(e1) / K)
+    stage_ms = np.array([[ev[i].elapsed_time(ev[i + 1]) for i in range(3)] for ev in stage_events]).mean(axis=0)
+
+    # end to end: pinned host inputs -> device -> step -> result back on the host, every step
+    for _ in range(2):
+        out_h.copy_(step(q_h.to(dev, non_blocking=True), iq_h.to(dev, non_blocking=True),
+                         iw_h.to(dev, non_blocking=True))[:, :, 0, :], non_blocking=True)
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(K):
+        o = step(q_h.to(dev, non_blocking=True), iq_h.to(dev, non_blocking=True), iw_h.to(dev, non_blocking=True))
+        out_h.copy_(o[:, :, 0, :], non_blocking=True)
+        torch.cuda.current_stream().synchronize()   # the caller consumes the result of every step
+    f1.record()
+    barrier()
+    ms_e2e = max_over_ranks(f0.elapsed_time(f1) / K)
+    clocks = sampler.stop()
+
+    hbm, tf, which = measured_peaks()
+    # algorithmic bytes of the dominant kernel (indexer score scan): FP8 keys read once, fp32 scores written once
+    idx_bytes = total * 64 + total * 4 + B * (16 * 64 * 2 + 16 * 4)
+    achieved = idx_bytes / (stage_ms[0] * 1e-3) / 1e9
+    step_bytes = idx_bytes + total * 4 + B * (kk * (576 + 2) + 64 * 576 * 2 + 64 * d_v * 4 + kk * 4 * 2)
+
+    line = {
+        "metric": METRIC, "value": world * B / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K,
+        "warmup": W, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD if not args.small else WORKLOAD + "_SMALL", "batch_per_gpu": B,
+                   "rows_total_per_gpu": total, "topk": kk, "heads": 64, "d_qk": 576, "d_v": d_v,
+                   "indexer": "16x64 fp8-e4m3 keys", "kv": "int8 + fp16 per-token scale",
+                   "parallelism": f"sequence-sharded x{world}, no collective",
+                   "l2": "inputs (1.7 GB per GPU) exceed L2, no flush needed"},
+        "e2e": {"value": world * B / (ms_e2e * 1e-3), "unit": UNIT,
+                "h2d_bytes_per_step": int(q_h.numel() * 2 + iq_h.numel() * 2 + iw_h.numel() * 4),
+                "d2h_bytes_per_step": int(out_h.numel() * 4), "ms_per_step": ms_e2e},
+        "gpu_launches": 6 * K,
+        "stage_ms": {"indexer_scores": float(stage_ms[0]), "topk_select": float(stage_ms[1]),
+                     "sparse_attention": float(stage_ms[2])},
+        "roofline": {"bound": "hbm", "kernel": "indexer_tc_kernel<64, fp8>", "achieved": achieved, "peak": hbm,
+                     "unit": "GB/s", "frac": achieved / hbm, "peak_source": which, "traffic": None,
+                     "frac_of_nominal_8TBs": achieved / 8000.0,
+                     "whole_step_GBs": step_bytes / (ms_step * 1e-3) / 1e9},
+        "clocks": clocks,
+    }
+
+    if rank == 0 and world == 1 and not args.no_extras and not args.small:
+        line["extras"] = run_extras(torch, dev, tf)
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cores = len(os.sched_getaffinity(0))
+        seqs = list(range(B))
+        t = cpu_decode_batch(c, seqs)
+        line["cpu_baseline"] = {"value": len(seqs) / t, "unit": UNIT, "cores": cores, "kind": "port",
+                                "sample": f"one pass over all {len(seqs)} sequences of the batch, NumPy float32"}
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_extras(torch, dev, tf_peak) -> dict:
+    """Secondary workloads, single GPU: config 1 (fp32 decode, latency) and config 2 (Qwen prefill)."""
+    from moespresso_b200 import synth
+    from moespresso_b200.deepseek_v4.decode_step import LatentCache, sparse_decode_step
+    from moespresso_b200.qwen.full_attention import sdpa_fa_prefill
+    ex = {}
+
+    def timeit(fn, iters=20, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / iters
+
+    try:
+        c = synth.config1()
+        t = lambda x: torch.from_numpy(x).to(dev)
+        cache = LatentCache(kv=t(c["kv"]), kv_scales=None, idx_keys=t(c["idx_keys"]),
+                            row_start=torch.zeros(1, dtype=torch.int64, device=dev),
+                            row_count=torch.tensor([4096], dtype=torch.int32, device=dev), max_rows=4096)
+        q, iq, iw = t(c["q"])[None], t(c["idx_q"])[None], t(c["idx_w"])[None]
+        ms = timeit(lambda: sparse_decode_step(q, iq, iw, cache, k=c["k"], scale=c["scale"], d_v=c["d_v"]))
+        ex["c1_fp32_decode_step_us"] = ms * 1e3
+    except Exception as e:  # report, do not hide
+        ex["c1_error"] = repr(e)
+    try:
+        c = synth.config2()
+        t = lambda x: torch.from_numpy(x).to(dev).to(torch.bfloat16)
+        q, k, v, g = t(c["q"]), t(c["k"]), t(c["v"]), t(c["gate"])
+        ms = timeit(lambda: sdpa_fa_prefill(q, k, v, c["scale"], gate=g, layout="lhd"), iters=10)
+        S, Hq, D = q.shape
+        flops = 4.0 * Hq * D * S * (S + 1) / 2
+        ex["c2_qwen_prefill_ms"] = ms
+        ex["c2_qwen_prefill_tflops_causal"] = flops / (ms * 1e-3) / 1e12
+        ex["c2_frac_of_bf16_peak"] = ex["c2_qwen_prefill_tflops_causal"] / tf_peak
+    except Exception as e:
+        ex["c2_error"] = repr(e)
+    return ex
+
+
+if __name__ == "__main__":
+    main()

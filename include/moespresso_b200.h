@@ -1,0 +1,226 @@
+/*
+ * moespresso_b200 — C ABI of the B200 (sm_100a) attention hot path.
+ *
+ * The reference project (steadfastgaze/MoEspresso) has no FFI for this path: its
+ * boundary is a set of module-level Python functions that launch Metal kernels
+ * through MLX.  Each entry point below is what a binding for one of those
+ * functions would call; the comment above it cites the reference function it
+ * replaces (path within that project : line).
+ *
+ * Conventions
+ *  - every pointer named in an args struct is DEVICE memory unless the comment
+ *    says "host"; the library never allocates or frees user-visible memory and
+ *    never synchronises the device; all work is enqueued on `stream`
+ *    (a cudaStream_t passed as void*);
+ *  - strides are in ELEMENTS, the innermost (feature) axis is contiguous;
+ *  - return value 0 = enqueued, negative = mxb_status, with a thread-local
+ *    message available from mxb_last_error();
+ *  - `status` members point at one device int32 that a kernel sets non-zero
+ *    when one of its bounded waits gave up (the launch still returns); may be
+ *    NULL.
+ */
+#ifndef MOESPRESSO_B200_H
+#define MOESPRESSO_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MXB_ABI_VERSION 1
+
+typedef enum {
+  MXB_F32 = 0,
+  MXB_F16 = 1,
+  MXB_BF16 = 2,
+  MXB_F8E4M3 = 3, /* FP8 E4M3FN, one byte per element */
+  MXB_I8 = 4      /* int8 with one fp16 scale per row */
+} mxb_dtype;
+
+typedef enum {
+  MXB_OK = 0,
+  MXB_ERR_INVALID = -1,     /* contract violation (shape, dtype, alignment) */
+  MXB_ERR_UNSUPPORTED = -2, /* valid request this build has no kernel for */
+  MXB_ERR_WORKSPACE = -3,   /* workspace missing or too small */
+  MXB_ERR_CUDA = -4         /* a CUDA runtime / driver call failed */
+} mxb_status;
+
+int mxb_abi_version(void);
+const char* mxb_last_error(void);
+
+/* ------------------------------------------------------------------------ *
+ * Indexer score.
+ * Replaces  indexer_scores_tiled_live(q, weights, index_comp, *, pos0, ratio)
+ *           src/moespresso/runtime/deepseek_v4/indexed_attention_kernel.py:1888-1961
+ * and the decode chain  q @ pool^T -> relu -> * w -> sum_h
+ *           src/moespresso/runtime/deepseek_v4/model.py:1041-1057,
+ *           fused_qat_indexer_scores, indexer_score_kernel.py:354-409.
+ *
+ *   scores[b,t,r] = sum_h weights[b,t,h] * max(q[b,h,t,:] . keys[b][r,:], 0)
+ *   ratio > 0 : scores[b,t,r] = -inf for r >= min((pos0+t+1)/ratio, rows(b))
+ *   ratio == 0: no mask (decode)
+ * keys of sequence b are rows [row_start[b], row_start[b] + row_count[b]) of one
+ * flat [rows_total, D] table (row_start NULL: b*n_rows; row_count NULL: n_rows).
+ * scores element (b,t,r) lives at
+ *   scores[(row_start ? row_start[b] : 0) + b*score_stride_b + t*score_stride_t + r].
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  const void* q;        /* [B,H,T,D] via strides */
+  int32_t q_dtype;      /* F32 | F16 | BF16 */
+  int64_t q_stride_b, q_stride_h, q_stride_t;
+  const void* keys;     /* [rows_total, D] contiguous */
+  int32_t key_dtype;    /* F32 | F16 | BF16 | F8E4M3 */
+  const float* weights; /* [B,T,H] contiguous */
+  float* scores;
+  int64_t score_stride_b, score_stride_t;
+  const int64_t* row_start; /* [B] or NULL */
+  const int32_t* row_count; /* [B] or NULL */
+  int32_t B, T, H, D;       /* D in {64,128}; 1 <= H <= 64 */
+  int64_t n_rows;           /* max rows of any sequence (host upper bound) */
+  int64_t rows_total;       /* rows in the flat key table */
+  int64_t pos0;
+  int32_t ratio;
+  int32_t flags;            /* MXB_INDEXER_* */
+  int32_t* status;
+} mxb_indexer_scores_args;
+
+#define MXB_INDEXER_EXACT_FP32 1 /* CUDA-core fp32 path even for 16-bit / fp8 operands */
+
+int mxb_indexer_scores(const mxb_indexer_scores_args* a, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * Top-k selection.
+ * Replaces  mx.argpartition(-scores, k-1)[..., :k] + mx.sort
+ *           src/moespresso/runtime/deepseek_v4/model.py:1003-1005,1057,1442-1451,
+ * the radix select of fused_decode_prep
+ *           src/moespresso/runtime/deepseek_v4/decode_attention_kernel.py:295-375,
+ * and the NumPy contract causal_indexer_topk
+ *           src/moespresso/runtime/deepseek_v4/attention.py:277-313.
+ *
+ * For every row: the ids of the k largest scores, ties to the LOWER id,
+ * -inf / NaN never selected, -0 == +0; ids written in ASCENDING order,
+ * unused slots -1.  Row i is scores[(row_start ? row_start[i] : i*row_stride) + j],
+ * j < (row_count ? row_count[i] : n).
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  const float* scores;
+  int64_t row_stride;
+  const int64_t* row_start; /* [rows] or NULL */
+  const int32_t* row_count; /* [rows] or NULL */
+  int32_t* out_ids;         /* [rows, k] contiguous */
+  int32_t rows;
+  int64_t n;                /* max row length (host upper bound) */
+  int32_t k;                /* 1 <= k <= 8192 */
+  void* workspace;
+  int64_t workspace_bytes;
+} mxb_topk_args;
+
+int64_t mxb_topk_workspace_bytes(int32_t rows, int64_t n, int32_t k);
+int mxb_topk_select(const mxb_topk_args* a, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * Indexed mixed (sparse) attention, decode and prefill forms.
+ * Replaces  indexed_mixed_attention_decode(q, raw_kv, comp_kv, topk, sinks, *, pos0, window, ratio, raw_start)
+ *           src/moespresso/runtime/deepseek_v4/indexed_attention_kernel.py:1496-1568
+ *           indexed_mixed_attention_prefill / _prefill_live_f16 / _prefill_live_f32 /
+ *           banded_prefill_attention_live   :2030-2108, :1571-1779, :1782-1885
+ *           fused_decode_sdpa (its attention arithmetic)
+ *           src/moespresso/runtime/deepseek_v4/decode_attention_kernel.py:733-786
+ *
+ * Token t of sequence b sits at position qpos = pos(b) + t.  It attends, per head,
+ * over (1) the raw-window rows visible to qpos, (2) the rows topk[b,t,:] of the
+ * compressed table in list order: id < 0 is skipped, the first id >= visible
+ * ends the walk; visible = ratio ? min((qpos+1)/ratio, rows(b)) : rows(b).
+ * K is the whole row (Dqk wide), V its first Dv features.  `sinks` (may be NULL)
+ * adds exp(sink_h) to the denominator only.  A zero denominator yields zeros.
+ *
+ * partial_ml == NULL : out[b,h,t,:] = normalised attention (out_dtype F32|BF16|F16).
+ * partial_ml != NULL : out must be F32 and receives sum_j exp(s_j - m) v_j;
+ *                      partial_ml[b,t,h] = (m, l) as two floats, [B,T,H,2]
+ *                      contiguous; the sink is NOT applied (mxb_merge_partials does).
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  const void* q;          /* [B,H,T,Dqk] via strides */
+  int32_t q_dtype;        /* F32 | F16 | BF16 */
+  int64_t q_stride_b, q_stride_h, q_stride_t;
+  const void* comp_kv;    /* flat [comp_rows_total, Dqk] */
+  int32_t kv_dtype;       /* F32 | F16 | BF16 | I8 */
+  const void* comp_scales;          /* fp16 [comp_rows_total], I8 only */
+  const int64_t* comp_row_start;    /* [B] or NULL: b*n_comp */
+  const int32_t* comp_row_count;    /* [B] or NULL: n_comp */
+  int64_t n_comp;
+  const void* raw_kv;     /* [B, raw_cap, Dqk] contiguous, kv_dtype; NULL when raw_cap == 0 */
+  const void* raw_scales; /* fp16 [B, raw_cap], I8 only */
+  int32_t raw_cap;
+  int32_t raw_start;
+  const int32_t* topk;    /* [B,T,k] contiguous */
+  int32_t k;
+  const float* sinks;     /* [H] or NULL */
+  void* out;
+  int32_t out_dtype;
+  int64_t out_stride_b, out_stride_h, out_stride_t;
+  float* partial_ml;
+  int32_t B, T, H, Dqk, Dv;
+  float scale;
+  int64_t pos0;            /* used when pos0_dev == NULL */
+  const int64_t* pos0_dev; /* [B] or NULL */
+  int32_t window, ratio;
+  int32_t n_splits;        /* 0 = choose */
+  void* workspace;
+  int64_t workspace_bytes;
+  int32_t* status;
+} mxb_sparse_attn_args;
+
+int64_t mxb_sparse_attn_workspace_bytes(const mxb_sparse_attn_args* a);
+int mxb_sparse_attn(const mxb_sparse_attn_args* a, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * Merge of (partial output, running max, running sum) triples.
+ * Replaces the cross-SIMD-group (m, l) merge + sink join of fused_decode_sdpa
+ *           src/moespresso/runtime/deepseek_v4/decode_attention_kernel.py:480-503
+ * and is the last step of KV-range sharding across GPUs.
+ *   o_parts [P, N, Dv] f32, ml_parts [P, N, 2] f32, N = B*T*H rows ordered (b,t,h).
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  const float* o_parts;
+  const float* ml_parts;
+  const float* sinks; /* [H] or NULL */
+  void* out;
+  int32_t out_dtype;
+  int64_t out_stride_b, out_stride_h, out_stride_t;
+  int32_t P, B, T, H, Dv;
+} mxb_merge_args;
+
+int mxb_merge_partials(const mxb_merge_args* a, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * Causal GQA flash prefill with sigmoid-gate epilogue (head_dim 256).
+ * Replaces  mlx_kquant.sdpa_fa_prefill_q8(queries, *past_k, *past_v, self_k, self_v, scale, bq, bk, stage)
+ *           call site src/moespresso/runtime/qwen/full_attention.py:372-382
+ * plus the  out * sigmoid(gate)  of FlashPrefillD256Attention.__call__  :396-397.
+ *
+ *   out[i,h,:] = softmax_j(scale * q[i,h,:].k[j,h/g,:], j <= i + (Skv - S)) v[:,h/g,:]
+ *                * sigmoid(gate[i,h,:])          (gate may be NULL), g = Hq/Hkv.
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  const void* q;    int64_t q_stride_s, q_stride_h;       /* [S,   Hq,  D] */
+  const void* k;    int64_t k_stride_s, k_stride_h;       /* [Skv, Hkv, D] */
+  const void* v;    int64_t v_stride_s, v_stride_h;       /* [Skv, Hkv, D] */
+  const void* gate; int64_t gate_stride_s, gate_stride_h; /* [S,   Hq,  D] or NULL */
+  void* out;        int64_t out_stride_s, out_stride_h;   /* [S,   Hq,  D] */
+  int32_t dtype;    /* BF16 | F16, all five tensors */
+  int32_t S, Skv, Hq, Hkv, D;
+  float scale;
+  void* workspace;
+  int64_t workspace_bytes;
+  int32_t* status;
+} mxb_flash_prefill_args;
+
+int64_t mxb_flash_prefill_workspace_bytes(const mxb_flash_prefill_args* a);
+int mxb_flash_prefill(const mxb_flash_prefill_args* a, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOESPRESSO_B200_H */

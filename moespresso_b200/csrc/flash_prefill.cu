@@ -1,0 +1,394 @@
+// Causal GQA flash prefill, head_dim 256, 16-bit operands, fp32 accumulation, with the
+// sigmoid-gate epilogue fused:  out = softmax(scale * Q K^T + causal) V * sigmoid(gate).
+//
+// One CTA = 128 query rows of one query head.  Six warps:
+//   warps 0-3  softmax + epilogue; thread r owns query row r = TMEM lane r
+//   warp  4    issues tcgen05.mma (one lane)
+//   warp  5    TMA producer (one lane)
+// Per 64-key tile:  S = Q K^T (M128 x N64 x K256) into one of two TMEM buffers;
+// the softmax warps read S from TMEM, keep a running maximum with lazy rescaling of
+// the TMEM-resident O (only when the maximum grew by more than 2^8), write P as a
+// 16-bit K-major swizzled tile to shared memory; O += P V (M128 x N256 x K64) with V
+// read from a pre-transposed copy (keys contiguous) so that every operand is K-major.
+// S of tile j+1 is issued before P of tile j is consumed, so the tensor pipe overlaps
+// the softmax.  TMEM: S0 [0,64) S1 [64,128) O [128,384).
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace mxb {
+
+constexpr int FB_M = 128, FB_N = 64, FB_D = 256;
+
+struct FlashSmem {
+  static constexpr int q_off = 0;                       // 4 slabs x [128 x 128 B]
+  static constexpr int k_off = q_off + 4 * 16384;       // 2 stages x 4 slabs x [64 x 128 B]
+  static constexpr int v_off = k_off + 2 * 32768;       // 2 stages x [256 x 128 B]
+  static constexpr int p_off = v_off + 2 * 32768;       // [128 x 128 B]
+  static constexpr int bar_off = p_off + 16384;
+  static constexpr int total = bar_off + 256;
+};
+
+struct FlashParams {
+  const void* gate;
+  int64_t g_ss, g_sh;
+  void* out;
+  int64_t o_ss, o_sh;
+  int32_t S, Skv, Hq, Hkv;
+  float scale_log2;  // scale * log2(e)
+  int32_t* status;
+};
+
+__global__ void transpose_v_kernel(const uint16_t* __restrict__ v, int64_t v_ss, int64_t v_sh, uint16_t* __restrict__ vt,
+                                   int Skv, int Skv_pad, int D) {
+  __shared__ uint16_t tile[32][33];
+  const int hk = blockIdx.z;
+  const int s0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int s = s0 + r, d = d0 + threadIdx.x;
+    tile[r][threadIdx.x] = (s < Skv && d < D) ? v[(int64_t)s * v_ss + (int64_t)hk * v_sh + d] : (uint16_t)0;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int d = d0 + r, s = s0 + threadIdx.x;
+    if (d < D && s < Skv_pad) vt[((int64_t)hk * D + d) * Skv_pad + s] = tile[threadIdx.x][r];
+  }
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  if constexpr (BF16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+template <bool BF16>
+__device__ __forceinline__ float2 unpack2(uint32_t u) {
+  if constexpr (BF16) return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
+  else return __half22float2(*reinterpret_cast<__half2*>(&u));
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(192, 1) flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
+                                                               const __grid_constant__ CUtensorMap tm_k,
+                                                               const __grid_constant__ CUtensorMap tm_vt,
+                                                               FlashParams p) {
+  using L = FlashSmem;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* q_s = smem + L::q_off;
+  uint8_t* k_s = smem + L::k_off;
+  uint8_t* v_s = smem + L::v_off;
+  uint8_t* p_s = smem + L::p_off;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::bar_off);
+  uint64_t* q_full = bars + 0;
+  uint64_t* k_full = bars + 1;   // [2]
+  uint64_t* k_empty = bars + 3;  // [2]
+  uint64_t* v_full = bars + 5;   // [2]
+  uint64_t* v_empty = bars + 7;  // [2]
+  uint64_t* s_ready = bars + 9;  // [2]
+  uint64_t* p_ready = bars + 11;
+  uint64_t* pv_done = bars + 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x;  // heavy (late) tiles first
+  const int head = blockIdx.y;
+  const int kvh = head / (p.Hq / p.Hkv);
+  const int m0 = qt * FB_M;
+  const int past = p.Skv - p.S;
+  int kv_end = m0 + FB_M + past;
+  if (kv_end > p.Skv) kv_end = p.Skv;
+  const int ntiles = (kv_end + FB_N - 1) / FB_N;
+
+  if (tid == 0) {
+    ptx::mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&k_full[i], 1);
+      ptx::mbar_init(&k_empty[i], 1);
+      ptx::mbar_init(&v_full[i], 1);
+      ptx::mbar_init(&v_empty[i], 1);
+      ptx::mbar_init(&s_ready[i], 1);
+    }
+    ptx::mbar_init(p_ready, 128);
+    ptx::mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    ptx::mbar_fence_init();
+  }
+  __syncwarp();
+  if (warp == 0) {
+    ptx::tmem_alloc(tmem_slot, 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_o = tmem_base + 128;
+
+  if (warp == 5) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      ptx::tma_prefetch_desc(&tm_q);
+      ptx::tma_prefetch_desc(&tm_k);
+      ptx::tma_prefetch_desc(&tm_vt);
+      ptx::mbar_expect_tx(q_full, 4 * 16384);
+      for (int kb = 0; kb < 4; ++kb) ptx::tma_load_3d(q_s + kb * 16384, &tm_q, q_full, kb * 64, m0, head);
+      for (int j = 0; j < ntiles; ++j) {
+        const int s = j & 1, u = j >> 1;
+        if (j >= 2) ptx::mbar_wait(&k_empty[s], (uint32_t)((u - 1) & 1), abort_flag);
+        ptx::mbar_expect_tx(&k_full[s], 32768);
+        for (int kb = 0; kb < 4; ++kb)
+          ptx::tma_load_3d(k_s + s * 32768 + kb * 8192, &tm_k, &k_full[s], kb * 64, j * FB_N, kvh);
+        if (j >= 2) ptx::mbar_wait(&v_empty[s], (uint32_t)((u - 1) & 1), abort_flag);
+        ptx::mbar_expect_tx(&v_full[s], 32768);
+        ptx::tma_load_3d(v_s + s * 32768, &tm_vt, &v_full[s], j * FB_N, 0, kvh);
+      }
+    }
+  } else if (warp == 4) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t fmt = BF16 ? ptx::kFmtBF16 : ptx::kFmtF16;
+      const uint32_t idesc_s = ptx::idesc_f16(fmt, fmt, FB_M, FB_N, 0, 0);
+      const uint32_t idesc_o = ptx::idesc_f16(fmt, fmt, FB_M, FB_D, 0, 0);
+      const uint32_t q_addr = ptx::smem_u32(q_s), k_addr = ptx::smem_u32(k_s), v_addr = ptx::smem_u32(v_s),
+                     p_addr = ptx::smem_u32(p_s);
+      auto issue_s = [&](int j) {
+        const int s = j & 1;
+        ptx::mbar_wait(&k_full[s], (uint32_t)((j >> 1) & 1), abort_flag);
+        ptx::tc_fence_after_sync();
+        const uint32_t d = tmem_base + (uint32_t)(s * FB_N);
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb)
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            const uint64_t ad = ptx::smem_desc_sw128(q_addr + kb * 16384 + ks * 32, 16, 1024);
+            const uint64_t bd = ptx::smem_desc_sw128(k_addr + s * 32768 + kb * 8192 + ks * 32, 16, 1024);
+            ptx::mma_f16_ss(d, ad, bd, idesc_s, (kb | ks) ? 1u : 0u);
+          }
+        ptx::mma_commit(&s_ready[s]);
+        ptx::mma_commit(&k_empty[s]);
+      };
+      ptx::mbar_wait(q_full, 0, abort_flag);
+      issue_s(0);
+      for (int j = 0; j < ntiles; ++j) {
+        if (j + 1 < ntiles) issue_s(j + 1);
+        const int s = j & 1;
+        ptx::mbar_wait(p_ready, (uint32_t)(j & 1), abort_flag);
+        ptx::mbar_wait(&v_full[s], (uint32_t)((j >> 1) & 1), abort_flag);
+        ptx::tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint64_t ad = ptx::smem_desc_sw128(p_addr + ks * 32, 16, 1024);
+          const uint64_t bd = ptx::smem_desc_sw128(v_addr + s * 32768 + ks * 32, 16, 1024);
+          ptx::mma_f16_ss(tmem_o, ad, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+        }
+        ptx::mma_commit(pv_done);
+        ptx::mma_commit(&v_empty[s]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax + epilogue
+    const int row = tid;             // 0..127
+    const int qi = m0 + row;         // query row
+    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    float m_used = -INFINITY, l = 0.f;
+    for (int j = 0; j < ntiles; ++j) {
+      const int s = j & 1;
+      ptx::mbar_wait(&s_ready[s], (uint32_t)((j >> 1) & 1), abort_flag);
+      ptx::tc_fence_after_sync();
+      uint32_t sv[64];
+      ptx::tmem_ld32(tmem_base + lane_off + (uint32_t)(s * FB_N), sv);
+      ptx::tmem_ld32(tmem_base + lane_off + (uint32_t)(s * FB_N + 32), sv + 32);
+      ptx::tmem_ld_wait();
+      const int key0 = j * FB_N;
+      const bool need_mask = key0 + FB_N - 1 > m0 + past;  // tile reaches past the first row's diagonal
+      float tmax = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        float x = __uint_as_float(sv[c]) * p.scale_log2;
+        if (need_mask && key0 + c > qi + past) x = -INFINITY;
+        sv[c] = __float_as_uint(x);
+        tmax = fmaxf(tmax, x);
+      }
+      float factor = 1.f;
+      bool grow = false;
+      if (j == 0) {
+        m_used = tmax;  // row 0's key 0 is always visible, so tmax is finite for valid rows
+      } else {
+        grow = tmax > m_used + 8.f;
+      }
+      if (j > 0) {
+        // P buffer and O are free / final only after the previous P.V finished
+        ptx::mbar_wait(pv_done, (uint32_t)((j - 1) & 1), abort_flag);
+        ptx::tc_fence_after_sync();
+        if (__any_sync(0xffffffffu, grow)) {
+          if (grow) {
+            factor = exp2f(m_used - tmax);
+            m_used = tmax;
+          }
+#pragma unroll 1
+          for (int c0 = 0; c0 < FB_D; c0 += 32) {
+            uint32_t ov[32];
+            ptx::tmem_ld32(tmem_o + lane_off + (uint32_t)c0, ov);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * factor);
+            ptx::tmem_st32(tmem_o + lane_off + (uint32_t)c0, ov);
+          }
+          ptx::tmem_st_wait();
+          l *= factor;
+        }
+      }
+      float psum = 0.f;
+      uint8_t* prow = p_s + row * 128;
+#pragma unroll
+      for (int c8 = 0; c8 < 8; ++c8) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float a = exp2f(__uint_as_float(sv[c8 * 8 + 2 * i]) - m_used);
+          const float b = exp2f(__uint_as_float(sv[c8 * 8 + 2 * i + 1]) - m_used);
+          psum += a + b;
+          w[i] = pack2<BF16>(a, b);
+        }
+        *reinterpret_cast<uint4*>(prow + ((c8 ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      l += psum;
+      ptx::fence_proxy_async_smem();
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(p_ready);
+    }
+    // epilogue
+    ptx::mbar_wait(pv_done, (uint32_t)((ntiles - 1) & 1), abort_flag);
+    ptx::tc_fence_after_sync();
+    const float inv_l = l > 0.f ? 1.f / l : 0.f;
+    const bool row_ok = qi < p.S;
+    const uint16_t* gptr = p.gate ? reinterpret_cast<const uint16_t*>(p.gate) + (int64_t)qi * p.g_ss + (int64_t)head * p.g_sh
+                                  : nullptr;
+    uint16_t* optr = reinterpret_cast<uint16_t*>(p.out) + (int64_t)qi * p.o_ss + (int64_t)head * p.o_sh;
+#pragma unroll 1
+    for (int c0 = 0; c0 < FB_D; c0 += 32) {
+      uint32_t ov[32];
+      ptx::tmem_ld32(tmem_o + lane_off + (uint32_t)c0, ov);
+      ptx::tmem_ld_wait();
+      if (row_ok) {
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8) {
+          uint4 g = make_uint4(0, 0, 0, 0);
+          if (gptr) g = __ldg(reinterpret_cast<const uint4*>(gptr + c0 + c8 * 8));
+          const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+          uint32_t w[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float a = __uint_as_float(ov[c8 * 8 + 2 * i]) * inv_l;
+            float b = __uint_as_float(ov[c8 * 8 + 2 * i + 1]) * inv_l;
+            if (gptr) {
+              const float2 gg = unpack2<BF16>(gw[i]);
+              a *= 1.f / (1.f + __expf(-gg.x));
+              b *= 1.f / (1.f + __expf(-gg.y));
+            }
+            w[i] = pack2<BF16>(a, b);
+          }
+          *reinterpret_cast<uint4*>(optr + c0 + c8 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+    }
+    ptx::tc_fence_before_sync();
+  }
+
+  __syncthreads();
+  if (warp == 0) ptx::tmem_dealloc(tmem_base, 512);
+  if (tid == 0 && *abort_flag && p.status) atomicExch(p.status, 1);
+}
+
+}  // namespace mxb
+
+using namespace mxb;
+
+static int flash_validate(const mxb_flash_prefill_args* a) {
+  MXB_REQUIRE(a != nullptr, MXB_ERR_INVALID, "flash prefill: null args");
+  MXB_REQUIRE(a->D == 256, MXB_ERR_INVALID, "flash prefill requires head_dim=256");
+  MXB_REQUIRE(a->dtype == MXB_BF16 || a->dtype == MXB_F16, MXB_ERR_INVALID,
+              "flash prefill requires bfloat16 or float16 operands");
+  MXB_REQUIRE(a->S > 0 && a->Skv >= a->S, MXB_ERR_INVALID, "flash prefill requires 1 <= S <= Skv");
+  MXB_REQUIRE(a->Hq > 0 && a->Hkv > 0 && a->Hq % a->Hkv == 0, MXB_ERR_INVALID,
+              "query heads must be a multiple of kv heads");
+  MXB_REQUIRE(a->q && a->k && a->v && a->out, MXB_ERR_INVALID, "flash prefill: null tensor");
+  return MXB_OK;
+}
+
+extern "C" int64_t mxb_flash_prefill_workspace_bytes(const mxb_flash_prefill_args* a) {
+  if (!a || a->Skv <= 0 || a->Hkv <= 0 || a->D <= 0) return 0;
+  return (int64_t)a->Hkv * a->D * round_up(a->Skv, 64) * 2;
+}
+
+extern "C" int mxb_flash_prefill(const mxb_flash_prefill_args* a, void* stream) {
+  int rc = flash_validate(a);
+  if (rc != MXB_OK) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int64_t need = mxb_flash_prefill_workspace_bytes(a);
+  MXB_REQUIRE(a->workspace && a->workspace_bytes >= need, MXB_ERR_WORKSPACE,
+              "flash prefill: workspace of %lld bytes required", (long long)need);
+  MXB_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 255) == 0, MXB_ERR_INVALID,
+              "flash prefill: workspace must be 256-byte aligned");
+  MXB_REQUIRE((reinterpret_cast<uintptr_t>(a->out) & 15) == 0 && a->out_stride_s % 8 == 0 && a->out_stride_h % 8 == 0,
+              MXB_ERR_INVALID, "out must be 16-byte aligned with strides that are multiples of 8 elements");
+  MXB_REQUIRE(!a->gate || ((reinterpret_cast<uintptr_t>(a->gate) & 15) == 0 && a->gate_stride_s % 8 == 0 &&
+                           a->gate_stride_h % 8 == 0),
+              MXB_ERR_INVALID, "gate must be 16-byte aligned with strides that are multiples of 8 elements");
+  const int Skv_pad = (int)round_up(a->Skv, 64);
+
+  {
+    dim3 blk(32, 8);
+    dim3 grd((unsigned)ceil_div(Skv_pad, 32), (unsigned)ceil_div(a->D, 32), (unsigned)a->Hkv);
+    transpose_v_kernel<<<grd, blk, 0, st>>>(reinterpret_cast<const uint16_t*>(a->v), a->v_stride_s, a->v_stride_h,
+                                            reinterpret_cast<uint16_t*>(a->workspace), a->Skv, Skv_pad, a->D);
+    MXB_CUDA_OK(cudaGetLastError());
+  }
+
+  const CUtensorMapDataType dt = a->dtype == MXB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUtensorMap tq, tk, tv;
+  {
+    uint64_t dims[3] = {(uint64_t)a->D, (uint64_t)a->S, (uint64_t)a->Hq};
+    uint64_t str[2] = {(uint64_t)a->q_stride_s * 2, (uint64_t)a->q_stride_h * 2};
+    uint32_t box[3] = {64, FB_M, 1};
+    rc = make_tensor_map(&tq, dt, 3, a->q, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != MXB_OK) return rc;
+  }
+  {
+    uint64_t dims[3] = {(uint64_t)a->D, (uint64_t)a->Skv, (uint64_t)a->Hkv};
+    uint64_t str[2] = {(uint64_t)a->k_stride_s * 2, (uint64_t)a->k_stride_h * 2};
+    uint32_t box[3] = {64, FB_N, 1};
+    rc = make_tensor_map(&tk, dt, 3, a->k, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != MXB_OK) return rc;
+  }
+  {
+    uint64_t dims[3] = {(uint64_t)Skv_pad, (uint64_t)a->D, (uint64_t)a->Hkv};
+    uint64_t str[2] = {(uint64_t)Skv_pad * 2, (uint64_t)a->D * Skv_pad * 2};
+    uint32_t box[3] = {64, FB_D, 1};
+    rc = make_tensor_map(&tv, dt, 3, a->workspace, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != MXB_OK) return rc;
+  }
+
+  FlashParams p{};
+  p.gate = a->gate; p.g_ss = a->gate_stride_s; p.g_sh = a->gate_stride_h;
+  p.out = a->out; p.o_ss = a->out_stride_s; p.o_sh = a->out_stride_h;
+  p.S = a->S; p.Skv = a->Skv; p.Hq = a->Hq; p.Hkv = a->Hkv;
+  p.scale_log2 = a->scale * 1.4426950408889634f;
+  p.status = a->status;
+  const int smem = FlashSmem::total + 1024;
+  dim3 grid((unsigned)ceil_div(a->S, FB_M), (unsigned)a->Hq);
+  if (a->dtype == MXB_BF16) {
+    MXB_CUDA_OK(cudaFuncSetAttribute(flash_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    flash_prefill_kernel<true><<<grid, 192, smem, st>>>(tq, tk, tv, p);
+  } else {
+    MXB_CUDA_OK(cudaFuncSetAttribute(flash_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    flash_prefill_kernel<false><<<grid, 192, smem, st>>>(tq, tk, tv, p);
+  }
+  MXB_CUDA_OK(cudaGetLastError());
+  return MXB_OK;
+}

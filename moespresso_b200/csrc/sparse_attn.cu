@@ -1,0 +1,421 @@
+// Indexed mixed (sparse) attention: per (sequence, token, head) an online softmax over
+// the raw-window rows visible to the token followed by the selected rows of the
+// compressed table, K = the whole row, V = its first Dv features.
+//
+// sparse_attn_kernel: one CTA = one (split, group of 8 heads, (sequence, token)).
+// A tile of 32 gathered rows is staged in shared memory as fp32 by 16-byte vector
+// loads (int8 rows are multiplied by their per-row fp16 scale while staging, fp16 /
+// bf16 rows are widened), then every warp (= one head) scores the 32 rows (lane = row),
+// updates its running (max, sum) and accumulates P.V with lane = feature.  Splits over
+// the row list write (o, m, l) partials that merge_kernel combines by log-sum-exp; the
+// sink joins once, in the merge (or in the single-split epilogue).
+#include "common.cuh"
+
+namespace mxb {
+
+constexpr int kTileRows = 32;
+constexpr int kHeadsPerCta = 8;
+constexpr int kMaxDvRegs = 16;  // Dv <= 512
+
+struct SparseParams {
+  const void* q;
+  int64_t q_sb, q_sh, q_st;
+  const void* comp_kv;
+  const __half* comp_scales;
+  const int64_t* comp_row_start;
+  const int32_t* comp_row_count;
+  int64_t n_comp;
+  const void* raw_kv;
+  const __half* raw_scales;
+  int32_t raw_cap, raw_start;
+  const int32_t* topk;
+  int32_t k;
+  const float* sinks;
+  void* out;
+  int64_t o_sb, o_sh, o_st;
+  float* partial_ml;   // external partial mode
+  float* ws_o;         // [nsplit][N][Dv]
+  float* ws_ml;        // [nsplit][N][2]
+  int32_t B, T, H, Dqk, Dv;
+  float scale;
+  int64_t pos0;
+  const int64_t* pos0_dev;
+  int32_t window, ratio;
+  int32_t nsplit;
+};
+
+template <int KVT>
+__device__ __forceinline__ void stage_row(float* dst, const void* src_row, int Dqk, float row_scale, int lane) {
+  constexpr int EPV = 16 / ElemBytes<KVT>::v;
+  const int nchunks = Dqk / EPV;
+  const uint4* src = reinterpret_cast<const uint4*>(src_row);
+  for (int c = lane; c < nchunks; c += 32) {
+    uint4 v = __ldg(src + c);
+    float f[EPV];
+    unpack16<KVT>(v, f);
+#pragma unroll
+    for (int j = 0; j < EPV; ++j) dst[c * EPV + j] = (KVT == MXB_I8) ? f[j] * row_scale : f[j];
+  }
+}
+
+template <int KVT, int QT, int OT>
+__global__ void __launch_bounds__(256) sparse_attn_kernel(SparseParams p) {
+  extern __shared__ float smem_f[];
+  const int ld = p.Dqk + 1;
+  float* rows_s = smem_f;                                  // [32][Dqk+1]
+  float* q_s = rows_s + kTileRows * ld;                    // [8][Dqk]
+  float* p_s = q_s + kHeadsPerCta * p.Dqk;                 // [8][32]
+  int* valid_s = reinterpret_cast<int*>(p_s + kHeadsPerCta * kTileRows);  // [32]
+  __shared__ int s_keff;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int split = blockIdx.x;
+  const int h = blockIdx.y * kHeadsPerCta + warp;
+  const int bt = blockIdx.z;
+  const int b = bt / p.T, t = bt % p.T;
+  const bool head_ok = h < p.H;
+
+  const int64_t pos_b = p.pos0_dev ? p.pos0_dev[b] : p.pos0;
+  const int64_t qpos = pos_b + t;
+  const int64_t last_pos = pos_b + p.T - 1;
+  const int64_t count = p.comp_row_count ? (int64_t)p.comp_row_count[b] : p.n_comp;
+  const int64_t cbase = p.comp_row_start ? p.comp_row_start[b] : (int64_t)b * p.n_comp;
+  int64_t visible = count;
+  if (p.ratio > 0) {
+    visible = (qpos + 1) / p.ratio;
+    if (visible > count) visible = count;
+  }
+  // raw window
+  int64_t first_raw_pos = 0, first = 0;
+  int n_raw = 0;
+  if (p.raw_cap > 0) {
+    first_raw_pos = last_pos + 1 - p.raw_cap;
+    const int64_t window_first = (p.window != 0 && qpos + 1 > p.window) ? qpos + 1 - p.window : 0;
+    first = first_raw_pos > window_first ? first_raw_pos : window_first;
+    if (first < 0) first = 0;
+    const int64_t last = qpos < last_pos ? qpos : last_pos;
+    n_raw = last >= first ? (int)(last - first + 1) : 0;
+  }
+  // first list entry that ends the walk
+  const int32_t* ids = p.topk + (int64_t)bt * p.k;
+  if (tid == 0) s_keff = p.k;
+  __syncthreads();
+  {
+    int mine = p.k;
+    for (int j = tid; j < p.k; j += blockDim.x)
+      if ((int64_t)ids[j] >= visible) { mine = j; break; }
+    if (mine < p.k) atomicMin(&s_keff, mine);
+  }
+  // q -> smem (fp32)
+  for (int i = tid; i < kHeadsPerCta * p.Dqk; i += blockDim.x) {
+    const int hh = blockIdx.y * kHeadsPerCta + i / p.Dqk, d = i % p.Dqk;
+    q_s[i] = hh < p.H ? load_elem<QT>(p.q, (int64_t)b * p.q_sb + (int64_t)hh * p.q_sh + (int64_t)t * p.q_st + d)
+                      : 0.f;
+  }
+  __syncthreads();
+  const int total = n_raw + s_keff;
+  int per = (total + p.nsplit - 1) / p.nsplit;
+  per = ((per + kTileRows - 1) / kTileRows) * kTileRows;
+  const int e_lo = min(split * per, total), e_hi = min(e_lo + per, total);
+
+  float M = -INFINITY, S = 0.f;
+  float o[kMaxDvRegs];
+#pragma unroll
+  for (int i = 0; i < kMaxDvRegs; ++i) o[i] = 0.f;
+  const int nreg = (p.Dv + 31) / 32;
+
+  for (int e0 = e_lo; e0 < e_hi; e0 += kTileRows) {
+    // stage up to 32 rows
+    for (int rr = warp; rr < kTileRows; rr += 8) {
+      const int e = e0 + rr;
+      const void* src = nullptr;
+      float rs = 1.f;
+      if (e < e_hi) {
+        if (e < n_raw) {
+          const int64_t pabs = first + e;
+          const int64_t phys = ((int64_t)p.raw_start + (pabs - first_raw_pos)) % p.raw_cap;
+          const int64_t ridx = (int64_t)b * p.raw_cap + phys;
+          src = reinterpret_cast<const char*>(p.raw_kv) + ridx * p.Dqk * ElemBytes<KVT>::v;
+          if (KVT == MXB_I8) rs = __half2float(p.raw_scales[ridx]);
+        } else {
+          const int32_t id = ids[e - n_raw];
+          if (id >= 0) {
+            const int64_t ridx = cbase + id;
+            src = reinterpret_cast<const char*>(p.comp_kv) + ridx * p.Dqk * ElemBytes<KVT>::v;
+            if (KVT == MXB_I8) rs = __half2float(p.comp_scales[ridx]);
+          }
+        }
+      }
+      float* dst = rows_s + rr * ld;
+      if (src) {
+        stage_row<KVT>(dst, src, p.Dqk, rs, lane);
+      } else {
+        for (int d = lane; d < p.Dqk; d += 32) dst[d] = 0.f;
+      }
+      if (lane == 0) valid_s[rr] = src != nullptr;
+    }
+    __syncthreads();
+
+    if (head_ok) {
+      const float* qh = q_s + warp * p.Dqk;
+      const float* rj = rows_s + lane * ld;
+      float dot = 0.f;
+      for (int d = 0; d < p.Dqk; ++d) dot = fmaf(qh[d], rj[d], dot);
+      const bool ok = valid_s[lane] != 0;
+      const float s = ok ? dot * p.scale : -INFINITY;
+      const float tmax = warp_max(s);
+      if (tmax > -INFINITY) {
+        const float m_new = fmaxf(M, tmax);
+        const float pj = ok ? expf(s - m_new) : 0.f;
+        const float corr = (M == -INFINITY) ? 0.f : expf(M - m_new);
+        S = S * corr + warp_sum(pj);
+        M = m_new;
+        p_s[warp * kTileRows + lane] = pj;
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < kMaxDvRegs; ++i) o[i] *= corr;
+        for (int j = 0; j < kTileRows; ++j) {
+          const float pw = p_s[warp * kTileRows + j];
+          const float* r = rows_s + j * ld + lane;
+#pragma unroll
+          for (int i = 0; i < kMaxDvRegs; ++i)
+            if (i < nreg) o[i] = fmaf(pw, (lane + 32 * i < p.Dv) ? r[32 * i] : 0.f, o[i]);
+        }
+        __syncwarp();
+      }
+    }
+    __syncthreads();
+  }
+
+  if (!head_ok) return;
+  const int64_t n_idx = (int64_t)bt * p.H + h;
+  if (p.nsplit == 1) {
+    if (p.partial_ml) {
+      float* outp = reinterpret_cast<float*>(p.out) + (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)t * p.o_st;
+#pragma unroll
+      for (int i = 0; i < kMaxDvRegs; ++i)
+        if (i < nreg && lane + 32 * i < p.Dv) outp[lane + 32 * i] = o[i];
+      if (lane == 0) {
+        p.partial_ml[n_idx * 2 + 0] = M;
+        p.partial_ml[n_idx * 2 + 1] = S;
+      }
+    } else {
+      const float sink = p.sinks ? p.sinks[h] : -INFINITY;
+      const float m2 = fmaxf(M, sink);
+      float den = 0.f, w = 0.f;
+      if (m2 > -INFINITY) {
+        w = (M == -INFINITY) ? 0.f : expf(M - m2);
+        den = S * w + ((sink == -INFINITY) ? 0.f : expf(sink - m2));
+      }
+      const float inv = den > 0.f ? w / den : 0.f;
+      const int64_t ob = (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)t * p.o_st;
+#pragma unroll
+      for (int i = 0; i < kMaxDvRegs; ++i)
+        if (i < nreg && lane + 32 * i < p.Dv) store_elem<OT>(p.out, ob + lane + 32 * i, o[i] * inv);
+    }
+  } else {
+    const int64_t N = (int64_t)p.B * p.T * p.H;
+    float* wo = p.ws_o + ((int64_t)split * N + n_idx) * p.Dv;
+#pragma unroll
+    for (int i = 0; i < kMaxDvRegs; ++i)
+      if (i < nreg && lane + 32 * i < p.Dv) wo[lane + 32 * i] = o[i];
+    if (lane == 0) {
+      p.ws_ml[((int64_t)split * N + n_idx) * 2 + 0] = M;
+      p.ws_ml[((int64_t)split * N + n_idx) * 2 + 1] = S;
+    }
+  }
+}
+
+// Merge P partials per (b,t,h) row in a fixed order.  finalize != 0: join the sink, normalise,
+// store in the output dtype; finalize == 0: store the merged un-normalised sum (fp32) and (m, l).
+struct MergeParams {
+  const float* o_parts;
+  const float* ml_parts;
+  const float* sinks;
+  void* out;
+  float* out_ml;
+  int64_t o_sb, o_sh, o_st;
+  int32_t P, B, T, H, Dv;
+  int32_t finalize;
+};
+
+template <int OT>
+__global__ void __launch_bounds__(128) merge_kernel(MergeParams p) {
+  const int64_t n = blockIdx.x;
+  const int64_t N = (int64_t)p.B * p.T * p.H;
+  const int h = (int)(n % p.H);
+  const int t = (int)((n / p.H) % p.T);
+  const int b = (int)(n / ((int64_t)p.H * p.T));
+  float m = -INFINITY;
+  for (int s = 0; s < p.P; ++s) m = fmaxf(m, p.ml_parts[((int64_t)s * N + n) * 2]);
+  const float sink = (p.finalize && p.sinks) ? p.sinks[h] : -INFINITY;
+  m = fmaxf(m, sink);
+  float l = 0.f;
+  if (m > -INFINITY) {
+    for (int s = 0; s < p.P; ++s) {
+      const float ms = p.ml_parts[((int64_t)s * N + n) * 2];
+      const float ls = p.ml_parts[((int64_t)s * N + n) * 2 + 1];
+      if (ms > -INFINITY) l = fmaf(ls, expf(ms - m), l);
+    }
+    if (sink > -INFINITY) l += expf(sink - m);
+  }
+  const int64_t ob = (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)t * p.o_st;
+  for (int d = threadIdx.x; d < p.Dv; d += blockDim.x) {
+    float acc = 0.f;
+    if (m > -INFINITY) {
+      for (int s = 0; s < p.P; ++s) {
+        const float ms = p.ml_parts[((int64_t)s * N + n) * 2];
+        if (ms > -INFINITY) acc = fmaf(p.o_parts[((int64_t)s * N + n) * p.Dv + d], expf(ms - m), acc);
+      }
+    }
+    if (p.finalize) store_elem<OT>(p.out, ob + d, l > 0.f ? acc / l : 0.f);
+    else reinterpret_cast<float*>(p.out)[ob + d] = acc;
+  }
+  if (!p.finalize && threadIdx.x == 0) {
+    p.out_ml[n * 2 + 0] = m;
+    p.out_ml[n * 2 + 1] = l;
+  }
+}
+
+static int launch_merge(const MergeParams& mp, int out_dtype, cudaStream_t st) {
+  const int64_t N = (int64_t)mp.B * mp.T * mp.H;
+  dim3 grid((unsigned)N);
+  if (out_dtype == MXB_F32) merge_kernel<MXB_F32><<<grid, 128, 0, st>>>(mp);
+  else if (out_dtype == MXB_BF16) merge_kernel<MXB_BF16><<<grid, 128, 0, st>>>(mp);
+  else merge_kernel<MXB_F16><<<grid, 128, 0, st>>>(mp);
+  MXB_CUDA_OK(cudaGetLastError());
+  return MXB_OK;
+}
+
+static int choose_splits(const mxb_sparse_attn_args* a) {
+  if (a->n_splits > 0) return a->n_splits > 64 ? 64 : a->n_splits;
+  const int64_t base = (int64_t)a->B * a->T * ceil_div(a->H, kHeadsPerCta);
+  const int64_t max_rows = (int64_t)a->k + a->raw_cap;
+  int64_t want = ceil_div(2 * (int64_t)sm_count(), base);
+  int64_t cap = ceil_div(max_rows, 2 * kTileRows);
+  if (cap < 1) cap = 1;
+  if (want > cap) want = cap;
+  if (want > 64) want = 64;
+  if (want < 1) want = 1;
+  return (int)want;
+}
+
+template <int KVT, int QT>
+static int launch_sparse(SparseParams& p, int out_dtype, size_t smem, dim3 grid, cudaStream_t st) {
+#define MXB_SP(OT)                                                                                         \
+  {                                                                                                        \
+    auto kern = sparse_attn_kernel<KVT, QT, OT>;                                                           \
+    MXB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));       \
+    kern<<<grid, 256, smem, st>>>(p);                                                                      \
+  }
+  if (out_dtype == MXB_F32 || p.nsplit > 1 || p.partial_ml) MXB_SP(MXB_F32)
+  else if (out_dtype == MXB_BF16) MXB_SP(MXB_BF16)
+  else MXB_SP(MXB_F16)
+#undef MXB_SP
+  MXB_CUDA_OK(cudaGetLastError());
+  return MXB_OK;
+}
+
+static int validate_sparse(const mxb_sparse_attn_args* a) {
+  MXB_REQUIRE(a != nullptr, MXB_ERR_INVALID, "sparse attention: null args");
+  MXB_REQUIRE(a->B > 0 && a->T > 0, MXB_ERR_INVALID, "q must contain at least one batch and token");
+  MXB_REQUIRE(a->H >= 1, MXB_ERR_INVALID, "q must contain at least one head");
+  MXB_REQUIRE(a->Dqk >= 32 && a->Dqk <= 1024 && a->Dqk % 16 == 0, MXB_ERR_INVALID,
+              "head width must be a multiple of 16 between 32 and 1024");
+  MXB_REQUIRE(a->Dv >= 1 && a->Dv <= a->Dqk && a->Dv <= 32 * kMaxDvRegs, MXB_ERR_INVALID,
+              "value width must be between 1 and min(head width, 512)");
+  MXB_REQUIRE(a->k >= 0, MXB_ERR_INVALID, "topk must have a non-negative width");
+  MXB_REQUIRE(a->raw_cap >= 0, MXB_ERR_INVALID, "raw_cap must be non-negative");
+  MXB_REQUIRE(a->raw_cap == 0 || (a->raw_start >= 0 && a->raw_start < a->raw_cap), MXB_ERR_INVALID,
+              "raw_start must be inside raw_kv");
+  MXB_REQUIRE(a->window >= 0 && a->ratio >= 0, MXB_ERR_INVALID, "window and ratio must be non-negative");
+  MXB_REQUIRE(a->q && a->out && (a->k == 0 || (a->topk && a->comp_kv)), MXB_ERR_INVALID,
+              "sparse attention: null tensor");
+  MXB_REQUIRE(a->raw_cap == 0 || a->raw_kv, MXB_ERR_INVALID, "raw_kv is null but raw_cap > 0");
+  MXB_REQUIRE(a->kv_dtype != MXB_I8 || (a->comp_scales && (a->raw_cap == 0 || a->raw_scales)), MXB_ERR_INVALID,
+              "int8 KV needs per-row scales");
+  MXB_REQUIRE((reinterpret_cast<uintptr_t>(a->comp_kv) & 15) == 0 && (reinterpret_cast<uintptr_t>(a->raw_kv) & 15) == 0,
+              MXB_ERR_INVALID, "KV tables must be 16-byte aligned");
+  MXB_REQUIRE(!a->partial_ml || a->out_dtype == MXB_F32, MXB_ERR_INVALID, "partial output must be float32");
+  return MXB_OK;
+}
+
+}  // namespace mxb
+
+using namespace mxb;
+
+extern "C" int64_t mxb_sparse_attn_workspace_bytes(const mxb_sparse_attn_args* a) {
+  if (!a || a->B <= 0 || a->T <= 0 || a->H <= 0) return 0;
+  const int ns = choose_splits(a);
+  if (ns <= 1) return 0;
+  const int64_t N = (int64_t)a->B * a->T * a->H;
+  return ns * N * ((int64_t)a->Dv + 2) * 4;
+}
+
+extern "C" int mxb_sparse_attn(const mxb_sparse_attn_args* a, void* stream) {
+  int rc = validate_sparse(a);
+  if (rc != MXB_OK) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  SparseParams p{};
+  p.q = a->q; p.q_sb = a->q_stride_b; p.q_sh = a->q_stride_h; p.q_st = a->q_stride_t;
+  p.comp_kv = a->comp_kv; p.comp_scales = reinterpret_cast<const __half*>(a->comp_scales);
+  p.comp_row_start = a->comp_row_start; p.comp_row_count = a->comp_row_count; p.n_comp = a->n_comp;
+  p.raw_kv = a->raw_kv; p.raw_scales = reinterpret_cast<const __half*>(a->raw_scales);
+  p.raw_cap = a->raw_cap; p.raw_start = a->raw_start;
+  p.topk = a->topk; p.k = a->k; p.sinks = a->sinks;
+  p.out = a->out; p.o_sb = a->out_stride_b; p.o_sh = a->out_stride_h; p.o_st = a->out_stride_t;
+  p.partial_ml = a->partial_ml;
+  p.B = a->B; p.T = a->T; p.H = a->H; p.Dqk = a->Dqk; p.Dv = a->Dv; p.scale = a->scale;
+  p.pos0 = a->pos0; p.pos0_dev = a->pos0_dev; p.window = a->window; p.ratio = a->ratio;
+  p.nsplit = choose_splits(a);
+
+  const int64_t N = (int64_t)a->B * a->T * a->H;
+  if (p.nsplit > 1) {
+    const int64_t need = p.nsplit * N * ((int64_t)a->Dv + 2) * 4;
+    MXB_REQUIRE(a->workspace && a->workspace_bytes >= need, MXB_ERR_WORKSPACE,
+                "sparse attention: workspace of %lld bytes required", (long long)need);
+    p.ws_o = reinterpret_cast<float*>(a->workspace);
+    p.ws_ml = p.ws_o + (int64_t)p.nsplit * N * a->Dv;
+  }
+  const size_t smem = ((size_t)kTileRows * (a->Dqk + 1) + (size_t)kHeadsPerCta * a->Dqk +
+                       (size_t)kHeadsPerCta * kTileRows + kTileRows) * 4;
+  dim3 grid((unsigned)p.nsplit, (unsigned)ceil_div(a->H, kHeadsPerCta), (unsigned)(a->B * a->T));
+
+  const int kt = a->kv_dtype, qt = a->q_dtype;
+#define MXB_PAIR(QT, KT) \
+  if (qt == QT && kt == KT) rc = launch_sparse<KT, QT>(p, a->out_dtype, smem, grid, st); else
+  MXB_PAIR(MXB_F32, MXB_F32)
+  MXB_PAIR(MXB_F32, MXB_F16)
+  MXB_PAIR(MXB_F32, MXB_BF16)
+  MXB_PAIR(MXB_F32, MXB_I8)
+  MXB_PAIR(MXB_F16, MXB_F16)
+  MXB_PAIR(MXB_F16, MXB_I8)
+  MXB_PAIR(MXB_BF16, MXB_BF16)
+  MXB_PAIR(MXB_BF16, MXB_I8)
+  return fail(MXB_ERR_UNSUPPORTED, "sparse attention: unsupported q/kv dtype pair (%d, %d)", qt, kt);
+#undef MXB_PAIR
+  if (rc != MXB_OK) return rc;
+
+  if (p.nsplit > 1) {
+    MergeParams mp{};
+    mp.o_parts = p.ws_o; mp.ml_parts = p.ws_ml; mp.sinks = a->sinks;
+    mp.out = a->out; mp.out_ml = a->partial_ml;
+    mp.o_sb = a->out_stride_b; mp.o_sh = a->out_stride_h; mp.o_st = a->out_stride_t;
+    mp.P = p.nsplit; mp.B = a->B; mp.T = a->T; mp.H = a->H; mp.Dv = a->Dv;
+    mp.finalize = a->partial_ml ? 0 : 1;
+    return launch_merge(mp, a->partial_ml ? MXB_F32 : a->out_dtype, st);
+  }
+  return MXB_OK;
+}
+
+extern "C" int mxb_merge_partials(const mxb_merge_args* a, void* stream) {
+  MXB_REQUIRE(a != nullptr, MXB_ERR_INVALID, "merge: null args");
+  MXB_REQUIRE(a->P >= 1 && a->B > 0 && a->T > 0 && a->H > 0 && a->Dv > 0, MXB_ERR_INVALID,
+              "merge: sizes must be positive");
+  MXB_REQUIRE(a->o_parts && a->ml_parts && a->out, MXB_ERR_INVALID, "merge: null tensor");
+  MergeParams mp{};
+  mp.o_parts = a->o_parts; mp.ml_parts = a->ml_parts; mp.sinks = a->sinks; mp.out = a->out; mp.out_ml = nullptr;
+  mp.o_sb = a->out_stride_b; mp.o_sh = a->out_stride_h; mp.o_st = a->out_stride_t;
+  mp.P = a->P; mp.B = a->B; mp.T = a->T; mp.H = a->H; mp.Dv = a->Dv; mp.finalize = 1;
+  return launch_merge(mp, a->out_dtype, reinterpret_cast<cudaStream_t>(stream));
+}

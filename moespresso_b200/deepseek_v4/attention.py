@@ -1,0 +1,99 @@
+"""Top-k selection and the indexer top-k contract on B200.
+
+``causal_indexer_topk`` keeps the signature of the reference's NumPy contract
+(``src/moespresso/runtime/deepseek_v4/attention.py:277-313``); ``topk_select`` is
+the device operator behind it and behind the served ``argpartition`` + ``sort``
+(``src/moespresso/runtime/deepseek_v4/model.py:1003-1005,1442-1451``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from .. import _abi
+from .._torchabi import ptr, require_cuda, stream_ptr, workspace
+
+
+def topk_select(scores, k: int, *, valid=None, row_start=None, n=None, order: str = "index"):
+    """Ids of the k largest finite scores of every row; ties to the lower id;
+    -inf / NaN never selected; -1 in unused slots.
+
+    scores: float32 ``[..., n]`` (rows are the leading axes) or, with ``row_start``
+    (int64 ``[rows]``) and ``valid`` (int32 ``[rows]``), one flat vector holding ragged
+    rows, ``n`` = the longest row.  ``order="index"``: ids ascending (what the
+    attention kernels walk); ``order="score"``: descending score, ties by ascending id
+    (the order of the NumPy contract).  Returns int32 ``[..., k]``.
+    """
+    dev = require_cuda(scores)
+    if scores.dtype != torch.float32:
+        raise ValueError("scores must be float32")
+    if int(k) <= 0:
+        raise ValueError("topk must be positive")
+    lib = _abi.load()
+    scores = scores.contiguous()
+    if row_start is None:
+        lead = scores.shape[:-1]
+        n_ = int(scores.shape[-1])
+        rows = 1
+        for s in lead:
+            rows *= int(s)
+        row_stride = n_
+    else:
+        lead = (int(row_start.numel()),)
+        rows = lead[0]
+        n_ = int(n)
+        row_stride = 0
+    out = torch.empty((rows, int(k)), dtype=torch.int32, device=dev)
+    if rows == 0:
+        return out.reshape(*lead, int(k))
+    if valid is not None:
+        valid = valid.to(torch.int32).contiguous()
+    a = _abi.TopkArgs()
+    a.scores = ptr(scores); a.row_stride = row_stride; a.row_start = ptr(row_start); a.row_count = ptr(valid)
+    a.out_ids = ptr(out); a.rows = rows; a.n = n_; a.k = int(k)
+    ws = workspace(lib.mxb_topk_workspace_bytes(rows, n_, int(k)), dev)
+    a.workspace = ptr(ws); a.workspace_bytes = 0 if ws is None else ws.numel()
+    _abi.check(lib.mxb_topk_select(C.byref(a), stream_ptr()))
+    out = out.reshape(*lead, int(k))
+    if order == "score":
+        if row_start is not None:
+            raise ValueError("score order is available for rectangular score matrices only")
+        flat = scores.reshape(rows, n_)
+        ids = out.reshape(rows, int(k)).long()
+        picked = torch.gather(flat, 1, ids.clamp(min=0))
+        picked = torch.where(ids >= 0, picked, torch.full_like(picked, float("-inf")))
+        perm = torch.sort(picked, dim=1, descending=True, stable=True).indices
+        out = torch.gather(ids, 1, perm).to(torch.int32).reshape(*lead, int(k))
+    elif order != "index":
+        raise ValueError("order must be 'index' or 'score'")
+    return out
+
+
+def causal_indexer_topk(raw_scores, head_weights, query_positions, pool_indices, ratio: int, *, topk: int = 512,
+                        index_head_dim: int = 128, n_heads: int = 64):
+    """Device form of the reference's ``causal_indexer_topk``: raw per-head scores
+    ``[queries, heads, pool_rows]`` and head weights ``[queries, heads]`` -> int64
+    ``[queries, min(topk, pool_rows)]`` pool ids in descending-score order, ``-1`` padded."""
+    if int(ratio) <= 0:
+        raise ValueError("ratio must be positive")
+    if int(topk) <= 0:
+        raise ValueError("topk must be positive")
+    require_cuda(raw_scores)
+    raw = raw_scores.to(torch.float32)
+    w = head_weights.to(torch.float32)
+    if raw.ndim != 3:
+        raise ValueError("raw_scores must have shape (queries, heads, pool_rows)")
+    if tuple(w.shape) != tuple(raw.shape[:2]):
+        raise ValueError("head_weights must have shape (queries, heads)")
+    scale = (index_head_dim ** -0.5) * (n_heads ** -0.5)
+    scores = (torch.clamp_min(raw, 0) * w[..., None]).sum(dim=1) * scale
+    qpos = torch.as_tensor(query_positions, device=raw.device, dtype=torch.int64).reshape(-1)
+    pool = torch.as_tensor(pool_indices, device=raw.device, dtype=torch.int64).reshape(-1)
+    vis = ((pool[None, :] + 1) * int(ratio)) <= (qpos[:, None] + 1)
+    scores = torch.where(vis, scores, torch.full_like(scores, float("-inf")))
+    width = min(int(topk), int(pool.numel()))
+    if width == 0:
+        return torch.empty((raw.shape[0], 0), dtype=torch.int64, device=raw.device)
+    ids = topk_select(scores, width, order="score").long()
+    return torch.where(ids >= 0, pool[ids.clamp(min=0)], torch.full_like(ids, -1))

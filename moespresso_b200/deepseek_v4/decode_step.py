@@ -1,0 +1,67 @@
+"""Batched sparse decode step: indexer score -> top-k -> indexed sparse attention.
+
+The reference runs this chain once per layer for batch 1
+(``_IndexerDS4ScoreContract.__call__`` then gather + SDPA,
+``src/moespresso/runtime/deepseek_v4/model.py:867-1065,1604-1650``; fused island
+``fused_decode_prep`` / ``fused_decode_sdpa``,
+``src/moespresso/runtime/deepseek_v4/decode_attention_kernel.py:669-786``).  Here a
+ragged batch of sequences shares one flat latent-KV table and one flat index-key
+table; every row of every sequence is visible (decode applies no causal mask,
+model.py:1047-1055).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .attention import topk_select
+from .indexed_attention_kernel import indexer_scores, sparse_attention
+
+
+@dataclass
+class LatentCache:
+    """Device-resident tables of a batch of sequences.
+
+    kv         [rows_total, Dqk]  int8 / bf16 / fp16 / fp32 latent rows (K = row, V = row[:d_v])
+    kv_scales  [rows_total]       fp16 per-row scale (int8 only, else None)
+    idx_keys   [rows_total, Di]   indexer keys (fp8-e4m3 / bf16 / fp16 / fp32)
+    row_start  [B] int64, row_count [B] int32; max_rows = longest sequence (host int)
+    """
+    kv: torch.Tensor
+    kv_scales: torch.Tensor | None
+    idx_keys: torch.Tensor
+    row_start: torch.Tensor
+    row_count: torch.Tensor
+    max_rows: int
+
+    @property
+    def batch(self) -> int:
+        return int(self.row_start.numel())
+
+
+def sparse_decode_step(q, idx_q, idx_w, cache: LatentCache, *, k: int, scale: float, d_v: int,
+                       sinks=None, out_dtype=torch.float32, exact_fp32: bool = False, partial: bool = False,
+                       return_ids: bool = False, return_scores: bool = False):
+    """q [B,H,Dqk]; idx_q [B,Hi,Di]; idx_w [B,Hi] float32.  Returns out [B,H,d_v]
+    (plus ids [B,k] int32 ascending / scores flat [rows_total] on request)."""
+    B = cache.batch
+    scores = indexer_scores(idx_q[:, :, None, :], idx_w[:, None, :].contiguous(), cache.idx_keys,
+                            n_rows=cache.max_rows, row_start=cache.row_start, row_count=cache.row_count,
+                            exact_fp32=exact_fp32)
+    ids = topk_select(scores, k, valid=cache.row_count, row_start=cache.row_start, n=cache.max_rows)
+    res = sparse_attention(q[:, :, None, :], cache.kv, ids[:, None, :], sinks, pos0=0, window=0, ratio=0,
+                           scale=scale, d_v=d_v, kv_scales=cache.kv_scales, comp_row_start=cache.row_start,
+                           comp_row_count=cache.row_count, n_comp=cache.max_rows, out_dtype=out_dtype,
+                           partial=partial)
+    if partial:
+        out, ml = res
+        out = (out[:, :, 0, :], ml[:, 0])
+    else:
+        out = res[:, :, 0, :]
+    extra = []
+    if return_ids:
+        extra.append(ids)
+    if return_scores:
+        extra.append(scores)
+    return (out, *extra) if extra else out

@@ -1,0 +1,206 @@
+"""Indexed mixed (sparse) attention against the CPU oracle.
+
+Tolerances (max-abs): 1e-4 for float32 inputs, 2e-2 for 16-bit / int8 inputs."""
+import numpy as np
+import pytest
+import torch
+
+from moespresso_b200 import synth
+from moespresso_b200.deepseek_v4 import indexed_attention_kernel as iak
+from oracle import ds4
+from tests.gpu_util import bf16_round, dev, f16_round, max_abs, need_gpu
+
+pytestmark = pytest.mark.gpu
+TOL_F32 = 1e-4
+TOL_16 = 2e-2
+
+
+def test_config1_decode_fp32():
+    need_gpu()
+    c = synth.config1()
+    ids = ds4.topk_ids(ds4.indexer_scores(c["idx_q"][None], c["idx_keys"], c["idx_w"][None]), c["k"])[0]
+    out = iak.indexed_mixed_attention_decode(dev(c["q"]), None, dev(c["kv"]), dev(ids.astype(np.int32)), None,
+                                             pos0=0, window=0, ratio=0, scale=c["scale"], d_v=c["d_v"])
+    ref = ds4.indexed_mixed_attention_decode(c["q"], None, c["kv"], ids, None, pos0=0, window=0, ratio=0,
+                                             scale=c["scale"], d_v=c["d_v"])
+    assert out.shape == (64, 512) and out.dtype == torch.float32
+    assert max_abs(out, ref) <= TOL_F32
+
+
+def test_reference_probe_shape_with_window_and_sinks():
+    """Seeded like the reference's own probe: q N(0,1) [H,512] fp32, raw 128x512 fp16,
+    comp Rx512 fp16, topk = arange(512), sinks N(0,1)."""
+    need_gpu()
+    rng = np.random.default_rng(123)
+    H, D, R = 64, 512, 961
+    q = rng.standard_normal((H, D)).astype(np.float32)
+    raw = f16_round(rng.standard_normal((128, D)))
+    comp = f16_round(rng.standard_normal((R, D)))
+    sinks = rng.standard_normal(H).astype(np.float32)
+    ids = np.arange(512, dtype=np.int32)
+    pos0 = 128 + R * 4 - 1
+    for raw_start in (0, 37):
+        out = iak.indexed_mixed_attention_decode(dev(q), dev(raw, torch.float16), dev(comp, torch.float16), dev(ids),
+                                                 dev(sinks), pos0=pos0, raw_start=raw_start)
+        ref = ds4.indexed_mixed_attention_decode(q, raw, comp, ids, sinks, pos0=pos0, raw_start=raw_start)
+        assert max_abs(out, ref) <= 2e-3   # the reference's own tolerance for this probe
+
+
+def test_skip_break_and_empty():
+    need_gpu()
+    rng = np.random.default_rng(1)
+    H, D, R = 8, 64, 40
+    q = rng.standard_normal((H, D)).astype(np.float32)
+    comp = rng.standard_normal((R, D)).astype(np.float32)
+    sinks = rng.standard_normal(H).astype(np.float32)
+    # visible = (19+1)//4 = 5 : -1 skipped, 7 ends the walk, 1 after it is never visited
+    ids = np.array([0, -1, 3, 4, 7, 1], np.int32)
+    out = iak.indexed_mixed_attention_decode(dev(q), None, dev(comp), dev(ids), dev(sinks), pos0=19, ratio=4)
+    ref = ds4.indexed_mixed_attention_decode(q, None, comp, ids, sinks, pos0=19, ratio=4)
+    assert max_abs(out, ref) <= TOL_F32
+    # nothing visible: with a sink the output is zero, without one it is zero as well
+    none = np.full(6, -1, np.int32)
+    for sk in (dev(sinks), None):
+        out = iak.indexed_mixed_attention_decode(dev(q), None, dev(comp), dev(none), sk, pos0=19, ratio=4)
+        assert float(out.abs().max()) == 0.0
+    # -inf sink == no sink
+    a = iak.indexed_mixed_attention_decode(dev(q), None, dev(comp), dev(ids), None, pos0=19, ratio=4)
+    b = iak.indexed_mixed_attention_decode(dev(q), None, dev(comp), dev(ids),
+                                           dev(np.full(H, -np.inf, np.float32)), pos0=19, ratio=4)
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("kvkind", ["bf16", "int8"])
+def test_batched_ragged_decode_16bit(kvkind):
+    need_gpu()
+    lens = [700, 129, 4096, 33]
+    c = synth.config3(seed=7, lens=lens, k=256)
+    rng = np.random.default_rng(0)
+    B = len(lens)
+    ids = np.stack([np.sort(rng.choice(n, size=256, replace=n < 256))[:256] if n >= 256 else
+                    np.concatenate([np.arange(n), np.full(256 - n, -1)]) for n in lens]).astype(np.int32)
+    if kvkind == "int8":
+        kv_t, sc_t = dev(c["kv"]), dev(c["kv_scales"])
+        rows = c["kv"].astype(np.float64) * c["kv_scales"].astype(np.float64)[:, None]
+    else:
+        rows32 = bf16_round(c["kv"].astype(np.float32) * c["kv_scales"].astype(np.float32)[:, None])
+        kv_t, sc_t, rows = dev(rows32, torch.bfloat16), None, rows32.astype(np.float64)
+    out = iak.sparse_attention(dev(c["q"], torch.bfloat16)[:, :, None, :], kv_t, dev(ids)[:, None, :], None,
+                               pos0=0, window=0, ratio=0, scale=c["scale"], d_v=c["d_v"], kv_scales=sc_t,
+                               comp_row_start=dev(c["row_start"]), comp_row_count=dev(c["lens"].astype(np.int32)),
+                               n_comp=max(lens))
+    assert out.shape == (B, 64, 1, 512)
+    for b in range(B):
+        s = c["row_start"][b]
+        ref = ds4.indexed_mixed_attention_decode(c["q"][b], None, rows[s:s + lens[b]], ids[b], None, pos0=0,
+                                                 window=0, ratio=0, scale=c["scale"], d_v=c["d_v"])
+        assert max_abs(out[b, :, 0], ref) <= TOL_16
+    # bf16 output
+    out16 = iak.sparse_attention(dev(c["q"], torch.bfloat16)[:, :, None, :], kv_t, dev(ids)[:, None, :], None,
+                                 pos0=0, window=0, ratio=0, scale=c["scale"], d_v=c["d_v"], kv_scales=sc_t,
+                                 comp_row_start=dev(c["row_start"]), comp_row_count=dev(c["lens"].astype(np.int32)),
+                                 n_comp=max(lens), out_dtype=torch.bfloat16)
+    assert out16.dtype == torch.bfloat16
+    assert max_abs(out16, out) <= float(out.abs().max()) * 2 ** -8 + 1e-6
+
+
+@pytest.mark.parametrize("qdt", ["f32", "f16", "bf16"])
+def test_prefill_live_matches_oracle(qdt):
+    need_gpu()
+    rng = np.random.default_rng(21)
+    B, H, T, D, R, k, raw_cap = 2, 16, 13, 64, 50, 12, 9
+    pos0 = 100
+    tdt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[qdt]
+    rnd = {"f32": lambda x: x.astype(np.float32), "f16": f16_round, "bf16": bf16_round}[qdt]
+    kvdt = torch.float16 if qdt != "bf16" else torch.bfloat16
+    kvr = f16_round if qdt != "bf16" else bf16_round
+    q = rnd(rng.standard_normal((B, H, T, D)))
+    raw = kvr(rng.standard_normal((B, 1, raw_cap, D)))
+    comp = kvr(rng.standard_normal((B, R, D)))
+    sinks = rng.standard_normal(H).astype(np.float32)
+    ids = np.sort(rng.integers(0, R, size=(B, T, k)), axis=-1).astype(np.int32)
+    ids[0, 3, :4] = -1
+    fn = iak.indexed_mixed_attention_prefill_live_f32 if qdt == "f32" else iak.indexed_mixed_attention_prefill_live_f16
+    out = fn(dev(q, tdt), dev(raw, kvdt), dev(comp, kvdt), dev(ids), dev(sinks), pos0=pos0, window=5, ratio=4,
+             raw_start=2)
+    assert out.shape == (B, H, T, D) and out.dtype == torch.float32
+    for b in range(B):
+        ref = ds4.indexed_mixed_attention_prefill(q[b].transpose(1, 0, 2), raw[b, 0], comp[b], ids[b], sinks,
+                                                  pos0=pos0, window=5, ratio=4, raw_start=2)
+        assert max_abs(out[b].permute(1, 0, 2), ref) <= (TOL_F32 if qdt == "f32" else 2e-3)
+    # chunk invariance: the second half of the chunk computed alone gives the same bits
+    h = T // 2
+    raw_half = raw  # raw buffer ends at the chunk's last token in both calls
+    out2 = fn(dev(q[:, :, h:], tdt), dev(raw_half, kvdt), dev(comp, kvdt), dev(ids[:, h:]), dev(sinks),
+              pos0=pos0 + h, window=5, ratio=4, raw_start=2)
+    assert torch.equal(out2, out[:, :, h:])
+    before = iak.prefill_consumer_call_counts()["prefill"]
+    fn(dev(q, tdt), dev(raw, kvdt), dev(comp, kvdt), dev(ids), dev(sinks), pos0=pos0, window=5, ratio=4)
+    assert iak.prefill_consumer_call_counts()["prefill"] == before + 1
+
+
+def test_splits_and_partials_merge():
+    need_gpu()
+    rng = np.random.default_rng(3)
+    H, D, Dv, R, k = 16, 96, 64, 3000, 700
+    q = rng.standard_normal((1, H, 1, D)).astype(np.float32)
+    comp = rng.standard_normal((R, D)).astype(np.float32)
+    sinks = rng.standard_normal(H).astype(np.float32)
+    ids = np.sort(rng.choice(R, size=k, replace=False)).astype(np.int32)
+    ref = ds4.indexed_mixed_attention_decode(q[0, :, 0], None, comp, ids, sinks, pos0=0, window=0, ratio=0, d_v=Dv)
+    outs = []
+    for ns in (1, 2, 7, 16):
+        o = iak.sparse_attention(dev(q), dev(comp), dev(ids)[None, None], dev(sinks), pos0=0, window=0, ratio=0,
+                                 d_v=Dv, n_splits=ns)
+        assert max_abs(o[0, :, 0], ref) <= TOL_F32
+        outs.append(o)
+    # two disjoint id ranges as partials, merged with the sink joining once
+    parts_o, parts_ml = [], []
+    for sub in (ids[:300], ids[300:]):
+        for ns in (1, 3):
+            pass
+        o, ml = iak.sparse_attention(dev(q), dev(comp), dev(sub)[None, None], None, pos0=0, window=0, ratio=0,
+                                     d_v=Dv, partial=True, out_layout="bthd", n_splits=3)
+        parts_o.append(o); parts_ml.append(ml)
+    merged = iak.merge_partials(torch.stack(parts_o), torch.stack(parts_ml), dev(sinks))
+    assert max_abs(merged[0, 0], ref) <= TOL_F32
+    # an empty partial (no rows) contributes nothing
+    o, ml = iak.sparse_attention(dev(q), dev(comp), dev(np.full(4, -1, np.int32))[None, None], None, pos0=0,
+                                 window=0, ratio=0, d_v=Dv, partial=True, out_layout="bthd")
+    merged = iak.merge_partials(torch.stack(parts_o + [o]), torch.stack(parts_ml + [ml]), dev(sinks))
+    assert max_abs(merged[0, 0], ref) <= TOL_F32
+
+
+def test_contract_errors():
+    need_gpu()
+    z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device="cuda")
+    with pytest.raises(ValueError, match="rank-2"):
+        iak.indexed_mixed_attention_decode(z(2, 8, 64), None, z(4, 64), z(4, dt=torch.int32), None, pos0=0)
+    with pytest.raises(ValueError, match="width must match"):
+        iak.indexed_mixed_attention_decode(z(8, 64), None, z(4, 32), z(4, dt=torch.int32), None, pos0=0)
+    with pytest.raises(ValueError, match="sinks must have shape"):
+        iak.indexed_mixed_attention_decode(z(8, 64), None, z(4, 64), z(4, dt=torch.int32), z(7), pos0=0)
+    with pytest.raises(ValueError, match="raw_start must be inside"):
+        iak.indexed_mixed_attention_decode(z(8, 64), z(4, 64), z(4, 64), z(4, dt=torch.int32), None, pos0=9,
+                                           raw_start=4)
+    with pytest.raises(ValueError, match="divisible by 8"):
+        iak.indexed_mixed_attention_prefill_live_f32(z(1, 12, 2, 64), None, z(1, 4, 64), z(1, 2, 4, dt=torch.int32),
+                                                     None, pos0=0)
+    with pytest.raises(ValueError, match="float16"):
+        iak.indexed_mixed_attention_prefill_live_f16(z(1, 16, 2, 64), None, z(1, 4, 64),
+                                                     z(1, 2, 4, dt=torch.int32), None, pos0=0)
+    with pytest.raises(ValueError, match="positive window and ratio"):
+        iak.banded_prefill_attention_live(z(1, 16, 2, 64), None, z(1, 4, 64), z(1, 2, 4, dt=torch.int32), None,
+                                          pos0=0, window=0, ratio=4)
+    with pytest.raises(ValueError, match="mma consumer"):
+        iak.banded_prefill_attention_live(z(1, 8, 2, 64), None, z(1, 4, 64), z(1, 2, 4, dt=torch.int32), None,
+                                          pos0=0, window=128, ratio=4)
+    with pytest.raises(ValueError, match="at least one compressed row"):
+        iak.indexer_scores_tiled_live(z(1, 16, 2, 64), z(1, 2, 16), z(1, 0, 64), pos0=0)
+    with pytest.raises(ValueError, match="head_dim=128"):
+        iak.indexer_scores_tiled_live(z(1, 16, 2, 32), z(1, 2, 16), z(1, 4, 32), pos0=0)
+    with pytest.raises(ValueError, match="float16"):
+        iak.indexer_scores_tiled_live(z(1, 16, 2, 64, dt=torch.float16), z(1, 2, 16), z(1, 4, 64), pos0=0)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        iak.indexed_mixed_attention_decode(torch.zeros(8, 64), None, torch.zeros(4, 64),
+                                           torch.zeros(4, dtype=torch.int32), None, pos0=0)
