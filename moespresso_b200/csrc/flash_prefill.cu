@@ -35,6 +35,7 @@ struct FlashParams {
   int64_t o_ss, o_sh;
   int32_t S, Skv, Hq, Hkv;
   float scale_log2;  // scale * log2(e)
+  int32_t q_head_inner, k_head_inner;  // tensor-map dimension order: (D, head, row) instead of (D, row, head)
   int32_t* status;
 };
 
@@ -136,13 +137,16 @@ __global__ void __launch_bounds__(192, 1) flash_prefill_kernel(const __grid_cons
       ptx::tma_prefetch_desc(&tm_k);
       ptx::tma_prefetch_desc(&tm_vt);
       ptx::mbar_expect_tx(q_full, 4 * 16384);
-      for (int kb = 0; kb < 4; ++kb) ptx::tma_load_3d(q_s + kb * 16384, &tm_q, q_full, kb * 64, m0, head);
+      for (int kb = 0; kb < 4; ++kb)
+        ptx::tma_load_3d(q_s + kb * 16384, &tm_q, q_full, kb * 64, p.q_head_inner ? head : m0,
+                         p.q_head_inner ? m0 : head);
       for (int j = 0; j < ntiles; ++j) {
         const int s = j & 1, u = j >> 1;
         if (j >= 2) ptx::mbar_wait(&k_empty[s], (uint32_t)((u - 1) & 1), abort_flag);
         ptx::mbar_expect_tx(&k_full[s], 32768);
         for (int kb = 0; kb < 4; ++kb)
-          ptx::tma_load_3d(k_s + s * 32768 + kb * 8192, &tm_k, &k_full[s], kb * 64, j * FB_N, kvh);
+          ptx::tma_load_3d(k_s + s * 32768 + kb * 8192, &tm_k, &k_full[s], kb * 64, p.k_head_inner ? kvh : j * FB_N,
+                           p.k_head_inner ? j * FB_N : kvh);
         if (j >= 2) ptx::mbar_wait(&v_empty[s], (uint32_t)((u - 1) & 1), abort_flag);
         ptx::mbar_expect_tx(&v_full[s], 32768);
         ptx::tma_load_3d(v_s + s * 32768, &tm_vt, &v_full[s], j * FB_N, 0, kvh);
@@ -352,17 +356,22 @@ extern "C" int mxb_flash_prefill(const mxb_flash_prefill_args* a, void* stream) 
 
   const CUtensorMapDataType dt = a->dtype == MXB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUtensorMap tq, tk, tv;
+  // cuTensorMapEncodeTiled wants ascending strides: put the head axis before the row axis when its
+  // stride is the smaller one ([rows, heads, D] layouts); the box is one head wide either way.
+  const bool q_hin = a->q_stride_h < a->q_stride_s, k_hin = a->k_stride_h < a->k_stride_s;
   {
-    uint64_t dims[3] = {(uint64_t)a->D, (uint64_t)a->S, (uint64_t)a->Hq};
-    uint64_t str[2] = {(uint64_t)a->q_stride_s * 2, (uint64_t)a->q_stride_h * 2};
-    uint32_t box[3] = {64, FB_M, 1};
+    uint64_t dims[3] = {(uint64_t)a->D, (uint64_t)(q_hin ? a->Hq : a->S), (uint64_t)(q_hin ? a->S : a->Hq)};
+    uint64_t str[2] = {(uint64_t)(q_hin ? a->q_stride_h : a->q_stride_s) * 2,
+                       (uint64_t)(q_hin ? a->q_stride_s : a->q_stride_h) * 2};
+    uint32_t box[3] = {64, q_hin ? 1u : (uint32_t)FB_M, q_hin ? (uint32_t)FB_M : 1u};
     rc = make_tensor_map(&tq, dt, 3, a->q, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != MXB_OK) return rc;
   }
   {
-    uint64_t dims[3] = {(uint64_t)a->D, (uint64_t)a->Skv, (uint64_t)a->Hkv};
-    uint64_t str[2] = {(uint64_t)a->k_stride_s * 2, (uint64_t)a->k_stride_h * 2};
-    uint32_t box[3] = {64, FB_N, 1};
+    uint64_t dims[3] = {(uint64_t)a->D, (uint64_t)(k_hin ? a->Hkv : a->Skv), (uint64_t)(k_hin ? a->Skv : a->Hkv)};
+    uint64_t str[2] = {(uint64_t)(k_hin ? a->k_stride_h : a->k_stride_s) * 2,
+                       (uint64_t)(k_hin ? a->k_stride_s : a->k_stride_h) * 2};
+    uint32_t box[3] = {64, k_hin ? 1u : (uint32_t)FB_N, k_hin ? (uint32_t)FB_N : 1u};
     rc = make_tensor_map(&tk, dt, 3, a->k, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != MXB_OK) return rc;
   }
@@ -380,6 +389,8 @@ extern "C" int mxb_flash_prefill(const mxb_flash_prefill_args* a, void* stream) 
   p.S = a->S; p.Skv = a->Skv; p.Hq = a->Hq; p.Hkv = a->Hkv;
   p.scale_log2 = a->scale * 1.4426950408889634f;
   p.status = a->status;
+  p.q_head_inner = q_hin ? 1 : 0;
+  p.k_head_inner = k_hin ? 1 : 0;
   const int smem = FlashSmem::total + 1024;
   dim3 grid((unsigned)ceil_div(a->S, FB_M), (unsigned)a->Hq);
   if (a->dtype == MXB_BF16) {

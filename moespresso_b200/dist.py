@@ -1,0 +1,146 @@
+"""Multi-GPU drivers for the sparse decode path: one process per GPU, torch.distributed.
+
+The reference is single-device; this partitioning is new.  Two cases:
+
+* sequence sharding — independent sequences are dealt to ranks, balanced by context
+  length; the step needs no collective (``assign_sequences``);
+* KV-range sharding of ONE long sequence — rank g owns latent rows
+  [g*R/G, (g+1)*R/G).  Per step: local indexer scores -> local exact top-k with global
+  row ids -> all_gather of (score, id) candidates (k * 8 bytes per rank) -> every rank
+  runs the same exact global selection (ties to the lower global id) and keeps the ids
+  it owns -> local sparse attention producing un-normalised (o, m, l) partials ->
+  all_gather of the partials -> log-sum-exp merge in rank order, the sink joining once.
+  The result equals the single-GPU result: the selected id set bit-for-bit (scores do
+  not depend on the partition), the output up to fp32 summation order.
+
+The device operators are injected through ``ops`` so that the host-side logic
+(candidate exchange, ownership, merge order) can be exercised on CPU ranks with the
+gloo backend.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+
+def assign_sequences(lens, world: int) -> list[list[int]]:
+    """Deal sequences to ranks: longest first onto the least-loaded rank (ties to the
+    lower rank); each rank's list is returned in ascending sequence order."""
+    lens = [int(x) for x in lens]
+    order = sorted(range(len(lens)), key=lambda i: (-lens[i], i))
+    load = [0] * world
+    out: list[list[int]] = [[] for _ in range(world)]
+    for i in order:
+        r = min(range(world), key=lambda j: (load[j], j))
+        out[r].append(i)
+        load[r] += lens[i]
+    return [sorted(x) for x in out]
+
+
+def row_range(n_rows: int, world: int, rank: int, align: int = 128) -> tuple[int, int]:
+    """Rows [lo, hi) of rank `rank`; boundaries are multiples of `align` (the score
+    kernel's tile height) except the last one."""
+    per = -(-n_rows // world)
+    per = -(-per // align) * align
+    lo = min(rank * per, n_rows)
+    return lo, min(lo + per, n_rows)
+
+
+@dataclass
+class RangeShard:
+    """This rank's slice of one sequence's tables (device tensors)."""
+    kv: torch.Tensor                 # [rows_local, Dqk]
+    kv_scales: torch.Tensor | None   # [rows_local] fp16 (int8 KV)
+    idx_keys: torch.Tensor           # [rows_local, Di]
+    row_lo: int                      # first global row owned
+
+
+class CudaOps:
+    """The CUDA operators behind the driver."""
+
+    def scores(self, idx_q, idx_w, keys):
+        from .deepseek_v4.indexed_attention_kernel import indexer_scores
+        return indexer_scores(idx_q[None, :, None, :], idx_w[None, None, :].contiguous(), keys,
+                              n_rows=int(keys.shape[0]))[0, 0]
+
+    def topk(self, scores, k):
+        from .deepseek_v4.attention import topk_select
+        return topk_select(scores[None], k)[0]
+
+    def attend_partial(self, q, kv, kv_scales, ids, scale, d_v):
+        from .deepseek_v4.indexed_attention_kernel import sparse_attention
+        o, ml = sparse_attention(q[None, :, None, :], kv, ids[None, None, :], None, pos0=0, window=0, ratio=0,
+                                 scale=scale, d_v=d_v, kv_scales=kv_scales, n_comp=int(kv.shape[0]), partial=True,
+                                 out_layout="bthd")
+        return o[0, 0], ml[0, 0]          # [H, Dv], [H, 2]
+
+    def merge(self, o_parts, ml_parts, sinks):
+        from .deepseek_v4.indexed_attention_kernel import merge_partials
+        return merge_partials(o_parts[:, None, None], ml_parts[:, None, None], sinks)[0, 0]
+
+
+def _all_gather(t: torch.Tensor, group=None) -> torch.Tensor:
+    world = dist.get_world_size(group)
+    out = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(out, t.contiguous(), group=group)
+    return torch.stack(out)
+
+
+def range_sharded_decode_step(q, idx_q, idx_w, shard: RangeShard, *, k: int, scale: float, d_v: int, sinks=None,
+                              ops=None, group=None, return_ids: bool = False):
+    """One decode step of ONE sequence whose rows are range-sharded over the ranks of
+    `group`.  q [H,Dqk], idx_q [Hi,Di], idx_w [Hi] are replicated.  Every rank returns the
+    full output [H,d_v] (and, on request, the global ids this rank attended)."""
+    ops = ops or CudaOps()
+    rows_local = int(shard.idx_keys.shape[0])
+    dev = q.device
+    # 1-2: local scores and local exact top-k (ascending local ids, -1 padded)
+    if rows_local > 0:
+        scores = ops.scores(idx_q, idx_w, shard.idx_keys)
+        local_ids = ops.topk(scores, k).long()
+        cand_scores = torch.where(local_ids >= 0, scores[local_ids.clamp(min=0)],
+                                  torch.full((k,), float("-inf"), device=dev))
+        cand_ids = torch.where(local_ids >= 0, local_ids + shard.row_lo, torch.full_like(local_ids, -1))
+    else:
+        cand_scores = torch.full((k,), float("-inf"), device=dev)
+        cand_ids = torch.full((k,), -1, dtype=torch.int64, device=dev)
+    # 3: exchange candidates.  Rank order == ascending global id order (range sharding), and
+    #    each rank's list is ascending, so position order == global id order.
+    all_scores = _all_gather(cand_scores.float(), group).reshape(-1)
+    all_ids = _all_gather(cand_ids, group).reshape(-1)
+    # 4: the same exact selection on every rank; ties go to the lower position == lower global id
+    pos = ops.topk(all_scores, k).long()
+    chosen = torch.where(pos >= 0, all_ids[pos.clamp(min=0)], torch.full_like(pos, -1))
+    hi = shard.row_lo + rows_local
+    mine = (chosen >= shard.row_lo) & (chosen < hi)
+    my_ids = torch.where(mine, chosen - shard.row_lo, torch.full_like(chosen, -1)).to(torch.int32)
+    # 5: partial attention over the rows this rank owns (none -> m = -inf, l = 0)
+    if rows_local > 0:
+        o, ml = ops.attend_partial(q, shard.kv, shard.kv_scales, my_ids, scale, d_v)
+    else:
+        H = int(q.shape[0])
+        o = torch.zeros((H, d_v), dtype=torch.float32, device=dev)
+        ml = torch.stack([torch.full((H,), float("-inf"), device=dev), torch.zeros(H, device=dev)], dim=1)
+    # 6-7: exchange partials, merge in rank order, sink joins once
+    o_parts = _all_gather(o.float(), group)
+    ml_parts = _all_gather(ml.float(), group)
+    out = ops.merge(o_parts, ml_parts, sinks)
+    if return_ids:
+        return out, chosen[mine]
+    return out
+
+
+def numpy_lens_to_tables(c: dict, seqs: list[int]) -> dict:
+    """Slice a synthetic batch (moespresso_b200.synth.config3 layout) down to `seqs`,
+    re-basing row_start; used by the sequence-sharded drivers and the benchmark."""
+    lens = np.asarray([c["lens"][i] for i in seqs], dtype=np.int64)
+    parts = [slice(int(c["row_start"][i]), int(c["row_start"][i] + c["lens"][i])) for i in seqs]
+    cat = lambda a: np.concatenate([a[p] for p in parts], axis=0) if parts else a[:0]
+    out = dict(c)
+    out.update(lens=lens, row_start=np.concatenate([[0], np.cumsum(lens)[:-1]]).astype(np.int64) if len(seqs) else
+               np.zeros(0, np.int64), kv=cat(c["kv"]), kv_scales=cat(c["kv_scales"]),
+               idx_key_bits=cat(c["idx_key_bits"]), q=c["q"][seqs], idx_q=c["idx_q"][seqs], idx_w=c["idx_w"][seqs])
+    return out

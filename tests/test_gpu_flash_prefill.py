@@ -59,6 +59,7 @@ def test_bhld_layout_and_peaked_softmax():
     assert max_abs(out, ref) <= 4e-2      # |V| is 4x the benchmark's amplitude here
 
 
+@torch.no_grad()
 def test_wrapper_module_counts_and_rejects():
     need_gpu()
     torch.manual_seed(0)
