@@ -167,10 +167,13 @@ typedef struct {
   const int64_t* pos0_dev; /* [B] or NULL */
   int32_t window, ratio;
   int32_t n_splits;        /* 0 = choose */
+  int32_t flags;           /* MXB_SPARSE_* */
   void* workspace;
   int64_t workspace_bytes;
   int32_t* status;
 } mxb_sparse_attn_args;
+
+#define MXB_SPARSE_EXACT_FP32 1 /* CUDA-core fp32 kernel even where the tensor-core kernel applies */
 
 int64_t mxb_sparse_attn_workspace_bytes(const mxb_sparse_attn_args* a);
 int mxb_sparse_attn(const mxb_sparse_attn_args* a, void* stream);

@@ -13,6 +13,7 @@ from . import _build
 
 F32, F16, BF16, F8E4M3, I8 = 0, 1, 2, 3, 4
 INDEXER_EXACT_FP32 = 1
+SPARSE_EXACT_FP32 = 1
 
 _p = C.c_void_p
 _i32 = C.c_int32
@@ -49,7 +50,7 @@ class SparseAttnArgs(C.Structure):
         ("out", _p), ("out_dtype", _i32), ("out_stride_b", _i64), ("out_stride_h", _i64), ("out_stride_t", _i64),
         ("partial_ml", _p),
         ("B", _i32), ("T", _i32), ("H", _i32), ("Dqk", _i32), ("Dv", _i32), ("scale", _f32),
-        ("pos0", _i64), ("pos0_dev", _p), ("window", _i32), ("ratio", _i32), ("n_splits", _i32),
+        ("pos0", _i64), ("pos0_dev", _p), ("window", _i32), ("ratio", _i32), ("n_splits", _i32), ("flags", _i32),
         ("workspace", _p), ("workspace_bytes", _i64), ("status", _p),
     ]
 

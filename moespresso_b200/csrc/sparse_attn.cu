@@ -10,6 +10,7 @@
 // the row list write (o, m, l) partials that merge_kernel combines by log-sum-exp; the
 // sink joins once, in the merge (or in the single-split epilogue).
 #include "common.cuh"
+#include "sparse_attn.cuh"
 
 namespace mxb {
 
@@ -17,32 +18,6 @@ constexpr int kTileRows = 32;
 constexpr int kHeadsPerCta = 8;
 constexpr int kMaxDvRegs = 16;  // Dv <= 512
 
-struct SparseParams {
-  const void* q;
-  int64_t q_sb, q_sh, q_st;
-  const void* comp_kv;
-  const __half* comp_scales;
-  const int64_t* comp_row_start;
-  const int32_t* comp_row_count;
-  int64_t n_comp;
-  const void* raw_kv;
-  const __half* raw_scales;
-  int32_t raw_cap, raw_start;
-  const int32_t* topk;
-  int32_t k;
-  const float* sinks;
-  void* out;
-  int64_t o_sb, o_sh, o_st;
-  float* partial_ml;   // external partial mode
-  float* ws_o;         // [nsplit][N][Dv]
-  float* ws_ml;        // [nsplit][N][2]
-  int32_t B, T, H, Dqk, Dv;
-  float scale;
-  int64_t pos0;
-  const int64_t* pos0_dev;
-  int32_t window, ratio;
-  int32_t nsplit;
-};
 
 template <int KVT>
 __device__ __forceinline__ void stage_row(float* dst, const void* src_row, int Dqk, float row_scale, int lane) {
@@ -287,7 +262,12 @@ static int launch_merge(const MergeParams& mp, int out_dtype, cudaStream_t st) {
   return MXB_OK;
 }
 
+static bool use_tc(const mxb_sparse_attn_args* a) {
+  return !(a->flags & MXB_SPARSE_EXACT_FP32) && sparse_tc_eligible(a->kv_dtype, a->q_dtype, a->H, a->Dqk, a->Dv);
+}
+
 static int choose_splits(const mxb_sparse_attn_args* a) {
+  if (use_tc(a)) return sparse_tc_splits(a->B, a->T, a->H, a->k, a->raw_cap, a->n_splits);
   if (a->n_splits > 0) return a->n_splits > 64 ? 64 : a->n_splits;
   const int64_t base = (int64_t)a->B * a->T * ceil_div(a->H, kHeadsPerCta);
   const int64_t max_rows = (int64_t)a->k + a->raw_cap;
@@ -368,6 +348,7 @@ extern "C" int mxb_sparse_attn(const mxb_sparse_attn_args* a, void* stream) {
   p.B = a->B; p.T = a->T; p.H = a->H; p.Dqk = a->Dqk; p.Dv = a->Dv; p.scale = a->scale;
   p.pos0 = a->pos0; p.pos0_dev = a->pos0_dev; p.window = a->window; p.ratio = a->ratio;
   p.nsplit = choose_splits(a);
+  p.status = a->status;
 
   const int64_t N = (int64_t)a->B * a->T * a->H;
   if (p.nsplit > 1) {
@@ -382,6 +363,9 @@ extern "C" int mxb_sparse_attn(const mxb_sparse_attn_args* a, void* stream) {
   dim3 grid((unsigned)p.nsplit, (unsigned)ceil_div(a->H, kHeadsPerCta), (unsigned)(a->B * a->T));
 
   const int kt = a->kv_dtype, qt = a->q_dtype;
+  if (use_tc(a)) {
+    rc = launch_sparse_tc(p, kt, qt, a->out_dtype, st);
+  } else
 #define MXB_PAIR(QT, KT) \
   if (qt == QT && kt == KT) rc = launch_sparse<KT, QT>(p, a->out_dtype, smem, grid, st); else
   MXB_PAIR(MXB_F32, MXB_F32)

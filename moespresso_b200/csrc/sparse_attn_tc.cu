@@ -1,0 +1,541 @@
+// Indexed mixed (sparse) attention on tcgen05 / TMEM for 16-bit and int8 KV tables.
+//
+// One CTA = one (split, sequence, token): all heads (<= 64) of that token share every
+// gathered row.  The gathered rows sit on the MMA M axis:
+//
+//   S^T[128 rows x 64 heads]  = Ktile[128 x Dqk] . Q^T          (A = row tile, K-major)
+//   O^T[Dv dims  x 64 heads] += Vtile^T[Dv x 128] . P^T          (A = the SAME row tile, read
+//                                                                 MN-major: dims contiguous)
+//
+// so one staged copy of the rows (128-byte-swizzled 64-feature slabs) feeds both
+// contractions and nothing is transposed.  Rows are gathered with 16-byte vector loads;
+// int8 rows are widened to fp16 integers (exact) while staging and their per-row scale is
+// folded into the logit (s = scale_j * q.int_j) and into P (p_j * scale_j), so the tensor
+// core multiplies exact values.  Thread = row for the softmax (TMEM lane), with a lazily
+// updated per-head reference maximum held in shared memory: the cross-row maximum is
+// reduced only when some logit exceeds the reference by more than 2^8, the
+// O accumulator in TMEM is rescaled only then.  The row sum uses the ROUNDED 16-bit P
+// values, so out = sum(p~ v) / sum(p~) is an exactly normalised average.  Splits over the
+// row list emit (o, m, l) partials for the log-sum-exp merge kernel.
+//
+// Operand type: fp16 for fp16 and int8 tables (q is rounded to fp16 on load, as the
+// reference kernels do), bf16 for bf16 tables.  TMEM: S^T at columns [0,64), O^T at
+// [64, 64 + Dv/2).
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+#include "sparse_attn.cuh"
+
+namespace mxb {
+
+constexpr int TC_ROWS = 128;
+constexpr int TC_HEADS = 64;
+constexpr float kRescaleGap = 8.f;  // log2 units
+
+struct TcLayout {
+  int nslab;       // Dqk / 64
+  int tile_off;    // rows tile: nslab slabs of [128 x 128 B]
+  int q_off;       // q operand: nslab slabs of [64 x 128 B]
+  int pt_off;      // P^T: 2 slabs of [64 heads x 128 B]
+  int misc_off;
+  int total;
+};
+
+__host__ __device__ inline TcLayout tc_layout(int Dqk, int Dv) {
+  TcLayout L;
+  L.nslab = Dqk / 64;
+  L.tile_off = 0;
+  L.q_off = L.nslab * 16384;
+  int end = L.q_off + L.nslab * 8192;
+  if (Dqk - Dv >= 64) {
+    L.pt_off = (Dv / 64) * 16384;  // the slab that only the logits need is free once S^T is done
+  } else {
+    L.pt_off = end;
+    end += 16384;
+  }
+  L.misc_off = end;
+  L.total = end + 5120;
+  return L;
+}
+
+struct TcMisc {
+  float m_ref[TC_HEADS];
+  float factor[TC_HEADS];
+  float colmax[4][TC_HEADS];
+  float l_tot[TC_HEADS];
+  float row_scale[TC_ROWS];
+  float inv_scale[TC_ROWS];
+  int valid[TC_ROWS];
+  const uint8_t* row_src[TC_ROWS];
+  uint64_t bar_s, bar_o;
+  uint32_t tmem_slot;
+  int abort_flag;
+  int keff;
+};
+
+// 16 int8 -> 16 fp16 integers (exact): bytes biased by 128 are dropped into the mantissa of 1024.0
+__device__ __forceinline__ void widen_i8x16_f16(const uint4& in, uint4& lo, uint4& hi) {
+  const uint32_t w[4] = {in.x ^ 0x80808080u, in.y ^ 0x80808080u, in.z ^ 0x80808080u, in.w ^ 0x80808080u};
+  uint32_t o[8];
+  const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t a = __byte_perm(w[i], 0x64646464u, 0x4140);
+    uint32_t b = __byte_perm(w[i], 0x64646464u, 0x4342);
+    __half2 ha = __hsub2(*reinterpret_cast<__half2*>(&a), bias);
+    __half2 hb = __hsub2(*reinterpret_cast<__half2*>(&b), bias);
+    o[2 * i] = *reinterpret_cast<uint32_t*>(&ha);
+    o[2 * i + 1] = *reinterpret_cast<uint32_t*>(&hb);
+  }
+  lo = make_uint4(o[0], o[1], o[2], o[3]);
+  hi = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint16_t to_op16(float x) {
+  if constexpr (BF16) {
+    __nv_bfloat16 v = __float2bfloat16_rn(x);
+    return *reinterpret_cast<uint16_t*>(&v);
+  } else {
+    __half v = __float2half_rn(x);
+    return *reinterpret_cast<uint16_t*>(&v);
+  }
+}
+template <bool BF16>
+__device__ __forceinline__ float from_op16(uint16_t u) {
+  if constexpr (BF16) return __bfloat162float(*reinterpret_cast<__nv_bfloat16*>(&u));
+  else return __half2float(*reinterpret_cast<__half*>(&u));
+}
+
+template <int KVT, int QT, int OT>
+__global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) {
+  constexpr bool BF16 = (KVT == MXB_BF16);
+  constexpr int EB = ElemBytes<KVT>::v;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const TcLayout L = tc_layout(p.Dqk, p.Dv);
+  uint8_t* tile = smem + L.tile_off;
+  uint8_t* q_s = smem + L.q_off;
+  uint8_t* pt = smem + L.pt_off;
+  TcMisc* mi = reinterpret_cast<TcMisc*>(smem + L.misc_off);
+  volatile int* abort_flag = &mi->abort_flag;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int quad = warp & 3, half_id = warp >> 2;
+  const int split = blockIdx.x;
+  const int bt = blockIdx.z;
+  const int b = bt / p.T, t = bt % p.T;
+  const int nslab = L.nslab;
+  const int n_mt = p.Dv / 128;
+
+  const int64_t pos_b = p.pos0_dev ? p.pos0_dev[b] : p.pos0;
+  const int64_t qpos = pos_b + t;
+  const int64_t last_pos = pos_b + p.T - 1;
+  const int64_t count = p.comp_row_count ? (int64_t)p.comp_row_count[b] : p.n_comp;
+  const int64_t cbase = p.comp_row_start ? p.comp_row_start[b] : (int64_t)b * p.n_comp;
+  int64_t visible = count;
+  if (p.ratio > 0) {
+    visible = (qpos + 1) / p.ratio;
+    if (visible > count) visible = count;
+  }
+  int64_t first_raw_pos = 0, first = 0;
+  int n_raw = 0;
+  if (p.raw_cap > 0) {
+    first_raw_pos = last_pos + 1 - p.raw_cap;
+    const int64_t window_first = (p.window != 0 && qpos + 1 > p.window) ? qpos + 1 - p.window : 0;
+    first = first_raw_pos > window_first ? first_raw_pos : window_first;
+    if (first < 0) first = 0;
+    const int64_t last = qpos < last_pos ? qpos : last_pos;
+    n_raw = last >= first ? (int)(last - first + 1) : 0;
+  }
+  const int32_t* ids = p.topk + (int64_t)bt * p.k;
+
+  if (tid == 0) {
+    ptx::mbar_init(&mi->bar_s, 1);
+    ptx::mbar_init(&mi->bar_o, 1);
+    mi->abort_flag = 0;
+    mi->keff = p.k;
+    ptx::mbar_fence_init();
+  }
+  if (tid < TC_HEADS) {
+    mi->m_ref[tid] = -INFINITY;
+    mi->l_tot[tid] = 0.f;
+  }
+  __syncwarp();
+  if (warp == 0) {
+    ptx::tmem_alloc(&mi->tmem_slot, 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = mi->tmem_slot;
+  const uint32_t tmem_o = tmem_base + 64;
+
+  {  // first list entry that ends the walk
+    int mine = p.k;
+    for (int j = tid; j < p.k; j += blockDim.x)
+      if ((int64_t)ids[j] >= visible) { mine = j; break; }
+    if (mine < p.k) atomicMin(&mi->keff, mine);
+  }
+  // q -> B operand of S^T: [64 heads x Dqk] K-major, 128-byte swizzle, rounded to the operand type
+  {
+    const bool vec = ((reinterpret_cast<uintptr_t>(p.q) & 15) == 0) && (p.q_sb % 8 == 0) && (p.q_sh % 8 == 0) &&
+                     (p.q_st % 8 == 0);
+    for (int i = tid; i < TC_HEADS * (p.Dqk / 8); i += blockDim.x) {
+      const int h = i / (p.Dqk / 8), c = i % (p.Dqk / 8);
+      alignas(16) uint16_t v[8];
+      if (h >= p.H) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = 0;
+      } else {
+        const int64_t base = (int64_t)b * p.q_sb + (int64_t)h * p.q_sh + (int64_t)t * p.q_st + c * 8;
+        float f[8];
+        if (vec) {
+          if constexpr (QT == MXB_F32) {
+            const float4 a = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + base));
+            const float4 bq = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + base) + 1);
+            f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = bq.x; f[5] = bq.y; f[6] = bq.z; f[7] = bq.w;
+          } else {
+            const uint4 u = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.q) + base));
+            unpack16<QT>(u, f);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] = load_elem<QT>(p.q, base + j);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = to_op16<BF16>(f[j]);
+      }
+      const int kb = c >> 3, cc = c & 7;
+      *reinterpret_cast<uint4*>(q_s + (size_t)kb * 8192 + (size_t)h * 128 + ((cc ^ (h & 7)) << 4)) =
+          *reinterpret_cast<uint4*>(v);
+    }
+  }
+  __syncthreads();
+  const int total = n_raw + mi->keff;
+  int per = (total + p.nsplit - 1) / p.nsplit;
+  per = ((per + TC_ROWS - 1) / TC_ROWS) * TC_ROWS;
+  const int e_lo = min(split * per, total), e_hi = min(e_lo + per, total);
+  const int ntiles = (e_hi - e_lo + TC_ROWS - 1) / TC_ROWS;
+
+  constexpr uint32_t fmt = BF16 ? ptx::kFmtBF16 : ptx::kFmtF16;
+  const uint32_t idesc_s = ptx::idesc_f16(fmt, fmt, 128, TC_HEADS, 0, 0);
+  const uint32_t idesc_o = ptx::idesc_f16(fmt, fmt, 128, TC_HEADS, 1, 0);  // A read MN-major
+  const uint32_t tile_addr = ptx::smem_u32(tile), q_addr = ptx::smem_u32(q_s), pt_addr = ptx::smem_u32(pt);
+  const float scale_log2 = p.scale * 1.4426950408889634f;
+
+  float l_thr[32];
+#pragma unroll
+  for (int c = 0; c < 32; ++c) l_thr[c] = 0.f;
+  bool have_o = false;
+
+  for (int it = 0; it < ntiles; ++it) {
+    const int e0 = e_lo + it * TC_ROWS;
+    // ---------------------------------------------------------------- gather 128 rows
+    // phase 0: lanes 0-15 of each warp resolve the source of the warp's 16 rows
+    if (lane < 16) {
+      const int rr = warp * 16 + lane;
+      const int e = e0 + rr;
+      const uint8_t* src = nullptr;
+      float rs = 1.f;
+      if (e < e_hi) {
+        if (e < n_raw) {
+          const int64_t pabs = first + e;
+          const int64_t phys = ((int64_t)p.raw_start + (pabs - first_raw_pos)) % p.raw_cap;
+          const int64_t ridx = (int64_t)b * p.raw_cap + phys;
+          src = reinterpret_cast<const uint8_t*>(p.raw_kv) + ridx * p.Dqk * EB;
+          if (KVT == MXB_I8) rs = __half2float(p.raw_scales[ridx]);
+        } else {
+          const int32_t id = ids[e - n_raw];
+          if (id >= 0) {
+            const int64_t ridx = cbase + id;
+            src = reinterpret_cast<const uint8_t*>(p.comp_kv) + ridx * p.Dqk * EB;
+            if (KVT == MXB_I8) rs = __half2float(p.comp_scales[ridx]);
+          }
+        }
+      }
+      mi->row_src[rr] = src;
+      mi->valid[rr] = src != nullptr;
+      mi->row_scale[rr] = rs;
+      mi->inv_scale[rr] = 1.f / rs;
+    }
+    __syncwarp();
+    // phase 1: up to 18 independent 16-byte loads per lane in flight, then widen / store
+    {
+      const int nch = p.Dqk * EB / 16;
+      int rpb = 16;
+      while (rpb * nch > 576) rpb >>= 1;
+      for (int r0 = 0; r0 < 16; r0 += rpb) {
+        uint4 v[18];
+#pragma unroll
+        for (int i = 0; i < 18; ++i) {
+          const int g = lane + 32 * i;
+          const int rl = g / nch, c = g - rl * nch;
+          v[i] = make_uint4(0, 0, 0, 0);
+          if (rl < rpb) {
+            const uint8_t* src = mi->row_src[warp * 16 + r0 + rl];
+            if (src) v[i] = __ldg(reinterpret_cast<const uint4*>(src) + c);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 18; ++i) {
+          const int g = lane + 32 * i;
+          const int rl = g / nch, c = g - rl * nch;
+          if (rl < rpb) {
+            const int rr = warp * 16 + r0 + rl;
+            uint8_t* drow = tile + (size_t)rr * 128;
+            const int sw = rr & 7;
+            if constexpr (KVT == MXB_I8) {
+              uint4 lo, hi;
+              widen_i8x16_f16(v[i], lo, hi);   // zero bytes (invalid row) widen to 0.0
+              const int kb = c >> 2, cc = (c & 3) * 2;
+              uint8_t* d = drow + (size_t)kb * 16384;
+              *reinterpret_cast<uint4*>(d + ((cc ^ sw) << 4)) = lo;
+              *reinterpret_cast<uint4*>(d + (((cc + 1) ^ sw) << 4)) = hi;
+            } else {
+              const int kb = c >> 3, cc = c & 7;
+              *reinterpret_cast<uint4*>(drow + (size_t)kb * 16384 + ((cc ^ sw) << 4)) = v[i];
+            }
+          }
+        }
+      }
+    }
+    ptx::fence_proxy_async_smem();
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+
+    // ---------------------------------------------------------------- S^T = Ktile . Q^T
+    if (tid == 0) {
+      ptx::tc_fence_after_sync();
+      for (int kb = 0; kb < nslab; ++kb) {
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint64_t ad = ptx::smem_desc_sw128(tile_addr + kb * 16384 + ks * 32, 16, 1024);
+          const uint64_t bd = ptx::smem_desc_sw128(q_addr + kb * 8192 + ks * 32, 16, 1024);
+          ptx::mma_f16_ss(tmem_base, ad, bd, idesc_s, (kb | ks) ? 1u : 0u);
+        }
+      }
+      ptx::mma_commit(&mi->bar_s);
+    }
+    ptx::mbar_wait(&mi->bar_s, (uint32_t)(it & 1), abort_flag);
+    ptx::tc_fence_after_sync();
+
+    // ---------------------------------------------------------------- softmax, thread = row
+    const int row = quad * 32 + lane;
+    const int col0 = half_id * 32;
+    uint32_t sv[32];
+    ptx::tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)col0, sv);
+    ptx::tmem_ld_wait();
+    const bool ok = mi->valid[row] != 0;
+    const float rs = mi->row_scale[row];
+    const float mul = scale_log2 * rs;
+    bool grow = false;
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+      const float x = ok ? __uint_as_float(sv[c]) * mul : -INFINITY;
+      sv[c] = __float_as_uint(x);
+      grow |= x > mi->m_ref[col0 + c] + kRescaleGap;
+    }
+    if (__syncthreads_or(grow ? 1 : 0)) {
+      // exact column maxima of this tile, new reference, rescale of what has been accumulated
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const float mx = warp_max(__uint_as_float(sv[c]));
+        if (lane == c) mi->colmax[quad][col0 + c] = mx;
+      }
+      __syncthreads();
+      if (tid < TC_HEADS) {
+        const float old = mi->m_ref[tid];
+        float mx = fmaxf(fmaxf(mi->colmax[0][tid], mi->colmax[1][tid]), fmaxf(mi->colmax[2][tid], mi->colmax[3][tid]));
+        mx = fmaxf(mx, old);
+        mi->factor[tid] = (old == -INFINITY) ? 0.f : exp2f(old - mx);
+        mi->m_ref[tid] = mx;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int c = 0; c < 32; ++c) l_thr[c] *= mi->factor[col0 + c];
+      if (have_o) {
+        // warp -> (lane quadrant, two of the four 128-dim blocks); columns = heads
+        for (int m2 = 0; m2 < 2; ++m2) {
+          const int mt = half_id * 2 + m2;
+          if (mt < n_mt) {
+#pragma unroll 1
+            for (int ch = 0; ch < 2; ++ch) {
+              uint32_t ov[32];
+              const uint32_t ta = tmem_o + ((uint32_t)(quad * 32) << 16) + (uint32_t)(mt * 64 + ch * 32);
+              ptx::tmem_ld32(ta, ov);
+              ptx::tmem_ld_wait();
+#pragma unroll
+              for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * mi->factor[ch * 32 + c]);
+              ptx::tmem_st32(ta, ov);
+            }
+          }
+        }
+        ptx::tmem_st_wait();
+      }
+    }
+    {
+      const float inv = mi->inv_scale[row];
+      const int slab = row >> 6, rj = row & 63;
+      uint8_t* pbase = pt + (size_t)slab * 8192 + (rj & 7) * 2;
+      const int cj = rj >> 3;
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const int h = col0 + c;
+        const float s = __uint_as_float(sv[c]);
+        const float pj = (s == -INFINITY) ? 0.f : exp2f(s - mi->m_ref[h]);
+        const uint16_t pr = to_op16<BF16>(KVT == MXB_I8 ? pj * rs : pj);
+        const float back = from_op16<BF16>(pr);
+        l_thr[c] += (KVT == MXB_I8) ? back * inv : back;
+        *reinterpret_cast<uint16_t*>(pbase + (size_t)h * 128 + ((cj ^ (h & 7)) << 4)) = pr;
+      }
+    }
+    ptx::fence_proxy_async_smem();
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+
+    // ---------------------------------------------------------------- O^T += Vtile^T . P^T
+    if (tid == 0) {
+      ptx::tc_fence_after_sync();
+      for (int mt = 0; mt < n_mt; ++mt) {
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          // A, MN-major: 64-feature blocks 16 KB apart (LBO), 8-row groups 1 KB apart (SBO); 16 rows per K step
+          const uint64_t ad = ptx::smem_desc_sw128(tile_addr + (2 * mt) * 16384 + ks * 2048, 16384, 1024);
+          const uint64_t bd = ptx::smem_desc_sw128(pt_addr + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024);
+          ptx::mma_f16_ss(tmem_o + (uint32_t)(mt * 64), ad, bd, idesc_o, (have_o || ks > 0) ? 1u : 0u);
+        }
+      }
+      ptx::mma_commit(&mi->bar_o);
+    }
+    have_o = true;
+    ptx::mbar_wait(&mi->bar_o, (uint32_t)(it & 1), abort_flag);  // the single row tile is rewritten next
+    ptx::tc_fence_after_sync();
+  }
+
+  // ------------------------------------------------------------------ reduce l over the 128 rows
+#pragma unroll
+  for (int c = 0; c < 32; ++c) {
+    const float s = warp_sum(l_thr[c]);
+    if (lane == c) mi->colmax[quad][half_id * 32 + c] = s;
+  }
+  __syncthreads();
+  if (tid < TC_HEADS) mi->l_tot[tid] = (mi->colmax[0][tid] + mi->colmax[1][tid]) + (mi->colmax[2][tid] + mi->colmax[3][tid]);
+  __syncthreads();
+
+  // ------------------------------------------------------------------ output
+  const int64_t N = (int64_t)p.B * p.T * p.H;
+  const bool direct = p.nsplit == 1;
+  for (int m2 = 0; m2 < 2; ++m2) {
+    const int mt = half_id * 2 + m2;
+    if (mt >= n_mt) continue;
+    const int d = mt * 128 + quad * 32 + lane;
+#pragma unroll 1
+    for (int ch = 0; ch < 2; ++ch) {
+      uint32_t ov[32];
+      if (have_o) {
+        ptx::tmem_ld32(tmem_o + ((uint32_t)(quad * 32) << 16) + (uint32_t)(mt * 64 + ch * 32), ov);
+        ptx::tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) ov[c] = 0u;
+      }
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const int h = ch * 32 + c;
+        if (h >= p.H) continue;
+        const float o = __uint_as_float(ov[c]);
+        if (direct && !p.partial_ml) {
+          const float m = mi->m_ref[h], l = mi->l_tot[h];
+          const float sink2 = p.sinks ? p.sinks[h] * 1.4426950408889634f : -INFINITY;
+          const float m2v = fmaxf(m, sink2);
+          float w = 0.f, den = 0.f;
+          if (m2v > -INFINITY) {
+            w = (m == -INFINITY) ? 0.f : exp2f(m - m2v);
+            den = l * w + ((sink2 == -INFINITY) ? 0.f : exp2f(sink2 - m2v));
+          }
+          const float r = den > 0.f ? o * (w / den) : 0.f;
+          store_elem<OT>(p.out, (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)t * p.o_st + d, r);
+        } else if (direct) {
+          reinterpret_cast<float*>(p.out)[(int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)t * p.o_st + d] = o;
+        } else {
+          p.ws_o[((int64_t)split * N + (int64_t)bt * p.H + h) * p.Dv + d] = o;
+        }
+      }
+    }
+  }
+  if (tid < p.H && (!direct || p.partial_ml)) {
+    // (m, l) in natural-log units for the merge kernel
+    const float m_nat = mi->m_ref[tid] == -INFINITY ? -INFINITY : mi->m_ref[tid] * 0.6931471805599453f;
+    float* ml = direct ? p.partial_ml + ((int64_t)bt * p.H + tid) * 2
+                       : p.ws_ml + ((int64_t)split * N + (int64_t)bt * p.H + tid) * 2;
+    ml[0] = m_nat;
+    ml[1] = mi->l_tot[tid];
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) ptx::tmem_dealloc(tmem_base, 512);
+  if (tid == 0 && *abort_flag) {
+    // a wait gave up: leave a visibly wrong marker for the caller
+    if (p.status) atomicExch(p.status, 2);
+  }
+}
+
+bool sparse_tc_eligible(int kv_dtype, int q_dtype, int H, int Dqk, int Dv) {
+  if (!(kv_dtype == MXB_F16 || kv_dtype == MXB_BF16 || kv_dtype == MXB_I8)) return false;
+  if (kv_dtype == MXB_BF16 && q_dtype == MXB_F16) return false;
+  if (H < 1 || H > TC_HEADS) return false;
+  if (Dqk % 64 != 0 || Dqk < 128 || Dqk > 576) return false;
+  if (Dv % 128 != 0 || Dv < 128 || Dv > 512 || Dv > Dqk) return false;
+  return tc_layout(Dqk, Dv).total + 1024 <= 227 * 1024;
+}
+
+int sparse_tc_splits(int B, int T, int H, int k, int raw_cap, int requested) {
+  const int64_t max_tiles = ceil_div((int64_t)k + raw_cap, TC_ROWS);
+  int64_t want;
+  if (requested > 0) {
+    want = requested;
+  } else {
+    const int64_t base = (int64_t)B * T;
+    want = (int64_t)sm_count() / (base > 0 ? base : 1);  // one wave of CTAs
+  }
+  if (want > max_tiles) want = max_tiles;
+  if (want > 64) want = 64;
+  if (want < 1) want = 1;
+  return (int)want;
+}
+
+template <int KVT, int QT>
+static int launch_tc_typed(SparseParams& p, int out_dtype, cudaStream_t st) {
+  const int smem = tc_layout(p.Dqk, p.Dv).total + 1024;
+  dim3 grid((unsigned)p.nsplit, 1, (unsigned)(p.B * p.T));
+#define MXB_TC(OT)                                                                                   \
+  {                                                                                                  \
+    auto kern = sparse_attn_tc_kernel<KVT, QT, OT>;                                                  \
+    MXB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));      \
+    kern<<<grid, 256, smem, st>>>(p);                                                                \
+  }
+  if (out_dtype == MXB_F32 || p.nsplit > 1 || p.partial_ml) MXB_TC(MXB_F32)
+  else if (out_dtype == MXB_BF16) MXB_TC(MXB_BF16)
+  else MXB_TC(MXB_F16)
+#undef MXB_TC
+  MXB_CUDA_OK(cudaGetLastError());
+  return MXB_OK;
+}
+
+int launch_sparse_tc(SparseParams& p, int kv_dtype, int q_dtype, int out_dtype, cudaStream_t st) {
+#define MXB_TCP(QT, KT) \
+  if (q_dtype == QT && kv_dtype == KT) return launch_tc_typed<KT, QT>(p, out_dtype, st);
+  MXB_TCP(MXB_F32, MXB_F16)
+  MXB_TCP(MXB_F16, MXB_F16)
+  MXB_TCP(MXB_F32, MXB_BF16)
+  MXB_TCP(MXB_BF16, MXB_BF16)
+  MXB_TCP(MXB_F32, MXB_I8)
+  MXB_TCP(MXB_F16, MXB_I8)
+  MXB_TCP(MXB_BF16, MXB_I8)
+#undef MXB_TCP
+  return fail(MXB_ERR_UNSUPPORTED, "sparse attention (tensor-core path): unsupported q/kv dtype pair (%d, %d)",
+              q_dtype, kv_dtype);
+}
+
+}  // namespace mxb

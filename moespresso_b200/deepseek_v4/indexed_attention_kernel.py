@@ -42,14 +42,16 @@ def check_status(status: torch.Tensor, what: str) -> None:
 def sparse_attention(q4, comp_kv, topk3, sinks, *, pos0, window, ratio, raw_kv=None, raw_start=0,
                      scale=None, d_v=None, kv_scales=None, raw_scales=None, comp_row_start=None,
                      comp_row_count=None, n_comp=None, pos0_dev=None, out=None, out_dtype=torch.float32,
-                     out_layout="bhtd", partial=False, n_splits=0):
+                     out_layout="bhtd", partial=False, n_splits=0, exact_fp32=False, check=False):
     """Launch the sparse attention kernel.
 
     q4 [B,H,T,Dqk] (any strides on the first three axes); comp_kv a flat
     [rows, Dqk] table (sequence b owns rows comp_row_start[b] .. +comp_row_count[b],
     default b*n_comp .. +n_comp); topk3 [B,T,k] int32; raw_kv [B,raw_cap,Dqk] or
     None.  Returns out [B,H,T,Dv] ("bhtd") or [B,T,H,Dv] ("bthd"); with
-    ``partial=True`` returns (un-normalised fp32 out, ml [B,T,H,2]).
+    ``partial=True`` returns (un-normalised fp32 out, ml [B,T,H,2]).  16-bit and int8
+    tables with up to 64 heads run on the tensor-core kernel; ``exact_fp32=True`` forces
+    the fp32 CUDA-core kernel (always used for float32 tables).
     """
     dev = require_cuda(q4, comp_kv, topk3)
     lib = _abi.load()
@@ -94,10 +96,14 @@ def sparse_attention(q4, comp_kv, topk3, sinks, *, pos0, window, ratio, raw_kv=N
     a.scale = float(Dqk) ** -0.5 if scale is None else float(scale)
     a.pos0 = int(pos0); a.pos0_dev = ptr(pos0_dev); a.window = int(window); a.ratio = int(ratio)
     a.n_splits = int(n_splits)
+    a.flags = _abi.SPARSE_EXACT_FP32 if exact_fp32 else 0
     ws = workspace(lib.mxb_sparse_attn_workspace_bytes(C.byref(a)), dev)
     a.workspace = ptr(ws); a.workspace_bytes = 0 if ws is None else ws.numel()
-    a.status = None
+    status = status_word(dev) if check else None
+    a.status = ptr(status)
     _abi.check(lib.mxb_sparse_attn(C.byref(a), stream_ptr()))
+    if check:
+        check_status(status, "sparse attention")
     return (out, ml) if partial else out
 
 

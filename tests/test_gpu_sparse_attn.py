@@ -204,3 +204,93 @@ def test_contract_errors():
     with pytest.raises(RuntimeError, match="CUDA tensors only"):
         iak.indexed_mixed_attention_decode(torch.zeros(8, 64), None, torch.zeros(4, 64),
                                            torch.zeros(4, dtype=torch.int32), None, pos0=0)
+
+
+@pytest.mark.parametrize("kvkind,qkind", [("f16", "f32"), ("bf16", "bf16"), ("int8", "bf16"), ("f16", "f16")])
+@pytest.mark.parametrize("Dqk,Dv,H", [(576, 512, 64), (512, 512, 64), (192, 128, 16)])
+def test_tensor_core_kernel_decode(kvkind, qkind, Dqk, Dv, H):
+    """tcgen05 kernel: raw window + selected rows + sinks + skipped ids, several splits,
+    against the oracle and against the fp32 CUDA-core kernel."""
+    need_gpu()
+    rng = np.random.default_rng(Dqk + H)
+    R, k, raw_cap = 3000, 700, 128
+    qr = {"f32": lambda x: x.astype(np.float32), "f16": f16_round, "bf16": bf16_round}[qkind]
+    qt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[qkind]
+    q = qr(rng.standard_normal((H, Dqk)))
+    sinks = rng.standard_normal(H).astype(np.float32)
+    ids = np.sort(rng.choice(R, size=k, replace=False)).astype(np.int32)
+    ids[5] = -1; ids[300] = -1
+    if kvkind == "int8":
+        comp_i = rng.integers(-127, 128, size=(R, Dqk), dtype=np.int8)
+        raw_i = rng.integers(-127, 128, size=(raw_cap, Dqk), dtype=np.int8)
+        cs = np.exp(rng.uniform(np.log(1e-3), np.log(1e-1), size=R)).astype(np.float16)
+        rs = np.exp(rng.uniform(np.log(1e-3), np.log(1e-1), size=raw_cap)).astype(np.float16)
+        comp_t, raw_t, cs_t, rs_t = dev(comp_i), dev(raw_i), dev(cs), dev(rs)
+        comp, raw = comp_i, raw_i
+        okw = dict(kv_scales=cs, raw_scales=rs)
+    else:
+        rnd = f16_round if kvkind == "f16" else bf16_round
+        kt = torch.float16 if kvkind == "f16" else torch.bfloat16
+        comp, raw = rnd(rng.standard_normal((R, Dqk))), rnd(rng.standard_normal((raw_cap, Dqk)))
+        comp_t, raw_t, cs_t, rs_t = dev(comp, kt), dev(raw, kt), None, None
+        okw = {}
+    pos0 = 128 + R * 4 - 1
+    scale = Dqk ** -0.5 * (20.0 if kvkind == "int8" else 1.0)   # int8 rows are ~0.3 rms: sharpen the softmax a bit
+    ref = ds4.indexed_mixed_attention_decode(q if kvkind != "f16" or qkind != "f32" else f16_round(q), raw, comp, ids,
+                                             sinks, pos0=pos0, raw_start=37, scale=scale, d_v=Dv, **okw)
+    tol = 2e-3 if kvkind == "f16" else TOL_16
+    outs = []
+    for ns in (0, 1, 3):
+        o = iak.indexed_mixed_attention_decode(dev(q, qt), raw_t, comp_t, dev(ids), dev(sinks), pos0=pos0,
+                                               raw_start=37, scale=scale, d_v=Dv, kv_scales=cs_t, raw_scales=rs_t)
+        o = iak.sparse_attention(dev(q, qt)[None, :, None, :], comp_t, dev(ids)[None, None], dev(sinks), pos0=pos0,
+                                 window=128, ratio=4, raw_kv=raw_t[None], raw_start=37, scale=scale, d_v=Dv,
+                                 kv_scales=cs_t, raw_scales=rs_t, n_splits=ns, check=True)[0, :, 0]
+        assert max_abs(o, ref) <= tol, (ns, max_abs(o, ref))
+        outs.append(o)
+    exact = iak.sparse_attention(dev(q, qt)[None, :, None, :], comp_t, dev(ids)[None, None], dev(sinks), pos0=pos0,
+                                 window=128, ratio=4, raw_kv=raw_t[None], raw_start=37, scale=scale, d_v=Dv,
+                                 kv_scales=cs_t, raw_scales=rs_t, exact_fp32=True)[0, :, 0]
+    assert max_abs(exact, ref) <= 2e-3
+    assert max_abs(outs[0], exact) <= tol
+
+
+def test_tensor_core_kernel_peaked_softmax_and_empty_tiles():
+    """Logits spread over hundreds of units force reference-maximum updates and O rescales;
+    a list with long runs of skipped ids gives tiles without any valid row."""
+    need_gpu()
+    rng = np.random.default_rng(77)
+    H, Dqk, Dv, R, k = 64, 576, 512, 4000, 1024
+    q = bf16_round(rng.standard_normal((H, Dqk)) * 4)
+    comp = bf16_round(rng.standard_normal((R, Dqk)) * np.linspace(0.2, 3.0, R)[:, None])   # late rows dominate
+    ids = np.sort(rng.choice(R, size=k, replace=False)).astype(np.int32)
+    ids[100:400] = -1
+    ref = ds4.indexed_mixed_attention_decode(q, None, comp, ids, None, pos0=0, window=0, ratio=0, scale=Dqk ** -0.5,
+                                             d_v=Dv)
+    for ns in (1, 2):
+        o = iak.sparse_attention(dev(q, torch.bfloat16)[None, :, None, :], dev(comp, torch.bfloat16),
+                                 dev(ids)[None, None], None, pos0=0, window=0, ratio=0, d_v=Dv, n_splits=ns,
+                                 check=True)[0, :, 0]
+        assert max_abs(o, ref) <= 2.5e-2, max_abs(o, ref)   # |v| reaches ~10 here
+    none = np.full(256, -1, np.int32)
+    o = iak.sparse_attention(dev(q, torch.bfloat16)[None, :, None, :], dev(comp, torch.bfloat16),
+                             dev(none)[None, None], None, pos0=0, window=0, ratio=0, d_v=Dv, check=True)
+    assert float(o.abs().max()) == 0.0
+
+
+def test_tensor_core_kernel_prefill_form():
+    need_gpu()
+    rng = np.random.default_rng(8)
+    B, H, T, Dqk, Dv, R, k = 2, 64, 5, 576, 512, 600, 256
+    pos0 = 2000
+    q = bf16_round(rng.standard_normal((B, H, T, Dqk)))
+    comp = bf16_round(rng.standard_normal((B, R, Dqk)))
+    ids = np.sort(rng.integers(0, R, size=(B, T, k)), axis=-1).astype(np.int32)
+    sinks = rng.standard_normal(H).astype(np.float32)
+    out = iak.indexed_mixed_attention_prefill_live_f16(dev(q, torch.bfloat16), None, dev(comp, torch.bfloat16),
+                                                       dev(ids), dev(sinks), pos0=pos0, ratio=4, d_v=Dv)
+    assert out.shape == (B, H, T, Dv)
+    for b in range(B):
+        ref = ds4.indexed_mixed_attention_prefill(q[b].transpose(1, 0, 2), None, comp[b], ids[b], sinks, pos0=pos0,
+                                                  ratio=4, d_v=Dv)
+        assert max_abs(out[b].permute(1, 0, 2), ref) <= TOL_16
