@@ -62,3 +62,20 @@ def status_word(device) -> torch.Tensor:
 
 def last_dim_contiguous(t: torch.Tensor) -> torch.Tensor:
     return t if t.stride(-1) == 1 else t.contiguous()
+
+
+# Optional per-entry-point device timing: set TIMER to a dict and every launch records a
+# pair of CUDA events on the current stream around the C call (name -> [(start, end), ...]).
+TIMER = None
+
+
+def launch(name: str, fn, args) -> int:
+    if TIMER is None:
+        return fn(C.byref(args), stream_ptr())
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    rc = fn(C.byref(args), stream_ptr())
+    e1.record()
+    TIMER.setdefault(name, []).append((e0, e1))
+    return rc

@@ -12,6 +12,7 @@ import ctypes as C
 import torch
 
 from .. import _abi
+from .. import _torchabi as _t
 from .._torchabi import ptr, require_cuda, stream_ptr, workspace
 
 
@@ -54,7 +55,7 @@ def topk_select(scores, k: int, *, valid=None, row_start=None, n=None, order: st
     a.out_ids = ptr(out); a.rows = rows; a.n = n_; a.k = int(k)
     ws = workspace(lib.mxb_topk_workspace_bytes(rows, n_, int(k)), dev)
     a.workspace = ptr(ws); a.workspace_bytes = 0 if ws is None else ws.numel()
-    _abi.check(lib.mxb_topk_select(C.byref(a), stream_ptr()))
+    _abi.check(_t.launch("topk_select", lib.mxb_topk_select, a))
     out = out.reshape(*lead, int(k))
     if order == "score":
         if row_start is not None:

@@ -65,3 +65,60 @@ def sparse_decode_step(q, idx_q, idx_w, cache: LatentCache, *, k: int, scale: fl
     if return_scores:
         extra.append(scores)
     return (out, *extra) if extra else out
+
+
+class SparseDecodePlan:
+    """A decode step with fixed shapes, pre-allocated buffers and (by default) one CUDA
+    graph holding its launches, so that a step costs one graph launch on the host.
+
+    The cache tensors are captured by address: the plan stays valid while ``cache`` keeps
+    its storage (rows appended in place within ``max_rows`` and updated ``row_count`` are
+    picked up, because the kernels read the counts from device memory).
+    """
+
+    def __init__(self, cache: LatentCache, *, heads: int, d_qk: int, idx_heads: int, idx_dim: int, k: int,
+                 scale: float, d_v: int, q_dtype=torch.bfloat16, out_dtype=torch.float32, sinks=None,
+                 graph: bool = True):
+        dev = cache.kv.device
+        B = cache.batch
+        self.cache, self.k, self.scale, self.d_v, self.sinks, self.out_dtype = cache, int(k), float(scale), int(d_v), sinks, out_dtype
+        self.q = torch.zeros((B, heads, d_qk), dtype=q_dtype, device=dev)
+        self.idx_q = torch.zeros((B, idx_heads, idx_dim), dtype=q_dtype, device=dev)
+        self.idx_w = torch.zeros((B, idx_heads), dtype=torch.float32, device=dev)
+        self.graph = None
+        self.out = None
+        self.ids = None
+        if graph:
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    self._step()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            torch.cuda.synchronize(dev)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.out, self.ids = self._step()
+            self.graph = g
+
+    def _step(self):
+        return sparse_decode_step(self.q, self.idx_q, self.idx_w, self.cache, k=self.k, scale=self.scale,
+                                  d_v=self.d_v, sinks=self.sinks, out_dtype=self.out_dtype, return_ids=True)
+
+    def load_inputs(self, q, idx_q, idx_w) -> None:
+        """Copy one step's inputs (device or pinned-host tensors) into the plan's buffers."""
+        self.q.copy_(q, non_blocking=True)
+        self.idx_q.copy_(idx_q, non_blocking=True)
+        self.idx_w.copy_(idx_w, non_blocking=True)
+
+    def launch(self):
+        """Run the step on the inputs currently in the plan's buffers; returns out [B,H,d_v]."""
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.out, self.ids = self._step()
+        return self.out
+
+    def run(self, q, idx_q, idx_w):
+        self.load_inputs(q, idx_q, idx_w)
+        return self.launch()

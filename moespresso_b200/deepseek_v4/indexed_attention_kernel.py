@@ -13,6 +13,7 @@ import ctypes as C
 import torch
 
 from .. import _abi
+from .. import _torchabi as _t
 from .._torchabi import dtype_code, last_dim_contiguous, ptr, require_cuda, status_word, stream_ptr, workspace
 
 _CONSUMER_CALL_COUNTS = {"decode": 0, "prefill": 0, "banded": 0}
@@ -101,7 +102,7 @@ def sparse_attention(q4, comp_kv, topk3, sinks, *, pos0, window, ratio, raw_kv=N
     a.workspace = ptr(ws); a.workspace_bytes = 0 if ws is None else ws.numel()
     status = status_word(dev) if check else None
     a.status = ptr(status)
-    _abi.check(lib.mxb_sparse_attn(C.byref(a), stream_ptr()))
+    _abi.check(_t.launch("sparse_attn", lib.mxb_sparse_attn, a))
     if check:
         check_status(status, "sparse attention")
     return (out, ml) if partial else out
@@ -121,7 +122,7 @@ def merge_partials(o_parts, ml_parts, sinks=None, *, out_dtype=torch.float32):
     a.out_dtype = dtype_code(out)
     a.out_stride_b, a.out_stride_t, a.out_stride_h = out.stride(0), out.stride(1), out.stride(2)
     a.P, a.B, a.T, a.H, a.Dv = P, B, T, H, Dv
-    _abi.check(lib.mxb_merge_partials(C.byref(a), stream_ptr()))
+    _abi.check(_t.launch("merge_partials", lib.mxb_merge_partials, a))
     return out
 
 
@@ -339,7 +340,7 @@ def indexer_scores(q, weights, keys_flat, *, n_rows, pos0=0, ratio=0, row_start=
     a.n_rows = int(n_rows); a.rows_total = rows_total; a.pos0 = int(pos0); a.ratio = int(ratio)
     a.flags = _abi.INDEXER_EXACT_FP32 if exact_fp32 else 0
     a.status = ptr(status)
-    _abi.check(lib.mxb_indexer_scores(C.byref(a), stream_ptr()))
+    _abi.check(_t.launch("indexer_scores", lib.mxb_indexer_scores, a))
     if check:
         check_status(status, "indexer scores")
     return out

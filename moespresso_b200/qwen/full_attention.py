@@ -14,6 +14,7 @@ import ctypes as C
 import torch
 
 from .. import _abi
+from .. import _torchabi as _t
 from .._torchabi import dtype_code, last_dim_contiguous, ptr, require_cuda, status_word, stream_ptr, workspace
 
 FLASH_HEAD_DIM = 256
@@ -70,7 +71,7 @@ def sdpa_fa_prefill(queries, keys, values, scale: float, *, gate=None, layout: s
     a.workspace = ptr(ws); a.workspace_bytes = 0 if ws is None else ws.numel()
     status = status_word(dev) if check else None
     a.status = ptr(status)
-    _abi.check(lib.mxb_flash_prefill(C.byref(a), stream_ptr()))
+    _abi.check(_t.launch("flash_prefill", lib.mxb_flash_prefill, a))
     if check and int(status.item()) != 0:
         raise _abi.MxbError("flash prefill: a device-side wait timed out")
     if layout == "bhld":
