@@ -86,6 +86,7 @@ typedef struct {
 } mxb_indexer_scores_args;
 
 #define MXB_INDEXER_EXACT_FP32 1 /* CUDA-core fp32 path even for 16-bit / fp8 operands */
+#define MXB_INDEXER_FP8_MMA 2    /* FP8 keys fed straight to the FP8 tensor-core path (reduced-precision accumulation) */
 
 int mxb_indexer_scores(const mxb_indexer_scores_args* a, void* stream);
 

@@ -13,6 +13,7 @@ from . import _build
 
 F32, F16, BF16, F8E4M3, I8 = 0, 1, 2, 3, 4
 INDEXER_EXACT_FP32 = 1
+INDEXER_FP8_MMA = 2
 SPARSE_EXACT_FP32 = 1
 
 _p = C.c_void_p

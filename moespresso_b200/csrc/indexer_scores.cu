@@ -404,6 +404,8 @@ static int launch_tc(IndexerParams& p, const mxb_indexer_scores_args* a, cudaStr
   return MXB_OK;
 }
 
+int launch_indexer_fp8(const mxb_indexer_scores_args* a, cudaStream_t st);  // indexer_scores_fp8.cu
+
 }  // namespace mxb
 
 using namespace mxb;
@@ -434,6 +436,7 @@ extern "C" int mxb_indexer_scores(const mxb_indexer_scores_args* a, void* stream
   const bool tc = !(a->flags & MXB_INDEXER_EXACT_FP32) && q16 && keys_match && q_vec_ok && (a->H % 16 == 0);
   if (tc) {
     const bool fp8 = a->key_dtype == MXB_F8E4M3;
+    if (fp8) return launch_indexer_fp8(a, st);
     if (a->D == 64) return fp8 ? launch_tc<64, true>(p, a, st) : launch_tc<64, false>(p, a, st);
     return fp8 ? launch_tc<128, true>(p, a, st) : launch_tc<128, false>(p, a, st);
   }

@@ -214,39 +214,53 @@ struct MergeParams {
   int32_t finalize;
 };
 
-template <int OT>
-__global__ void __launch_bounds__(128) merge_kernel(MergeParams p) {
-  const int64_t n = blockIdx.x;
+template <int OT, int VEC>
+__global__ void __launch_bounds__(256) merge_kernel(MergeParams p) {
+  // one thread = one (row, VEC consecutive features); partial loads are independent, so many are in flight
   const int64_t N = (int64_t)p.B * p.T * p.H;
+  const int per_row = p.Dv / VEC;
+  const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (idx >= N * per_row) return;
+  const int64_t n = idx / per_row;
+  const int d0 = (int)(idx % per_row) * VEC;
   const int h = (int)(n % p.H);
   const int t = (int)((n / p.H) % p.T);
   const int b = (int)(n / ((int64_t)p.H * p.T));
   float m = -INFINITY;
-  for (int s = 0; s < p.P; ++s) m = fmaxf(m, p.ml_parts[((int64_t)s * N + n) * 2]);
+  for (int s = 0; s < p.P; ++s) m = fmaxf(m, __ldg(p.ml_parts + ((int64_t)s * N + n) * 2));
   const float sink = (p.finalize && p.sinks) ? p.sinks[h] : -INFINITY;
   m = fmaxf(m, sink);
   float l = 0.f;
+  float acc[VEC];
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
   if (m > -INFINITY) {
     for (int s = 0; s < p.P; ++s) {
-      const float ms = p.ml_parts[((int64_t)s * N + n) * 2];
-      const float ls = p.ml_parts[((int64_t)s * N + n) * 2 + 1];
-      if (ms > -INFINITY) l = fmaf(ls, expf(ms - m), l);
+      const float ms = __ldg(p.ml_parts + ((int64_t)s * N + n) * 2);
+      const float ls = __ldg(p.ml_parts + ((int64_t)s * N + n) * 2 + 1);
+      if (ms > -INFINITY) {
+        const float w = expf(ms - m);
+        l = fmaf(ls, w, l);
+        const float* src = p.o_parts + ((int64_t)s * N + n) * p.Dv + d0;
+        if constexpr (VEC == 4) {
+          const float4 v = __ldg(reinterpret_cast<const float4*>(src));
+          acc[0] = fmaf(v.x, w, acc[0]); acc[1] = fmaf(v.y, w, acc[1]);
+          acc[2] = fmaf(v.z, w, acc[2]); acc[3] = fmaf(v.w, w, acc[3]);
+        } else {
+          acc[0] = fmaf(__ldg(src), w, acc[0]);
+        }
+      }
     }
     if (sink > -INFINITY) l += expf(sink - m);
   }
-  const int64_t ob = (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)t * p.o_st;
-  for (int d = threadIdx.x; d < p.Dv; d += blockDim.x) {
-    float acc = 0.f;
-    if (m > -INFINITY) {
-      for (int s = 0; s < p.P; ++s) {
-        const float ms = p.ml_parts[((int64_t)s * N + n) * 2];
-        if (ms > -INFINITY) acc = fmaf(p.o_parts[((int64_t)s * N + n) * p.Dv + d], expf(ms - m), acc);
-      }
-    }
-    if (p.finalize) store_elem<OT>(p.out, ob + d, l > 0.f ? acc / l : 0.f);
-    else reinterpret_cast<float*>(p.out)[ob + d] = acc;
+  const int64_t ob = (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)t * p.o_st + d0;
+  const float inv = (p.finalize ? (l > 0.f ? 1.f / l : 0.f) : 1.f);
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) {
+    if (p.finalize) store_elem<OT>(p.out, ob + j, acc[j] * inv);
+    else reinterpret_cast<float*>(p.out)[ob + j] = acc[j];
   }
-  if (!p.finalize && threadIdx.x == 0) {
+  if (!p.finalize && d0 == 0) {
     p.out_ml[n * 2 + 0] = m;
     p.out_ml[n * 2 + 1] = l;
   }
@@ -254,10 +268,16 @@ __global__ void __launch_bounds__(128) merge_kernel(MergeParams p) {
 
 static int launch_merge(const MergeParams& mp, int out_dtype, cudaStream_t st) {
   const int64_t N = (int64_t)mp.B * mp.T * mp.H;
-  dim3 grid((unsigned)N);
-  if (out_dtype == MXB_F32) merge_kernel<MXB_F32><<<grid, 128, 0, st>>>(mp);
-  else if (out_dtype == MXB_BF16) merge_kernel<MXB_BF16><<<grid, 128, 0, st>>>(mp);
-  else merge_kernel<MXB_F16><<<grid, 128, 0, st>>>(mp);
+  const bool vec = (mp.Dv % 4 == 0) && ((reinterpret_cast<uintptr_t>(mp.o_parts) & 15) == 0);
+  const int64_t items = N * (vec ? mp.Dv / 4 : mp.Dv);
+  dim3 grid((unsigned)ceil_div(items, 256));
+#define MXB_MG(OT)                                             \
+  if (vec) merge_kernel<OT, 4><<<grid, 256, 0, st>>>(mp);      \
+  else merge_kernel<OT, 1><<<grid, 256, 0, st>>>(mp);
+  if (out_dtype == MXB_F32) { MXB_MG(MXB_F32) }
+  else if (out_dtype == MXB_BF16) { MXB_MG(MXB_BF16) }
+  else { MXB_MG(MXB_F16) }
+#undef MXB_MG
   MXB_CUDA_OK(cudaGetLastError());
   return MXB_OK;
 }

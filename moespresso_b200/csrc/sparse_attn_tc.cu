@@ -90,6 +90,12 @@ __device__ __forceinline__ void widen_i8x16_f16(const uint4& in, uint4& lo, uint
   hi = make_uint4(o[4], o[5], o[6], o[7]);
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <bool BF16>
 __device__ __forceinline__ uint16_t to_op16(float x) {
   if constexpr (BF16) {
@@ -173,8 +179,11 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
 
   {  // first list entry that ends the walk
     int mine = p.k;
-    for (int j = tid; j < p.k; j += blockDim.x)
-      if ((int64_t)ids[j] >= visible) { mine = j; break; }
+#pragma unroll 4
+    for (int j = tid; j < p.k; j += 256) {   // no early exit: the loads stay independent
+      const int64_t v = ids[j];
+      if (v >= visible && j < mine) mine = j;
+    }
     if (mine < p.k) atomicMin(&mi->keff, mine);
   }
   // q -> B operand of S^T: [64 heads x Dqk] K-major, 128-byte swizzle, rounded to the operand type
@@ -229,6 +238,18 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
   for (int c = 0; c < 32; ++c) l_thr[c] = 0.f;
   bool have_o = false;
 
+  // gather plan: the i-th 16-byte load of this lane covers (local row, chunk) = tab[i] (row << 16 | chunk)
+  const int nch = p.Dqk * EB / 16;
+  int rpb = 16;
+  while (rpb * nch > 576) rpb >>= 1;
+  uint32_t tab[18];
+#pragma unroll
+  for (int i = 0; i < 18; ++i) {
+    const int g = lane + 32 * i;
+    const int rl = g / nch;
+    tab[i] = rl < rpb ? ((uint32_t)rl << 16) | (uint32_t)(g - rl * nch) : 0xFFFFFFFFu;
+  }
+
   for (int it = 0; it < ntiles; ++it) {
     const int e0 = e_lo + it * TC_ROWS;
     // ---------------------------------------------------------------- gather 128 rows
@@ -261,41 +282,33 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
     }
     __syncwarp();
     // phase 1: up to 18 independent 16-byte loads per lane in flight, then widen / store
-    {
-      const int nch = p.Dqk * EB / 16;
-      int rpb = 16;
-      while (rpb * nch > 576) rpb >>= 1;
-      for (int r0 = 0; r0 < 16; r0 += rpb) {
-        uint4 v[18];
+    for (int r0 = 0; r0 < 16; r0 += rpb) {
+      uint4 v[18];
 #pragma unroll
-        for (int i = 0; i < 18; ++i) {
-          const int g = lane + 32 * i;
-          const int rl = g / nch, c = g - rl * nch;
-          v[i] = make_uint4(0, 0, 0, 0);
-          if (rl < rpb) {
-            const uint8_t* src = mi->row_src[warp * 16 + r0 + rl];
-            if (src) v[i] = __ldg(reinterpret_cast<const uint4*>(src) + c);
-          }
+      for (int i = 0; i < 18; ++i) {
+        v[i] = make_uint4(0, 0, 0, 0);
+        if (tab[i] != 0xFFFFFFFFu) {
+          const uint8_t* src = mi->row_src[warp * 16 + r0 + (int)(tab[i] >> 16)];
+          if (src) v[i] = __ldg(reinterpret_cast<const uint4*>(src) + (tab[i] & 0xFFFFu));
         }
+      }
 #pragma unroll
-        for (int i = 0; i < 18; ++i) {
-          const int g = lane + 32 * i;
-          const int rl = g / nch, c = g - rl * nch;
-          if (rl < rpb) {
-            const int rr = warp * 16 + r0 + rl;
-            uint8_t* drow = tile + (size_t)rr * 128;
-            const int sw = rr & 7;
-            if constexpr (KVT == MXB_I8) {
-              uint4 lo, hi;
-              widen_i8x16_f16(v[i], lo, hi);   // zero bytes (invalid row) widen to 0.0
-              const int kb = c >> 2, cc = (c & 3) * 2;
-              uint8_t* d = drow + (size_t)kb * 16384;
-              *reinterpret_cast<uint4*>(d + ((cc ^ sw) << 4)) = lo;
-              *reinterpret_cast<uint4*>(d + (((cc + 1) ^ sw) << 4)) = hi;
-            } else {
-              const int kb = c >> 3, cc = c & 7;
-              *reinterpret_cast<uint4*>(drow + (size_t)kb * 16384 + ((cc ^ sw) << 4)) = v[i];
-            }
+      for (int i = 0; i < 18; ++i) {
+        if (tab[i] != 0xFFFFFFFFu) {
+          const int rr = warp * 16 + r0 + (int)(tab[i] >> 16);
+          const int c = (int)(tab[i] & 0xFFFFu);
+          uint8_t* drow = tile + (size_t)rr * 128;
+          const int sw = rr & 7;
+          if constexpr (KVT == MXB_I8) {
+            uint4 lo, hi;
+            widen_i8x16_f16(v[i], lo, hi);   // zero bytes (invalid row) widen to 0.0
+            const int kb = c >> 2, cc = (c & 3) * 2;
+            uint8_t* d = drow + (size_t)kb * 16384;
+            *reinterpret_cast<uint4*>(d + ((cc ^ sw) << 4)) = lo;
+            *reinterpret_cast<uint4*>(d + (((cc + 1) ^ sw) << 4)) = hi;
+          } else {
+            const int kb = c >> 3, cc = c & 7;
+            *reinterpret_cast<uint4*>(drow + (size_t)kb * 16384 + ((cc ^ sw) << 4)) = v[i];
           }
         }
       }
@@ -383,7 +396,7 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
       for (int c = 0; c < 32; ++c) {
         const int h = col0 + c;
         const float s = __uint_as_float(sv[c]);
-        const float pj = (s == -INFINITY) ? 0.f : exp2f(s - mi->m_ref[h]);
+        const float pj = (s == -INFINITY) ? 0.f : fast_exp2(s - mi->m_ref[h]);
         const uint16_t pr = to_op16<BF16>(KVT == MXB_I8 ? pj * rs : pj);
         const float back = from_op16<BF16>(pr);
         l_thr[c] += (KVT == MXB_I8) ? back * inv : back;
@@ -426,10 +439,31 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
   // ------------------------------------------------------------------ output
   const int64_t N = (int64_t)p.B * p.T * p.H;
   const bool direct = p.nsplit == 1;
+  const bool finalize = direct && !p.partial_ml;
+  if (tid < TC_HEADS) {
+    // per-head factor applied to O^T: 1 for partial output, exp(m - m') / denominator with the sink joined otherwise
+    float fac = 1.f;
+    if (finalize) {
+      const float m = mi->m_ref[tid], l = mi->l_tot[tid];
+      const float sink2 = (p.sinks && tid < p.H) ? p.sinks[tid] * 1.4426950408889634f : -INFINITY;
+      const float m2v = fmaxf(m, sink2);
+      float w = 0.f, den = 0.f;
+      if (m2v > -INFINITY) {
+        w = (m == -INFINITY) ? 0.f : exp2f(m - m2v);
+        den = l * w + ((sink2 == -INFINITY) ? 0.f : exp2f(sink2 - m2v));
+      }
+      fac = den > 0.f ? w / den : 0.f;
+    }
+    mi->factor[tid] = fac;
+  }
+  __syncthreads();
   for (int m2 = 0; m2 < 2; ++m2) {
     const int mt = half_id * 2 + m2;
     if (mt >= n_mt) continue;
     const int d = mt * 128 + quad * 32 + lane;
+    const int64_t obase = direct ? (int64_t)b * p.o_sb + (int64_t)t * p.o_st + d
+                                 : ((int64_t)split * N + (int64_t)bt * p.H) * p.Dv + d;
+    const int64_t ostep = direct ? p.o_sh : (int64_t)p.Dv;
 #pragma unroll 1
     for (int ch = 0; ch < 2; ++ch) {
       uint32_t ov[32];
@@ -444,23 +478,10 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
       for (int c = 0; c < 32; ++c) {
         const int h = ch * 32 + c;
         if (h >= p.H) continue;
-        const float o = __uint_as_float(ov[c]);
-        if (direct && !p.partial_ml) {
-          const float m = mi->m_ref[h], l = mi->l_tot[h];
-          const float sink2 = p.sinks ? p.sinks[h] * 1.4426950408889634f : -INFINITY;
-          const float m2v = fmaxf(m, sink2);
-          float w = 0.f, den = 0.f;
-          if (m2v > -INFINITY) {
-            w = (m == -INFINITY) ? 0.f : exp2f(m - m2v);
-            den = l * w + ((sink2 == -INFINITY) ? 0.f : exp2f(sink2 - m2v));
-          }
-          const float r = den > 0.f ? o * (w / den) : 0.f;
-          store_elem<OT>(p.out, (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)t * p.o_st + d, r);
-        } else if (direct) {
-          reinterpret_cast<float*>(p.out)[(int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)t * p.o_st + d] = o;
-        } else {
-          p.ws_o[((int64_t)split * N + (int64_t)bt * p.H + h) * p.Dv + d] = o;
-        }
+        const float o = __uint_as_float(ov[c]) * mi->factor[h];
+        if (finalize) store_elem<OT>(p.out, obase + h * ostep, o);
+        else if (direct) reinterpret_cast<float*>(p.out)[obase + h * ostep] = o;
+        else p.ws_o[obase + h * ostep] = o;
       }
     }
   }

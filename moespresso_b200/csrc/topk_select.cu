@@ -9,17 +9,16 @@
 //  * topk_row_kernel      — one CTA per row, the row's keys resident in shared memory
 //    (rows up to kSmemRowMax); four 8-bit radix passes, then an ordered emission
 //    through a block scan, so the output is ascending without a sort.
-//  * topk_hist / filter / finish — rows longer than that (up to 2^31 - 1): an 11-bit
-//    histogram pass over all CTAs, a filter pass that emits the strictly-above
-//    rows and compacts the threshold bin's candidates, and a one-CTA finish that
-//    resolves the remaining 21 bits, the ties by lowest index, and sorts the ids.
+//  * topk_stream_kernel   — rows longer than that (up to 2^31 - 1): one CTA streams the
+//    row twice from L2 (11-bit histogram, then strictly-above ids + the threshold bin's
+//    candidates), resolves the remaining 21 bits and the ties by lowest index among the
+//    candidates, and sorts the selected ids.
 #include "common.cuh"
 
 namespace mxb {
 
 constexpr int kSmemRowMax = 45056;  // 176 KB of keys
 constexpr int kBigBins = 2048;      // top 11 bits
-constexpr int kBigChunk = 16384;    // elements per CTA in the multi-CTA passes
 
 __device__ __forceinline__ uint32_t score_key_full(float x) {
   if (!(fabsf(x) <= 3.402823466e38f)) return 0u;  // NaN and +-inf are never selected
@@ -100,12 +99,9 @@ struct TopkParams {
   int32_t rows;
   int64_t n;
   int32_t k;
-  // multi-CTA path scratch
-  uint32_t* hist;      // [rows][kBigBins]
-  uint32_t* counters;  // [rows][4]: above count, candidate count
+  // global scratch for a threshold bin that does not fit in shared memory
   uint32_t* cand_key;  // [rows][n]
   int32_t* cand_idx;   // [rows][n]
-  int32_t* above_idx;  // [rows][k]
 };
 
 // --------------------------------------------------------------------------
@@ -183,139 +179,97 @@ __global__ void __launch_bounds__(1024) topk_row_kernel(TopkParams p) {
 }
 
 // --------------------------------------------------------------------------
-// long rows: histogram -> filter -> finish
+// long rows: one CTA per row streams the row twice (the scores were just written by
+// the score kernel and sit in L2): pass 1 = 11-bit histogram in shared memory, pass 2 =
+// strictly-above ids and the threshold bin's candidates into shared memory (global
+// scratch only if the bin holds more than kCandSmem entries, e.g. all-equal scores);
+// then the remaining 21 bits, the ties by lowest id and a bitonic sort of the ids.
 // --------------------------------------------------------------------------
-__global__ void __launch_bounds__(512) topk_hist_kernel(TopkParams p) {
-  __shared__ uint32_t hist[kBigBins];
-  const int row = blockIdx.y;
-  const int64_t n = p.row_count ? min((int64_t)p.row_count[row], p.n) : p.n;
-  const int64_t lo = (int64_t)blockIdx.x * kBigChunk;
-  if (lo >= n) return;
-  const int64_t hi = min(lo + kBigChunk, n);
-  const int64_t base = p.row_start ? p.row_start[row] : (int64_t)row * p.row_stride;
-  for (int i = threadIdx.x; i < kBigBins; i += blockDim.x) hist[i] = 0;
-  __syncthreads();
-  for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-    uint32_t key = score_key_full(p.scores[base + i]);
-    if (key) atomicAdd(&hist[key >> 21], 1u);
-  }
-  __syncthreads();
-  uint32_t* g = p.hist + (int64_t)row * kBigBins;
-  for (int i = threadIdx.x; i < kBigBins; i += blockDim.x)
-    if (hist[i]) atomicAdd(&g[i], hist[i]);
-}
+constexpr int kCandSmem = 16384;
 
-// Threshold bin of a row from its global 2048-bin histogram.  Executed by the whole CTA
-// (>= 256 threads).  Outputs through shared memory: k_eff, thr_bin, count above the bin.
-__device__ __forceinline__ void big_threshold(const uint32_t* g, int k, uint32_t* sh /*[260]*/, uint32_t* k_eff,
-                                              uint32_t* thr_bin, uint32_t* above) {
+__global__ void __launch_bounds__(1024) topk_stream_kernel(TopkParams p, int sort_n) {
+  extern __shared__ uint32_t dyn[];
+  int32_t* sel = reinterpret_cast<int32_t*>(dyn);                 // [sort_n]
+  uint32_t* ck_s = dyn + sort_n;                                  // [kCandSmem]
+  int32_t* ci_s = reinterpret_cast<int32_t*>(ck_s + kCandSmem);   // [kCandSmem]
+  __shared__ uint32_t hist[kBigBins];
+  __shared__ uint32_t warp_sums[32];
+  __shared__ uint32_t s_total, s_keff, s_bin, s_above, s_cnt_bin, s_na, s_nc, s_digit, s_dabove;
+
+  const int row = blockIdx.x;
   const int tid = threadIdx.x;
-  // thread t (< 256) sums bins [2047-8t-7, 2047-8t], highest first
-  uint32_t loc[8];
-  uint32_t s = 0;
-  if (tid < 256) {
+  const int64_t n = p.row_count ? min((int64_t)p.row_count[row], p.n) : p.n;
+  const int64_t base = p.row_start ? p.row_start[row] : (int64_t)row * p.row_stride;
+  const float* src = p.scores + base;
+  int32_t* out = p.out_ids + (int64_t)row * p.k;
+
+  for (int i = tid; i < kBigBins; i += 1024) hist[i] = 0;
+  if (tid == 0) { s_na = 0; s_nc = 0; s_keff = 0; s_bin = 0; s_above = 0; s_cnt_bin = 0; }
+  __syncthreads();
+  // ---- pass 1
+  for (int64_t i = tid; i < n; i += 4096) {
+    float x[4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      loc[j] = g[2047 - (tid * 8 + j)];
-      s += loc[j];
+    for (int u = 0; u < 4; ++u) x[u] = (i + 1024 * u < n) ? __ldg(src + i + 1024 * u) : -INFINITY;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t key = score_key_full(x[u]);
+      if (key) atomicAdd(&hist[key >> 21], 1u);
     }
-    sh[tid] = s;
   }
   __syncthreads();
-  // inclusive scan over 256 entries (Hillis-Steele, in place with double sync)
-  for (int o = 1; o < 256; o <<= 1) {
-    uint32_t t = 0;
-    if (tid < 256 && tid >= o) t = sh[tid - o];
-    __syncthreads();
-    if (tid < 256) sh[tid] += t;
-    __syncthreads();
-  }
-  const uint32_t total = sh[255];
-  const uint32_t ke = min((uint32_t)k, total);
-  if (tid == 0) {
-    *k_eff = ke;
-    *thr_bin = 0;
-    *above = 0;
+  // ---- threshold bin: thread t owns bins 2047-2t and 2046-2t (descending)
+  {
+    const uint32_t h0 = hist[2047 - 2 * tid], h1 = hist[2046 - 2 * tid];
+    const uint32_t excl = block_excl_scan(h0 + h1, warp_sums, &s_total);
+    const uint32_t ke = min((uint32_t)p.k, s_total);
+    if (tid == 0) s_keff = ke;
+    if (ke > 0 && excl < ke && excl + h0 + h1 >= ke) {
+      if (excl + h0 >= ke) { s_bin = 2047 - 2 * tid; s_above = excl; s_cnt_bin = h0; }
+      else { s_bin = 2046 - 2 * tid; s_above = excl + h0; s_cnt_bin = h1; }
+    }
   }
   __syncthreads();
-  if (tid < 256 && ke > 0) {
-    const uint32_t incl = sh[tid], excl = incl - s;
-    if (excl < ke && incl >= ke) {
-      uint32_t run = excl;
+  const uint32_t k_eff = s_keff;
+  for (int i = tid + (int)k_eff; i < p.k; i += 1024) out[i] = -1;
+  if (k_eff == 0) return;
+  const uint32_t bin = s_bin, n_above = s_above, C = s_cnt_bin;
+  const bool in_smem = C <= (uint32_t)kCandSmem;
+  uint32_t* ck = in_smem ? ck_s : p.cand_key + (int64_t)row * p.n;
+  int32_t* ci = in_smem ? ci_s : p.cand_idx + (int64_t)row * p.n;
+  for (int i = tid; i < sort_n; i += 1024) sel[i] = 0x7FFFFFFF;
+  __syncthreads();
+  // ---- pass 2
+  for (int64_t i = tid; i < n; i += 4096) {
+    float x[4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        if (run + loc[j] >= ke) {
-          *thr_bin = 2047 - (tid * 8 + j);
-          *above = run;
-          break;
-        }
-        run += loc[j];
+    for (int u = 0; u < 4; ++u) x[u] = (i + 1024 * u < n) ? __ldg(src + i + 1024 * u) : -INFINITY;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t key = score_key_full(x[u]);
+      if (!key) continue;
+      const uint32_t kb = key >> 21;
+      if (kb > bin) {
+        sel[atomicAdd(&s_na, 1u)] = (int32_t)(i + 1024 * u);
+      } else if (kb == bin) {
+        const uint32_t pos = atomicAdd(&s_nc, 1u);
+        ck[pos] = key;
+        ci[pos] = (int32_t)(i + 1024 * u);
       }
     }
   }
   __syncthreads();
-}
 
-__global__ void __launch_bounds__(512) topk_filter_kernel(TopkParams p) {
-  __shared__ uint32_t sh[260];
-  __shared__ uint32_t s_keff, s_bin, s_above;
-  const int row = blockIdx.y;
-  const int64_t n = p.row_count ? min((int64_t)p.row_count[row], p.n) : p.n;
-  const int64_t lo = (int64_t)blockIdx.x * kBigChunk;
-  if (lo >= n) return;
-  const int64_t hi = min(lo + kBigChunk, n);
-  const int64_t base = p.row_start ? p.row_start[row] : (int64_t)row * p.row_stride;
-  big_threshold(p.hist + (int64_t)row * kBigBins, p.k, sh, &s_keff, &s_bin, &s_above);
-  if (s_keff == 0) return;
-  const uint32_t bin = s_bin;
-  uint32_t* cnt = p.counters + (int64_t)row * 4;
-  uint32_t* ck = p.cand_key + (int64_t)row * p.n;
-  int32_t* ci = p.cand_idx + (int64_t)row * p.n;
-  int32_t* ab = p.above_idx + (int64_t)row * p.k;
-  for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-    uint32_t key = score_key_full(p.scores[base + i]);
-    if (!key) continue;
-    uint32_t kb = key >> 21;
-    if (kb > bin) {
-      uint32_t pos = atomicAdd(&cnt[0], 1u);
-      if (pos < (uint32_t)p.k) ab[pos] = (int32_t)i;
-    } else if (kb == bin) {
-      uint32_t pos = atomicAdd(&cnt[1], 1u);
-      ck[pos] = key;
-      ci[pos] = (int32_t)i;
-    }
-  }
-}
-
-// One CTA per row: resolve the threshold inside the candidate bin, the ties, and sort.
-__global__ void __launch_bounds__(1024) topk_finish_kernel(TopkParams p, int sort_n) {
-  extern __shared__ int32_t sel[];  // [sort_n] ids to sort (padded with INT_MAX)
-  __shared__ uint32_t sh[260];
-  __shared__ uint32_t hist[256];
-  __shared__ uint32_t s_keff, s_bin, s_above, s_digit, s_dabove, s_cnt;
-  const int row = blockIdx.x;
-  const int tid = threadIdx.x;
-  int32_t* out = p.out_ids + (int64_t)row * p.k;
-  big_threshold(p.hist + (int64_t)row * kBigBins, p.k, sh, &s_keff, &s_bin, &s_above);
-  const uint32_t k_eff = s_keff;
-  for (int i = tid + (int)k_eff; i < p.k; i += blockDim.x) out[i] = -1;
-  if (k_eff == 0) return;
-  const uint32_t n_above = s_above;
-  const uint32_t C = p.counters[(int64_t)row * 4 + 1];
-  const uint32_t* ck = p.cand_key + (int64_t)row * p.n;
-  const int32_t* ci = p.cand_idx + (int64_t)row * p.n;
-  const int32_t* ab = p.above_idx + (int64_t)row * p.k;
-
-  // radix select of the `want` largest among the C candidates on the low 21 bits (8+8+5)
+  // ---- the `want` largest among the C candidates on the low 21 bits (8 + 8 + 5)
   uint32_t want = k_eff - n_above;
-  uint32_t prefix = s_bin << 21, prefix_mask = 0xFFE00000u;
+  uint32_t prefix = bin << 21, prefix_mask = 0xFFE00000u;
   const int shifts[3] = {13, 5, 0};
   const uint32_t widths[3] = {255u, 255u, 31u};
   for (int ps = 0; ps < 3; ++ps) {
     if (tid < 256) hist[tid] = 0;
     __syncthreads();
-    for (uint32_t i = tid; i < C; i += blockDim.x) {
-      uint32_t key = ck[i];
+    for (uint32_t i = tid; i < C; i += 1024) {
+      const uint32_t key = ck[i];
       if ((key & prefix_mask) == prefix) atomicAdd(&hist[(key >> shifts[ps]) & widths[ps]], 1u);
     }
     __syncthreads();
@@ -327,72 +281,66 @@ __global__ void __launch_bounds__(1024) topk_finish_kernel(TopkParams p, int sor
     __syncthreads();
   }
   const uint32_t thr = prefix;
-  const uint32_t need = want;  // ties to take (lowest indices), >= 1
-
-  // ties: find the need-th smallest index among candidates with key == thr (indices are unique)
-  uint32_t ipre = 0, imask = 0, iwant = need;
-  for (int shift = 24; shift >= 0; shift -= 8) {
-    if (tid < 256) hist[tid] = 0;
-    __syncthreads();
-    for (uint32_t i = tid; i < C; i += blockDim.x) {
-      if (ck[i] == thr) {
-        uint32_t v = ~(uint32_t)ci[i];  // descending scan of ~idx == ascending idx
-        if ((v & imask) == ipre) atomicAdd(&hist[(v >> shift) & 255u], 1u);
+  const uint32_t need = want;  // ties to take (lowest ids), >= 1
+  // ---- ties: the need-th smallest id among candidates with key == thr (ids are unique)
+  if (tid == 0) s_total = 0;
+  __syncthreads();
+  {
+    uint32_t nt = 0;
+    for (uint32_t i = tid; i < C; i += 1024) nt += ck[i] == thr;
+    nt = __reduce_add_sync(0xffffffffu, nt);
+    if ((tid & 31) == 0 && nt) atomicAdd(&s_total, nt);
+  }
+  __syncthreads();
+  uint32_t idx_thr = 0xFFFFFFFFu;  // all ties taken
+  if (s_total > need) {
+    uint32_t ipre = 0, imask = 0, iwant = need;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+      if (tid < 256) hist[tid] = 0;
+      __syncthreads();
+      for (uint32_t i = tid; i < C; i += 1024) {
+        if (ck[i] == thr) {
+          const uint32_t v = ~(uint32_t)ci[i];  // descending scan of ~id == ascending id
+          if ((v & imask) == ipre) atomicAdd(&hist[(v >> shift) & 255u], 1u);
+        }
       }
+      __syncthreads();
+      if (tid < 32) pick_digit_256(hist, iwant, &s_digit, &s_dabove);
+      __syncthreads();
+      ipre |= s_digit << shift;
+      imask |= 255u << shift;
+      iwant -= s_dabove;
+      __syncthreads();
     }
-    __syncthreads();
-    if (tid < 32) pick_digit_256(hist, iwant, &s_digit, &s_dabove);
-    __syncthreads();
-    ipre |= s_digit << shift;
-    imask |= 255u << shift;
-    iwant -= s_dabove;
-    __syncthreads();
+    idx_thr = ~ipre;
   }
-  const uint32_t idx_thr = ~ipre;  // ties with idx <= idx_thr are taken
-
-  if (tid == 0) s_cnt = 0;
-  for (int i = tid; i < sort_n; i += blockDim.x) sel[i] = 0x7FFFFFFF;
-  __syncthreads();
-  for (uint32_t i = tid; i < n_above; i += blockDim.x) sel[i] = ab[i];
-  for (uint32_t i = tid; i < C; i += blockDim.x) {
-    uint32_t key = ck[i];
-    int32_t id = ci[i];
-    if (key > thr || (key == thr && (uint32_t)id <= idx_thr)) {
-      uint32_t pos = atomicAdd(&s_cnt, 1u);
-      if (n_above + pos < (uint32_t)sort_n) sel[n_above + pos] = id;
-    }
+  for (uint32_t i = tid; i < C; i += 1024) {
+    const uint32_t key = ck[i];
+    const int32_t id = ci[i];
+    if (key > thr || (key == thr && (uint32_t)id <= idx_thr)) sel[atomicAdd(&s_na, 1u)] = id;
   }
   __syncthreads();
-  // bitonic sort ascending
+  // ---- bitonic sort ascending (padding = INT_MAX)
   for (int size = 2; size <= sort_n; size <<= 1) {
     for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      for (int i = tid; i < sort_n / 2; i += blockDim.x) {
-        int a = 2 * i - (i & (stride - 1));
-        int b = a + stride;
-        bool up = ((a & size) == 0);
-        int32_t x = sel[a], y = sel[b];
-        if ((x > y) == up) {
-          sel[a] = y;
-          sel[b] = x;
-        }
+      for (int i = tid; i < sort_n / 2; i += 1024) {
+        const int a = 2 * i - (i & (stride - 1));
+        const int b = a + stride;
+        const bool up = ((a & size) == 0);
+        const int32_t x = sel[a], y = sel[b];
+        if ((x > y) == up) { sel[a] = y; sel[b] = x; }
       }
       __syncthreads();
     }
   }
-  for (uint32_t i = tid; i < k_eff; i += blockDim.x) out[i] = sel[i];
+  for (uint32_t i = tid; i < k_eff; i += 1024) out[i] = sel[i];
 }
 
-static void big_layout(int32_t rows, int64_t n, int32_t k, size_t* hist_off, size_t* cnt_off, size_t* ck_off,
-                       size_t* ci_off, size_t* ab_off, size_t* total) {
+static void big_layout(int32_t rows, int64_t n, size_t* ck_off, size_t* ci_off, size_t* total) {
   size_t o = 0;
-  *hist_off = o; o += (size_t)rows * kBigBins * 4;
-  *cnt_off = o;  o += (size_t)rows * 4 * 4;
-  o = (size_t)round_up((int64_t)o, 256);
   *ck_off = o;   o += (size_t)rows * (size_t)n * 4;
   o = (size_t)round_up((int64_t)o, 256);
   *ci_off = o;   o += (size_t)rows * (size_t)n * 4;
-  o = (size_t)round_up((int64_t)o, 256);
-  *ab_off = o;   o += (size_t)rows * (size_t)k * 4;
   *total = (size_t)round_up((int64_t)o, 256);
 }
 
@@ -403,8 +351,8 @@ using namespace mxb;
 extern "C" int64_t mxb_topk_workspace_bytes(int32_t rows, int64_t n, int32_t k) {
   if (rows <= 0 || n <= 0 || k <= 0) return 0;
   if (n <= kSmemRowMax) return 0;
-  size_t a, b, c, d, e, total;
-  big_layout(rows, n, k, &a, &b, &c, &d, &e, &total);
+  size_t a, b, total;
+  big_layout(rows, n, &a, &b, &total);
   return (int64_t)total;
 }
 
@@ -429,25 +377,18 @@ extern "C" int mxb_topk_select(const mxb_topk_args* a, void* stream) {
     return MXB_OK;
   }
 
-  size_t ho, co, cko, cio, abo, total;
-  big_layout(a->rows, a->n, a->k, &ho, &co, &cko, &cio, &abo, &total);
+  size_t cko, cio, total;
+  big_layout(a->rows, a->n, &cko, &cio, &total);
   MXB_REQUIRE(a->workspace != nullptr && a->workspace_bytes >= (int64_t)total, MXB_ERR_WORKSPACE,
               "topk: workspace of %lld bytes required", (long long)total);
   char* ws = reinterpret_cast<char*>(a->workspace);
-  p.hist = reinterpret_cast<uint32_t*>(ws + ho);
-  p.counters = reinterpret_cast<uint32_t*>(ws + co);
   p.cand_key = reinterpret_cast<uint32_t*>(ws + cko);
   p.cand_idx = reinterpret_cast<int32_t*>(ws + cio);
-  p.above_idx = reinterpret_cast<int32_t*>(ws + abo);
-  MXB_CUDA_OK(cudaMemsetAsync(ws, 0, cko, st));  // histograms + counters
-  dim3 grid((unsigned)ceil_div(a->n, kBigChunk), (unsigned)a->rows);
-  topk_hist_kernel<<<grid, 512, 0, st>>>(p);
-  MXB_CUDA_OK(cudaGetLastError());
-  topk_filter_kernel<<<grid, 512, 0, st>>>(p);
-  MXB_CUDA_OK(cudaGetLastError());
   int sort_n = 2;
   while (sort_n < a->k) sort_n <<= 1;
-  topk_finish_kernel<<<a->rows, 1024, (size_t)sort_n * 4, st>>>(p, sort_n);
+  const size_t smem = (size_t)sort_n * 4 + (size_t)kCandSmem * 8;
+  MXB_CUDA_OK(cudaFuncSetAttribute(topk_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  topk_stream_kernel<<<a->rows, 1024, smem, st>>>(p, sort_n);
   MXB_CUDA_OK(cudaGetLastError());
   return MXB_OK;
 }

@@ -260,7 +260,7 @@ def indexer_score_operands(q, index_comp):
 
 
 def indexer_scores_tiled_live(q, weights, index_comp, *, pos0: int, ratio: int = 4, exact_fp32: bool = False,
-                              out=None, check: bool = False):
+                              fp8_mma: bool = False, out=None, check: bool = False):
     """Indexer scores with the causal compressed-row mask
     (reference: indexed_attention_kernel.py:1888-1961).
 
@@ -268,7 +268,9 @@ def indexer_scores_tiled_live(q, weights, index_comp, *, pos0: int, ratio: int =
     scale factors folded in), index_comp ``[batch, n_comp, D]``; D is 64 or 128.
     Operand pairs: both float32, both float16, both bfloat16, or 16-bit q with
     float8_e4m3fn rows.  Returns float32 ``[batch, tokens, n_comp]`` with ``-inf`` at rows
-    ``>= min((pos0+t+1)//ratio, n_comp)``; ``ratio=0`` applies no mask.
+    ``>= min((pos0+t+1)//ratio, n_comp)``; ``ratio=0`` applies no mask.  ``fp8_mma=True``
+    (float8 rows only) uses the FP8 tensor-core path directly: faster to feed, but its
+    reduced-precision accumulation leaves ~1e-3 relative error in the scores.
     """
     if q.ndim != 4 or weights.ndim != 3 or index_comp.ndim != 3:
         raise ValueError("q, weights, and index_comp must be BHLD/BLH/BPD")
@@ -301,12 +303,12 @@ def indexer_scores_tiled_live(q, weights, index_comp, *, pos0: int, ratio: int =
         raise ValueError("index_comp must contain at least one compressed row")
     _SCORES_TILED_CALL_COUNTS[form] += 1
     scores = indexer_scores(q, weights, index_comp.reshape(batch * n_comp, head_dim), n_rows=n_comp, pos0=pos0,
-                            ratio=ratio, exact_fp32=exact_fp32, out=out, check=check)
+                            ratio=ratio, exact_fp32=exact_fp32, fp8_mma=fp8_mma, out=out, check=check)
     return scores
 
 
 def indexer_scores(q, weights, keys_flat, *, n_rows, pos0=0, ratio=0, row_start=None, row_count=None,
-                   exact_fp32=False, out=None, check=False):
+                   exact_fp32=False, fp8_mma=False, out=None, check=False):
     """General launcher: q [B,H,T,D], weights [B,T,H] f32, keys_flat [rows_total, D].
 
     Uniform batches (row_start None): returns [B,T,n_rows].  Ragged batches (T == 1,
@@ -338,7 +340,7 @@ def indexer_scores(q, weights, keys_flat, *, n_rows, pos0=0, ratio=0, row_start=
     a.row_start = ptr(row_start); a.row_count = ptr(row_count)
     a.B, a.T, a.H, a.D = B, T, H, D
     a.n_rows = int(n_rows); a.rows_total = rows_total; a.pos0 = int(pos0); a.ratio = int(ratio)
-    a.flags = _abi.INDEXER_EXACT_FP32 if exact_fp32 else 0
+    a.flags = (_abi.INDEXER_EXACT_FP32 if exact_fp32 else 0) | (_abi.INDEXER_FP8_MMA if fp8_mma else 0)
     a.status = ptr(status)
     _abi.check(_t.launch("indexer_scores", lib.mxb_indexer_scores, a))
     if check:
