@@ -160,18 +160,20 @@ __global__ void __launch_bounds__(192, 1) flash_prefill_kernel(const __grid_cons
       const uint32_t idesc_o = ptx::idesc_f16(fmt, fmt, FB_M, FB_D, 0, 0);
       const uint32_t q_addr = ptx::smem_u32(q_s), k_addr = ptx::smem_u32(k_s), v_addr = ptx::smem_u32(v_s),
                      p_addr = ptx::smem_u32(p_s);
+      const uint64_t q_desc = ptx::smem_desc_sw128(q_addr, 16, 1024), k_desc = ptx::smem_desc_sw128(k_addr, 16, 1024),
+                     v_desc = ptx::smem_desc_sw128(v_addr, 16, 1024), p_desc = ptx::smem_desc_sw128(p_addr, 16, 1024);
       auto issue_s = [&](int j) {
         const int s = j & 1;
         ptx::mbar_wait(&k_full[s], (uint32_t)((j >> 1) & 1), abort_flag);
         ptx::tc_fence_after_sync();
         const uint32_t d = tmem_base + (uint32_t)(s * FB_N);
+        const uint64_t kd = ptx::desc_advance(k_desc, s * 32768);
 #pragma unroll
         for (int kb = 0; kb < 4; ++kb)
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
-            const uint64_t ad = ptx::smem_desc_sw128(q_addr + kb * 16384 + ks * 32, 16, 1024);
-            const uint64_t bd = ptx::smem_desc_sw128(k_addr + s * 32768 + kb * 8192 + ks * 32, 16, 1024);
-            ptx::mma_f16_ss(d, ad, bd, idesc_s, (kb | ks) ? 1u : 0u);
+            ptx::mma_f16_ss(d, ptx::desc_advance(q_desc, kb * 16384 + ks * 32),
+                            ptx::desc_advance(kd, kb * 8192 + ks * 32), idesc_s, (kb | ks) ? 1u : 0u);
           }
         ptx::mma_commit(&s_ready[s]);
         ptx::mma_commit(&k_empty[s]);
@@ -186,9 +188,8 @@ __global__ void __launch_bounds__(192, 1) flash_prefill_kernel(const __grid_cons
         ptx::tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
-          const uint64_t ad = ptx::smem_desc_sw128(p_addr + ks * 32, 16, 1024);
-          const uint64_t bd = ptx::smem_desc_sw128(v_addr + s * 32768 + ks * 32, 16, 1024);
-          ptx::mma_f16_ss(tmem_o, ad, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+          ptx::mma_f16_ss(tmem_o, ptx::desc_advance(p_desc, ks * 32), ptx::desc_advance(v_desc, s * 32768 + ks * 32),
+                          idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
         }
         ptx::mma_commit(pv_done);
         ptx::mma_commit(&v_empty[s]);

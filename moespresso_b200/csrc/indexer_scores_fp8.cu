@@ -25,7 +25,20 @@
 
 namespace mxb {
 
+#if defined(MXB_TRACE_MMA)
+#define TR(role, i)
+#define TRM(role, i) do { if (tr_on && (i) < 64) tr[(role) * 64 + (i)] = clock64(); } while (0)
+#elif defined(MXB_TRACE)
+#define TR(role, i) do { if (tr_on && (i) < 64) tr[(role) * 64 + (i)] = clock64(); } while (0)
+#define TRM(role, i)
+#else
+#define TR(role, i)
+#define TRM(role, i)
+#endif
+
 struct Fp8Params {
+  const uint8_t* keys;
+  int64_t rows_total;
   const void* q;
   int q_is_bf16;
   int64_t q_sb, q_sh, q_st;
@@ -105,6 +118,11 @@ indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
   const int ntiles = (int)((span + 127) / 128);
   const int nt = min(p.t_tile, p.T - t0);
   const int N = p.N, H = p.H, n_acc = p.n_acc;
+#if defined(MXB_TRACE) || defined(MXB_TRACE_MMA)
+  long long* tr = reinterpret_cast<long long*>(p.status);
+  const bool tr_on = p.status && blockIdx.x == 1 && blockIdx.z == 0 && lane == 0;
+  if (tr_on && tid == 0) tr[6 * 64] = clock64();
+#endif
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
@@ -192,17 +210,31 @@ indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
       for (int i = 0; i < ntiles; ++i) {
         const int s = i % S;
         if (i >= S) ptx::mbar_wait(&raw_empty[s], (uint32_t)((i / S - 1) & 1), abort_flag);
-        ptx::mbar_expect_tx(&raw_full[s], (uint32_t)C::kRaw);
-        ptx::tma_load_2d(raw_buf + (size_t)s * C::kRaw, &tmap, &raw_full[s], 0,
-                         (int32_t)(rbase + row0 + (int64_t)i * 128));
+        const int64_t grow = rbase + row0 + (int64_t)i * 128;
+        TR(0, i);
+        if constexpr (DIRECT) {
+          ptx::mbar_expect_tx(&raw_full[s], (uint32_t)C::kRaw);
+          ptx::tma_load_2d(raw_buf + (size_t)s * C::kRaw, &tmap, &raw_full[s], 0, (int32_t)grow);
+        } else {
+          // the 128 rows of a tile are contiguous in the table: one untiled bulk copy, clamped at the table end
+          int64_t rows = p.rows_total - grow;
+          if (rows > 128) rows = 128;
+          const uint32_t bytes = (uint32_t)(rows * D);
+          ptx::mbar_expect_tx(&raw_full[s], bytes);
+          ptx::bulk_load_1d(raw_buf + (size_t)s * C::kRaw, p.keys + grow * D, bytes, &raw_full[s]);
+        }
       }
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t b_addr = ptx::smem_u32(b_buf);
+      const uint64_t a_desc0 = ptx::smem_desc_sw128(ptx::smem_u32(a16_buf), 16, 1024);
+      const uint64_t b_desc0 = ptx::smem_desc_sw128(b_addr, 16, 1024);
+      const uint32_t idesc16 = ptx::idesc_f16(ptx::kFmtF16, ptx::kFmtF16, 128, (uint32_t)N, 0, 0);
+      int a = 0, ab = 0;                 // accumulator / operand-buffer ring positions
+      uint32_t a_ph = 1, ab_ph = 0;      // parity to wait for: acc_empty of the previous use, a_full of this use
       for (int i = 0; i < ntiles; ++i) {
-        const int a = i % n_acc;
         const uint32_t d_tmem = tmem_base + (uint32_t)(a * p.acc_stride);
         if constexpr (DIRECT) {
           constexpr uint32_t kMode = (D == 64) ? 4u : 2u;   // 64-byte / 128-byte swizzle
@@ -221,23 +253,29 @@ indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
           }
           ptx::mma_commit(&raw_empty[s]);
         } else {
-          const int ab = i % NA;
-          ptx::mbar_wait(&a_full[ab], (uint32_t)((i / NA) & 1), abort_flag);
-          if (i >= n_acc) ptx::mbar_wait(&acc_empty[a], (uint32_t)((i / n_acc - 1) & 1), abort_flag);
+          // descriptors differ from the precomputed bases only in their start-address field
+          TRM(0, i);
+          ptx::mbar_wait(&a_full[ab], ab_ph, abort_flag);
+          TRM(1, i);
+          if (i >= n_acc) ptx::mbar_wait(&acc_empty[a], a_ph, abort_flag);
+          TRM(2, i);
           ptx::tc_fence_after_sync();
-          const uint32_t idesc = ptx::idesc_f16(ptx::kFmtF16, ptx::kFmtF16, 128, (uint32_t)N, 0, 0);
-          const uint32_t a_addr = ptx::smem_u32(a16_buf) + ab * C::kA16;
+          const uint64_t ad0 = ptx::desc_advance(a_desc0, (uint32_t)(ab * C::kA16));
 #pragma unroll
           for (int kb = 0; kb < D / 64; ++kb)
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-              const uint64_t ad = ptx::smem_desc_sw128(a_addr + kb * 16384 + ks * 32, 16, 1024);
-              const uint64_t bd = ptx::smem_desc_sw128(b_addr + kb * N * 128 + ks * 32, 16, 1024);
-              ptx::mma_f16_ss(d_tmem, ad, bd, idesc, (kb | ks) ? 1u : 0u);
-            }
+            for (int ks = 0; ks < 4; ++ks)
+              ptx::mma_f16_ss(d_tmem, ptx::desc_advance(ad0, kb * 16384 + ks * 32),
+                              ptx::desc_advance(b_desc0, kb * N * 128 + ks * 32), idesc16, (kb | ks) ? 1u : 0u);
+          TRM(3, i);
           ptx::mma_commit(&a_empty[ab]);
+          TRM(4, i);
+          TR(3, i);
         }
         ptx::mma_commit(&acc_full[a]);
+        TRM(5, i);
+        if (++a == n_acc) { a = 0; a_ph ^= 1u; }
+        if (NA > 0 && ++ab == NA) { ab = 0; ab_ph ^= 1u; }
       }
     }
   } else if (warp >= kConvWarp0) {
@@ -250,6 +288,7 @@ indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
         const int s = i % S;
         ptx::mbar_wait(&raw_full[s], (uint32_t)((i / S) & 1), abort_flag);
         if (i >= NA) ptx::mbar_wait(&a_empty[cw], (uint32_t)((i / NA - 1) & 1), abort_flag);
+        TR(1, i);
         const uint8_t* raw = raw_buf + (size_t)s * C::kRaw;
 #pragma unroll 4
         for (int ci = lane; ci < 128 * CPR; ci += 32) {
@@ -270,6 +309,7 @@ indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
         ptx::fence_proxy_async_smem();
         ptx::mbar_arrive(&a_full[cw]);
         ptx::mbar_arrive(&raw_empty[s]);
+        TR(2, i);
       }
     }
   } else {
@@ -281,6 +321,7 @@ indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
       const int a = i % n_acc;
       ptx::mbar_wait(&acc_full[a], (uint32_t)((i / n_acc) & 1), abort_flag);
       ptx::tc_fence_after_sync();
+      if (quad == 0) TR(4, i);
       const int64_t r = row0 + (int64_t)i * 128 + rloc;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * p.acc_stride);
       for (int t = 0; t < nt; ++t) {
@@ -314,12 +355,15 @@ indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
       }
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(&acc_empty[a]);
+      if (quad == 0) TR(5, i);
     }
   }
 
   __syncthreads();
   if (warp == 0) ptx::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+#if !defined(MXB_TRACE) && !defined(MXB_TRACE_MMA)
   if (tid == 0 && *abort_flag && p.status) atomicExch(p.status, 1);
+#endif
 }
 
 template <int D, bool DIRECT>
@@ -367,6 +411,7 @@ static int launch_fp8_d(Fp8Params& p, const mxb_indexer_scores_args* a, cudaStre
 
 int launch_indexer_fp8(const mxb_indexer_scores_args* a, cudaStream_t st) {
   Fp8Params p{};
+  p.keys = reinterpret_cast<const uint8_t*>(a->keys); p.rows_total = a->rows_total;
   p.q = a->q; p.q_is_bf16 = a->q_dtype == MXB_BF16;
   p.q_sb = a->q_stride_b; p.q_sh = a->q_stride_h; p.q_st = a->q_stride_t;
   p.weights = a->weights; p.scores = a->scores; p.s_sb = a->score_stride_b; p.s_st = a->score_stride_t;

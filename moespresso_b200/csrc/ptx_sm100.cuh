@@ -89,6 +89,14 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// Untiled bulk copy of `bytes` contiguous bytes (multiple of 16, both addresses 16-byte aligned).
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
 // ---------------------------------------------------------------- TMEM ------
 // Allocate `cols` (power of two >= 32) TMEM columns; executed by one full warp.
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t cols) {
@@ -168,6 +176,9 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
   d |= (uint64_t)mode << 61;
   return d;
 }
+
+// Move a descriptor's start address by `bytes` (multiple of 16; the sum must stay below 256 KB).
+__device__ __forceinline__ uint64_t desc_advance(uint64_t d, uint32_t bytes) { return d + (uint64_t)(bytes >> 4); }
 
 constexpr uint32_t kFmtF16 = 0, kFmtBF16 = 1;
 // Instruction descriptor for kind::f8f6f4 with E4M3 operands and fp32 accumulation.

@@ -232,6 +232,10 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
   const uint32_t idesc_o = ptx::idesc_f16(fmt, fmt, 128, TC_HEADS, 1, 0);  // A read MN-major
   const uint32_t tile_addr = ptx::smem_u32(tile), q_addr = ptx::smem_u32(q_s), pt_addr = ptx::smem_u32(pt);
   const float scale_log2 = p.scale * 1.4426950408889634f;
+  const uint64_t tile_desc_k = ptx::smem_desc_sw128(tile_addr, 16, 1024);
+  const uint64_t tile_desc_mn = ptx::smem_desc_sw128(tile_addr, 16384, 1024);
+  const uint64_t q_desc = ptx::smem_desc_sw128(q_addr, 16, 1024);
+  const uint64_t pt_desc = ptx::smem_desc_sw128(pt_addr, 16, 1024);
 
   float l_thr[32];
 #pragma unroll
@@ -323,9 +327,8 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
       for (int kb = 0; kb < nslab; ++kb) {
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
-          const uint64_t ad = ptx::smem_desc_sw128(tile_addr + kb * 16384 + ks * 32, 16, 1024);
-          const uint64_t bd = ptx::smem_desc_sw128(q_addr + kb * 8192 + ks * 32, 16, 1024);
-          ptx::mma_f16_ss(tmem_base, ad, bd, idesc_s, (kb | ks) ? 1u : 0u);
+          ptx::mma_f16_ss(tmem_base, ptx::desc_advance(tile_desc_k, kb * 16384 + ks * 32),
+                          ptx::desc_advance(q_desc, kb * 8192 + ks * 32), idesc_s, (kb | ks) ? 1u : 0u);
         }
       }
       ptx::mma_commit(&mi->bar_s);
@@ -414,9 +417,9 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           // A, MN-major: 64-feature blocks 16 KB apart (LBO), 8-row groups 1 KB apart (SBO); 16 rows per K step
-          const uint64_t ad = ptx::smem_desc_sw128(tile_addr + (2 * mt) * 16384 + ks * 2048, 16384, 1024);
-          const uint64_t bd = ptx::smem_desc_sw128(pt_addr + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024);
-          ptx::mma_f16_ss(tmem_o + (uint32_t)(mt * 64), ad, bd, idesc_o, (have_o || ks > 0) ? 1u : 0u);
+          ptx::mma_f16_ss(tmem_o + (uint32_t)(mt * 64), ptx::desc_advance(tile_desc_mn, (2 * mt) * 16384 + ks * 2048),
+                          ptx::desc_advance(pt_desc, (ks >> 2) * 8192 + (ks & 3) * 32), idesc_o,
+                          (have_o || ks > 0) ? 1u : 0u);
         }
       }
       ptx::mma_commit(&mi->bar_o);
