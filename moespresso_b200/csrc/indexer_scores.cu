@@ -405,6 +405,8 @@ static int launch_tc(IndexerParams& p, const mxb_indexer_scores_args* a, cudaStr
 }
 
 int launch_indexer_fp8(const mxb_indexer_scores_args* a, cudaStream_t st);  // indexer_scores_fp8.cu
+bool indexer_decode_eligible(const mxb_indexer_scores_args* a);                // indexer_decode.cu
+int launch_indexer_decode(const mxb_indexer_scores_args* a, cudaStream_t st);
 
 }  // namespace mxb
 
@@ -429,6 +431,7 @@ extern "C" int mxb_indexer_scores(const mxb_indexer_scores_args* a, void* stream
   p.B = a->B; p.T = a->T; p.H = a->H; p.n_rows = a->n_rows;
   p.pos0 = a->pos0; p.ratio = a->ratio; p.status = a->status;
 
+  if (indexer_decode_eligible(a)) return launch_indexer_decode(a, st);
   const bool q16 = a->q_dtype == MXB_F16 || a->q_dtype == MXB_BF16;
   const bool keys_match = a->key_dtype == a->q_dtype || a->key_dtype == MXB_F8E4M3;
   const bool q_vec_ok = (reinterpret_cast<uintptr_t>(a->q) & 15) == 0 && a->q_stride_b % 8 == 0 &&

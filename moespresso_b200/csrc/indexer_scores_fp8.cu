@@ -63,9 +63,10 @@ struct Fp8Params {
 
 constexpr int kDrainSets = 2;
 constexpr int kDrainWarps = 4 * kDrainSets;
+constexpr int kMmaWarps = 2;               // two issuing threads: tile i belongs to issuer i % 2
 constexpr int kMmaWarp = kDrainWarps;
-constexpr int kTmaWarp = kDrainWarps + 1;
-constexpr int kConvWarp0 = kDrainWarps + 2;
+constexpr int kTmaWarp = kDrainWarps + kMmaWarps;
+constexpr int kConvWarp0 = kTmaWarp + 1;
 
 template <int D, bool DIRECT>
 struct Fp8Cfg {
@@ -225,16 +226,19 @@ indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
         }
       }
     }
-  } else if (warp == kMmaWarp) {
-    // ------------------------------------------------------------ MMA issuer
+  } else if (warp >= kMmaWarp && warp < kMmaWarp + kMmaWarps) {
+    // ------------------------------------------------------------ MMA issuers
+    // A single thread needs ~1000 cycles per tile for its waits, four MMAs and two commits, more than
+    // the 700 cycles a tile may take at HBM speed with two CTAs per SM; two issuers alternate tiles.
     if (lane == 0) {
+      const int mw = warp - kMmaWarp;
       const uint32_t b_addr = ptx::smem_u32(b_buf);
       const uint64_t a_desc0 = ptx::smem_desc_sw128(ptx::smem_u32(a16_buf), 16, 1024);
       const uint64_t b_desc0 = ptx::smem_desc_sw128(b_addr, 16, 1024);
       const uint32_t idesc16 = ptx::idesc_f16(ptx::kFmtF16, ptx::kFmtF16, 128, (uint32_t)N, 0, 0);
-      int a = 0, ab = 0;                 // accumulator / operand-buffer ring positions
+      int a = mw % n_acc, ab = NA > 0 ? mw % (NA > 0 ? NA : 1) : 0;   // ring positions of this issuer's first tile
       uint32_t a_ph = 1, ab_ph = 0;      // parity to wait for: acc_empty of the previous use, a_full of this use
-      for (int i = 0; i < ntiles; ++i) {
+      for (int i = mw; i < ntiles; i += kMmaWarps) {
         const uint32_t d_tmem = tmem_base + (uint32_t)(a * p.acc_stride);
         if constexpr (DIRECT) {
           constexpr uint32_t kMode = (D == 64) ? 4u : 2u;   // 64-byte / 128-byte swizzle
@@ -274,8 +278,12 @@ indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
         }
         ptx::mma_commit(&acc_full[a]);
         TRM(5, i);
-        if (++a == n_acc) { a = 0; a_ph ^= 1u; }
-        if (NA > 0 && ++ab == NA) { ab = 0; ab_ph ^= 1u; }
+        a += kMmaWarps;
+        if (a >= n_acc) { a -= n_acc; a_ph ^= 1u; }
+        if (NA > 0) {
+          ab += kMmaWarps;
+          if (ab >= NA) { ab -= NA; ab_ph ^= 1u; }
+        }
       }
     }
   } else if (warp >= kConvWarp0) {
@@ -377,6 +385,7 @@ static int launch_fp8_d(Fp8Params& p, const mxb_indexer_scores_args* a, cudaStre
   p.acc_stride = (int)round_up(p.N, 32);
   int n_acc = 512 / p.acc_stride;
   if (n_acc > 8) n_acc = 8;
+  n_acc &= ~1;   // even: the two MMA issuers stride the ring by two
   p.n_acc = n_acc;
   int cols = 32;
   while (cols < n_acc * p.acc_stride) cols <<= 1;
@@ -386,10 +395,10 @@ static int launch_fp8_d(Fp8Params& p, const mxb_indexer_scores_args* a, cudaStre
   const int64_t tiles = ceil_div(p.n_rows, 128);
   const int smem = C::b_off + p.b_bytes + 256 * 4 + 56 * 8 + 64 + 1024;
   const int ctas_per_sm = smem <= 113 * 1024 ? 2 : 1;
-  // static chunks of rows per CTA: about two CTAs per resident slot, at least 8 tiles each
-  int64_t want_ctas = (int64_t)sm_count() * ctas_per_sm * 2;
+  // static chunks of rows per CTA, several per resident slot so that ragged sequences balance
+  int64_t want_ctas = (int64_t)sm_count() * ctas_per_sm * 6;
   int64_t per = ceil_div(tiles * p.B * t_tiles, want_ctas);
-  if (per < 8) per = 8;
+  if (per < 16) per = 16;
   if (per > tiles) per = tiles;
   p.rows_per_cta = (int)(per * 128);
 
