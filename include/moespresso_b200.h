@@ -120,6 +120,15 @@ typedef struct {
 int64_t mxb_topk_workspace_bytes(int32_t rows, int64_t n, int32_t k);
 int mxb_topk_select(const mxb_topk_args* a, void* stream);
 
+/* No counterpart in the reference: the same selection for callers that must not allocate
+ * device memory (a server whose memory pool is frozen after start-up, code inside another
+ * allocator's callback).  `workspace` / `workspace_bytes` are ignored; the candidate
+ * scratch is an 8 MiB array built into the library (2^20 entries), so rows * n must not
+ * exceed 2^20.  Calls nothing that allocates.  The first call on each device looks up the
+ * array's device address: make it before any stream capture.  All calls share the array:
+ * calls whose kernels could overlap on the GPU must be ordered (same stream). */
+int mxb_topk_select_static(const mxb_topk_args* a, void* stream);
+
 /* ------------------------------------------------------------------------ *
  * Indexed mixed (sparse) attention, decode and prefill forms.
  * Replaces  indexed_mixed_attention_decode(q, raw_kv, comp_kv, topk, sinks, *, pos0, window, ratio, raw_start)

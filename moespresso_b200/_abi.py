@@ -82,6 +82,7 @@ EXPORTS = {
     "mxb_indexer_scores": (C.c_int, [C.POINTER(IndexerScoresArgs), _p]),
     "mxb_topk_workspace_bytes": (_i64, [_i32, _i64, _i32]),
     "mxb_topk_select": (C.c_int, [C.POINTER(TopkArgs), _p]),
+    "mxb_topk_select_static": (C.c_int, [C.POINTER(TopkArgs), _p]),
     "mxb_sparse_attn_workspace_bytes": (_i64, [C.POINTER(SparseAttnArgs)]),
     "mxb_sparse_attn": (C.c_int, [C.POINTER(SparseAttnArgs), _p]),
     "mxb_merge_partials": (C.c_int, [C.POINTER(MergeArgs), _p]),

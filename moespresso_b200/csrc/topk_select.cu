@@ -13,6 +13,8 @@
 //    row twice from L2 (11-bit histogram, then strictly-above ids + the threshold bin's
 //    candidates), resolves the remaining 21 bits and the ties by lowest index among the
 //    candidates, and sorts the selected ids.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace mxb {
@@ -384,6 +386,72 @@ extern "C" int mxb_topk_select(const mxb_topk_args* a, void* stream) {
   char* ws = reinterpret_cast<char*>(a->workspace);
   p.cand_key = reinterpret_cast<uint32_t*>(ws + cko);
   p.cand_idx = reinterpret_cast<int32_t*>(ws + cio);
+  int sort_n = 2;
+  while (sort_n < a->k) sort_n <<= 1;
+  const size_t smem = (size_t)sort_n * 4 + (size_t)kCandSmem * 8;
+  MXB_CUDA_OK(cudaFuncSetAttribute(topk_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  topk_stream_kernel<<<a->rows, 1024, smem, st>>>(p, sort_n);
+  MXB_CUDA_OK(cudaGetLastError());
+  return MXB_OK;
+}
+
+// --------------------------------------------------------------------------
+// Top-k for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot hand over a workspace: a serving process that froze
+// its memory pool after start-up, or code running inside another framework's allocator
+// callback, where cudaMalloc (or any allocating library call) is off limits.  This entry
+// point gives them the long-row selection with its candidate scratch in a fixed array
+// that is part of the library image: kStaticCandEntries (key, id) pairs = 8 MiB, held by
+// every GPU that loads the library until the process exits.
+//
+// The array's name is only a host-side handle here; the kernel needs the device address,
+// which cudaGetSymbolAddress returns for the CURRENT device.  It is looked up once per
+// device, on the first call made with that device current — make that first call before
+// any stream capture.  Every call shares the array (it keeps the previous call's
+// candidates; nothing in it has to start at zero because the kernel's counters live in
+// shared memory), so two calls whose kernels overlap on the GPU race on it: keep calls on
+// one stream, or otherwise ordered.  rows * n above kStaticCandEntries is rejected.
+// --------------------------------------------------------------------------
+namespace mxb {
+constexpr int64_t kStaticCandEntries = (int64_t)1 << 20;
+static __device__ __align__(256) uint32_t g_static_cand[2 * kStaticCandEntries];
+
+static int static_cand_address(uint32_t** out) {
+  static std::mutex mu;
+  static uint32_t* per_device[64] = {nullptr};
+  int dev = -1;
+  MXB_CUDA_OK(cudaGetDevice(&dev));
+  MXB_REQUIRE(dev >= 0 && dev < 64, MXB_ERR_UNSUPPORTED, "topk (static scratch): device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!per_device[dev]) {
+    void* ptr = nullptr;
+    MXB_CUDA_OK(cudaGetSymbolAddress(&ptr, g_static_cand));
+    per_device[dev] = reinterpret_cast<uint32_t*>(ptr);
+  }
+  *out = per_device[dev];
+  return MXB_OK;
+}
+}  // namespace mxb
+
+extern "C" int mxb_topk_select_static(const mxb_topk_args* a, void* stream) {
+  MXB_REQUIRE(a != nullptr, MXB_ERR_INVALID, "topk: null args");
+  MXB_REQUIRE(a->rows > 0 && a->n > 0, MXB_ERR_INVALID, "topk: scores must contain at least one row and column");
+  MXB_REQUIRE(a->k >= 1 && a->k <= 8192, MXB_ERR_INVALID, "topk must be between 1 and 8192");
+  MXB_REQUIRE(a->scores && a->out_ids, MXB_ERR_INVALID, "topk: null tensor");
+  MXB_REQUIRE((int64_t)a->rows * a->n <= kStaticCandEntries, MXB_ERR_INVALID,
+              "topk (static scratch): rows * n = %lld exceeds the built-in scratch of %lld entries; "
+              "use mxb_topk_select with a workspace",
+              (long long)((int64_t)a->rows * a->n), (long long)kStaticCandEntries);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  uint32_t* scratch = nullptr;
+  int rc = static_cand_address(&scratch);
+  if (rc != MXB_OK) return rc;
+  TopkParams p{};
+  p.scores = a->scores; p.row_stride = a->row_stride; p.row_start = a->row_start; p.row_count = a->row_count;
+  p.out_ids = a->out_ids; p.rows = a->rows; p.n = a->n; p.k = a->k;
+  p.cand_key = scratch;
+  p.cand_idx = reinterpret_cast<int32_t*>(scratch + kStaticCandEntries);
   int sort_n = 2;
   while (sort_n < a->k) sort_n <<= 1;
   const size_t smem = (size_t)sort_n * 4 + (size_t)kCandSmem * 8;

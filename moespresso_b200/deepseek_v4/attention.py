@@ -98,3 +98,32 @@ def causal_indexer_topk(raw_scores, head_weights, query_positions, pool_indices,
         return torch.empty((raw.shape[0], 0), dtype=torch.int64, device=raw.device)
     ids = topk_select(scores, width, order="score").long()
     return torch.where(ids >= 0, pool[ids.clamp(min=0)], torch.full_like(ids, -1))
+
+
+def topk_select_static(scores, k: int, out, *, valid=None, row_start=None, n=None):
+    """``topk_select`` for callers that cannot allocate device memory at call time (a
+    server with a frozen memory pool, code running inside an allocator callback): the
+    caller passes the int32 output ``[rows, k]`` and the kernel's candidate scratch is the
+    8 MiB array built into the library, so ``rows * n`` is limited to 2**20.  Ids come back
+    ascending, ``-1`` padded, exactly as from ``topk_select``.  Calls share the scratch:
+    keep them on one stream.  The first call on a device resolves the scratch address and
+    should happen outside stream capture."""
+    dev = require_cuda(scores, out)
+    if scores.dtype != torch.float32 or not scores.is_contiguous():
+        raise ValueError("scores must be contiguous float32")
+    if out.dtype != torch.int32 or not out.is_contiguous():
+        raise ValueError("out must be contiguous int32")
+    lib = _abi.load()
+    if row_start is None:
+        n_ = int(scores.shape[-1])
+        rows = scores.numel() // n_
+        row_stride = n_
+    else:
+        rows, n_, row_stride = int(row_start.numel()), int(n), 0
+    if out.numel() != rows * int(k):
+        raise ValueError("out must have rows * k elements")
+    a = _abi.TopkArgs()
+    a.scores = ptr(scores); a.row_stride = row_stride; a.row_start = ptr(row_start); a.row_count = ptr(valid)
+    a.out_ids = ptr(out); a.rows = rows; a.n = n_; a.k = int(k)
+    _abi.check(_t.launch("topk_select_static", lib.mxb_topk_select_static, a))
+    return out
