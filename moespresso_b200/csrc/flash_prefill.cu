@@ -1,10 +1,11 @@
 // Causal GQA flash prefill, head_dim 256, 16-bit operands, fp32 accumulation, with the
 // sigmoid-gate epilogue fused:  out = softmax(scale * Q K^T + causal) V * sigmoid(gate).
 //
-// One CTA = 128 query rows of one query head.  Six warps:
+// One CTA = 128 query rows of one query head.  Seven warps:
 //   warps 0-3  softmax + epilogue; thread r owns query row r = TMEM lane r
-//   warp  4    issues tcgen05.mma (one lane)
+//   warp  4    issues the S = Q K^T MMAs (one lane)
 //   warp  5    TMA producer (one lane)
+//   warp  6    issues the O += P V MMAs (one lane)
 // Per 64-key tile:  S = Q K^T (M128 x N64 x K256) into one of two TMEM buffers;
 // the softmax warps read S from TMEM, keep a running maximum with lazy rescaling of
 // the TMEM-resident O (only when the maximum grew by more than 2^8), write P as a
@@ -72,7 +73,7 @@ __device__ __forceinline__ float2 unpack2(uint32_t u) {
 }
 
 template <bool BF16>
-__global__ void __launch_bounds__(192, 1) flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
+__global__ void __launch_bounds__(224, 1) flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
                                                                const __grid_constant__ CUtensorMap tm_k,
                                                                const __grid_constant__ CUtensorMap tm_vt,
                                                                FlashParams p) {
@@ -92,7 +93,8 @@ __global__ void __launch_bounds__(192, 1) flash_prefill_kernel(const __grid_cons
   uint64_t* s_ready = bars + 9;  // [2]
   uint64_t* p_ready = bars + 11;
   uint64_t* pv_done = bars + 12;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* s_free = bars + 13;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -116,6 +118,8 @@ __global__ void __launch_bounds__(192, 1) flash_prefill_kernel(const __grid_cons
     }
     ptx::mbar_init(p_ready, 128);
     ptx::mbar_init(pv_done, 1);
+    ptx::mbar_init(&s_free[0], 128);
+    ptx::mbar_init(&s_free[1], 128);
     *abort_flag = 0;
     ptx::mbar_fence_init();
   }
@@ -153,44 +157,48 @@ __global__ void __launch_bounds__(192, 1) flash_prefill_kernel(const __grid_cons
       }
     }
   } else if (warp == 4) {
-    // ------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------ S = Q K^T issuer
+    // Issuing one tcgen05.mma costs a thread ~80 cycles; S (16 MMAs per tile) and P V (4 MMAs) write
+    // different TMEM columns, so they are issued by two threads in two warps and neither waits for the other.
     if (lane == 0) {
       constexpr uint32_t fmt = BF16 ? ptx::kFmtBF16 : ptx::kFmtF16;
       const uint32_t idesc_s = ptx::idesc_f16(fmt, fmt, FB_M, FB_N, 0, 0);
-      const uint32_t idesc_o = ptx::idesc_f16(fmt, fmt, FB_M, FB_D, 0, 0);
-      const uint32_t q_addr = ptx::smem_u32(q_s), k_addr = ptx::smem_u32(k_s), v_addr = ptx::smem_u32(v_s),
-                     p_addr = ptx::smem_u32(p_s);
-      const uint64_t q_desc = ptx::smem_desc_sw128(q_addr, 16, 1024), k_desc = ptx::smem_desc_sw128(k_addr, 16, 1024),
-                     v_desc = ptx::smem_desc_sw128(v_addr, 16, 1024), p_desc = ptx::smem_desc_sw128(p_addr, 16, 1024);
-      auto issue_s = [&](int j) {
+      const uint64_t q_desc = ptx::smem_desc_sw128(ptx::smem_u32(q_s), 16, 1024);
+      const uint64_t k_desc = ptx::smem_desc_sw128(ptx::smem_u32(k_s), 16, 1024);
+      ptx::mbar_wait(q_full, 0, abort_flag);
+      for (int j = 0; j < ntiles; ++j) {
         const int s = j & 1;
         ptx::mbar_wait(&k_full[s], (uint32_t)((j >> 1) & 1), abort_flag);
+        if (j >= 2) ptx::mbar_wait(&s_free[s], (uint32_t)(((j >> 1) - 1) & 1), abort_flag);  // softmax read S(j-2)
         ptx::tc_fence_after_sync();
         const uint32_t d = tmem_base + (uint32_t)(s * FB_N);
         const uint64_t kd = ptx::desc_advance(k_desc, s * 32768);
 #pragma unroll
         for (int kb = 0; kb < 4; ++kb)
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
+          for (int ks = 0; ks < 4; ++ks)
             ptx::mma_f16_ss(d, ptx::desc_advance(q_desc, kb * 16384 + ks * 32),
                             ptx::desc_advance(kd, kb * 8192 + ks * 32), idesc_s, (kb | ks) ? 1u : 0u);
-          }
         ptx::mma_commit(&s_ready[s]);
         ptx::mma_commit(&k_empty[s]);
-      };
-      ptx::mbar_wait(q_full, 0, abort_flag);
-      issue_s(0);
+      }
+    }
+  } else if (warp == 6) {
+    // ------------------------------------------------------------ O += P V issuer
+    if (lane == 0) {
+      constexpr uint32_t fmt = BF16 ? ptx::kFmtBF16 : ptx::kFmtF16;
+      const uint32_t idesc_o = ptx::idesc_f16(fmt, fmt, FB_M, FB_D, 0, 0);
+      const uint64_t v_desc = ptx::smem_desc_sw128(ptx::smem_u32(v_s), 16, 1024);
+      const uint64_t p_desc = ptx::smem_desc_sw128(ptx::smem_u32(p_s), 16, 1024);
       for (int j = 0; j < ntiles; ++j) {
-        if (j + 1 < ntiles) issue_s(j + 1);
         const int s = j & 1;
         ptx::mbar_wait(p_ready, (uint32_t)(j & 1), abort_flag);
         ptx::mbar_wait(&v_full[s], (uint32_t)((j >> 1) & 1), abort_flag);
         ptx::tc_fence_after_sync();
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
+        for (int ks = 0; ks < 4; ++ks)
           ptx::mma_f16_ss(tmem_o, ptx::desc_advance(p_desc, ks * 32), ptx::desc_advance(v_desc, s * 32768 + ks * 32),
                           idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
-        }
         ptx::mma_commit(pv_done);
         ptx::mma_commit(&v_empty[s]);
       }
@@ -209,6 +217,8 @@ __global__ void __launch_bounds__(192, 1) flash_prefill_kernel(const __grid_cons
       ptx::tmem_ld32(tmem_base + lane_off + (uint32_t)(s * FB_N), sv);
       ptx::tmem_ld32(tmem_base + lane_off + (uint32_t)(s * FB_N + 32), sv + 32);
       ptx::tmem_ld_wait();
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(&s_free[s]);
       const int key0 = j * FB_N;
       const bool need_mask = key0 + FB_N - 1 > m0 + past;  // tile reaches past the first row's diagonal
       float tmax = -INFINITY;
@@ -396,10 +406,10 @@ extern "C" int mxb_flash_prefill(const mxb_flash_prefill_args* a, void* stream) 
   dim3 grid((unsigned)ceil_div(a->S, FB_M), (unsigned)a->Hq);
   if (a->dtype == MXB_BF16) {
     MXB_CUDA_OK(cudaFuncSetAttribute(flash_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    flash_prefill_kernel<true><<<grid, 192, smem, st>>>(tq, tk, tv, p);
+    flash_prefill_kernel<true><<<grid, 224, smem, st>>>(tq, tk, tv, p);
   } else {
     MXB_CUDA_OK(cudaFuncSetAttribute(flash_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    flash_prefill_kernel<false><<<grid, 192, smem, st>>>(tq, tk, tv, p);
+    flash_prefill_kernel<false><<<grid, 224, smem, st>>>(tq, tk, tv, p);
   }
   MXB_CUDA_OK(cudaGetLastError());
   return MXB_OK;

@@ -27,6 +27,12 @@
 
 namespace mxb {
 
+#ifdef MXB_TRACE_SP
+#define TRS(k, i) do { if (tr_on && (i) < 16) tr[(k) * 16 + (i)] = clock64(); } while (0)
+#else
+#define TRS(k, i)
+#endif
+
 constexpr int TC_ROWS = 128;
 constexpr int TC_HEADS = 64;
 constexpr float kRescaleGap = 8.f;  // log2 units
@@ -154,6 +160,11 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
     n_raw = last >= first ? (int)(last - first + 1) : 0;
   }
   const int32_t* ids = p.topk + (int64_t)bt * p.k;
+#ifdef MXB_TRACE_SP
+  long long* tr = reinterpret_cast<long long*>(p.status);
+  const bool tr_on = p.status && blockIdx.x == 0 && blockIdx.z == 0 && tid == 0;
+  TRS(7, 0);
+#endif
 
   if (tid == 0) {
     ptx::mbar_init(&mi->bar_s, 1);
@@ -256,6 +267,7 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
 
   for (int it = 0; it < ntiles; ++it) {
     const int e0 = e_lo + it * TC_ROWS;
+    TRS(0, it);
     // ---------------------------------------------------------------- gather 128 rows
     // phase 0: lanes 0-15 of each warp resolve the source of the warp's 16 rows
     if (lane < 16) {
@@ -322,6 +334,7 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
     __syncthreads();
 
     // ---------------------------------------------------------------- S^T = Ktile . Q^T
+    TRS(1, it);
     if (tid == 0) {
       ptx::tc_fence_after_sync();
       for (int kb = 0; kb < nslab; ++kb) {
@@ -332,11 +345,13 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
         }
       }
       ptx::mma_commit(&mi->bar_s);
+      TRS(2, it);
     }
     ptx::mbar_wait(&mi->bar_s, (uint32_t)(it & 1), abort_flag);
     ptx::tc_fence_after_sync();
 
     // ---------------------------------------------------------------- softmax, thread = row
+    TRS(3, it);
     const int row = quad * 32 + lane;
     const int col0 = half_id * 32;
     uint32_t sv[32];
@@ -411,6 +426,7 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
     __syncthreads();
 
     // ---------------------------------------------------------------- O^T += Vtile^T . P^T
+    TRS(4, it);
     if (tid == 0) {
       ptx::tc_fence_after_sync();
       for (int mt = 0; mt < n_mt; ++mt) {
@@ -423,10 +439,12 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
         }
       }
       ptx::mma_commit(&mi->bar_o);
+      TRS(5, it);
     }
     have_o = true;
     ptx::mbar_wait(&mi->bar_o, (uint32_t)(it & 1), abort_flag);  // the single row tile is rewritten next
     ptx::tc_fence_after_sync();
+    TRS(6, it);
   }
 
   // ------------------------------------------------------------------ reduce l over the 128 rows
@@ -499,10 +517,13 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
   ptx::tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) ptx::tmem_dealloc(tmem_base, 512);
+  TRS(7, 1);
+#ifndef MXB_TRACE_SP
   if (tid == 0 && *abort_flag) {
     // a wait gave up: leave a visibly wrong marker for the caller
     if (p.status) atomicExch(p.status, 2);
   }
+#endif
 }
 
 bool sparse_tc_eligible(int kv_dtype, int q_dtype, int H, int Dqk, int Dv) {
