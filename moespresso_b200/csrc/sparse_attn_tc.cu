@@ -168,7 +168,7 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
 
   if (tid == 0) {
     ptx::mbar_init(&mi->bar_s, 1);
-    ptx::mbar_init(&mi->bar_o, 1);
+    ptx::mbar_init(&mi->bar_o, (uint32_t)(p.Dv / 128));
     mi->abort_flag = 0;
     mi->keff = p.k;
     ptx::mbar_fence_init();
@@ -295,6 +295,31 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
       mi->valid[rr] = src != nullptr;
       mi->row_scale[rr] = rs;
       mi->inv_scale[rr] = 1.f / rs;
+    }
+    else if (it + 1 < ntiles) {
+      // lanes 16-31: pull the NEXT tile's rows (and scales) into L2 while this tile is processed
+      const int e = e0 + TC_ROWS + warp * 16 + (lane - 16);
+      if (e < e_hi) {
+        const uint8_t* src = nullptr;
+        if (e < n_raw) {
+          const int64_t phys = ((int64_t)p.raw_start + (first + e - first_raw_pos)) % p.raw_cap;
+          const int64_t ridx = (int64_t)b * p.raw_cap + phys;
+          src = reinterpret_cast<const uint8_t*>(p.raw_kv) + ridx * p.Dqk * EB;
+          if (KVT == MXB_I8) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.raw_scales + ridx));
+        } else {
+          const int32_t id = ids[e - n_raw];
+          if (id >= 0) {
+            const int64_t ridx = cbase + id;
+            src = reinterpret_cast<const uint8_t*>(p.comp_kv) + ridx * p.Dqk * EB;
+            if (KVT == MXB_I8) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.comp_scales + ridx));
+          }
+        }
+        if (src) {
+          const int row_bytes = p.Dqk * EB;
+          for (int off = 0; off < row_bytes; off += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(src + off));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(src + row_bytes - 1));
+        }
+      }
     }
     __syncwarp();
     // phase 1: up to 18 independent 16-byte loads per lane in flight, then widen / store
@@ -427,16 +452,16 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
 
     // ---------------------------------------------------------------- O^T += Vtile^T . P^T
     TRS(4, it);
-    if (tid == 0) {
+    if (lane == 0 && warp < n_mt) {
+      // one issuing thread per 128-feature block of O^T (separate TMEM columns, so no ordering between them)
+      const int mt = warp;
       ptx::tc_fence_after_sync();
-      for (int mt = 0; mt < n_mt; ++mt) {
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          // A, MN-major: 64-feature blocks 16 KB apart (LBO), 8-row groups 1 KB apart (SBO); 16 rows per K step
-          ptx::mma_f16_ss(tmem_o + (uint32_t)(mt * 64), ptx::desc_advance(tile_desc_mn, (2 * mt) * 16384 + ks * 2048),
-                          ptx::desc_advance(pt_desc, (ks >> 2) * 8192 + (ks & 3) * 32), idesc_o,
-                          (have_o || ks > 0) ? 1u : 0u);
-        }
+      for (int ks = 0; ks < 8; ++ks) {
+        // A, MN-major: 64-feature blocks 16 KB apart (LBO), 8-row groups 1 KB apart (SBO); 16 rows per K step
+        ptx::mma_f16_ss(tmem_o + (uint32_t)(mt * 64), ptx::desc_advance(tile_desc_mn, (2 * mt) * 16384 + ks * 2048),
+                        ptx::desc_advance(pt_desc, (ks >> 2) * 8192 + (ks & 3) * 32), idesc_o,
+                        (have_o || ks > 0) ? 1u : 0u);
       }
       ptx::mma_commit(&mi->bar_o);
       TRS(5, it);

@@ -16,81 +16,9 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "topk_common.cuh"
 
 namespace mxb {
-
-constexpr int kSmemRowMax = 45056;  // 176 KB of keys
-constexpr int kBigBins = 2048;      // top 11 bits
-
-__device__ __forceinline__ uint32_t score_key_full(float x) {
-  if (!(fabsf(x) <= 3.402823466e38f)) return 0u;  // NaN and +-inf are never selected
-  uint32_t b = __float_as_uint(x + 0.0f);         // -0 + 0 = +0
-  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
-}
-
-// Find, scanning digits from 255 down, the digit where the running count reaches `want`.
-// hist[256] in shared memory; executed by warp 0; results through shared scalars.
-__device__ __forceinline__ void pick_digit_256(const uint32_t* hist, uint32_t want, uint32_t* out_digit,
-                                               uint32_t* out_above) {
-  const int lane = threadIdx.x & 31;
-  // lane l owns digits [255 - 8l - 7, 255 - 8l], highest first
-  uint32_t loc[8];
-  uint32_t s = 0;
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    loc[j] = hist[255 - (lane * 8 + j)];
-    s += loc[j];
-  }
-  uint32_t incl = s;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= o) incl += t;
-  }
-  const uint32_t excl = incl - s;
-  const bool mine = excl < want && incl >= want;
-  if (mine) {
-    uint32_t run = excl;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if (run + loc[j] >= want) {
-        *out_digit = 255 - (lane * 8 + j);
-        *out_above = run;
-        break;
-      }
-      run += loc[j];
-    }
-  }
-}
-
-// block-wide exclusive scan of one uint per thread (1024 threads max); returns exclusive prefix,
-// total through *total.
-__device__ __forceinline__ uint32_t block_excl_scan(uint32_t v, uint32_t* warp_sums, uint32_t* total) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  uint32_t incl = v;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= o) incl += t;
-  }
-  if (lane == 31) warp_sums[warp] = incl;
-  __syncthreads();
-  if (warp == 0) {
-    uint32_t w = (lane < (int)(blockDim.x >> 5)) ? warp_sums[lane] : 0;
-    uint32_t wi = w;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      uint32_t t = __shfl_up_sync(0xffffffffu, wi, o);
-      if (lane >= o) wi += t;
-    }
-    warp_sums[lane] = wi - w;
-    if (lane == 31) *total = wi;
-  }
-  __syncthreads();
-  uint32_t r = warp_sums[warp] + incl - v;
-  __syncthreads();
-  return r;
-}
 
 struct TopkParams {
   const float* scores;
@@ -188,6 +116,13 @@ __global__ void __launch_bounds__(1024) topk_row_kernel(TopkParams p) {
 // then the remaining 21 bits, the ties by lowest id and a bitonic sort of the ids.
 // --------------------------------------------------------------------------
 constexpr int kCandSmem = 16384;
+constexpr int kStreamUnroll = 16;   // independent loads in flight per thread in the streaming passes
+
+#ifdef MXB_TRACE_TK
+#define TRK(k) do { if (threadIdx.x == 0 && blockIdx.x == MXB_TRACE_TK) reinterpret_cast<long long*>(p.cand_key)[k] = clock64(); } while (0)
+#else
+#define TRK(k)
+#endif
 
 __global__ void __launch_bounds__(1024) topk_stream_kernel(TopkParams p, int sort_n) {
   extern __shared__ uint32_t dyn[];
@@ -208,18 +143,21 @@ __global__ void __launch_bounds__(1024) topk_stream_kernel(TopkParams p, int sor
   for (int i = tid; i < kBigBins; i += 1024) hist[i] = 0;
   if (tid == 0) { s_na = 0; s_nc = 0; s_keff = 0; s_bin = 0; s_above = 0; s_cnt_bin = 0; }
   __syncthreads();
+  TRK(0);
   // ---- pass 1
-  for (int64_t i = tid; i < n; i += 4096) {
-    float x[4];
+  for (int64_t i0 = 0; i0 < n; i0 += 1024 * kStreamUnroll) {   // trip count uniform over the CTA (warp-wide votes inside)
+    const int64_t i = i0 + tid;
+    float x[kStreamUnroll];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) x[u] = (i + 1024 * u < n) ? __ldg(src + i + 1024 * u) : -INFINITY;
+    for (int u = 0; u < kStreamUnroll; ++u) x[u] = (i + 1024 * u < n) ? __ldg(src + i + 1024 * u) : -INFINITY;
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < kStreamUnroll; ++u) {
       const uint32_t key = score_key_full(x[u]);
       if (key) atomicAdd(&hist[key >> 21], 1u);
     }
   }
   __syncthreads();
+  TRK(1);
   // ---- threshold bin: thread t owns bins 2047-2t and 2046-2t (descending)
   {
     const uint32_t h0 = hist[2047 - 2 * tid], h1 = hist[2046 - 2 * tid];
@@ -241,20 +179,31 @@ __global__ void __launch_bounds__(1024) topk_stream_kernel(TopkParams p, int sor
   int32_t* ci = in_smem ? ci_s : p.cand_idx + (int64_t)row * p.n;
   for (int i = tid; i < sort_n; i += 1024) sel[i] = 0x7FFFFFFF;
   __syncthreads();
+  TRK(2);
   // ---- pass 2
-  for (int64_t i = tid; i < n; i += 4096) {
-    float x[4];
+  for (int64_t i0 = 0; i0 < n; i0 += 1024 * kStreamUnroll) {   // trip count uniform over the CTA (warp-wide votes inside)
+    const int64_t i = i0 + tid;
+    float x[kStreamUnroll];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) x[u] = (i + 1024 * u < n) ? __ldg(src + i + 1024 * u) : -INFINITY;
+    for (int u = 0; u < kStreamUnroll; ++u) x[u] = (i + 1024 * u < n) ? __ldg(src + i + 1024 * u) : -INFINITY;
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < kStreamUnroll; ++u) {
       const uint32_t key = score_key_full(x[u]);
-      if (!key) continue;
       const uint32_t kb = key >> 21;
-      if (kb > bin) {
-        sel[atomicAdd(&s_na, 1u)] = (int32_t)(i + 1024 * u);
-      } else if (kb == bin) {
-        const uint32_t pos = atomicAdd(&s_nc, 1u);
+      const bool above = key && kb > bin, cand = key && kb == bin;
+      const uint32_t lane_lt = (1u << (tid & 31)) - 1u;
+      const uint32_t m_above = __ballot_sync(0xffffffffu, above), m_cand = __ballot_sync(0xffffffffu, cand);
+      uint32_t base_a = 0, base_c = 0;
+      if ((tid & 31) == 0) {   // one counter update per warp
+        if (m_above) base_a = atomicAdd(&s_na, (uint32_t)__popc(m_above));
+        if (m_cand) base_c = atomicAdd(&s_nc, (uint32_t)__popc(m_cand));
+      }
+      base_a = __shfl_sync(0xffffffffu, base_a, 0);
+      base_c = __shfl_sync(0xffffffffu, base_c, 0);
+      if (above) {
+        sel[base_a + __popc(m_above & lane_lt)] = (int32_t)(i + 1024 * u);
+      } else if (cand) {
+        const uint32_t pos = base_c + __popc(m_cand & lane_lt);
         ck[pos] = key;
         ci[pos] = (int32_t)(i + 1024 * u);
       }
@@ -262,6 +211,7 @@ __global__ void __launch_bounds__(1024) topk_stream_kernel(TopkParams p, int sor
   }
   __syncthreads();
 
+  TRK(3);
   // ---- the `want` largest among the C candidates on the low 21 bits (8 + 8 + 5)
   uint32_t want = k_eff - n_above;
   uint32_t prefix = bin << 21, prefix_mask = 0xFFE00000u;
@@ -284,6 +234,7 @@ __global__ void __launch_bounds__(1024) topk_stream_kernel(TopkParams p, int sor
   }
   const uint32_t thr = prefix;
   const uint32_t need = want;  // ties to take (lowest ids), >= 1
+  TRK(4);
   // ---- ties: the need-th smallest id among candidates with key == thr (ids are unique)
   if (tid == 0) s_total = 0;
   __syncthreads();
@@ -322,6 +273,7 @@ __global__ void __launch_bounds__(1024) topk_stream_kernel(TopkParams p, int sor
     if (key > thr || (key == thr && (uint32_t)id <= idx_thr)) sel[atomicAdd(&s_na, 1u)] = id;
   }
   __syncthreads();
+  TRK(5);
   // ---- bitonic sort ascending (padding = INT_MAX)
   for (int size = 2; size <= sort_n; size <<= 1) {
     for (int stride = size >> 1; stride > 0; stride >>= 1) {
@@ -335,16 +287,13 @@ __global__ void __launch_bounds__(1024) topk_stream_kernel(TopkParams p, int sor
       __syncthreads();
     }
   }
+  TRK(6);
   for (uint32_t i = tid; i < k_eff; i += 1024) out[i] = sel[i];
+  TRK(7);
 }
 
-static void big_layout(int32_t rows, int64_t n, size_t* ck_off, size_t* ci_off, size_t* total) {
-  size_t o = 0;
-  *ck_off = o;   o += (size_t)rows * (size_t)n * 4;
-  o = (size_t)round_up((int64_t)o, 256);
-  *ci_off = o;   o += (size_t)rows * (size_t)n * 4;
-  *total = (size_t)round_up((int64_t)o, 256);
-}
+int64_t topk_multi_workspace(int32_t rows, int64_t n, int32_t k);   // topk_multi.cu
+int launch_topk_multi(const mxb_topk_args* a, cudaStream_t st);
 
 }  // namespace mxb
 
@@ -353,9 +302,7 @@ using namespace mxb;
 extern "C" int64_t mxb_topk_workspace_bytes(int32_t rows, int64_t n, int32_t k) {
   if (rows <= 0 || n <= 0 || k <= 0) return 0;
   if (n <= kSmemRowMax) return 0;
-  size_t a, b, total;
-  big_layout(rows, n, &a, &b, &total);
-  return (int64_t)total;
+  return topk_multi_workspace(rows, n, k);
 }
 
 extern "C" int mxb_topk_select(const mxb_topk_args* a, void* stream) {
@@ -379,20 +326,7 @@ extern "C" int mxb_topk_select(const mxb_topk_args* a, void* stream) {
     return MXB_OK;
   }
 
-  size_t cko, cio, total;
-  big_layout(a->rows, a->n, &cko, &cio, &total);
-  MXB_REQUIRE(a->workspace != nullptr && a->workspace_bytes >= (int64_t)total, MXB_ERR_WORKSPACE,
-              "topk: workspace of %lld bytes required", (long long)total);
-  char* ws = reinterpret_cast<char*>(a->workspace);
-  p.cand_key = reinterpret_cast<uint32_t*>(ws + cko);
-  p.cand_idx = reinterpret_cast<int32_t*>(ws + cio);
-  int sort_n = 2;
-  while (sort_n < a->k) sort_n <<= 1;
-  const size_t smem = (size_t)sort_n * 4 + (size_t)kCandSmem * 8;
-  MXB_CUDA_OK(cudaFuncSetAttribute(topk_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  topk_stream_kernel<<<a->rows, 1024, smem, st>>>(p, sort_n);
-  MXB_CUDA_OK(cudaGetLastError());
-  return MXB_OK;
+  return launch_topk_multi(a, st);
 }
 
 // --------------------------------------------------------------------------
