@@ -283,7 +283,7 @@ def main():
         "gpu_launches": 6 * K,
         "launch": "one CUDA graph per step (6 kernels + 1 memset)" if not args.no_graph else "eager",
         "entry_point_ms": stage_ms,
-        "roofline": {"bound": "hbm", "kernel": "indexer_tc_kernel<64, fp8>", "achieved": achieved, "peak": hbm,
+        "roofline": {"bound": "hbm", "kernel": "indexer_decode_kernel<64, 16 heads>", "achieved": achieved, "peak": hbm,
                      "unit": "GB/s", "frac": achieved / hbm, "peak_source": which, "traffic": None,
                      "frac_of_nominal_8TBs": achieved / 8000.0,
                      "whole_step_GBs": step_bytes / (ms_step * 1e-3) / 1e9},
@@ -346,6 +346,33 @@ def run_extras(torch, dev, tf_peak) -> dict:
         ex["c2_frac_of_bf16_peak"] = ex["c2_qwen_prefill_tflops_causal"] / tf_peak
     except Exception as e:
         ex["c2_error"] = repr(e)
+    try:
+        # config 4: 4096-token chunk over 32768 ratio-4 compressed rows, top-k 2048 per token, bf16.
+        # Inputs are generated on the device (same shapes and N(0,1) distributions as synth.config4).
+        from moespresso_b200 import _torchabi
+        from moespresso_b200.deepseek_v4.prefill_step import sparse_prefill_step
+        T, R, H, Dqk, Dv, Hi, Di, kk = 4096, 32768, 64, 576, 512, 16, 64, 2048
+        g = torch.Generator(device=dev).manual_seed(2)
+        rn = lambda *sh: torch.randn(*sh, generator=g, device=dev, dtype=torch.float32)
+        kv, q = rn(R, Dqk).to(torch.bfloat16), rn(T, H, Dqk).to(torch.bfloat16)
+        iq, ik, iw = rn(T, Hi, Di).to(torch.bfloat16), rn(R, Di).to(torch.bfloat16), rn(T, Hi) / 4
+        run = lambda: sparse_prefill_step(q, kv, iq, ik, iw, pos0=131072 - T, ratio=4, k=kk, scale=Dqk ** -0.5,
+                                          d_v=Dv, window=0)
+        run(); torch.cuda.synchronize()
+        _torchabi.TIMER = {}
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); run(); b.record(); torch.cuda.synchronize()
+        timer, _torchabi.TIMER = _torchabi.TIMER, None
+        tot = {name: sum(x.elapsed_time(y) for x, y in evs) for name, evs in timer.items()}
+        ex["c4_chunk_ms"] = a.elapsed_time(b)
+        ex["c4_entry_point_ms"] = tot
+        if tot.get("indexer_scores"):
+            ex["c4_indexer_tflops"] = 2.0 * T * Hi * Di * R / (tot["indexer_scores"] * 1e-3) / 1e12
+        if tot.get("sparse_attn"):
+            ex["c4_sparse_attn_tflops"] = 2.0 * T * H * kk * (Dqk + Dv) / (tot["sparse_attn"] * 1e-3) / 1e12
+            ex["c4_gathered_GBs"] = T * kk * Dqk * 2 / (tot["sparse_attn"] * 1e-3) / 1e9
+    except Exception as e:
+        ex["c4_error"] = repr(e)
     return ex
 
 

@@ -1,15 +1,12 @@
 // Indexer score:  scores[b,t,r] = sum_h w[b,t,h] * relu(q[b,h,t,:] . key[b][r,:])
 //
 // Two kernels.
-//  * indexer_tc_kernel   — 16-bit or FP8-E4M3 keys.  Key rows sit on the MMA M axis
-//    (128 rows per tile, streamed by TMA), the (token, head) pairs of one token tile
-//    on N, D = 64/128 on K.  tcgen05.mma accumulates in TMEM; the drain applies
-//    relu, the head weights and the head sum in a fixed order, so a row's score
-//    does not depend on how rows are partitioned over CTAs or GPUs.  FP8 keys are
-//    widened to the 16-bit operand type in shared memory (every E4M3 value is exact
-//    in bf16 and fp16), so products are exact and only fp32 accumulation rounds.
-//    The kernel is HBM-bound for decode (one pass over the key table) and
-//    tensor/drain-bound for prefill.
+//  * indexer_tc_kernel   — 16-bit keys (bf16 / fp16, same type as q).  Key rows sit on the MMA
+//    M axis (128 rows per tile, streamed by TMA), the (token, head) pairs of one token tile on N,
+//    D = 64/128 on K.  tcgen05.mma accumulates in TMEM; the drain applies relu, the head weights
+//    and the head sum in a fixed order, so a row's score does not depend on how rows are
+//    partitioned over CTAs or GPUs.  FP8 key tables are handled by indexer_decode.cu (one token)
+//    and indexer_scores_fp8.cu (token tiles).
 //  * indexer_exact_kernel — fp32 FMA on CUDA cores in a fixed order, for fp32
 //    operands (1e-5 agreement with a float64 evaluation) and as the explicit
 //    MXB_INDEXER_EXACT_FP32 mode for any operand type.
@@ -106,48 +103,23 @@ __global__ void __launch_bounds__(128) indexer_exact_kernel(IndexerParams p) {
 // --------------------------------------------------------------------------
 constexpr int kStages = 4;
 
-template <int D, bool FP8>
+template <int D>
 struct TcSmem {
-  static constexpr int kRawBytes = FP8 ? 128 * D : 0;       // one raw FP8 tile
   static constexpr int kABytes = 128 * D * 2;               // one 16-bit operand tile
-  static constexpr int kNumA = FP8 ? 2 : kStages;
   static constexpr int a_off = 0;
-  static constexpr int raw_off = a_off + kNumA * kABytes;
-  static constexpr int b_off = raw_off + kStages * kRawBytes;  // q tile, up to 256 x D x 2
+  static constexpr int b_off = a_off + kStages * kABytes;   // q tile, up to 256 x D x 2
   static constexpr int w_off = b_off + 256 * D * 2;
   static constexpr int bar_off = w_off + 256 * 4;
   static constexpr int total = bar_off + 128;
 };
 
-// Widen 16 FP8 bytes to 16 values of the 16-bit operand type (two 16-byte chunks).
-template <bool BF16>
-__device__ __forceinline__ void widen_fp8x16(const uint4& in, uint4& lo, uint4& hi) {
-  const uint16_t* pr = reinterpret_cast<const uint16_t*>(&in);
-  uint32_t o[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)pr[i], __NV_E4M3);
-    __half2 h2 = *reinterpret_cast<__half2*>(&hr);
-    if constexpr (BF16) {
-      float2 f = __half22float2(h2);
-      __nv_bfloat162 b2 = __float22bfloat162_rn(f);
-      o[i] = *reinterpret_cast<uint32_t*>(&b2);
-    } else {
-      o[i] = *reinterpret_cast<uint32_t*>(&h2);
-    }
-  }
-  lo = make_uint4(o[0], o[1], o[2], o[3]);
-  hi = make_uint4(o[4], o[5], o[6], o[7]);
-}
-
-template <int D, bool FP8>
+template <int D>
 __global__ void __launch_bounds__(128, 1) indexer_tc_kernel(const __grid_constant__ CUtensorMap tmap,
                                                             IndexerParams p, int q_is_bf16) {
-  using L = TcSmem<D, FP8>;
+  using L = TcSmem<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* a_buf = smem + L::a_off;
-  uint8_t* raw_buf = smem + L::raw_off;
   uint8_t* b_buf = smem + L::b_off;
   float* w_s = reinterpret_cast<float*>(smem + L::w_off);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::bar_off);  // [kStages]
@@ -209,18 +181,14 @@ __global__ void __launch_bounds__(128, 1) indexer_tc_kernel(const __grid_constan
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  constexpr uint32_t kTileTx = FP8 ? 128 * D : 128 * D * 2;
+  constexpr uint32_t kTileTx = 128 * D * 2;
   auto issue_load = [&](int tile) {
     const int s = tile % kStages;
     ptx::mbar_expect_tx(&full_bar[s], kTileTx);
     const int32_t y = (int32_t)(rbase + row0 + (int64_t)tile * 128);
-    if constexpr (FP8) {
-      ptx::tma_load_2d(raw_buf + (size_t)s * L::kRawBytes, &tmap, &full_bar[s], 0, y);
-    } else {
 #pragma unroll
-      for (int kb = 0; kb < D / 64; ++kb)
-        ptx::tma_load_2d(a_buf + (size_t)s * L::kABytes + (size_t)kb * 16384, &tmap, &full_bar[s], kb * 64, y);
-    }
+    for (int kb = 0; kb < D / 64; ++kb)
+      ptx::tma_load_2d(a_buf + (size_t)s * L::kABytes + (size_t)kb * 16384, &tmap, &full_bar[s], kb * 64, y);
   };
 
   int issued = 0;
@@ -236,12 +204,10 @@ __global__ void __launch_bounds__(128, 1) indexer_tc_kernel(const __grid_constan
     const int acc = tile & 1;
     ptx::mbar_wait(&mma_bar[acc], (uint32_t)((tile >> 1) & 1), abort_flag);
     ptx::tc_fence_after_sync();
-    if constexpr (!FP8) {
-      // the operand stage of `tile` is free again: refill it
-      if (tid == 0 && issued < ntiles && (issued % kStages) == (tile % kStages)) {
-        issue_load(issued);
-        ++issued;
-      }
+    // the operand stage of `tile` is free again: refill it
+    if (tid == 0 && issued < ntiles && (issued % kStages) == (tile % kStages)) {
+      issue_load(issued);
+      ++issued;
     }
     const int64_t r = row0 + (int64_t)tile * 128 + tid;
     const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * p.acc_stride);
@@ -267,27 +233,7 @@ __global__ void __launch_bounds__(128, 1) indexer_tc_kernel(const __grid_constan
   for (int i = 0; i < ntiles; ++i) {
     const int s = i % kStages;
     ptx::mbar_wait(&full_bar[s], (uint32_t)((i / kStages) & 1), abort_flag);
-    uint8_t* a_tile;
-    if constexpr (FP8) {
-      a_tile = a_buf + (size_t)(i & 1) * L::kABytes;
-      const uint8_t* raw = raw_buf + (size_t)s * L::kRawBytes;
-      constexpr int CPR = D / 16;  // 16-byte FP8 chunks per row
-      for (int ci = tid; ci < 128 * CPR; ci += 128) {
-        const int row = ci / CPR, cc = ci % CPR;
-        uint4 in = *reinterpret_cast<const uint4*>(raw + (size_t)row * D + cc * 16);
-        uint4 lo, hi;
-        if (q_is_bf16) widen_fp8x16<true>(in, lo, hi); else widen_fp8x16<false>(in, lo, hi);
-        const int e = cc * 16;
-        const int kb = e >> 6;
-        const int c = (e & 63) >> 3;  // even: chunks c and c+1 hold the 16 values
-        uint8_t* dst = a_tile + (size_t)kb * 16384 + (size_t)row * 128;
-        *reinterpret_cast<uint4*>(dst + ((c ^ (row & 7)) << 4)) = lo;
-        *reinterpret_cast<uint4*>(dst + (((c + 1) ^ (row & 7)) << 4)) = hi;
-      }
-      ptx::fence_proxy_async_smem();
-    } else {
-      a_tile = a_buf + (size_t)s * L::kABytes;
-    }
+    uint8_t* a_tile = a_buf + (size_t)s * L::kABytes;
     ptx::tc_fence_before_sync();
     __syncthreads();
     if (tid == 0) {
@@ -305,12 +251,6 @@ __global__ void __launch_bounds__(128, 1) indexer_tc_kernel(const __grid_constan
         }
       }
       ptx::mma_commit(&mma_bar[i & 1]);
-      if constexpr (FP8) {
-        if (issued < ntiles) {  // raw stage s was consumed by every thread before the barrier above
-          issue_load(issued);
-          ++issued;
-        }
-      }
     }
     if (i > 0) epilogue(i - 1);
   }
@@ -363,9 +303,9 @@ static int dispatch_exact(IndexerParams& p, int qt, int kt, cudaStream_t st) {
   return fail(MXB_ERR_UNSUPPORTED, "indexer scores: unsupported q/key dtype pair (%d, %d)", qt, kt);
 }
 
-template <int D, bool FP8>
+template <int D>
 static int launch_tc(IndexerParams& p, const mxb_indexer_scores_args* a, cudaStream_t st) {
-  using L = TcSmem<D, FP8>;
+  using L = TcSmem<D>;
   int t_tile = 256 / p.H;
   if (t_tile > p.T) t_tile = p.T;
   p.t_tile = t_tile;
@@ -385,17 +325,14 @@ static int launch_tc(IndexerParams& p, const mxb_indexer_scores_args* a, cudaStr
 
   CUtensorMap tmap;
   uint64_t dims[2] = {(uint64_t)D, (uint64_t)a->rows_total};
-  uint64_t strides[1] = {(uint64_t)D * (FP8 ? 1 : 2)};
-  uint32_t box[2] = {FP8 ? (uint32_t)D : 64u, 128u};
+  uint64_t strides[1] = {(uint64_t)D * 2};
+  uint32_t box[2] = {64u, 128u};
   int rc = make_tensor_map(&tmap,
-                           FP8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
-                               : (a->key_dtype == MXB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                           : CU_TENSOR_MAP_DATA_TYPE_FLOAT16),
-                           2, a->keys, dims, strides, box,
-                           FP8 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B);
+                           a->key_dtype == MXB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                           2, a->keys, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != MXB_OK) return rc;
 
-  auto kern = indexer_tc_kernel<D, FP8>;
+  auto kern = indexer_tc_kernel<D>;
   const int smem = L::total + 1024;
   MXB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid((unsigned)ceil_div(p.n_rows, p.rows_per_cta), (unsigned)t_tiles, (unsigned)p.B);
@@ -440,8 +377,8 @@ extern "C" int mxb_indexer_scores(const mxb_indexer_scores_args* a, void* stream
   if (tc) {
     const bool fp8 = a->key_dtype == MXB_F8E4M3;
     if (fp8) return launch_indexer_fp8(a, st);
-    if (a->D == 64) return fp8 ? launch_tc<64, true>(p, a, st) : launch_tc<64, false>(p, a, st);
-    return fp8 ? launch_tc<128, true>(p, a, st) : launch_tc<128, false>(p, a, st);
+    if (a->D == 64) return launch_tc<64>(p, a, st);
+    return launch_tc<128>(p, a, st);
   }
   if (a->D == 64) return dispatch_exact<64>(p, a->q_dtype, a->key_dtype, st);
   return dispatch_exact<128>(p, a->q_dtype, a->key_dtype, st);

@@ -59,7 +59,7 @@ __host__ __device__ inline TcLayout tc_layout(int Dqk, int Dv) {
     end += 16384;
   }
   L.misc_off = end;
-  L.total = end + 5120;
+  L.total = end + 8192;
   return L;
 }
 
@@ -68,10 +68,10 @@ struct TcMisc {
   float factor[TC_HEADS];
   float colmax[4][TC_HEADS];
   float l_tot[TC_HEADS];
-  float row_scale[TC_ROWS];
-  float inv_scale[TC_ROWS];
-  int valid[TC_ROWS];
-  const uint8_t* row_src[TC_ROWS];
+  float row_scale[2][TC_ROWS];       // per-tile row metadata, double-buffered: the next tile's rows are
+  float inv_scale[2][TC_ROWS];       // resolved (ids -> addresses -> scales) while the tensor core works
+  int valid[2][TC_ROWS];
+  const uint8_t* row_src[2][TC_ROWS];
   uint64_t bar_s, bar_o;
   uint32_t tmem_slot;
   int abort_flag;
@@ -202,7 +202,7 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
     const bool vec = ((reinterpret_cast<uintptr_t>(p.q) & 15) == 0) && (p.q_sb % 8 == 0) && (p.q_sh % 8 == 0) &&
                      (p.q_st % 8 == 0);
     for (int i = tid; i < TC_HEADS * (p.Dqk / 8); i += blockDim.x) {
-      const int h = i / (p.Dqk / 8), c = i % (p.Dqk / 8);
+      const int h = i & (TC_HEADS - 1), c = i >> 6;   // a warp writes 32 different rows: conflict-free stores
       alignas(16) uint16_t v[8];
       if (h >= p.H) {
 #pragma unroll
@@ -253,26 +253,19 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
   for (int c = 0; c < 32; ++c) l_thr[c] = 0.f;
   bool have_o = false;
 
-  // gather plan: the i-th 16-byte load of this lane covers (local row, chunk) = tab[i] (row << 16 | chunk)
+  // gather plan: one warp instruction covers 8 rows x 4 consecutive 16-byte chunks (lane = row%8 + 8*chunk):
+  // the 8 rows have 8 different swizzle phases, so the 128-bit shared-memory stores are conflict-free, and
+  // the 4 chunks of a row are 64 contiguous bytes in global memory.
   const int nch = p.Dqk * EB / 16;
-  int rpb = 16;
-  while (rpb * nch > 576) rpb >>= 1;
-  uint32_t tab[18];
-#pragma unroll
-  for (int i = 0; i < 18; ++i) {
-    const int g = lane + 32 * i;
-    const int rl = g / nch;
-    tab[i] = rl < rpb ? ((uint32_t)rl << 16) | (uint32_t)(g - rl * nch) : 0xFFFFFFFFu;
-  }
+  const int ncg = (nch + 3) / 4;   // groups of 4 chunks per row
+  const int r8 = lane & 7, cl = lane >> 3;
 
-  for (int it = 0; it < ntiles; ++it) {
-    const int e0 = e_lo + it * TC_ROWS;
-    TRS(0, it);
-    // ---------------------------------------------------------------- gather 128 rows
-    // phase 0: lanes 0-15 of each warp resolve the source of the warp's 16 rows
+  // lanes 0-15 of each warp resolve the warp's 16 rows of the tile starting at list entry `te0` into
+  // metadata buffer `buf` and pull the rows towards L2
+  auto resolve_tile = [&](int te0, int buf) {
     if (lane < 16) {
       const int rr = warp * 16 + lane;
-      const int e = e0 + rr;
+      const int e = te0 + rr;
       const uint8_t* src = nullptr;
       float rs = 1.f;
       if (e < e_hi) {
@@ -291,65 +284,55 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
           }
         }
       }
-      mi->row_src[rr] = src;
-      mi->valid[rr] = src != nullptr;
-      mi->row_scale[rr] = rs;
-      mi->inv_scale[rr] = 1.f / rs;
-    }
-    else if (it + 1 < ntiles) {
-      // lanes 16-31: pull the NEXT tile's rows (and scales) into L2 while this tile is processed
-      const int e = e0 + TC_ROWS + warp * 16 + (lane - 16);
-      if (e < e_hi) {
-        const uint8_t* src = nullptr;
-        if (e < n_raw) {
-          const int64_t phys = ((int64_t)p.raw_start + (first + e - first_raw_pos)) % p.raw_cap;
-          const int64_t ridx = (int64_t)b * p.raw_cap + phys;
-          src = reinterpret_cast<const uint8_t*>(p.raw_kv) + ridx * p.Dqk * EB;
-          if (KVT == MXB_I8) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.raw_scales + ridx));
-        } else {
-          const int32_t id = ids[e - n_raw];
-          if (id >= 0) {
-            const int64_t ridx = cbase + id;
-            src = reinterpret_cast<const uint8_t*>(p.comp_kv) + ridx * p.Dqk * EB;
-            if (KVT == MXB_I8) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.comp_scales + ridx));
-          }
-        }
-        if (src) {
-          const int row_bytes = p.Dqk * EB;
-          for (int off = 0; off < row_bytes; off += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(src + off));
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(src + row_bytes - 1));
-        }
+      if (src) {
+        const int row_bytes = p.Dqk * EB;
+        for (int off = 0; off < row_bytes; off += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(src + off));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(src + row_bytes - 1));
       }
+      mi->row_src[buf][rr] = src;
+      mi->valid[buf][rr] = src != nullptr;
+      mi->row_scale[buf][rr] = rs;
+      mi->inv_scale[buf][rr] = 1.f / rs;
     }
+  };
+  if (ntiles > 0) resolve_tile(e_lo, 0);
+
+  for (int it = 0; it < ntiles; ++it) {
+    const int e0 = e_lo + it * TC_ROWS;
+    TRS(0, it);
+    // ---------------------------------------------------------------- gather 128 rows
+    const int mb = it & 1;   // metadata buffer of this tile (filled before the loop or during the previous tile)
     __syncwarp();
     // phase 1: up to 18 independent 16-byte loads per lane in flight, then widen / store
-    for (int r0 = 0; r0 < 16; r0 += rpb) {
-      uint4 v[18];
+    {
+      const uint8_t* src_lo = mi->row_src[mb][warp * 16 + r8];
+      const uint8_t* src_hi = mi->row_src[mb][warp * 16 + 8 + r8];
+      for (int cg0 = 0; cg0 < ncg; cg0 += 9) {
+        uint4 v[18];
 #pragma unroll
-      for (int i = 0; i < 18; ++i) {
-        v[i] = make_uint4(0, 0, 0, 0);
-        if (tab[i] != 0xFFFFFFFFu) {
-          const uint8_t* src = mi->row_src[warp * 16 + r0 + (int)(tab[i] >> 16)];
-          if (src) v[i] = __ldg(reinterpret_cast<const uint4*>(src) + (tab[i] & 0xFFFFu));
+        for (int i = 0; i < 18; ++i) {
+          const int c = (cg0 + (i >> 1)) * 4 + cl;
+          const uint8_t* src = (i & 1) ? src_hi : src_lo;
+          v[i] = make_uint4(0, 0, 0, 0);
+          if (src && c < nch) v[i] = __ldg(reinterpret_cast<const uint4*>(src) + c);
         }
-      }
 #pragma unroll
-      for (int i = 0; i < 18; ++i) {
-        if (tab[i] != 0xFFFFFFFFu) {
-          const int rr = warp * 16 + r0 + (int)(tab[i] >> 16);
-          const int c = (int)(tab[i] & 0xFFFFu);
-          uint8_t* drow = tile + (size_t)rr * 128;
-          const int sw = rr & 7;
-          if constexpr (KVT == MXB_I8) {
-            uint4 lo, hi;
-            widen_i8x16_f16(v[i], lo, hi);   // zero bytes (invalid row) widen to 0.0
-            const int kb = c >> 2, cc = (c & 3) * 2;
-            uint8_t* d = drow + (size_t)kb * 16384;
-            *reinterpret_cast<uint4*>(d + ((cc ^ sw) << 4)) = lo;
-            *reinterpret_cast<uint4*>(d + (((cc + 1) ^ sw) << 4)) = hi;
-          } else {
-            const int kb = c >> 3, cc = c & 7;
-            *reinterpret_cast<uint4*>(drow + (size_t)kb * 16384 + ((cc ^ sw) << 4)) = v[i];
+        for (int i = 0; i < 18; ++i) {
+          const int c = (cg0 + (i >> 1)) * 4 + cl;
+          if (c < nch) {
+            const int rr = warp * 16 + (i & 1) * 8 + r8;
+            uint8_t* drow = tile + (size_t)rr * 128;
+            if constexpr (KVT == MXB_I8) {
+              uint4 lo, hi;
+              widen_i8x16_f16(v[i], lo, hi);   // zero bytes (invalid row) widen to 0.0
+              const int kb = c >> 2, cc = (c & 3) * 2;
+              uint8_t* d = drow + (size_t)kb * 16384;
+              *reinterpret_cast<uint4*>(d + ((cc ^ r8) << 4)) = lo;
+              *reinterpret_cast<uint4*>(d + (((cc + 1) ^ r8) << 4)) = hi;
+            } else {
+              const int kb = c >> 3, cc = c & 7;
+              *reinterpret_cast<uint4*>(drow + (size_t)kb * 16384 + ((cc ^ r8) << 4)) = v[i];
+            }
           }
         }
       }
@@ -372,6 +355,7 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
       ptx::mma_commit(&mi->bar_s);
       TRS(2, it);
     }
+    if (it + 1 < ntiles) resolve_tile(e0 + TC_ROWS, mb ^ 1);   // hidden behind the MMAs just issued
     ptx::mbar_wait(&mi->bar_s, (uint32_t)(it & 1), abort_flag);
     ptx::tc_fence_after_sync();
 
@@ -382,8 +366,8 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
     uint32_t sv[32];
     ptx::tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)col0, sv);
     ptx::tmem_ld_wait();
-    const bool ok = mi->valid[row] != 0;
-    const float rs = mi->row_scale[row];
+    const bool ok = mi->valid[mb][row] != 0;
+    const float rs = mi->row_scale[mb][row];
     const float mul = scale_log2 * rs;
     bool grow = false;
 #pragma unroll
@@ -431,7 +415,7 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
       }
     }
     {
-      const float inv = mi->inv_scale[row];
+      const float inv = mi->inv_scale[mb][row];
       const int slab = row >> 6, rj = row & 63;
       uint8_t* pbase = pt + (size_t)slab * 8192 + (rj & 7) * 2;
       const int cj = rj >> 3;

@@ -6,7 +6,7 @@
 //                 into the row's global histogram;
 //   topk_mfilter  grid (parts, rows): threshold bin from the global histogram, then
 //                 strictly-above ids -> above_idx[row], threshold-bin candidates -> cand[row]
-//                 (one atomic per warp per class);
+//                 (keys of a sweep live in registers; one block scan and one global atomic per class per sweep);
 //   topk_mfinish  grid (rows): remaining 21 bits and the ties (lowest id first) among the
 //                 candidates, then an id BITMAP in shared memory turns the unordered set
 //                 into ascending output by a prefix scan of popcounts (no sort).
@@ -18,6 +18,7 @@ namespace mxb {
 
 constexpr int kMThreads = 512;
 constexpr int kMUnroll = 8;
+constexpr int kFilterRegs = 32;                // keys per thread per sweep of the filter kernel
 constexpr int kFinishCandSmem = 12288;        // candidate pairs kept in shared memory by the finish kernel
 constexpr int64_t kBitmapMaxN = 1 << 20;      // 128 KB bitmap
 
@@ -97,56 +98,74 @@ __device__ __forceinline__ void row_threshold(const uint32_t* g, int k, uint32_t
   __syncthreads();
 }
 
+#ifdef MXB_TRACE_MF
+#define TRF(k) do { if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) reinterpret_cast<long long*>(p.cand_idx + p.n - 64)[k] = clock64(); } while (0)
+#else
+#define TRF(k)
+#endif
+
 __global__ void __launch_bounds__(kMThreads) topk_mfilter_kernel(TopkMultiParams p) {
   __shared__ uint32_t warp_sums[32];
-  __shared__ uint32_t s_total, s_thr[4];
+  __shared__ uint32_t s_total, s_thr[4], s_base[2];
   const int row = blockIdx.y, tid = threadIdx.x, lane = tid & 31;
   const int64_t n = p.row_count ? min((int64_t)p.row_count[row], p.n) : p.n;
   const int64_t lo = (int64_t)blockIdx.x * p.part;
   if (lo >= n) return;
   const int64_t hi = min(lo + p.part, n);
   const float* src = p.scores + (p.row_start ? p.row_start[row] : (int64_t)row * p.row_stride);
+  TRF(0);
   if (tid < 4) s_thr[tid] = 0;
   __syncthreads();
   row_threshold(p.hist + (int64_t)row * kBigBins, p.k, warp_sums, &s_total, s_thr);
+  TRF(1);
   if (s_thr[0] == 0) return;
   const uint32_t bin = s_thr[1];
   uint32_t* cnt = p.counters + (int64_t)row * 4;
   int32_t* ab = p.above_idx + (int64_t)row * p.k;
   uint32_t* ck = p.cand_key + (int64_t)row * p.n;
   int32_t* ci = p.cand_idx + (int64_t)row * p.n;
-  const uint32_t lane_lt = (1u << lane) - 1u;
-  for (int64_t i0 = lo; i0 < hi; i0 += kMThreads * kMUnroll) {   // uniform trip count: votes inside
-    float x[kMUnroll];
+  // Sweeps of kMThreads * kFilterRegs elements held in registers: count this thread's hits, one block
+  // scan, ONE global atomic per class per sweep (same-address atomics serialise in L2), then write.
+  (void)lane;
+  for (int64_t i0 = lo; i0 < hi; i0 += (int64_t)kMThreads * kFilterRegs) {
+    uint32_t key[kFilterRegs];
 #pragma unroll
-    for (int u = 0; u < kMUnroll; ++u) {
-      const int64_t i = i0 + tid + u * kMThreads;
-      x[u] = i < hi ? __ldg(src + i) : -INFINITY;
+    for (int u = 0; u < kFilterRegs; ++u) {
+      const int64_t i = i0 + tid + (int64_t)u * kMThreads;
+      key[u] = i < hi ? score_key_full(__ldg(src + i)) : 0u;
     }
+    TRF(2);
+    uint32_t na = 0, nc = 0;
 #pragma unroll
-    for (int u = 0; u < kMUnroll; ++u) {
-      const uint32_t key = score_key_full(x[u]);
-      const uint32_t kb = key >> 21;
-      const bool above = key && kb > bin, cand = key && kb == bin;
-      const uint32_t m_above = __ballot_sync(0xffffffffu, above), m_cand = __ballot_sync(0xffffffffu, cand);
-      if ((m_above | m_cand) == 0) continue;   // warp-uniform
-      uint32_t base_a = 0, base_c = 0;
-      if (lane == 0) {
-        if (m_above) base_a = atomicAdd(&cnt[0], (uint32_t)__popc(m_above));
-        if (m_cand) base_c = atomicAdd(&cnt[1], (uint32_t)__popc(m_cand));
-      }
-      base_a = __shfl_sync(0xffffffffu, base_a, 0);
-      base_c = __shfl_sync(0xffffffffu, base_c, 0);
-      const int32_t id = (int32_t)(i0 + tid + u * kMThreads);
-      if (above) {
-        const uint32_t pos = base_a + __popc(m_above & lane_lt);
-        if (pos < (uint32_t)p.k) ab[pos] = id;
-      } else if (cand) {
-        const uint32_t pos = base_c + __popc(m_cand & lane_lt);
-        ck[pos] = key;
-        ci[pos] = id;
+    for (int u = 0; u < kFilterRegs; ++u) {
+      const uint32_t kb = key[u] >> 21;
+      na += (key[u] != 0 && kb > bin);
+      nc += (key[u] != 0 && kb == bin);
+    }
+    TRF(3);
+    uint32_t pa = block_excl_scan(na, warp_sums, &s_total);
+    if (tid == 0) s_base[0] = s_total ? atomicAdd(&cnt[0], s_total) : 0u;
+    uint32_t pc = block_excl_scan(nc, warp_sums, &s_total);
+    if (tid == 0) s_base[1] = s_total ? atomicAdd(&cnt[1], s_total) : 0u;
+    __syncthreads();
+    pa += s_base[0];
+    pc += s_base[1];
+    TRF(4);
+#pragma unroll
+    for (int u = 0; u < kFilterRegs; ++u) {
+      const uint32_t kb = key[u] >> 21;
+      const int32_t id = (int32_t)(i0 + tid + (int64_t)u * kMThreads);
+      if (key[u] != 0 && kb > bin) {
+        if (pa < (uint32_t)p.k) ab[pa] = id;
+        ++pa;
+      } else if (key[u] != 0 && kb == bin) {
+        ck[pc] = key[u];
+        ci[pc] = id;
+        ++pc;
       }
     }
+    __syncthreads();
+    TRF(5);
   }
 }
 
