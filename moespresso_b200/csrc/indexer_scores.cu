@@ -376,7 +376,7 @@ extern "C" int mxb_indexer_scores(const mxb_indexer_scores_args* a, void* stream
   const bool tc = !(a->flags & MXB_INDEXER_EXACT_FP32) && q16 && keys_match && q_vec_ok && (a->H % 16 == 0);
   if (tc) {
     const bool fp8 = a->key_dtype == MXB_F8E4M3;
-    if (fp8) return launch_indexer_fp8(a, st);
+    if (fp8 || !(a->flags & 4)) return launch_indexer_fp8(a, st);   // flag 4 (temporary): previous in-order kernel
     if (a->D == 64) return launch_tc<64>(p, a, st);
     return launch_tc<128>(p, a, st);
   }

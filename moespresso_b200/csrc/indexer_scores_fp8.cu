@@ -61,23 +61,29 @@ struct Fp8Params {
   int32_t* status;
 };
 
-constexpr int kDrainSets = 2;
-constexpr int kDrainWarps = 4 * kDrainSets;
+constexpr int kWiden = 0, kDirect = 1, kKeys16 = 2;   // operand modes
 constexpr int kMmaWarps = 2;               // two issuing threads: tile i belongs to issuer i % 2
-constexpr int kMmaWarp = kDrainWarps;
-constexpr int kTmaWarp = kDrainWarps + kMmaWarps;
-constexpr int kConvWarp0 = kTmaWarp + 1;
 
-template <int D, bool DIRECT>
+template <int D, int MODE>
 struct Fp8Cfg {
-  static constexpr int kStages = DIRECT ? 8 : 4;            // raw FP8 tiles in flight
-  static constexpr int kNA = DIRECT ? 0 : (D == 64 ? 4 : 2);  // 16-bit operand buffers = widening warps
+  static constexpr int kStages = MODE == kDirect ? 8 : (MODE == kWiden ? 4 : 0);   // raw FP8 tiles in flight
+  // 16-bit operand buffers (WIDEN: one per widening warp; KEYS16: the TMA ring itself)
+  static constexpr int kNA = MODE == kDirect ? 0 : (MODE == kWiden ? (D == 64 ? 4 : 2) : (D == 64 ? 4 : 3));
+  static constexpr int kConv = MODE == kWiden ? kNA : 0;                            // widening warps
+  // drain warps: kTileGroups tiles drained concurrently, each by kColSplit groups of 4 warps that share
+  // the tile's columns (the wide prefill tiles of KEYS16 need more drain threads per tile)
+  static constexpr int kTileGroups = 2;
+  static constexpr int kColSplit = MODE == kKeys16 ? 2 : 1;
+  static constexpr int kDrainWarps = 4 * kTileGroups * kColSplit;
+  static constexpr int kMmaWarp = kDrainWarps;
+  static constexpr int kTmaWarp = kDrainWarps + kMmaWarps;
+  static constexpr int kConvWarp0 = kTmaWarp + 1;
   static constexpr int kRaw = 128 * D;
   static constexpr int kA16 = 128 * D * 2;
   static constexpr int raw_off = 0;
   static constexpr int a16_off = raw_off + kStages * kRaw;
   static constexpr int b_off = a16_off + kNA * kA16;        // + b_bytes, then weights and barriers
-  static constexpr int kThreads = 32 * (kConvWarp0 + kNA);
+  static constexpr int kThreads = 32 * (kConvWarp0 + kConv);
 };
 
 __device__ __forceinline__ float e4m3_round(float x, uint8_t* bits) {
@@ -86,10 +92,13 @@ __device__ __forceinline__ float e4m3_round(float x, uint8_t* bits) {
   return __half2float(__half(__nv_cvt_fp8_to_halfraw(b, __NV_E4M3)));
 }
 
-template <int D, bool DIRECT>
-__global__ void __launch_bounds__(Fp8Cfg<D, DIRECT>::kThreads, 1)
+template <int D, int MODE>
+__global__ void __launch_bounds__(Fp8Cfg<D, MODE>::kThreads, 1)
 indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
-  using C = Fp8Cfg<D, DIRECT>;
+  using C = Fp8Cfg<D, MODE>;
+  constexpr bool DIRECT = MODE == kDirect;
+  constexpr bool K16 = MODE == kKeys16;
+  constexpr int kMmaWarp = C::kMmaWarp, kTmaWarp = C::kTmaWarp, kConvWarp0 = C::kConvWarp0;
   constexpr int S = C::kStages;
   constexpr int NA = C::kNA;
   extern __shared__ uint8_t smem_raw[];
@@ -131,12 +140,12 @@ indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
       ptx::mbar_init(&raw_empty[s], DIRECT ? 1 : 32);
     }
     for (int a = 0; a < NA; ++a) {
-      ptx::mbar_init(&a_full[a], 32);
+      ptx::mbar_init(&a_full[a], K16 ? 1 : 32);
       ptx::mbar_init(&a_empty[a], 1);
     }
     for (int a = 0; a < n_acc; ++a) {
       ptx::mbar_init(&acc_full[a], 1);
-      ptx::mbar_init(&acc_empty[a], 128);
+      ptx::mbar_init(&acc_empty[a], 128 * C::kColSplit);
     }
     *abort_flag = 0;
     ptx::mbar_fence_init();
@@ -167,7 +176,7 @@ indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
     }
     amax = warp_max(amax);
     int a = 0;
-    if (amax > 0.f && amax < 3.0e38f) {
+    if (!K16 && amax > 0.f && amax < 3.0e38f) {   // 16-bit keys: the query is used as it is
       int e;
       frexpf(amax, &e);                       // amax = m * 2^e, m in [0.5, 1)
       a = (DIRECT ? 8 : 14) - e;              // amax * 2^a in [128, 256) resp. [2^13, 2^14)
@@ -193,8 +202,15 @@ indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
       } else {
         const int n = r;                      // column = t * H + h
         const int kb = d >> 6, c = (d & 63) >> 3, within = d & 7;
-        reinterpret_cast<__half*>(b_buf + (size_t)kb * N * 128 + (size_t)n * 128 + ((c ^ (n & 7)) << 4))[within] =
-            __float2half_rn(xs);
+        uint16_t bits;
+        if (K16 && p.q_is_bf16) {
+          __nv_bfloat16 v = __float2bfloat16_rn(xs);
+          bits = *reinterpret_cast<uint16_t*>(&v);
+        } else {
+          __half v = __float2half_rn(xs);
+          bits = *reinterpret_cast<uint16_t*>(&v);
+        }
+        reinterpret_cast<uint16_t*>(b_buf + (size_t)kb * N * 128 + (size_t)n * 128 + ((c ^ (n & 7)) << 4))[within] = bits;
       }
     }
     if (lane == 0) w_s[r] = (t < nt) ? ldexpf(p.weights[((int64_t)b * p.T + t0 + t) * H + h], -a) : 0.f;
@@ -209,11 +225,24 @@ indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       for (int i = 0; i < ntiles; ++i) {
-        const int s = i % S;
-        if (i >= S) ptx::mbar_wait(&raw_empty[s], (uint32_t)((i / S - 1) & 1), abort_flag);
+        int s = 0;
+        if constexpr (!K16) {
+          s = i % S;
+          if (i >= S) ptx::mbar_wait(&raw_empty[s], (uint32_t)((i / S - 1) & 1), abort_flag);
+        }
         const int64_t grow = rbase + row0 + (int64_t)i * 128;
         TR(0, i);
-        if constexpr (DIRECT) {
+        if constexpr (K16) {
+          // 16-bit keys go straight into the swizzled operand ring
+          constexpr int NAk = C::kNA;
+          const int ab = i % NAk;
+          if (i >= NAk) ptx::mbar_wait(&a_empty[ab], (uint32_t)((i / NAk - 1) & 1), abort_flag);
+          ptx::mbar_expect_tx(&a_full[ab], (uint32_t)C::kA16);
+#pragma unroll
+          for (int kb = 0; kb < D / 64; ++kb)
+            ptx::tma_load_2d(a16_buf + (size_t)ab * C::kA16 + (size_t)kb * 16384, &tmap, &a_full[ab], kb * 64,
+                             (int32_t)grow);
+        } else if constexpr (DIRECT) {
           ptx::mbar_expect_tx(&raw_full[s], (uint32_t)C::kRaw);
           ptx::tma_load_2d(raw_buf + (size_t)s * C::kRaw, &tmap, &raw_full[s], 0, (int32_t)grow);
         } else {
@@ -235,7 +264,8 @@ indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
       const uint32_t b_addr = ptx::smem_u32(b_buf);
       const uint64_t a_desc0 = ptx::smem_desc_sw128(ptx::smem_u32(a16_buf), 16, 1024);
       const uint64_t b_desc0 = ptx::smem_desc_sw128(b_addr, 16, 1024);
-      const uint32_t idesc16 = ptx::idesc_f16(ptx::kFmtF16, ptx::kFmtF16, 128, (uint32_t)N, 0, 0);
+      const uint32_t fmt16 = (K16 && p.q_is_bf16) ? ptx::kFmtBF16 : ptx::kFmtF16;
+      const uint32_t idesc16 = ptx::idesc_f16(fmt16, fmt16, 128, (uint32_t)N, 0, 0);
       int a = mw % n_acc, ab = NA > 0 ? mw % (NA > 0 ? NA : 1) : 0;   // ring positions of this issuer's first tile
       uint32_t a_ph = 1, ab_ph = 0;      // parity to wait for: acc_empty of the previous use, a_full of this use
       for (int i = mw; i < ntiles; i += kMmaWarps) {
@@ -288,7 +318,7 @@ indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
     }
   } else if (warp >= kConvWarp0) {
     // ------------------------------------------------------------ widening warps (WIDEN only)
-    if constexpr (!DIRECT) {
+    if constexpr (MODE == kWiden) {
       const int cw = warp - kConvWarp0;   // owns operand buffer cw, handles tiles cw, cw + NA, ...
       uint8_t* a_tile = a16_buf + (size_t)cw * C::kA16;
       constexpr int CPR = D / 16;         // 16-byte FP8 chunks per row
@@ -323,16 +353,19 @@ indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
   } else {
     // ------------------------------------------------------------ drain: thread = key row
     const int set = warp >> 2, quad = warp & 3;
+    const int tg = set / C::kColSplit, ch = set % C::kColSplit;   // tile group, share of the tile's tokens
+    const int t_per = (p.t_tile + C::kColSplit - 1) / C::kColSplit;
+    const int t_lo = min(ch * t_per, nt), t_hi = min(t_lo + t_per, nt);
     const int rloc = quad * 32 + lane;
     const int64_t sbase = (p.row_start ? p.row_start[b] : 0) + (int64_t)b * p.s_sb;
-    for (int i = set; i < ntiles; i += kDrainSets) {
+    for (int i = tg; i < ntiles; i += C::kTileGroups) {
       const int a = i % n_acc;
       ptx::mbar_wait(&acc_full[a], (uint32_t)((i / n_acc) & 1), abort_flag);
       ptx::tc_fence_after_sync();
       if (quad == 0) TR(4, i);
       const int64_t r = row0 + (int64_t)i * 128 + rloc;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * p.acc_stride);
-      for (int t = 0; t < nt; ++t) {
+      for (int t = t_lo; t < t_hi; ++t) {
         float sum = 0.f;
         for (int c0 = 0; c0 < H; c0 += 16) {
           uint32_t v1[16];
@@ -374,9 +407,11 @@ indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
 #endif
 }
 
-template <int D, bool DIRECT>
+template <int D, int MODE>
 static int launch_fp8_d(Fp8Params& p, const mxb_indexer_scores_args* a, cudaStream_t st) {
-  using C = Fp8Cfg<D, DIRECT>;
+  using C = Fp8Cfg<D, MODE>;
+  constexpr bool DIRECT = MODE == kDirect;
+  constexpr bool K16 = MODE == kKeys16;
   const int cols_per_token = (DIRECT ? 2 : 1) * p.H;
   int t_tile = 256 / cols_per_token;
   if (t_tile > p.T) t_tile = p.T;
@@ -403,14 +438,24 @@ static int launch_fp8_d(Fp8Params& p, const mxb_indexer_scores_args* a, cudaStre
   p.rows_per_cta = (int)(per * 128);
 
   CUtensorMap tmap;
-  uint64_t dims[2] = {(uint64_t)D, (uint64_t)a->rows_total};
-  uint64_t strides[1] = {(uint64_t)D};
-  uint32_t box[2] = {(uint32_t)D, 128u};
-  const CUtensorMapSwizzle sw = !DIRECT ? CU_TENSOR_MAP_SWIZZLE_NONE
-                                        : (D == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
-  int rc = make_tensor_map(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a->keys, dims, strides, box, sw);
+  int rc;
+  if (K16) {
+    uint64_t dims[2] = {(uint64_t)D, (uint64_t)a->rows_total};
+    uint64_t strides[1] = {(uint64_t)D * 2};
+    uint32_t box[2] = {64u, 128u};
+    rc = make_tensor_map(&tmap,
+                         a->key_dtype == MXB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                         2, a->keys, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  } else {
+    uint64_t dims[2] = {(uint64_t)D, (uint64_t)a->rows_total};
+    uint64_t strides[1] = {(uint64_t)D};
+    uint32_t box[2] = {(uint32_t)D, 128u};
+    const CUtensorMapSwizzle sw = !DIRECT ? CU_TENSOR_MAP_SWIZZLE_NONE
+                                          : (D == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
+    rc = make_tensor_map(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a->keys, dims, strides, box, sw);
+  }
   if (rc != MXB_OK) return rc;
-  auto kern = indexer_fp8_kernel<D, DIRECT>;
+  auto kern = indexer_fp8_kernel<D, MODE>;
   MXB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid((unsigned)ceil_div(p.n_rows, p.rows_per_cta), (unsigned)t_tiles, (unsigned)p.B);
   kern<<<grid, C::kThreads, smem, st>>>(tmap, p);
@@ -418,6 +463,7 @@ static int launch_fp8_d(Fp8Params& p, const mxb_indexer_scores_args* a, cudaStre
   return MXB_OK;
 }
 
+// FP8 key tables (widened or fed to the FP8 tensor path) and 16-bit key tables (bf16 / fp16, same type as q).
 int launch_indexer_fp8(const mxb_indexer_scores_args* a, cudaStream_t st) {
   Fp8Params p{};
   p.keys = reinterpret_cast<const uint8_t*>(a->keys); p.rows_total = a->rows_total;
@@ -427,9 +473,11 @@ int launch_indexer_fp8(const mxb_indexer_scores_args* a, cudaStream_t st) {
   p.row_start = a->row_start; p.row_count = a->row_count;
   p.B = a->B; p.T = a->T; p.H = a->H; p.n_rows = a->n_rows; p.pos0 = a->pos0; p.ratio = a->ratio;
   p.status = a->status;
+  if (a->key_dtype != MXB_F8E4M3)
+    return a->D == 64 ? launch_fp8_d<64, kKeys16>(p, a, st) : launch_fp8_d<128, kKeys16>(p, a, st);
   const bool direct = (a->flags & MXB_INDEXER_FP8_MMA) != 0;
-  if (a->D == 64) return direct ? launch_fp8_d<64, true>(p, a, st) : launch_fp8_d<64, false>(p, a, st);
-  return direct ? launch_fp8_d<128, true>(p, a, st) : launch_fp8_d<128, false>(p, a, st);
+  if (a->D == 64) return direct ? launch_fp8_d<64, kDirect>(p, a, st) : launch_fp8_d<64, kWiden>(p, a, st);
+  return direct ? launch_fp8_d<128, kDirect>(p, a, st) : launch_fp8_d<128, kWiden>(p, a, st);
 }
 
 }  // namespace mxb

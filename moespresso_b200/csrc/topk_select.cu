@@ -67,12 +67,23 @@ __global__ void __launch_bounds__(1024) topk_row_kernel(TopkParams p) {
   if (k_eff == 0) return;
 
   uint32_t prefix = 0, prefix_mask = 0, want = k_eff;
+  // Scores cluster in a few exponent values, so one shared histogram would serialise almost every
+  // atomic on the same address; each warp counts into its own 256 bins, merged afterwards.
+  uint32_t* whist = keys + p.n;                    // [warps][256]
+  const int nwarps = (int)blockDim.x >> 5;
+  uint32_t* my_hist = whist + (tid >> 5) * 256;
   for (int shift = 24; shift >= 0; shift -= 8) {
-    if (tid < 256) hist[tid] = 0;
+    for (int i = tid; i < nwarps * 256; i += blockDim.x) whist[i] = 0;
     __syncthreads();
     for (int i = tid; i < n; i += blockDim.x) {
       uint32_t key = keys[i];
-      if (key != 0 && (key & prefix_mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+      if (key != 0 && (key & prefix_mask) == prefix) atomicAdd(&my_hist[(key >> shift) & 255u], 1u);
+    }
+    __syncthreads();
+    if (tid < 256) {
+      uint32_t t = 0;
+      for (int w = 0; w < nwarps; ++w) t += whist[w * 256 + tid];
+      hist[tid] = t;
     }
     __syncthreads();
     if (tid < 32) pick_digit_256(hist, want, &s_digit, &s_above);
@@ -86,7 +97,8 @@ __global__ void __launch_bounds__(1024) topk_row_kernel(TopkParams p) {
   const uint32_t need = want;  // ties to take, >= 1
 
   // ordered emission: thread t owns the contiguous slice [t*per, (t+1)*per)
-  const int per = (n + (int)blockDim.x - 1) / (int)blockDim.x;
+  // (odd slice length: lanes of a warp then walk different shared-memory banks)
+  const int per = ((n + (int)blockDim.x - 1) / (int)blockDim.x) | 1;
   const int lo = min(tid * per, n), hi = min(lo + per, n);
   uint32_t ca = 0, ct = 0;
   for (int i = lo; i < hi; ++i) {
@@ -317,10 +329,10 @@ extern "C" int mxb_topk_select(const mxb_topk_args* a, void* stream) {
   p.out_ids = a->out_ids; p.rows = a->rows; p.n = a->n; p.k = a->k;
 
   if (a->n <= kSmemRowMax) {
-    size_t smem = (size_t)a->n * 4;
+    int threads = a->n >= 8192 ? 1024 : (a->n >= 2048 ? 512 : 256);
+    size_t smem = (size_t)a->n * 4 + (size_t)(threads / 32) * 256 * 4;   // keys + per-warp histograms
     if (smem > 48 * 1024)
       MXB_CUDA_OK(cudaFuncSetAttribute(topk_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    int threads = a->n >= 8192 ? 1024 : (a->n >= 2048 ? 512 : 256);
     topk_row_kernel<<<a->rows, threads, smem, st>>>(p);
     MXB_CUDA_OK(cudaGetLastError());
     return MXB_OK;
