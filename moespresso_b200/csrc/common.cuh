@@ -27,8 +27,8 @@ int fail(int code, const char* fmt, ...);
       return ::mxb::fail(MXB_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__)); \
   } while (0)
 
-inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
-inline int64_t round_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
+__host__ __device__ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+__host__ __device__ inline int64_t round_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
 
 int sm_count();
 
