@@ -68,15 +68,16 @@ struct TcMisc {
   float factor[TC_HEADS];
   float colmax[4][TC_HEADS];
   float l_tot[TC_HEADS];
-  float row_scale[2][TC_ROWS];       // per-tile row metadata, double-buffered: the next tile's rows are
-  float inv_scale[2][TC_ROWS];       // resolved (ids -> addresses -> scales) while the tensor core works
-  int valid[2][TC_ROWS];
-  const uint8_t* row_src[2][TC_ROWS];
+  float row_scale[3][TC_ROWS];          // per-tile row metadata, three deep: rows are resolved (ids -> addresses
+  const uint8_t* row_src[3][TC_ROWS];   // -> scales) two tiles ahead, so that the loads of the next tile can be
+                                        // issued as soon as the registers that carry them are free; null = no row
   uint64_t bar_s, bar_o;
   uint32_t tmem_slot;
   int abort_flag;
   int keff;
 };
+
+static_assert(sizeof(TcMisc) <= 8192, "TcMisc must fit the 8 KB the layout reserves for it");
 
 // 16 int8 -> 16 fp16 integers (exact): bytes biased by 128 are dropped into the mantissa of 1024.0
 __device__ __forceinline__ void widen_i8x16_f16(const uint4& in, uint4& lo, uint4& hi) {
@@ -201,34 +202,48 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
   {
     const bool vec = ((reinterpret_cast<uintptr_t>(p.q) & 15) == 0) && (p.q_sb % 8 == 0) && (p.q_sh % 8 == 0) &&
                      (p.q_st % 8 == 0);
-    for (int i = tid; i < TC_HEADS * (p.Dqk / 8); i += blockDim.x) {
-      const int h = i & (TC_HEADS - 1), c = i >> 6;   // a warp writes 32 different rows: conflict-free stores
-      alignas(16) uint16_t v[8];
-      if (h >= p.H) {
+    // batches of kQB items per thread: all global loads of a batch are in flight before the first conversion
+    constexpr int kQB = 6;
+    const int n_items = TC_HEADS * (p.Dqk / 8);
+    for (int i0 = tid; i0 < n_items; i0 += 256 * kQB) {
+      float f[kQB][8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = 0;
-      } else {
-        const int64_t base = (int64_t)b * p.q_sb + (int64_t)h * p.q_sh + (int64_t)t * p.q_st + c * 8;
-        float f[8];
-        if (vec) {
-          if constexpr (QT == MXB_F32) {
-            const float4 a = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + base));
-            const float4 bq = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + base) + 1);
-            f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = bq.x; f[5] = bq.y; f[6] = bq.z; f[7] = bq.w;
+      for (int j = 0; j < kQB; ++j) {
+        const int i = i0 + j * 256;
+        const int h = i & (TC_HEADS - 1), c = i >> 6;   // a warp writes 32 different rows: conflict-free stores
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[j][e] = 0.f;
+        if (i < n_items && h < p.H) {
+          const int64_t base = (int64_t)b * p.q_sb + (int64_t)h * p.q_sh + (int64_t)t * p.q_st + c * 8;
+          if (vec) {
+            if constexpr (QT == MXB_F32) {
+              const float4 a = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + base));
+              const float4 bq = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + base) + 1);
+              f[j][0] = a.x; f[j][1] = a.y; f[j][2] = a.z; f[j][3] = a.w;
+              f[j][4] = bq.x; f[j][5] = bq.y; f[j][6] = bq.z; f[j][7] = bq.w;
+            } else {
+              const uint4 u = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.q) + base));
+              unpack16<QT>(u, f[j]);
+            }
           } else {
-            const uint4 u = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.q) + base));
-            unpack16<QT>(u, f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[j][e] = load_elem<QT>(p.q, base + e);
           }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) f[j] = load_elem<QT>(p.q, base + j);
         }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = to_op16<BF16>(f[j]);
       }
-      const int kb = c >> 3, cc = c & 7;
-      *reinterpret_cast<uint4*>(q_s + (size_t)kb * 8192 + (size_t)h * 128 + ((cc ^ (h & 7)) << 4)) =
-          *reinterpret_cast<uint4*>(v);
+#pragma unroll
+      for (int j = 0; j < kQB; ++j) {
+        const int i = i0 + j * 256;
+        if (i < n_items) {
+          const int h = i & (TC_HEADS - 1), c = i >> 6;
+          alignas(16) uint16_t v[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = to_op16<BF16>(f[j][e]);
+          const int kb = c >> 3, cc = c & 7;
+          *reinterpret_cast<uint4*>(q_s + (size_t)kb * 8192 + (size_t)h * 128 + ((cc ^ (h & 7)) << 4)) =
+              *reinterpret_cast<uint4*>(v);
+        }
+      }
     }
   }
   __syncthreads();
@@ -260,11 +275,11 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
   const int ncg = (nch + 3) / 4;   // groups of 4 chunks per row
   const int r8 = lane & 7, cl = lane >> 3;
 
-  // lanes 0-15 of each warp resolve the warp's 16 rows of the tile starting at list entry `te0` into
-  // metadata buffer `buf` and pull the rows towards L2
+  // warps 1-7 resolve the 128 rows of the tile starting at list entry `te0` (ids -> addresses -> scales) into
+  // metadata buffer `buf` and pull the rows towards L2; warp 0 is busy issuing the QK MMAs meanwhile
   auto resolve_tile = [&](int te0, int buf) {
-    if (lane < 16) {
-      const int rr = warp * 16 + lane;
+    const int rr = (warp - 1) + 7 * lane;
+    if (warp >= 1 && rr < TC_ROWS) {
       const int e = te0 + rr;
       const uint8_t* src = nullptr;
       float rs = 1.f;
@@ -290,52 +305,62 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
         asm volatile("prefetch.global.L2 [%0];" ::"l"(src + row_bytes - 1));
       }
       mi->row_src[buf][rr] = src;
-      mi->valid[buf][rr] = src != nullptr;
       mi->row_scale[buf][rr] = rs;
-      mi->inv_scale[buf][rr] = 1.f / rs;
     }
   };
-  if (ntiles > 0) resolve_tile(e_lo, 0);
+  // Raw rows travel through registers: 18 independent 16-byte loads per lane (9 groups of 4 chunks for
+  // each of the lane's two rows).  The loads of the NEXT tile are issued right after this tile's QK MMAs
+  // and land during its softmax and PV; only the widening and the shared-memory stores stay on the
+  // critical path.
+  uint4 v[18];
+  auto issue_loads = [&](int mbuf, int cg0) {
+    const uint8_t* src_lo = mi->row_src[mbuf][warp * 16 + r8];
+    const uint8_t* src_hi = mi->row_src[mbuf][warp * 16 + 8 + r8];
+#pragma unroll
+    for (int i = 0; i < 18; ++i) {
+      const int c = (cg0 + (i >> 1)) * 4 + cl;
+      const uint8_t* src = (i & 1) ? src_hi : src_lo;
+      v[i] = make_uint4(0, 0, 0, 0);
+      if (src && c < nch) v[i] = __ldg(reinterpret_cast<const uint4*>(src) + c);
+    }
+  };
+  auto store_loaded = [&](int cg0) {
+#pragma unroll
+    for (int i = 0; i < 18; ++i) {
+      const int c = (cg0 + (i >> 1)) * 4 + cl;
+      if (c < nch) {
+        const int rr = warp * 16 + (i & 1) * 8 + r8;
+        uint8_t* drow = tile + (size_t)rr * 128;
+        if constexpr (KVT == MXB_I8) {
+          uint4 lo, hi;
+          widen_i8x16_f16(v[i], lo, hi);   // zero bytes (invalid row) widen to 0.0
+          const int kb = c >> 2, cc = (c & 3) * 2;
+          uint8_t* d = drow + (size_t)kb * 16384;
+          *reinterpret_cast<uint4*>(d + ((cc ^ r8) << 4)) = lo;
+          *reinterpret_cast<uint4*>(d + (((cc + 1) ^ r8) << 4)) = hi;
+        } else {
+          const int kb = c >> 3, cc = c & 7;
+          *reinterpret_cast<uint4*>(drow + (size_t)kb * 16384 + ((cc ^ r8) << 4)) = v[i];
+        }
+      }
+    }
+  };
+  if (ntiles > 0) {
+    resolve_tile(e_lo, 0);
+    __syncthreads();
+    issue_loads(0, 0);
+    if (ntiles > 1) resolve_tile(e_lo + TC_ROWS, 1);
+  }
 
   for (int it = 0; it < ntiles; ++it) {
     const int e0 = e_lo + it * TC_ROWS;
     TRS(0, it);
-    // ---------------------------------------------------------------- gather 128 rows
-    const int mb = it & 1;   // metadata buffer of this tile (filled before the loop or during the previous tile)
-    __syncwarp();
-    // phase 1: up to 18 independent 16-byte loads per lane in flight, then widen / store
-    {
-      const uint8_t* src_lo = mi->row_src[mb][warp * 16 + r8];
-      const uint8_t* src_hi = mi->row_src[mb][warp * 16 + 8 + r8];
-      for (int cg0 = 0; cg0 < ncg; cg0 += 9) {
-        uint4 v[18];
-#pragma unroll
-        for (int i = 0; i < 18; ++i) {
-          const int c = (cg0 + (i >> 1)) * 4 + cl;
-          const uint8_t* src = (i & 1) ? src_hi : src_lo;
-          v[i] = make_uint4(0, 0, 0, 0);
-          if (src && c < nch) v[i] = __ldg(reinterpret_cast<const uint4*>(src) + c);
-        }
-#pragma unroll
-        for (int i = 0; i < 18; ++i) {
-          const int c = (cg0 + (i >> 1)) * 4 + cl;
-          if (c < nch) {
-            const int rr = warp * 16 + (i & 1) * 8 + r8;
-            uint8_t* drow = tile + (size_t)rr * 128;
-            if constexpr (KVT == MXB_I8) {
-              uint4 lo, hi;
-              widen_i8x16_f16(v[i], lo, hi);   // zero bytes (invalid row) widen to 0.0
-              const int kb = c >> 2, cc = (c & 3) * 2;
-              uint8_t* d = drow + (size_t)kb * 16384;
-              *reinterpret_cast<uint4*>(d + ((cc ^ r8) << 4)) = lo;
-              *reinterpret_cast<uint4*>(d + (((cc + 1) ^ r8) << 4)) = hi;
-            } else {
-              const int kb = c >> 3, cc = c & 7;
-              *reinterpret_cast<uint4*>(drow + (size_t)kb * 16384 + ((cc ^ r8) << 4)) = v[i];
-            }
-          }
-        }
-      }
+    // ---------------------------------------------------------------- rows of this tile -> operand layout
+    const int mb = it % 3;   // metadata buffer of this tile (filled two tiles ago, or before the loop)
+    store_loaded(0);
+    for (int cg0 = 9; cg0 < ncg; cg0 += 9) {   // rows wider than 9 chunk groups (16-bit tables): the rest, in place
+      issue_loads(mb, cg0);
+      store_loaded(cg0);
     }
     ptx::fence_proxy_async_smem();
     ptx::tc_fence_before_sync();
@@ -355,7 +380,11 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
       ptx::mma_commit(&mi->bar_s);
       TRS(2, it);
     }
-    if (it + 1 < ntiles) resolve_tile(e0 + TC_ROWS, mb ^ 1);   // hidden behind the MMAs just issued
+    // While the MMAs are issued and run: the next tile's rows start travelling into registers (their metadata
+    // was resolved a tile ago; the threads sit here while the load queue drains, which is dead time anyway),
+    // and warps 1-7 resolve the tile after that.
+    if (it + 1 < ntiles) issue_loads((it + 1) % 3, 0);
+    if (it + 2 < ntiles) resolve_tile(e0 + 2 * TC_ROWS, (it + 2) % 3);
     ptx::mbar_wait(&mi->bar_s, (uint32_t)(it & 1), abort_flag);
     ptx::tc_fence_after_sync();
 
@@ -366,7 +395,7 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
     uint32_t sv[32];
     ptx::tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)col0, sv);
     ptx::tmem_ld_wait();
-    const bool ok = mi->valid[mb][row] != 0;
+    const bool ok = mi->row_src[mb][row] != nullptr;
     const float rs = mi->row_scale[mb][row];
     const float mul = scale_log2 * rs;
     bool grow = false;
@@ -415,7 +444,7 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
       }
     }
     {
-      const float inv = mi->inv_scale[mb][row];
+      const float inv = 1.f / rs;
       const int slab = row >> 6, rj = row & 63;
       uint8_t* pbase = pt + (size_t)slab * 8192 + (rj & 7) * 2;
       const int cj = rj >> 3;

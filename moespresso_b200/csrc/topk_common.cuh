@@ -78,4 +78,36 @@ __device__ __forceinline__ uint32_t block_excl_scan(uint32_t v, uint32_t* warp_s
   return r;
 }
 
+// Threshold bin of a 2048-bin histogram (global or shared memory): the bin, counted from the top,
+// where the running count reaches min(k, total).  All 512 or 1024 threads of the CTA take part;
+// s_out must be zero on entry.
+// Thread t owns bins top-down in groups of `per` = 2048 / blockDim.x.
+__device__ __forceinline__ void row_threshold(const uint32_t* g, int k, uint32_t* warp_sums, uint32_t* s_total,
+                                              uint32_t* s_out /* k_eff, bin, above, cnt */) {
+  const int tid = threadIdx.x;
+  const int per = kBigBins / (int)blockDim.x;   // 4 (512 threads) or 2 (1024 threads)
+  uint32_t loc[4];
+  uint32_t s = 0;
+  for (int j = 0; j < per; ++j) {
+    loc[j] = g[kBigBins - 1 - (tid * per + j)];
+    s += loc[j];
+  }
+  const uint32_t excl = block_excl_scan(s, warp_sums, s_total);
+  const uint32_t ke = min((uint32_t)k, *s_total);
+  if (tid == 0) s_out[0] = ke;
+  if (ke > 0 && excl < ke && excl + s >= ke) {
+    uint32_t run = excl;
+    for (int j = 0; j < per; ++j) {
+      if (run + loc[j] >= ke) {
+        s_out[1] = kBigBins - 1 - (tid * per + j);
+        s_out[2] = run;
+        s_out[3] = loc[j];
+        break;
+      }
+      run += loc[j];
+    }
+  }
+  __syncthreads();
+}
+
 }  // namespace mxb

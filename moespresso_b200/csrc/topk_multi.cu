@@ -68,36 +68,6 @@ __global__ void __launch_bounds__(kMThreads) topk_mhist_kernel(TopkMultiParams p
     if (hist[i]) atomicAdd(&g[i], hist[i]);
 }
 
-// Threshold of a row from its global histogram; all kMThreads (or 1024) threads take part.
-// Thread t owns bins top-down in groups of `per` = 2048 / blockDim.x.
-__device__ __forceinline__ void row_threshold(const uint32_t* g, int k, uint32_t* warp_sums, uint32_t* s_total,
-                                              uint32_t* s_out /* k_eff, bin, above, cnt */) {
-  const int tid = threadIdx.x;
-  const int per = kBigBins / (int)blockDim.x;   // 4 (512 threads) or 2 (1024 threads)
-  uint32_t loc[4];
-  uint32_t s = 0;
-  for (int j = 0; j < per; ++j) {
-    loc[j] = g[kBigBins - 1 - (tid * per + j)];
-    s += loc[j];
-  }
-  const uint32_t excl = block_excl_scan(s, warp_sums, s_total);
-  const uint32_t ke = min((uint32_t)k, *s_total);
-  if (tid == 0) s_out[0] = ke;
-  if (ke > 0 && excl < ke && excl + s >= ke) {
-    uint32_t run = excl;
-    for (int j = 0; j < per; ++j) {
-      if (run + loc[j] >= ke) {
-        s_out[1] = kBigBins - 1 - (tid * per + j);
-        s_out[2] = run;
-        s_out[3] = loc[j];
-        break;
-      }
-      run += loc[j];
-    }
-  }
-  __syncthreads();
-}
-
 #ifdef MXB_TRACE_MF
 #define TRF(k) do { if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) reinterpret_cast<long long*>(p.cand_idx + p.n - 64)[k] = clock64(); } while (0)
 #else

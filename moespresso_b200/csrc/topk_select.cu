@@ -306,6 +306,8 @@ __global__ void __launch_bounds__(1024) topk_stream_kernel(TopkParams p, int sor
 
 int64_t topk_multi_workspace(int32_t rows, int64_t n, int32_t k);   // topk_multi.cu
 int launch_topk_multi(const mxb_topk_args* a, cudaStream_t st);
+int topk_cluster_size(int32_t rows, int64_t n);                        // topk_cluster.cu
+int launch_topk_cluster(const mxb_topk_args* a, int cs, cudaStream_t st);
 
 }  // namespace mxb
 
@@ -313,7 +315,7 @@ using namespace mxb;
 
 extern "C" int64_t mxb_topk_workspace_bytes(int32_t rows, int64_t n, int32_t k) {
   if (rows <= 0 || n <= 0 || k <= 0) return 0;
-  if (n <= kSmemRowMax) return 0;
+  if (topk_cluster_size(rows, n) > 0 || n <= kSmemRowMax) return 0;
   return topk_multi_workspace(rows, n, k);
 }
 
@@ -328,6 +330,7 @@ extern "C" int mxb_topk_select(const mxb_topk_args* a, void* stream) {
   p.scores = a->scores; p.row_stride = a->row_stride; p.row_start = a->row_start; p.row_count = a->row_count;
   p.out_ids = a->out_ids; p.rows = a->rows; p.n = a->n; p.k = a->k;
 
+  if (const int cs = topk_cluster_size(a->rows, a->n)) return launch_topk_cluster(a, cs, st);
   if (a->n <= kSmemRowMax) {
     int threads = a->n >= 8192 ? 1024 : (a->n >= 2048 ? 512 : 256);
     size_t smem = (size_t)a->n * 4 + (size_t)(threads / 32) * 256 * 4;   // keys + per-warp histograms

@@ -63,7 +63,8 @@ def test_host_side_validation_needs_no_gpu():
     f.D, f.dtype = 128, 2
     assert lib.mxb_flash_prefill(C.byref(f), None) == -1
     assert b"head_dim=256" in lib.mxb_last_error()
-    assert lib.mxb_topk_workspace_bytes(2, 131072, 2048) >= 2 * 131072 * 8
+    assert lib.mxb_topk_workspace_bytes(2, 131072, 2048) == 0            # one cluster per row, keys in shared memory
+    assert lib.mxb_topk_workspace_bytes(2, 1 << 20, 2048) >= 2 * (1 << 20) * 8
     assert lib.mxb_topk_workspace_bytes(4096, 32768, 2048) == 0
 
 

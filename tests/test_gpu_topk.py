@@ -51,6 +51,17 @@ def test_long_rows(n, k, rows):
     _check(rng.standard_normal((rows, n)).astype(np.float32), k)
 
 
+@pytest.mark.parametrize("n,k,rows", [(16384, 1, 1), (16385, 2048, 1), (100003, 8192, 2), (360448, 2048, 1),
+                                      (360449, 2048, 1), (20000, 512, 80)])
+def test_kernel_boundaries(n, k, rows):
+    """Shapes either side of the switches between the one-CTA, cluster and multi-launch kernels."""
+    need_gpu()
+    rng = np.random.default_rng(n * 3 + k)
+    s = rng.standard_normal((rows, n)).astype(np.float32)
+    s[:, ::97] = s[:, 5:6]                                                    # a value repeated across all parts
+    _check(s, k)
+
+
 def test_long_rows_ties():
     need_gpu()
     rng = np.random.default_rng(4)
