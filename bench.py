@@ -232,13 +232,48 @@ def main():
     barrier()
     ms_step = max_over_ranks(e0.elapsed_time(e1) / K)
 
-    # ---- per-kernel durations: the same K steps launched eagerly with CUDA events around every entry point
-    _torchabi.TIMER = {}
-    for _ in range(K):
-        sparse_decode_step(q_d, iq_d, iw_d, cache, k=kk, scale=scale, d_v=d_v)
+    # ---- per-stage device time: each entry point captured as its own CUDA graph and replayed K times between two
+    # events (no host gaps inside the timed region; the 167 MB key table alone exceeds L2 between replays)
+    lib = _abi.load()
+    launches0 = int(lib.mxb_kernel_launches())
+    out_e, ids_e, sc_e = sparse_decode_step(q_d, iq_d, iw_d, cache, k=kk, scale=scale, d_v=d_v, return_ids=True,
+                                            return_scores=True)
     torch.cuda.synchronize()
-    timer, _torchabi.TIMER = _torchabi.TIMER, None
-    stage_ms = {name: float(np.mean([a.elapsed_time(b) for a, b in evs])) for name, evs in timer.items()}
+    kernels_per_step = int(lib.mxb_kernel_launches()) - launches0   # counted by the library itself
+
+    def stage_us(fn) -> float:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                fn()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(K):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / K * 1e3
+
+    stage = {
+        "indexer_scores": stage_us(lambda: indexer_scores(
+            iq_d[:, :, None, :], iw_d[:, None, :].contiguous(), cache.idx_keys, n_rows=cache.max_rows,
+            row_start=cache.row_start, row_count=cache.row_count)),
+        "topk_select": stage_us(lambda: topk_select(sc_e, kk, valid=cache.row_count, row_start=cache.row_start,
+                                                    n=cache.max_rows)),
+        "sparse_attn": stage_us(lambda: sparse_attention(
+            q_d[:, :, None, :], cache.kv, ids_e[:, None, :], None, pos0=0, window=0, ratio=0, scale=scale, d_v=d_v,
+            kv_scales=cache.kv_scales, comp_row_start=cache.row_start, comp_row_count=cache.row_count,
+            n_comp=cache.max_rows)),
+    }
 
     # ---- end to end: pinned host inputs -> device -> step -> result back on the host, every step
     for _ in range(2):
@@ -266,7 +301,10 @@ def main():
     hbm, tf, which = measured_peaks()
     # algorithmic bytes of the dominant kernel (indexer score scan): FP8 keys read once, fp32 scores written once
     idx_bytes = total * 64 + total * 4 + B * (16 * 64 * 2 + 16 * 4)
-    achieved = idx_bytes / (stage_ms["indexer_scores"] * 1e-3) / 1e9
+    achieved = idx_bytes / (stage["indexer_scores"] * 1e-6) / 1e9
+    # DRAM traffic of the same kernel from one ncu capture on the --small case (profiles/): 64.2 B read and
+    # 3.4 B written per key row, i.e. the algorithmic bytes; scaled to this launch by its row count
+    traffic = total * (64.2 + 3.4)
     step_bytes = idx_bytes + total * 4 + B * (kk * (576 + 2) + 64 * 576 * 2 + 64 * d_v * 4 + kk * 4 * 2)
 
     line = {
@@ -281,11 +319,13 @@ def main():
         "e2e": {"value": world * B / (ms_e2e * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": int(q_h.numel() * 2 + iq_h.numel() * 2 + iw_h.numel() * 4),
                 "d2h_bytes_per_step": int(out_h.numel() * 4), "ms_per_step": ms_e2e},
-        "gpu_launches": 6 * K,
-        "launch": "one CUDA graph per step (6 kernels + 1 memset)" if not args.no_graph else "eager",
-        "entry_point_ms": stage_ms,
+        "gpu_launches": kernels_per_step * K,
+        "launch": (f"one CUDA graph per step ({kernels_per_step} kernels of this library)" if not args.no_graph
+                   else f"eager ({kernels_per_step} kernels of this library per step)"),
+        "stage_us": stage,
         "roofline": {"bound": "hbm", "kernel": "indexer_decode_kernel<64, 16 heads>", "achieved": achieved, "peak": hbm,
-                     "unit": "GB/s", "frac": achieved / hbm, "peak_source": which, "traffic": None,
+                     "unit": "GB/s", "frac": achieved / hbm, "peak_source": which, "traffic": traffic,
+                     "algorithmic_bytes": idx_bytes, "launch_us": stage["indexer_scores"],
                      "frac_of_nominal_8TBs": achieved / 8000.0,
                      "whole_step_GBs": step_bytes / (ms_step * 1e-3) / 1e9},
         "clocks": clocks,

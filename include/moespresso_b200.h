@@ -48,6 +48,9 @@ typedef enum {
 
 int mxb_abi_version(void);
 const char* mxb_last_error(void);
+/* Kernels this library has enqueued so far in this process (launches recorded into a CUDA graph count once,
+ * when captured).  For benchmarks and tests that want to see that the device path ran. */
+int64_t mxb_kernel_launches(void);
 
 /* ------------------------------------------------------------------------ *
  * Indexer score.

@@ -79,6 +79,7 @@ class FlashPrefillArgs(C.Structure):
 EXPORTS = {
     "mxb_abi_version": (C.c_int, []),
     "mxb_last_error": (C.c_char_p, []),
+    "mxb_kernel_launches": (C.c_int64, []),
     "mxb_indexer_scores": (C.c_int, [C.POINTER(IndexerScoresArgs), _p]),
     "mxb_topk_workspace_bytes": (_i64, [_i32, _i64, _i32]),
     "mxb_topk_select": (C.c_int, [C.POINTER(TopkArgs), _p]),

@@ -31,6 +31,8 @@ __host__ __device__ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + 
 __host__ __device__ inline int64_t round_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
 
 int sm_count();
+void note_launch(int n = 1);   // counts kernels enqueued by this library (mxb_kernel_launches)
+
 
 // ---- element loads as float -------------------------------------------------
 template <int DT>

@@ -360,6 +360,7 @@ extern "C" int mxb_flash_prefill(const mxb_flash_prefill_args* a, void* stream) 
   {
     dim3 blk(32, 8);
     dim3 grd((unsigned)ceil_div(Skv_pad, 32), (unsigned)ceil_div(a->D, 32), (unsigned)a->Hkv);
+    note_launch();
     transpose_v_kernel<<<grd, blk, 0, st>>>(reinterpret_cast<const uint16_t*>(a->v), a->v_stride_s, a->v_stride_h,
                                             reinterpret_cast<uint16_t*>(a->workspace), a->Skv, Skv_pad, a->D);
     MXB_CUDA_OK(cudaGetLastError());
@@ -407,9 +408,11 @@ extern "C" int mxb_flash_prefill(const mxb_flash_prefill_args* a, void* stream) 
   if (a->dtype == MXB_BF16) {
     MXB_CUDA_OK(cudaFuncSetAttribute(flash_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     flash_prefill_kernel<true><<<grid, 224, smem, st>>>(tq, tk, tv, p);
+    note_launch();
   } else {
     MXB_CUDA_OK(cudaFuncSetAttribute(flash_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     flash_prefill_kernel<false><<<grid, 224, smem, st>>>(tq, tk, tv, p);
+    note_launch();
   }
   MXB_CUDA_OK(cudaGetLastError());
   return MXB_OK;

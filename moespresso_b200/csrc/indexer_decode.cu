@@ -252,6 +252,7 @@ static int launch_decode_nt(DecodeIdxParams& p, cudaStream_t st) {
   const int64_t most = ceil_div(p.n_rows * p.B, (int64_t)kDecCtaRows);
   if (ctas > most) ctas = most;
   kern<<<(unsigned)ctas, kDecWarps * 32, smem, st>>>(p);
+  note_launch();
   MXB_CUDA_OK(cudaGetLastError());
   return MXB_OK;
 }

@@ -106,6 +106,7 @@ static int launch_exact(IndexerParams& p, cudaStream_t st) {
   if (smem > 48 * 1024) MXB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid((unsigned)ceil_div(p.n_rows, 128), (unsigned)ceil_div(p.T, t_tile), (unsigned)p.B);
   kern<<<grid, 128, smem, st>>>(p);
+  note_launch();
   MXB_CUDA_OK(cudaGetLastError());
   return MXB_OK;
 }

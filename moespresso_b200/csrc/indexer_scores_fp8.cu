@@ -459,6 +459,7 @@ static int launch_fp8_d(Fp8Params& p, const mxb_indexer_scores_args* a, cudaStre
   MXB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid((unsigned)ceil_div(p.n_rows, p.rows_per_cta), (unsigned)t_tiles, (unsigned)p.B);
   kern<<<grid, C::kThreads, smem, st>>>(tmap, p);
+  note_launch();
   MXB_CUDA_OK(cudaGetLastError());
   return MXB_OK;
 }

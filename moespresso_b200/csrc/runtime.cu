@@ -4,6 +4,8 @@
 #include <cstdio>
 #include <mutex>
 
+#include <atomic>
+
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
@@ -78,5 +80,11 @@ int make_tensor_map(CUtensorMap* out, CUtensorMapDataType dt, int rank, const vo
 
 }  // namespace mxb
 
+namespace mxb {
+static std::atomic<long long> g_launches{0};
+void note_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+}  // namespace mxb
+
+extern "C" int64_t mxb_kernel_launches(void) { return mxb::g_launches.load(std::memory_order_relaxed); }
 extern "C" int mxb_abi_version(void) { return MXB_ABI_VERSION; }
 extern "C" const char* mxb_last_error(void) { return mxb::g_err; }

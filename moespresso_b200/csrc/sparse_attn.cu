@@ -278,6 +278,7 @@ static int launch_merge(const MergeParams& mp, int out_dtype, cudaStream_t st) {
   else if (out_dtype == MXB_BF16) { MXB_MG(MXB_BF16) }
   else { MXB_MG(MXB_F16) }
 #undef MXB_MG
+  note_launch();
   MXB_CUDA_OK(cudaGetLastError());
   return MXB_OK;
 }
@@ -312,6 +313,7 @@ static int launch_sparse(SparseParams& p, int out_dtype, size_t smem, dim3 grid,
   else if (out_dtype == MXB_BF16) MXB_SP(MXB_BF16)
   else MXB_SP(MXB_F16)
 #undef MXB_SP
+  note_launch();
   MXB_CUDA_OK(cudaGetLastError());
   return MXB_OK;
 }

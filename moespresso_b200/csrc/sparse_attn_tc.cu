@@ -25,6 +25,7 @@
 #include "ptx_sm100.cuh"
 #include "sparse_attn.cuh"
 
+
 namespace mxb {
 
 #ifdef MXB_TRACE_SP
@@ -35,7 +36,14 @@ namespace mxb {
 
 constexpr int TC_ROWS = 128;
 constexpr int TC_HEADS = 64;
-constexpr float kRescaleGap = 8.f;  // log2 units
+// The running reference m_ref of a head moves only when a score exceeds it by more than a gap (log2 units):
+// P = 2^(s - m_ref) may then be as large as 2^gap.  bf16 operands have fp32's range; fp16 operands top out at
+// 65504, and the int8 path folds the row's dequantisation scale into P, so its gap shrinks by log2(scale) when
+// that is positive.
+constexpr float kRescaleGapF16 = 15.f;
+constexpr float kRescaleGapBF16 = 60.f;
+
+constexpr int kTcMiscBytes = 8192;   // reserved for TcMisc
 
 struct TcLayout {
   int nslab;       // Dqk / 64
@@ -59,7 +67,7 @@ __host__ __device__ inline TcLayout tc_layout(int Dqk, int Dv) {
     end += 16384;
   }
   L.misc_off = end;
-  L.total = end + 8192;
+  L.total = end + kTcMiscBytes;
   return L;
 }
 
@@ -68,16 +76,18 @@ struct TcMisc {
   float factor[TC_HEADS];
   float colmax[4][TC_HEADS];
   float l_tot[TC_HEADS];
-  float row_scale[3][TC_ROWS];          // per-tile row metadata, three deep: rows are resolved (ids -> addresses
-  const uint8_t* row_src[3][TC_ROWS];   // -> scales) two tiles ahead, so that the loads of the next tile can be
-                                        // issued as soon as the registers that carry them are free; null = no row
+  float row_scale[3][TC_ROWS];   // per-tile row metadata, three deep: rows are resolved (ids -> addresses -> scales)
+  uint32_t row_ref[3][TC_ROWS];  // two tiles ahead, so that the loads of the next tile can be issued as soon as the
+                                 // registers that carry them are free.  row_ref: kNoRow, or row index within its
+                                 // table (< 2^31) with bit 31 set for the raw table
   uint64_t bar_s, bar_o;
   uint32_t tmem_slot;
   int abort_flag;
   int keff;
 };
 
-static_assert(sizeof(TcMisc) <= 8192, "TcMisc must fit the 8 KB the layout reserves for it");
+constexpr uint32_t kNoRow = 0xFFFFFFFFu;
+static_assert(sizeof(TcMisc) <= kTcMiscBytes, "TcMisc must fit the bytes the layout reserves for it");
 
 // 16 int8 -> 16 fp16 integers (exact): bytes biased by 128 are dropped into the mantissa of 1024.0
 __device__ __forceinline__ void widen_i8x16_f16(const uint4& in, uint4& lo, uint4& hi) {
@@ -118,6 +128,31 @@ __device__ __forceinline__ float from_op16(uint16_t u) {
   if constexpr (BF16) return __bfloat162float(*reinterpret_cast<__nv_bfloat16*>(&u));
   else return __half2float(*reinterpret_cast<__half*>(&u));
 }
+
+// Two floats -> two operand-type values in one register (low half = a), and what they round back to.
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack_op16x2(float a, float b, float& back_a, float& back_b) {
+  if constexpr (BF16) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    const float2 f = __bfloat1622float2(v);
+    back_a = f.x;
+    back_b = f.y;
+    return *reinterpret_cast<const uint32_t*>(&v);
+  } else {
+    const __half2 v = __floats2half2_rn(a, b);
+    const float2 f = __half22float2(v);
+    back_a = f.x;
+    back_b = f.y;
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+}
+
+// order-preserving map between floats (no NaN) and signed integers
+__device__ __forceinline__ int float_order(float x) {
+  const int i = __float_as_int(x);
+  return i ^ ((i >> 31) & 0x7fffffff);
+}
+__device__ __forceinline__ float order_float(int i) { return __int_as_float(i ^ ((i >> 31) & 0x7fffffff)); }
 
 template <int KVT, int QT, int OT>
 __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) {
@@ -188,8 +223,40 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = mi->tmem_slot;
   const uint32_t tmem_o = tmem_base + 64;
+  TRS(12, 0);
 
-  {  // first list entry that ends the walk
+  // q -> B operand of S^T: [64 heads x Dqk] K-major, 128-byte swizzle, rounded to the operand type.
+  // Item i = (head i % 64, 16-byte chunk i / 64): a warp writes 32 different rows, conflict-free stores.
+  const bool q_vec = ((reinterpret_cast<uintptr_t>(p.q) & 15) == 0) && (p.q_sb % 8 == 0) && (p.q_sh % 8 == 0) &&
+                     (p.q_st % 8 == 0);
+  const int n_items = TC_HEADS * (p.Dqk / 8);
+  auto store_q_item = [&](int i, const float* f) {
+    const int h = i & (TC_HEADS - 1), c = i >> 6;
+    uint32_t w[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float b0, b1;
+      w[e] = pack_op16x2<BF16>(f[2 * e], f[2 * e + 1], b0, b1);
+    }
+    const int kb = c >> 3, cc = c & 7;
+    *reinterpret_cast<uint4*>(q_s + (size_t)kb * 8192 + (size_t)h * 128 + ((cc ^ (h & 7)) << 4)) =
+        make_uint4(w[0], w[1], w[2], w[3]);
+  };
+  constexpr int kQB = 18;   // 16-bit q, vector path: this many 16-byte loads in flight per thread
+  uint4 qraw[kQB];
+  const bool q_fast = q_vec && QT != MXB_F32;
+  if (q_fast) {
+#pragma unroll
+    for (int j = 0; j < kQB; ++j) {
+      const int i = tid + j * 256;
+      const int h = i & (TC_HEADS - 1), c = i >> 6;
+      qraw[j] = make_uint4(0, 0, 0, 0);
+      if (i < n_items && h < p.H)
+        qraw[j] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.q) + (int64_t)b * p.q_sb +
+                                                       (int64_t)h * p.q_sh + (int64_t)t * p.q_st + c * 8));
+    }
+  }
+  {  // first list entry that ends the walk (its loads overlap the q loads above)
     int mine = p.k;
 #pragma unroll 4
     for (int j = tid; j < p.k; j += 256) {   // no early exit: the loads stay independent
@@ -198,55 +265,44 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
     }
     if (mine < p.k) atomicMin(&mi->keff, mine);
   }
-  // q -> B operand of S^T: [64 heads x Dqk] K-major, 128-byte swizzle, rounded to the operand type
-  {
-    const bool vec = ((reinterpret_cast<uintptr_t>(p.q) & 15) == 0) && (p.q_sb % 8 == 0) && (p.q_sh % 8 == 0) &&
-                     (p.q_st % 8 == 0);
-    // batches of kQB items per thread: all global loads of a batch are in flight before the first conversion
-    constexpr int kQB = 6;
-    const int n_items = TC_HEADS * (p.Dqk / 8);
-    for (int i0 = tid; i0 < n_items; i0 += 256 * kQB) {
-      float f[kQB][8];
+  TRS(12, 1);
+  if (q_fast) {
 #pragma unroll
-      for (int j = 0; j < kQB; ++j) {
-        const int i = i0 + j * 256;
-        const int h = i & (TC_HEADS - 1), c = i >> 6;   // a warp writes 32 different rows: conflict-free stores
-#pragma unroll
-        for (int e = 0; e < 8; ++e) f[j][e] = 0.f;
-        if (i < n_items && h < p.H) {
-          const int64_t base = (int64_t)b * p.q_sb + (int64_t)h * p.q_sh + (int64_t)t * p.q_st + c * 8;
-          if (vec) {
-            if constexpr (QT == MXB_F32) {
-              const float4 a = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + base));
-              const float4 bq = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + base) + 1);
-              f[j][0] = a.x; f[j][1] = a.y; f[j][2] = a.z; f[j][3] = a.w;
-              f[j][4] = bq.x; f[j][5] = bq.y; f[j][6] = bq.z; f[j][7] = bq.w;
-            } else {
-              const uint4 u = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.q) + base));
-              unpack16<QT>(u, f[j]);
-            }
-          } else {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) f[j][e] = load_elem<QT>(p.q, base + e);
-          }
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < kQB; ++j) {
-        const int i = i0 + j * 256;
-        if (i < n_items) {
-          const int h = i & (TC_HEADS - 1), c = i >> 6;
-          alignas(16) uint16_t v[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) v[e] = to_op16<BF16>(f[j][e]);
-          const int kb = c >> 3, cc = c & 7;
-          *reinterpret_cast<uint4*>(q_s + (size_t)kb * 8192 + (size_t)h * 128 + ((cc ^ (h & 7)) << 4)) =
-              *reinterpret_cast<uint4*>(v);
-        }
+    for (int j = 0; j < kQB; ++j) {
+      const int i = tid + j * 256;
+      if (i < n_items) {
+        float f[8];
+        if constexpr (QT != MXB_F32) unpack16<QT>(qraw[j], f);
+        store_q_item(i, f);
       }
     }
   }
+  for (int i = tid + (q_fast ? kQB * 256 : 0); i < n_items; i += 256) {   // wide rows, fp32 q, unaligned q
+    const int h = i & (TC_HEADS - 1), c = i >> 6;
+    float f[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = 0.f;
+    if (h < p.H) {
+      const int64_t base = (int64_t)b * p.q_sb + (int64_t)h * p.q_sh + (int64_t)t * p.q_st + c * 8;
+      if (q_vec) {
+        if constexpr (QT == MXB_F32) {
+          const float4 a = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + base));
+          const float4 bq = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + base) + 1);
+          f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = bq.x; f[5] = bq.y; f[6] = bq.z; f[7] = bq.w;
+        } else {
+          const uint4 u = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.q) + base));
+          unpack16<QT>(u, f);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = load_elem<QT>(p.q, base + e);
+      }
+    }
+    store_q_item(i, f);
+  }
+  TRS(12, 2);
   __syncthreads();
+  TRS(12, 3);
   const int total = n_raw + mi->keff;
   int per = (total + p.nsplit - 1) / p.nsplit;
   per = ((per + TC_ROWS - 1) / TC_ROWS) * TC_ROWS;
@@ -275,47 +331,65 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
   const int ncg = (nch + 3) / 4;   // groups of 4 chunks per row
   const int r8 = lane & 7, cl = lane >> 3;
 
-  // warps 1-7 resolve the 128 rows of the tile starting at list entry `te0` (ids -> addresses -> scales) into
-  // metadata buffer `buf` and pull the rows towards L2; warp 0 is busy issuing the QK MMAs meanwhile
-  auto resolve_tile = [&](int te0, int buf) {
-    const int rr = (warp - 1) + 7 * lane;
-    if (warp >= 1 && rr < TC_ROWS) {
-      const int e = te0 + rr;
-      const uint8_t* src = nullptr;
-      float rs = 1.f;
-      if (e < e_hi) {
-        if (e < n_raw) {
-          const int64_t pabs = first + e;
-          const int64_t phys = ((int64_t)p.raw_start + (pabs - first_raw_pos)) % p.raw_cap;
-          const int64_t ridx = (int64_t)b * p.raw_cap + phys;
-          src = reinterpret_cast<const uint8_t*>(p.raw_kv) + ridx * p.Dqk * EB;
-          if (KVT == MXB_I8) rs = __half2float(p.raw_scales[ridx]);
-        } else {
-          const int32_t id = ids[e - n_raw];
-          if (id >= 0) {
-            const int64_t ridx = cbase + id;
-            src = reinterpret_cast<const uint8_t*>(p.comp_kv) + ridx * p.Dqk * EB;
-            if (KVT == MXB_I8) rs = __half2float(p.comp_scales[ridx]);
-          }
-        }
-      }
-      if (src) {
-        const int row_bytes = p.Dqk * EB;
-        for (int off = 0; off < row_bytes; off += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(src + off));
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(src + row_bytes - 1));
-      }
-      mi->row_src[buf][rr] = src;
-      mi->row_scale[buf][rr] = rs;
+  // Row metadata (list id -> row address -> dequantisation scale) is a chain of dependent global loads.  Warps
+  // 1-7 (warp 0 issues the QK MMAs) run it as a pipeline, one stage per tile iteration, so that nobody ever
+  // waits on it: stage A fetches the list id, stage B turns it into the address, fetches the scale and pulls
+  // the row towards L2, and the last stage publishes both in shared memory, two tiles before they are needed.
+  const int rr_res = (warp - 1) + 7 * lane;
+  const bool resolver = warp >= 1 && rr_res < TC_ROWS;
+  auto fetch_id = [&](int T) -> int32_t {   // -1: no compressed row behind this slot
+    if (!resolver || T >= ntiles) return -1;
+    const int e = e_lo + T * TC_ROWS + rr_res;
+    return (e < e_hi && e >= n_raw) ? ids[e - n_raw] : -1;
+  };
+  auto fetch_row = [&](int T, int32_t id, uint32_t& ref, float& rs) {
+    const uint8_t* src = nullptr;
+    ref = kNoRow;
+    rs = 1.f;
+    if (!resolver || T >= ntiles) return;
+    const int e = e_lo + T * TC_ROWS + rr_res;
+    if (e >= e_hi) return;
+    if (e < n_raw) {
+      const int64_t pabs = first + e;
+      const int64_t phys = ((int64_t)p.raw_start + (pabs - first_raw_pos)) % p.raw_cap;
+      const int64_t ridx = (int64_t)b * p.raw_cap + phys;
+      src = reinterpret_cast<const uint8_t*>(p.raw_kv) + ridx * p.Dqk * EB;
+      ref = (uint32_t)ridx | 0x80000000u;
+      if (KVT == MXB_I8) rs = __half2float(p.raw_scales[ridx]);
+    } else if (id >= 0) {
+      const int64_t ridx = cbase + id;
+      src = reinterpret_cast<const uint8_t*>(p.comp_kv) + ridx * p.Dqk * EB;
+      ref = (uint32_t)ridx;
+      if (KVT == MXB_I8) rs = __half2float(p.comp_scales[ridx]);
+    }
+    if (src) {
+      const int row_bytes = p.Dqk * EB;
+      for (int off = 0; off < row_bytes; off += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(src + off));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(src + row_bytes - 1));
     }
   };
+  auto publish_row = [&](int T, uint32_t ref, float rs) {
+    if (resolver && T < ntiles) {
+      mi->row_ref[T % 3][rr_res] = ref;
+      mi->row_scale[T % 3][rr_res] = rs;
+    }
+  };
+  auto row_address = [&](uint32_t ref) -> const uint8_t* {
+    if (ref == kNoRow) return nullptr;
+    const uint8_t* base = reinterpret_cast<const uint8_t*>((ref >> 31) ? p.raw_kv : p.comp_kv);
+    return base + (int64_t)(ref & 0x7FFFFFFFu) * (p.Dqk * EB);
+  };
+  int32_t id_a = -1;          // stage A result: list id of this lane's row of tile it + 3
+  uint32_t src_b = kNoRow;    // stage B result: row and scale of this lane's row of tile it + 2
+  float rs_b = 1.f;
   // Raw rows travel through registers: 18 independent 16-byte loads per lane (9 groups of 4 chunks for
   // each of the lane's two rows).  The loads of the NEXT tile are issued right after this tile's QK MMAs
   // and land during its softmax and PV; only the widening and the shared-memory stores stay on the
   // critical path.
   uint4 v[18];
   auto issue_loads = [&](int mbuf, int cg0) {
-    const uint8_t* src_lo = mi->row_src[mbuf][warp * 16 + r8];
-    const uint8_t* src_hi = mi->row_src[mbuf][warp * 16 + 8 + r8];
+    const uint8_t* src_lo = row_address(mi->row_ref[mbuf][warp * 16 + r8]);
+    const uint8_t* src_hi = row_address(mi->row_ref[mbuf][warp * 16 + 8 + r8]);
 #pragma unroll
     for (int i = 0; i < 18; ++i) {
       const int c = (cg0 + (i >> 1)) * 4 + cl;
@@ -346,14 +420,24 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
     }
   };
   if (ntiles > 0) {
-    resolve_tile(e_lo, 0);
+    // prime the pipeline: tiles 0 and 1 published, tile 2 through stage B, tile 3 through stage A
+    const int32_t i0 = fetch_id(0), i1 = fetch_id(1), i2 = fetch_id(2);
+    id_a = fetch_id(3);
+    uint32_t s0, s1;
+    float r0, r1;
+    fetch_row(0, i0, s0, r0);
+    fetch_row(1, i1, s1, r1);
+    fetch_row(2, i2, src_b, rs_b);
+    publish_row(0, s0, r0);
+    publish_row(1, s1, r1);
+    TRS(12, 4);
     __syncthreads();
+    TRS(12, 5);
     issue_loads(0, 0);
-    if (ntiles > 1) resolve_tile(e_lo + TC_ROWS, 1);
+    TRS(12, 6);
   }
 
   for (int it = 0; it < ntiles; ++it) {
-    const int e0 = e_lo + it * TC_ROWS;
     TRS(0, it);
     // ---------------------------------------------------------------- rows of this tile -> operand layout
     const int mb = it % 3;   // metadata buffer of this tile (filled two tiles ago, or before the loop)
@@ -368,6 +452,13 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
 
     // ---------------------------------------------------------------- S^T = Ktile . Q^T
     TRS(1, it);
+    // While the MMAs are issued and run: one step of the metadata pipeline (nothing in it waits), then the next
+    // tile's rows start travelling into registers; the threads sit in that while the load queue drains, which
+    // is dead time anyway.  The issuing thread takes its own branch so that the other 31 lanes of its warp can
+    // queue their loads while it feeds the tensor core.
+    publish_row(it + 2, src_b, rs_b);
+    fetch_row(it + 3, id_a, src_b, rs_b);
+    id_a = fetch_id(it + 4);
     if (tid == 0) {
       ptx::tc_fence_after_sync();
       for (int kb = 0; kb < nslab; ++kb) {
@@ -379,12 +470,10 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
       }
       ptx::mma_commit(&mi->bar_s);
       TRS(2, it);
+      if (it + 1 < ntiles) issue_loads((it + 1) % 3, 0);
+    } else {
+      if (it + 1 < ntiles) issue_loads((it + 1) % 3, 0);
     }
-    // While the MMAs are issued and run: the next tile's rows start travelling into registers (their metadata
-    // was resolved a tile ago; the threads sit here while the load queue drains, which is dead time anyway),
-    // and warps 1-7 resolve the tile after that.
-    if (it + 1 < ntiles) issue_loads((it + 1) % 3, 0);
-    if (it + 2 < ntiles) resolve_tile(e0 + 2 * TC_ROWS, (it + 2) % 3);
     ptx::mbar_wait(&mi->bar_s, (uint32_t)(it & 1), abort_flag);
     ptx::tc_fence_after_sync();
 
@@ -395,22 +484,27 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
     uint32_t sv[32];
     ptx::tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)col0, sv);
     ptx::tmem_ld_wait();
-    const bool ok = mi->row_src[mb][row] != nullptr;
+    TRS(8, it);
+    const bool ok = mi->row_ref[mb][row] != kNoRow;
     const float rs = mi->row_scale[mb][row];
     const float mul = scale_log2 * rs;
+    float gap = BF16 ? kRescaleGapBF16 : kRescaleGapF16;
+    if (KVT == MXB_I8 && rs > 1.f) gap -= log2f(rs);
     bool grow = false;
 #pragma unroll
     for (int c = 0; c < 32; ++c) {
       const float x = ok ? __uint_as_float(sv[c]) * mul : -INFINITY;
       sv[c] = __float_as_uint(x);
-      grow |= x > mi->m_ref[col0 + c] + kRescaleGap;
+      grow |= x > mi->m_ref[col0 + c] + gap;
     }
+    TRS(9, it);
     if (__syncthreads_or(grow ? 1 : 0)) {
       // exact column maxima of this tile, new reference, rescale of what has been accumulated
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
-        const float mx = warp_max(__uint_as_float(sv[c]));
-        if (lane == c) mi->colmax[quad][col0 + c] = mx;
+        // one integer warp reduction per column on an order-preserving image of the float
+        const int o = __reduce_max_sync(0xffffffffu, float_order(__uint_as_float(sv[c])));
+        if (lane == c) mi->colmax[quad][col0 + c] = order_float(o);
       }
       __syncthreads();
       if (tid < TC_HEADS) {
@@ -443,22 +537,31 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
         ptx::tmem_st_wait();
       }
     }
+    TRS(10, it);
     {
       const float inv = 1.f / rs;
       const int slab = row >> 6, rj = row & 63;
       uint8_t* pbase = pt + (size_t)slab * 8192 + (rj & 7) * 2;
       const int cj = rj >> 3;
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
+      for (int c = 0; c < 32; c += 2) {   // two heads per step: one packed conversion each way
         const int h = col0 + c;
-        const float s = __uint_as_float(sv[c]);
-        const float pj = (s == -INFINITY) ? 0.f : fast_exp2(s - mi->m_ref[h]);
-        const uint16_t pr = to_op16<BF16>(KVT == MXB_I8 ? pj * rs : pj);
-        const float back = from_op16<BF16>(pr);
-        l_thr[c] += (KVT == MXB_I8) ? back * inv : back;
-        *reinterpret_cast<uint16_t*>(pbase + (size_t)h * 128 + ((cj ^ (h & 7)) << 4)) = pr;
+        const float s0 = __uint_as_float(sv[c]), s1 = __uint_as_float(sv[c + 1]);
+        float p0 = (s0 == -INFINITY) ? 0.f : fast_exp2(s0 - mi->m_ref[h]);
+        float p1 = (s1 == -INFINITY) ? 0.f : fast_exp2(s1 - mi->m_ref[h + 1]);
+        if (KVT == MXB_I8) {
+          p0 *= rs;
+          p1 *= rs;
+        }
+        float b0, b1;
+        const uint32_t pr = pack_op16x2<BF16>(p0, p1, b0, b1);
+        l_thr[c] += (KVT == MXB_I8) ? b0 * inv : b0;
+        l_thr[c + 1] += (KVT == MXB_I8) ? b1 * inv : b1;
+        *reinterpret_cast<uint16_t*>(pbase + (size_t)h * 128 + ((cj ^ (h & 7)) << 4)) = (uint16_t)(pr & 0xffffu);
+        *reinterpret_cast<uint16_t*>(pbase + (size_t)(h + 1) * 128 + ((cj ^ ((h + 1) & 7)) << 4)) = (uint16_t)(pr >> 16);
       }
     }
+    TRS(11, it);
     ptx::fence_proxy_async_smem();
     ptx::tc_fence_before_sync();
     __syncthreads();
@@ -486,15 +589,26 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
   }
 
   // ------------------------------------------------------------------ reduce l over the 128 rows
+  // Butterfly over the warp: at each step a lane keeps half of its columns and hands the other half to its
+  // partner, so 31 shuffles (not 32 x 5) leave lane L with the warp's sum of column L.
+  {
 #pragma unroll
-  for (int c = 0; c < 32; ++c) {
-    const float s = warp_sum(l_thr[c]);
-    if (lane == c) mi->colmax[quad][half_id * 32 + c] = s;
+    for (int step = 16; step >= 1; step >>= 1) {
+      const bool upper = (lane & step) != 0;
+#pragma unroll
+      for (int c = 0; c < step; ++c) {
+        const float send = upper ? l_thr[c] : l_thr[c + step];
+        const float keep = upper ? l_thr[c + step] : l_thr[c];
+        l_thr[c] = keep + __shfl_xor_sync(0xffffffffu, send, step);
+      }
+    }
+    mi->colmax[quad][half_id * 32 + lane] = l_thr[0];
   }
   __syncthreads();
   if (tid < TC_HEADS) mi->l_tot[tid] = (mi->colmax[0][tid] + mi->colmax[1][tid]) + (mi->colmax[2][tid] + mi->colmax[3][tid]);
   __syncthreads();
 
+  TRS(13, 0);
   // ------------------------------------------------------------------ output
   const int64_t N = (int64_t)p.B * p.T * p.H;
   const bool direct = p.nsplit == 1;
@@ -544,6 +658,7 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
       }
     }
   }
+  TRS(13, 1);
   if (tid < p.H && (!direct || p.partial_ml)) {
     // (m, l) in natural-log units for the merge kernel
     const float m_nat = mi->m_ref[tid] == -INFINITY ? -INFINITY : mi->m_ref[tid] * 0.6931471805599453f;
@@ -602,6 +717,7 @@ static int launch_tc_typed(SparseParams& p, int out_dtype, cudaStream_t st) {
   else if (out_dtype == MXB_BF16) MXB_TC(MXB_BF16)
   else MXB_TC(MXB_F16)
 #undef MXB_TC
+  note_launch();
   MXB_CUDA_OK(cudaGetLastError());
   return MXB_OK;
 }

@@ -29,9 +29,8 @@ namespace mxb {
 constexpr int kCThreads = 512;
 constexpr int kCWarps = kCThreads / 32;
 constexpr int kCMaxCluster = 8;                 // portable cluster size
-constexpr int kCPartUnit = kCThreads;           // parts are multiples of 16 warps x 32 lanes
+constexpr int kCPartUnit = kCThreads * 4;       // parts are multiples of 16 warps x 32 lanes x 4 keys
 constexpr int kCPartMax = 45056;                // keys per CTA (176 KB)
-constexpr int kCLoadUnroll = 8;
 
 struct TopkClusterParams {
   const float* scores;
@@ -93,27 +92,43 @@ __global__ void __launch_bounds__(kCThreads) topk_cluster_kernel(TopkClusterPara
   const int part = (int)round_up(ceil_div(n_row, (int64_t)cs), (int64_t)kCPartUnit);   // <= kCPartMax (host)
   const int64_t lo = (int64_t)rank * part;
   const int cnt = (int)(n_row - lo < 0 ? 0 : (n_row - lo > part ? part : n_row - lo));
-  const int wchunk = part / kCWarps;          // ids of one warp: [wbase, wbase + wchunk), lanes interleaved
-  const int iters = wchunk / 32;              // same for every thread of the cluster
-  const int wbase = warp * wchunk;
+  const int wchunk = part / kCWarps;          // ids of one warp: [wbase, wbase + wchunk)
+  const int iters = wchunk / 128;             // same for every thread of the cluster; a lane owns 4 consecutive ids
+  const int wbase = warp * wchunk + lane * 4;
   const float* src = p.scores + (p.row_start ? p.row_start[row] : (int64_t)row * p.row_stride) + lo;
+  const bool src_vec = (reinterpret_cast<uintptr_t>(src) & 15) == 0;
   int32_t* out = p.out_ids + (int64_t)row * p.k;
 
   TRC(1);
   // ---- digit 1 (top 11 bits) while loading
-  for (int it0 = 0; it0 < iters; it0 += kCLoadUnroll) {
-    float x[kCLoadUnroll];
+  for (int it0 = 0; it0 < iters; it0 += 2) {
+    float x[2][4];
 #pragma unroll
-    for (int u = 0; u < kCLoadUnroll; ++u) {
-      const int e = wbase + (it0 + u) * 32 + lane;
-      x[u] = (it0 + u < iters && e < cnt) ? __ldg(src + e) : -INFINITY;
+    for (int u = 0; u < 2; ++u) {
+      const int e = wbase + (it0 + u) * 128;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) x[u][j] = -INFINITY;
+      if (it0 + u < iters) {
+        if (src_vec && e + 3 < cnt) {
+          const float4 v = __ldg(reinterpret_cast<const float4*>(src + e));
+          x[u][0] = v.x; x[u][1] = v.y; x[u][2] = v.z; x[u][3] = v.w;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (e + j < cnt) x[u][j] = __ldg(src + e + j);
+        }
+      }
     }
 #pragma unroll
-    for (int u = 0; u < kCLoadUnroll; ++u) {
+    for (int u = 0; u < 2; ++u) {
       if (it0 + u < iters) {
-        const uint32_t key = score_key_full(x[u]);
-        keys[wbase + (it0 + u) * 32 + lane] = key;
-        if (key) atomicAdd(&lhist[key >> 21], 1u);
+        uint32_t k4[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          k4[j] = score_key_full(x[u][j]);
+          if (k4[j]) atomicAdd(&lhist[k4[j] >> 21], 1u);
+        }
+        *reinterpret_cast<uint4*>(&keys[wbase + (it0 + u) * 128]) = make_uint4(k4[0], k4[1], k4[2], k4[3]);
       }
     }
   }
@@ -136,8 +151,11 @@ __global__ void __launch_bounds__(kCThreads) topk_cluster_kernel(TopkClusterPara
 
   // ---- digit 2 (next 11 bits) among keys in the threshold bin
   for (int it = 0; it < iters; ++it) {
-    const uint32_t key = keys[wbase + it * 32 + lane];
-    if ((key >> 21) == bin1) atomicAdd(&lhist[(key >> 10) & 2047u], 1u);   // valid keys are >= 0x00800000, bin1 >= 4
+    const uint4 k4 = *reinterpret_cast<const uint4*>(&keys[wbase + it * 128]);
+    const uint32_t kk[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j)   // valid keys are >= 0x00800000, so bin1 >= 4 and key 0 never matches
+      if ((kk[j] >> 21) == bin1) atomicAdd(&lhist[(kk[j] >> 10) & 2047u], 1u);
   }
   __syncthreads();
   TRC(7);
@@ -150,8 +168,11 @@ __global__ void __launch_bounds__(kCThreads) topk_cluster_kernel(TopkClusterPara
 
   // ---- digit 3 (last 10 bits)
   for (int it = 0; it < iters; ++it) {
-    const uint32_t key = keys[wbase + it * 32 + lane];
-    if ((key >> 10) == prefix22) atomicAdd(&lhist[key & 1023u], 1u);
+    const uint4 k4 = *reinterpret_cast<const uint4*>(&keys[wbase + it * 128]);
+    const uint32_t kk[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if ((kk[j] >> 10) == prefix22) atomicAdd(&lhist[kk[j] & 1023u], 1u);
   }
   __syncthreads();
   TRC(9);
@@ -166,9 +187,9 @@ __global__ void __launch_bounds__(kCThreads) topk_cluster_kernel(TopkClusterPara
   // ---- counts of (greater, equal) keys per warp chunk, per CTA, per cluster
   uint32_t c_gt = 0, c_eq = 0;
   for (int it = 0; it < iters; ++it) {
-    const uint32_t key = keys[wbase + it * 32 + lane];
-    c_gt += key > thr;
-    c_eq += key == thr;
+    const uint4 k4 = *reinterpret_cast<const uint4*>(&keys[wbase + it * 128]);
+    c_gt += (k4.x > thr) + (k4.y > thr) + (k4.z > thr) + (k4.w > thr);
+    c_eq += (k4.x == thr) + (k4.y == thr) + (k4.z == thr) + (k4.w == thr);
   }
   c_gt = __reduce_add_sync(0xffffffffu, c_gt);
   c_eq = __reduce_add_sync(0xffffffffu, c_eq);
@@ -200,19 +221,34 @@ __global__ void __launch_bounds__(kCThreads) topk_cluster_kernel(TopkClusterPara
   }
 
   TRC(13);
-  // ---- ordered emission
+  // ---- ordered emission: ids ascend with (iteration, lane, slot), so the output slot of a selected id is
+  // (greater keys before it) + min(equal keys before it, need)
   if (c_gt == 0 && (c_eq == 0 || eq_run >= need)) return;   // nothing of this warp's chunk is selected
   const uint32_t lt = (1u << lane) - 1u;
   for (int it = 0; it < iters; ++it) {
-    const int e = wbase + it * 32 + lane;
-    const uint32_t key = keys[e];
-    const bool gt = key > thr, eq = key == thr;
-    const uint32_t m_gt = __ballot_sync(0xffffffffu, gt);
-    const uint32_t m_eq = __ballot_sync(0xffffffffu, eq);
-    const uint32_t eq_ord = eq_run + __popc(m_eq & lt);
-    if (gt || (eq && eq_ord < need)) out[gt_run + __popc(m_gt & lt) + min(eq_ord, need)] = (int32_t)(lo + e);
-    gt_run += __popc(m_gt);
-    eq_run += __popc(m_eq);
+    const int e = wbase + it * 128;
+    const uint4 k4 = *reinterpret_cast<const uint4*>(&keys[e]);
+    const uint32_t kk[4] = {k4.x, k4.y, k4.z, k4.w};
+    uint32_t gt_below = 0, eq_below = 0, gt_all = 0, eq_all = 0;   // over lower lanes / over the whole warp
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t m_gt = __ballot_sync(0xffffffffu, kk[j] > thr);
+      const uint32_t m_eq = __ballot_sync(0xffffffffu, kk[j] == thr);
+      gt_below += __popc(m_gt & lt);
+      eq_below += __popc(m_eq & lt);
+      gt_all += __popc(m_gt);
+      eq_all += __popc(m_eq);
+    }
+    uint32_t g = gt_run + gt_below, q = eq_run + eq_below;   // counts before this lane's first key
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const bool gt = kk[j] > thr, eq = kk[j] == thr;
+      if (gt || (eq && q < need)) out[g + min(q, need)] = (int32_t)(lo + e + j);
+      g += gt;
+      q += eq;
+    }
+    gt_run += gt_all;
+    eq_run += eq_all;
   }
   TRC(14);
 }
@@ -258,6 +294,7 @@ int launch_topk_cluster(const mxb_topk_args* a, int cs, cudaStream_t st) {
   cfg.attrs = at;
   cfg.numAttrs = 1;
   MXB_CUDA_OK(cudaLaunchKernelEx(&cfg, topk_cluster_kernel, p));
+  note_launch();
   return MXB_OK;
 }
 

@@ -340,6 +340,7 @@ int launch_topk_multi(const mxb_topk_args* a, cudaStream_t st) {
   const size_t smem = words * 4 + (size_t)kFinishCandSmem * 8;
   MXB_CUDA_OK(cudaFuncSetAttribute(topk_mfinish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   topk_mfinish_kernel<<<a->rows, 1024, smem, st>>>(p, use_bitmap, sort_n);
+  note_launch(3);
   MXB_CUDA_OK(cudaGetLastError());
   return MXB_OK;
 }

@@ -337,6 +337,7 @@ extern "C" int mxb_topk_select(const mxb_topk_args* a, void* stream) {
     if (smem > 48 * 1024)
       MXB_CUDA_OK(cudaFuncSetAttribute(topk_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     topk_row_kernel<<<a->rows, threads, smem, st>>>(p);
+    note_launch();
     MXB_CUDA_OK(cudaGetLastError());
     return MXB_OK;
   }
@@ -406,6 +407,7 @@ extern "C" int mxb_topk_select_static(const mxb_topk_args* a, void* stream) {
   const size_t smem = (size_t)sort_n * 4 + (size_t)kCandSmem * 8;
   MXB_CUDA_OK(cudaFuncSetAttribute(topk_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   topk_stream_kernel<<<a->rows, 1024, smem, st>>>(p, sort_n);
+  note_launch();
   MXB_CUDA_OK(cudaGetLastError());
   return MXB_OK;
 }
