@@ -197,13 +197,13 @@ def main():
     iq_h = torch.from_numpy(c["idx_q"]).to(torch.bfloat16).pin_memory()
     iw_h = torch.from_numpy(c["idx_w"]).pin_memory()
     q_d, iq_d, iw_d = q_h.to(dev), iq_h.to(dev), iw_h.to(dev)
-    out_h = torch.empty((B, 64, d_v), dtype=torch.float32).pin_memory()
+    out_h = torch.empty((B, 64, d_v), dtype=torch.bfloat16).pin_memory()   # the step's result in the activation type
 
     from moespresso_b200 import _torchabi
     from moespresso_b200.deepseek_v4.decode_step import SparseDecodePlan, sparse_decode_step
 
     plan = SparseDecodePlan(cache, heads=64, d_qk=576, idx_heads=16, idx_dim=64, k=kk, scale=scale, d_v=d_v,
-                            q_dtype=torch.bfloat16, graph=not args.no_graph)
+                            q_dtype=torch.bfloat16, out_dtype=torch.bfloat16, graph=not args.no_graph)
     plan.load_inputs(q_d, iq_d, iw_d)
 
     def barrier():
@@ -237,7 +237,7 @@ def main():
     lib = _abi.load()
     launches0 = int(lib.mxb_kernel_launches())
     out_e, ids_e, sc_e = sparse_decode_step(q_d, iq_d, iw_d, cache, k=kk, scale=scale, d_v=d_v, return_ids=True,
-                                            return_scores=True)
+                                            return_scores=True, out_dtype=torch.bfloat16)
     torch.cuda.synchronize()
     kernels_per_step = int(lib.mxb_kernel_launches()) - launches0   # counted by the library itself
 
@@ -272,7 +272,7 @@ def main():
         "sparse_attn": stage_us(lambda: sparse_attention(
             q_d[:, :, None, :], cache.kv, ids_e[:, None, :], None, pos0=0, window=0, ratio=0, scale=scale, d_v=d_v,
             kv_scales=cache.kv_scales, comp_row_start=cache.row_start, comp_row_count=cache.row_count,
-            n_comp=cache.max_rows)),
+            n_comp=cache.max_rows, out_dtype=torch.bfloat16)),
     }
 
     # ---- end to end: pinned host inputs -> device -> step -> result back on the host, every step
@@ -305,7 +305,7 @@ def main():
     # DRAM traffic of the same kernel from one ncu capture on the --small case (profiles/): 64.2 B read and
     # 3.4 B written per key row, i.e. the algorithmic bytes; scaled to this launch by its row count
     traffic = total * (64.2 + 3.4)
-    step_bytes = idx_bytes + total * 4 + B * (kk * (576 + 2) + 64 * 576 * 2 + 64 * d_v * 4 + kk * 4 * 2)
+    step_bytes = idx_bytes + total * 4 + B * (kk * (576 + 2) + 64 * 576 * 2 + 64 * d_v * 2 + kk * 4 * 2)
 
     line = {
         "metric": METRIC, "value": world * B / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K,
@@ -318,7 +318,7 @@ def main():
                    "l2": "inputs (1.7 GB per GPU) exceed L2, no flush needed"},
         "e2e": {"value": world * B / (ms_e2e * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": int(q_h.numel() * 2 + iq_h.numel() * 2 + iw_h.numel() * 4),
-                "d2h_bytes_per_step": int(out_h.numel() * 4), "ms_per_step": ms_e2e},
+                "d2h_bytes_per_step": int(out_h.numel() * out_h.element_size()), "ms_per_step": ms_e2e},
         "gpu_launches": kernels_per_step * K,
         "launch": (f"one CUDA graph per step ({kernels_per_step} kernels of this library)" if not args.no_graph
                    else f"eager ({kernels_per_step} kernels of this library per step)"),

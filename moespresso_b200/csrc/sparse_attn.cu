@@ -226,32 +226,67 @@ __global__ void __launch_bounds__(256) merge_kernel(MergeParams p) {
   const int h = (int)(n % p.H);
   const int t = (int)((n / p.H) % p.T);
   const int b = (int)(n / ((int64_t)p.H * p.T));
-  float m = -INFINITY;
-  for (int s = 0; s < p.P; ++s) m = fmaxf(m, __ldg(p.ml_parts + ((int64_t)s * N + n) * 2));
   const float sink = (p.finalize && p.sinks) ? p.sinks[h] : -INFINITY;
-  m = fmaxf(m, sink);
-  float l = 0.f;
+  float m = -INFINITY, l = 0.f;
   float acc[VEC];
 #pragma unroll
   for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
-  if (m > -INFINITY) {
-    for (int s = 0; s < p.P; ++s) {
-      const float ms = __ldg(p.ml_parts + ((int64_t)s * N + n) * 2);
-      const float ls = __ldg(p.ml_parts + ((int64_t)s * N + n) * 2 + 1);
-      if (ms > -INFINITY) {
-        const float w = expf(ms - m);
-        l = fmaf(ls, w, l);
-        const float* src = p.o_parts + ((int64_t)s * N + n) * p.Dv + d0;
-        if constexpr (VEC == 4) {
-          const float4 v = __ldg(reinterpret_cast<const float4*>(src));
-          acc[0] = fmaf(v.x, w, acc[0]); acc[1] = fmaf(v.y, w, acc[1]);
-          acc[2] = fmaf(v.z, w, acc[2]); acc[3] = fmaf(v.w, w, acc[3]);
-        } else {
-          acc[0] = fmaf(__ldg(src), w, acc[0]);
-        }
+  constexpr int kFast = 8;
+  if (VEC == 4 && p.P <= kFast) {
+    // every load of the row is issued before anything depends on one: a single round trip to L2
+    float4 v[kFast];
+    float ms[kFast], ls[kFast];
+#pragma unroll
+    for (int s = 0; s < kFast; ++s) {
+      ms[s] = -INFINITY;
+      ls[s] = 0.f;
+      v[s] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (s < p.P) {
+        const float2 ml = __ldg(reinterpret_cast<const float2*>(p.ml_parts + ((int64_t)s * N + n) * 2));
+        ms[s] = ml.x;
+        ls[s] = ml.y;
+        v[s] = __ldg(reinterpret_cast<const float4*>(p.o_parts + ((int64_t)s * N + n) * p.Dv + d0));
       }
     }
-    if (sink > -INFINITY) l += expf(sink - m);
+#pragma unroll
+    for (int s = 0; s < kFast; ++s) m = fmaxf(m, ms[s]);
+    m = fmaxf(m, sink);
+    if (m > -INFINITY) {
+#pragma unroll
+      for (int s = 0; s < kFast; ++s) {   // split order: the same sum on every run
+        if (s < p.P && ms[s] > -INFINITY) {
+          const float w = expf(ms[s] - m);
+          l = fmaf(ls[s], w, l);
+          acc[0] = fmaf(v[s].x, w, acc[0]);
+          if constexpr (VEC == 4) {
+            acc[1] = fmaf(v[s].y, w, acc[1]); acc[2] = fmaf(v[s].z, w, acc[2]); acc[3] = fmaf(v[s].w, w, acc[3]);
+          }
+        }
+      }
+      if (sink > -INFINITY) l += expf(sink - m);
+    }
+  } else {
+    for (int s = 0; s < p.P; ++s) m = fmaxf(m, __ldg(p.ml_parts + ((int64_t)s * N + n) * 2));
+    m = fmaxf(m, sink);
+    if (m > -INFINITY) {
+      for (int s = 0; s < p.P; ++s) {
+        const float ms = __ldg(p.ml_parts + ((int64_t)s * N + n) * 2);
+        const float ls = __ldg(p.ml_parts + ((int64_t)s * N + n) * 2 + 1);
+        if (ms > -INFINITY) {
+          const float w = expf(ms - m);
+          l = fmaf(ls, w, l);
+          const float* src = p.o_parts + ((int64_t)s * N + n) * p.Dv + d0;
+          if constexpr (VEC == 4) {
+            const float4 v = __ldg(reinterpret_cast<const float4*>(src));
+            acc[0] = fmaf(v.x, w, acc[0]); acc[1] = fmaf(v.y, w, acc[1]);
+            acc[2] = fmaf(v.z, w, acc[2]); acc[3] = fmaf(v.w, w, acc[3]);
+          } else {
+            acc[0] = fmaf(__ldg(src), w, acc[0]);
+          }
+        }
+      }
+      if (sink > -INFINITY) l += expf(sink - m);
+    }
   }
   const int64_t ob = (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)t * p.o_st + d0;
   const float inv = (p.finalize ? (l > 0.f ? 1.f / l : 0.f) : 1.f);
@@ -268,7 +303,8 @@ __global__ void __launch_bounds__(256) merge_kernel(MergeParams p) {
 
 static int launch_merge(const MergeParams& mp, int out_dtype, cudaStream_t st) {
   const int64_t N = (int64_t)mp.B * mp.T * mp.H;
-  const bool vec = (mp.Dv % 4 == 0) && ((reinterpret_cast<uintptr_t>(mp.o_parts) & 15) == 0);
+  const bool vec = (mp.Dv % 4 == 0) && ((reinterpret_cast<uintptr_t>(mp.o_parts) & 15) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(mp.ml_parts) & 7) == 0);
   const int64_t items = N * (vec ? mp.Dv / 4 : mp.Dv);
   dim3 grid((unsigned)ceil_div(items, 256));
 #define MXB_MG(OT)                                             \
