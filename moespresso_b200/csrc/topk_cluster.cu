@@ -31,6 +31,7 @@ constexpr int kCWarps = kCThreads / 32;
 constexpr int kCMaxCluster = 8;                 // portable cluster size
 constexpr int kCPartUnit = kCThreads * 4;       // parts are multiples of 16 warps x 32 lanes x 4 keys
 constexpr int kCPartMax = 45056;                // keys per CTA (176 KB)
+constexpr int kCListCap = 128;                  // entries per warp in each of the four 16-bit lists (16 KB per CTA)
 
 struct TopkClusterParams {
   const float* scores;
@@ -41,6 +42,7 @@ struct TopkClusterParams {
   int32_t rows;
   int64_t n;
   int32_t k;
+  int32_t part_cap;   // keys per CTA the launch reserved shared memory for
 };
 
 #ifdef MXB_TRACE_TC
@@ -61,14 +63,37 @@ __device__ __forceinline__ void push_hist(cg::cluster_group& cluster, uint32_t* 
   }
 }
 
+// Adds the non-zero bins of a 256-bin `local` into `remote` of every CTA of the cluster and clears `local`.
+__device__ __forceinline__ void push_hist256(cg::cluster_group& cluster, uint32_t* local, uint32_t* remote, int cs) {
+  if (threadIdx.x < 256) {
+    const uint32_t v = local[threadIdx.x];
+    if (v) {
+      local[threadIdx.x] = 0;
+      for (int r = 0; r < cs; ++r) atomicAdd(cluster.map_shared_rank(remote + threadIdx.x, r), v);
+    }
+  }
+}
+
+// number of entries of the ascending list `a[0..n)` that are < x
+__device__ __forceinline__ int lower_rank(const uint16_t* a, int n, uint32_t x) {
+  int lo = 0, hi = n;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (a[mid] < x) lo = mid + 1; else hi = mid;
+  }
+  return lo;
+}
+
 __global__ void __launch_bounds__(kCThreads) topk_cluster_kernel(TopkClusterParams p) {
-  extern __shared__ uint32_t keys[];              // this CTA's part of the row
+  extern __shared__ uint32_t keys[];              // this CTA's part of the row, then the per-warp lists
   __shared__ uint32_t lhist[kBigBins];            // histogram of the part, one digit at a time
-  __shared__ uint32_t ghist[3][kBigBins];         // histogram of the row, one per digit (summed by all CTAs)
+  __shared__ uint32_t ghist[kBigBins];            // digit 1 of the whole row (summed by all CTAs)
+  __shared__ uint32_t ghs[3][256];                // digits 2-4 of the whole row
   __shared__ uint32_t warp_sums[32];
-  __shared__ uint32_t s_total, s_thr[3][4];
+  __shared__ uint32_t s_total, s_thr[4], s_digit, s_dabove;
   __shared__ uint32_t cl_cnt[2][kCMaxCluster];    // (greater, equal) counts of every CTA of the cluster
   __shared__ uint32_t w_cnt[2][kCWarps];
+  __shared__ int s_overflow;
 
   cg::cluster_group cluster = cg::this_cluster();
   const int cs = (int)cluster.num_blocks();
@@ -79,25 +104,35 @@ __global__ void __launch_bounds__(kCThreads) topk_cluster_kernel(TopkClusterPara
   TRC(0);
   for (int i = tid; i < kBigBins; i += kCThreads) {
     lhist[i] = 0;
-    ghist[0][i] = 0;
-    ghist[1][i] = 0;
-    ghist[2][i] = 0;
+    ghist[i] = 0;
   }
-  if (tid < 12) (&s_thr[0][0])[tid] = 0;
+  for (int i = tid; i < 3 * 256; i += kCThreads) (&ghs[0][0])[i] = 0;
+  if (tid < 4) s_thr[tid] = 0;
+  if (tid == 0) s_overflow = 0;
   __syncthreads();
   cluster.barrier_arrive();   // my row histograms are clear; waited for before the first push
 
   int64_t n_row = p.row_count ? (int64_t)p.row_count[row] : p.n;
   n_row = n_row < 0 ? 0 : (n_row > p.n ? p.n : n_row);
-  const int part = (int)round_up(ceil_div(n_row, (int64_t)cs), (int64_t)kCPartUnit);   // <= kCPartMax (host)
+  const int part = (int)round_up(ceil_div(n_row, (int64_t)cs), (int64_t)kCPartUnit);   // <= part_cap (host)
   const int64_t lo = (int64_t)rank * part;
   const int cnt = (int)(n_row - lo < 0 ? 0 : (n_row - lo > part ? part : n_row - lo));
-  const int wchunk = part / kCWarps;          // ids of one warp: [wbase, wbase + wchunk)
+  const int wchunk = part / kCWarps;          // ids of one warp: [warp * wchunk, + wchunk)
   const int iters = wchunk / 128;             // same for every thread of the cluster; a lane owns 4 consecutive ids
   const int wbase = warp * wchunk + lane * 4;
   const float* src = p.scores + (p.row_start ? p.row_start[row] : (int64_t)row * p.row_stride) + lo;
   const bool src_vec = (reinterpret_cast<uintptr_t>(src) & 15) == 0;
   int32_t* out = p.out_ids + (int64_t)row * p.k;
+  // per-warp lists behind the keys (offsets are relative to the warp's chunk, ascending):
+  //   above: keys whose digit 1 is above the threshold bin (selected for sure)
+  //   cand : keys in the threshold bin, with exclusive prefix counts of (greater, equal) filled in at the end
+  uint16_t* lists = reinterpret_cast<uint16_t*>(keys + p.part_cap);
+  uint16_t* above_off = lists + (0 * kCWarps + warp) * kCListCap;
+  uint16_t* cand_off = lists + (1 * kCWarps + warp) * kCListCap;
+  uint16_t* cand_gt = lists + (2 * kCWarps + warp) * kCListCap;
+  uint16_t* cand_eq = lists + (3 * kCWarps + warp) * kCListCap;
+  const uint32_t* wkeys = keys + warp * wchunk;
+  const uint32_t lt = (1u << lane) - 1u;
 
   TRC(1);
   // ---- digit 1 (top 11 bits) while loading
@@ -136,63 +171,138 @@ __global__ void __launch_bounds__(kCThreads) topk_cluster_kernel(TopkClusterPara
   TRC(2);
   cluster.barrier_wait();
   TRC(3);
-  push_hist(cluster, lhist, ghist[0], cs);
+  push_hist(cluster, lhist, ghist, cs);
   TRC(4);
   cluster.sync();
   TRC(5);
-  row_threshold(ghist[0], p.k, warp_sums, &s_total, s_thr[0]);
+  row_threshold(ghist, p.k, warp_sums, &s_total, s_thr);
   TRC(6);
-  const uint32_t k_eff = s_thr[0][0];
+  const uint32_t k_eff = s_thr[0];
   if (rank == 0)
     for (int i = tid + (int)k_eff; i < p.k; i += kCThreads) out[i] = -1;
   if (k_eff == 0) return;   // the same in every CTA of the cluster; all remote traffic so far is complete
-  const uint32_t bin1 = s_thr[0][1];
-  uint32_t want = k_eff - s_thr[0][2];
+  const uint32_t bin1 = s_thr[1];   // valid keys are >= 0x00800000, so bin1 >= 4 and key 0 is in no list
+  uint32_t want = k_eff - s_thr[2];
 
-  // ---- digit 2 (next 11 bits) among keys in the threshold bin
+  // ---- one pass over the keys: ordered lists of the "above" and "candidate" keys of every warp chunk,
+  //      digit 2 (bits 20..13) of the candidates
+  int n_a = 0, n_c = 0;   // warp-uniform list lengths (may exceed the capacity: then the CTA falls back)
   for (int it = 0; it < iters; ++it) {
     const uint4 k4 = *reinterpret_cast<const uint4*>(&keys[wbase + it * 128]);
     const uint32_t kk[4] = {k4.x, k4.y, k4.z, k4.w};
+    bool isa[4], isc[4];
+    uint32_t mine = 0;   // this lane's counts: above in bits 0..15, candidates in bits 16..31
 #pragma unroll
-    for (int j = 0; j < 4; ++j)   // valid keys are >= 0x00800000, so bin1 >= 4 and key 0 never matches
-      if ((kk[j] >> 21) == bin1) atomicAdd(&lhist[(kk[j] >> 10) & 2047u], 1u);
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t bin = kk[j] >> 21;
+      isa[j] = bin > bin1;
+      isc[j] = bin == bin1;
+      mine += (isa[j] ? 1u : 0u) + (isc[j] ? 0x10000u : 0u);
+    }
+    uint32_t incl = mine;   // one warp scan carries both counts
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t y = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += y;
+    }
+    const uint32_t all = __shfl_sync(0xffffffffu, incl, 31);
+    const uint32_t a_below = (incl - mine) & 0xffffu, c_below = (incl - mine) >> 16;
+    const uint32_t a_all = all & 0xffffu, c_all = all >> 16;
+    int pa = n_a + (int)a_below, pc = n_c + (int)c_below;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint16_t off = (uint16_t)(it * 128 + lane * 4 + j);
+      if (isa[j]) {
+        if (pa < kCListCap) above_off[pa] = off;
+        ++pa;
+      }
+      if (isc[j]) {
+        if (pc < kCListCap) cand_off[pc] = off;
+        ++pc;
+        atomicAdd(&lhist[(kk[j] >> 13) & 255u], 1u);
+      }
+    }
+    n_a += (int)a_all;
+    n_c += (int)c_all;
   }
+  if (lane == 0 && (n_a > kCListCap || n_c > kCListCap)) s_overflow = 1;
   __syncthreads();
   TRC(7);
-  push_hist(cluster, lhist, ghist[1], cs);
+  const bool listed = s_overflow == 0;   // per CTA: otherwise the later steps scan all keys of the part
+  push_hist256(cluster, lhist, ghs[0], cs);
   cluster.sync();
   TRC(8);
-  row_threshold(ghist[1], (int)want, warp_sums, &s_total, s_thr[1]);
-  const uint32_t prefix22 = (bin1 << 11) | s_thr[1][1];
-  want -= s_thr[1][2];
-
-  // ---- digit 3 (last 10 bits)
-  for (int it = 0; it < iters; ++it) {
-    const uint4 k4 = *reinterpret_cast<const uint4*>(&keys[wbase + it * 128]);
-    const uint32_t kk[4] = {k4.x, k4.y, k4.z, k4.w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-      if ((kk[j] >> 10) == prefix22) atomicAdd(&lhist[kk[j] & 1023u], 1u);
-  }
+  if (tid < 32) pick_digit_256(ghs[0], want, &s_digit, &s_dabove);
   __syncthreads();
   TRC(9);
-  push_hist(cluster, lhist, ghist[2], cs);
-  cluster.sync();
+  uint32_t prefix = (bin1 << 21) | (s_digit << 13), pmask = 0xFFFFE000u;
+  want -= s_dabove;
+
+  // ---- digits 3 (bits 12..5) and 4 (bits 4..0)
+#pragma unroll 1
+  for (int dg = 0; dg < 2; ++dg) {
+    const int shift = dg == 0 ? 5 : 0;
+    const uint32_t width = dg == 0 ? 255u : 31u;
+    if (listed) {
+      for (int i0 = 0; i0 < n_c; i0 += 32) {
+        const int i = i0 + lane;
+        if (i < n_c) {
+          const uint32_t key = wkeys[cand_off[i]];
+          if ((key & pmask) == prefix) atomicAdd(&lhist[(key >> shift) & width], 1u);
+        }
+      }
+    } else {
+      for (int it = 0; it < iters; ++it) {
+        const uint4 k4 = *reinterpret_cast<const uint4*>(&keys[wbase + it * 128]);
+        const uint32_t kk[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if ((kk[j] & pmask) == prefix) atomicAdd(&lhist[(kk[j] >> shift) & width], 1u);
+      }
+    }
+    __syncthreads();
+    push_hist256(cluster, lhist, ghs[1 + dg], cs);
+    cluster.sync();
+    if (tid < 32) pick_digit_256(ghs[1 + dg], want, &s_digit, &s_dabove);
+    __syncthreads();
+    prefix |= s_digit << shift;
+    pmask |= width << shift;
+    want -= s_dabove;
+    __syncthreads();   // s_digit / s_dabove are rewritten by the next digit
+  }
   TRC(10);
-  row_threshold(ghist[2], (int)want, warp_sums, &s_total, s_thr[2]);
-  const uint32_t thr = (prefix22 << 10) | s_thr[2][1];
-  const uint32_t need = want - s_thr[2][2];   // ties on thr to take, lowest ids first (1 <= need <= count of thr)
+  const uint32_t thr = prefix;
+  const uint32_t need = want;   // ties on thr to take, lowest ids first (1 <= need <= count of thr)
 
   TRC(11);
   // ---- counts of (greater, equal) keys per warp chunk, per CTA, per cluster
   uint32_t c_gt = 0, c_eq = 0;
-  for (int it = 0; it < iters; ++it) {
-    const uint4 k4 = *reinterpret_cast<const uint4*>(&keys[wbase + it * 128]);
-    c_gt += (k4.x > thr) + (k4.y > thr) + (k4.z > thr) + (k4.w > thr);
-    c_eq += (k4.x == thr) + (k4.y == thr) + (k4.z == thr) + (k4.w == thr);
+  if (listed) {
+    // candidates in list order; leave the exclusive prefix counts behind for the emission
+    uint32_t run_gt = 0, run_eq = 0;
+    for (int i0 = 0; i0 < n_c; i0 += 32) {
+      const int i = i0 + lane;
+      const uint32_t key = i < n_c ? wkeys[cand_off[i]] : 0u;
+      const uint32_t m_gt = __ballot_sync(0xffffffffu, key > thr);
+      const uint32_t m_eq = __ballot_sync(0xffffffffu, key == thr);
+      if (i < n_c) {
+        cand_gt[i] = (uint16_t)(run_gt + __popc(m_gt & lt));
+        cand_eq[i] = (uint16_t)(run_eq + __popc(m_eq & lt));
+      }
+      run_gt += __popc(m_gt);
+      run_eq += __popc(m_eq);
+    }
+    c_gt = (uint32_t)n_a + run_gt;   // warp-uniform already
+    c_eq = run_eq;
+  } else {
+    for (int it = 0; it < iters; ++it) {
+      const uint4 k4 = *reinterpret_cast<const uint4*>(&keys[wbase + it * 128]);
+      c_gt += (k4.x > thr) + (k4.y > thr) + (k4.z > thr) + (k4.w > thr);
+      c_eq += (k4.x == thr) + (k4.y == thr) + (k4.z == thr) + (k4.w == thr);
+    }
+    c_gt = __reduce_add_sync(0xffffffffu, c_gt);
+    c_eq = __reduce_add_sync(0xffffffffu, c_eq);
   }
-  c_gt = __reduce_add_sync(0xffffffffu, c_gt);
-  c_eq = __reduce_add_sync(0xffffffffu, c_eq);
   if (lane == 0) {
     w_cnt[0][warp] = c_gt;
     w_cnt[1][warp] = c_eq;
@@ -221,34 +331,67 @@ __global__ void __launch_bounds__(kCThreads) topk_cluster_kernel(TopkClusterPara
   }
 
   TRC(13);
-  // ---- ordered emission: ids ascend with (iteration, lane, slot), so the output slot of a selected id is
+  // ---- ordered emission: ids ascend with the position in the row, so the output slot of a selected id is
   // (greater keys before it) + min(equal keys before it, need)
   if (c_gt == 0 && (c_eq == 0 || eq_run >= need)) return;   // nothing of this warp's chunk is selected
-  const uint32_t lt = (1u << lane) - 1u;
-  for (int it = 0; it < iters; ++it) {
-    const int e = wbase + it * 128;
-    const uint4 k4 = *reinterpret_cast<const uint4*>(&keys[e]);
-    const uint32_t kk[4] = {k4.x, k4.y, k4.z, k4.w};
-    uint32_t gt_below = 0, eq_below = 0, gt_all = 0, eq_all = 0;   // over lower lanes / over the whole warp
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint32_t m_gt = __ballot_sync(0xffffffffu, kk[j] > thr);
-      const uint32_t m_eq = __ballot_sync(0xffffffffu, kk[j] == thr);
-      gt_below += __popc(m_gt & lt);
-      eq_below += __popc(m_eq & lt);
-      gt_all += __popc(m_gt);
-      eq_all += __popc(m_eq);
+  const int64_t id0 = lo + (int64_t)warp * wchunk;
+  if (listed) {
+    // candidates: before a candidate lie the above-keys with a smaller offset and the candidates before it
+    for (int i0 = 0; i0 < n_c; i0 += 32) {
+      const int i = i0 + lane;
+      if (i < n_c) {
+        const uint32_t off = cand_off[i];
+        const uint32_t key = wkeys[off];
+        const uint32_t q = eq_run + cand_eq[i];
+        if (key > thr || (key == thr && q < need)) {
+          const uint32_t g = gt_run + (uint32_t)lower_rank(above_off, n_a, off) + cand_gt[i];
+          out[g + min(q, need)] = (int32_t)(id0 + off);
+        }
+      }
     }
-    uint32_t g = gt_run + gt_below, q = eq_run + eq_below;   // counts before this lane's first key
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const bool gt = kk[j] > thr, eq = kk[j] == thr;
-      if (gt || (eq && q < need)) out[g + min(q, need)] = (int32_t)(lo + e + j);
-      g += gt;
-      q += eq;
+    // above-keys: before one lie the above-keys before it and the candidates with a smaller offset
+    for (int i0 = 0; i0 < n_a; i0 += 32) {
+      const int i = i0 + lane;
+      if (i < n_a) {
+        const uint32_t off = above_off[i];
+        const int rc = lower_rank(cand_off, n_c, off);   // candidates before this key
+        uint32_t g_c, q_c;   // (greater, equal) among those: prefix counts of entry rc, or the totals at the end
+        if (rc < n_c) {
+          g_c = cand_gt[rc];
+          q_c = cand_eq[rc];
+        } else {
+          g_c = c_gt - (uint32_t)n_a;
+          q_c = c_eq;
+        }
+        out[gt_run + (uint32_t)i + g_c + min(eq_run + q_c, need)] = (int32_t)(id0 + off);
+      }
     }
-    gt_run += gt_all;
-    eq_run += eq_all;
+  } else {
+    for (int it = 0; it < iters; ++it) {
+      const int e = wbase + it * 128;
+      const uint4 k4 = *reinterpret_cast<const uint4*>(&keys[e]);
+      const uint32_t kk[4] = {k4.x, k4.y, k4.z, k4.w};
+      uint32_t gt_below = 0, eq_below = 0, gt_all = 0, eq_all = 0;   // over lower lanes / over the whole warp
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t m_gt = __ballot_sync(0xffffffffu, kk[j] > thr);
+        const uint32_t m_eq = __ballot_sync(0xffffffffu, kk[j] == thr);
+        gt_below += __popc(m_gt & lt);
+        eq_below += __popc(m_eq & lt);
+        gt_all += __popc(m_gt);
+        eq_all += __popc(m_eq);
+      }
+      uint32_t g = gt_run + gt_below, q = eq_run + eq_below;   // counts before this lane's first key
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const bool gt = kk[j] > thr, eq = kk[j] == thr;
+        if (gt || (eq && q < need)) out[g + min(q, need)] = (int32_t)(lo + e + j);
+        g += gt;
+        q += eq;
+      }
+      gt_run += gt_all;
+      eq_run += eq_all;
+    }
   }
   TRC(14);
 }
@@ -279,7 +422,8 @@ int launch_topk_cluster(const mxb_topk_args* a, int cs, cudaStream_t st) {
   const int64_t part_cap = round_up(ceil_div(a->n, (int64_t)cs), (int64_t)kCPartUnit);
   MXB_REQUIRE(part_cap <= kCPartMax, MXB_ERR_INVALID, "topk: row length %lld exceeds the cluster kernel's capacity",
               (long long)a->n);
-  const size_t smem = (size_t)part_cap * 4;
+  p.part_cap = (int32_t)part_cap;
+  const size_t smem = (size_t)part_cap * 4 + (size_t)4 * kCWarps * kCListCap * sizeof(uint16_t);
   MXB_CUDA_OK(cudaFuncSetAttribute(topk_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)((int64_t)a->rows * cs));
