@@ -1,7 +1,7 @@
 // Hand-written PTX wrappers for the Blackwell (sm_100a) data path:
 // mbarrier, TMA (cp.async.bulk.tensor), tcgen05 MMA / TMEM, and the shared-memory
-// and instruction descriptors tcgen05.mma consumes.  No cluster multicast is used
-// anywhere (every kernel runs as a 1-CTA "cluster").
+// and instruction descriptors tcgen05.mma consumes.  Every copy here targets the issuing
+// CTA's own shared memory only.
 #pragma once
 
 #include <cuda.h>

@@ -68,3 +68,24 @@ def test_config3_shaped_step(lens):
                                                  ratio=0, scale=c["scale"], d_v=c["d_v"],
                                                  kv_scales=c["kv_scales"][s:s + n])
         assert max_abs(out[b], ref) <= 2e-2
+
+
+@pytest.mark.parametrize("graph", [True, False])
+def test_plan_matches_eager_step(graph):
+    """The CUDA-graph plan returns the bits of the eager step, from device or pinned-host inputs."""
+    need_gpu()
+    from moespresso_b200.deepseek_v4.decode_step import SparseDecodePlan
+    c = synth.config3(seed=3, lens=[3000, 2500, 6000])
+    cache = LatentCache(kv=dev(c["kv"]), kv_scales=dev(c["kv_scales"]), idx_keys=fp8_from_bits(c["idx_key_bits"]),
+                        row_start=dev(c["row_start"]), row_count=dev(c["lens"].astype(np.int32)), max_rows=6000)
+    q, iq, iw = dev(c["q"], torch.bfloat16), dev(c["idx_q"], torch.bfloat16), dev(c["idx_w"])
+    eager = sparse_decode_step(q, iq, iw, cache, k=c["k"], scale=c["scale"], d_v=c["d_v"], out_dtype=torch.bfloat16)
+    plan = SparseDecodePlan(cache, heads=64, d_qk=576, idx_heads=16, idx_dim=64, k=c["k"], scale=c["scale"],
+                            d_v=c["d_v"], q_dtype=torch.bfloat16, out_dtype=torch.bfloat16, graph=graph)
+    out = plan.run(q, iq, iw)
+    torch.cuda.synchronize()
+    assert torch.equal(out, eager)
+    plan.q.zero_()
+    out = plan.run(q.cpu().pin_memory(), iq.cpu().pin_memory(), iw.cpu().pin_memory())
+    torch.cuda.synchronize()
+    assert torch.equal(out, eager)
