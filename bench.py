@@ -302,9 +302,9 @@ def main():
     # algorithmic bytes of the dominant kernel (indexer score scan): FP8 keys read once, fp32 scores written once
     idx_bytes = total * 64 + total * 4 + B * (16 * 64 * 2 + 16 * 4)
     achieved = idx_bytes / (stage["indexer_scores"] * 1e-6) / 1e9
-    # DRAM traffic of the same kernel from one ncu capture on the --small case (profiles/): 64.2 B read and
-    # 3.4 B written per key row, i.e. the algorithmic bytes; scaled to this launch by its row count
-    traffic = total * (64.2 + 3.4)
+    # DRAM traffic of the same kernel from one ncu capture on the --small case (profiles/): 65.0 B read and
+    # 4.8 B written per key row against 68 B algorithmic; scaled to this launch by its row count
+    traffic = total * (65.0 + 4.8)
     step_bytes = idx_bytes + total * 4 + B * (kk * (576 + 2) + 64 * 576 * 2 + 64 * d_v * 2 + kk * 4 * 2)
 
     line = {
