@@ -94,6 +94,46 @@ typedef struct {
 int mxb_indexer_scores(const mxb_indexer_scores_args* a, void* stream);
 
 /* ------------------------------------------------------------------------ *
+ * Indexer QAT: Hadamard-128 + e2m1 round trip over 32-element groups, applied to
+ * query heads and pool rows before the indexer score.
+ * Replaces  indexer_qat_rows     src/moespresso/runtime/deepseek_v4/indexer_score_kernel.py:284-317
+ *           (helper :78-134), indexer_q_qat_live
+ *           src/moespresso/runtime/deepseek_v4/indexed_attention_kernel.py:1989-2027,
+ *           and the composed _dsv4_indexer_qat  src/moespresso/runtime/deepseek_v4/model.py:720-749.
+ *   x [n_rows, 128] f32 | f16 | bf16 (contiguous) -> out [n_rows, 128] f32.
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  const void* x;
+  int32_t x_dtype;
+  float* out;
+  int64_t n_rows;
+  int32_t width; /* must be 128 */
+} mxb_indexer_qat_args;
+
+int mxb_indexer_qat(const mxb_indexer_qat_args* a, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * Score tail of the fixed-state decode chain over per-head score rows.
+ * Replaces  fused_score_tail  src/moespresso/runtime/deepseek_v4/indexer_score_kernel.py:562-615
+ *           (kernel :450-490).
+ *   scores [H, capacity] f32, weights_raw [H] f32 | f16 | bf16, params int32 (params[1] = valid
+ *   columns) -> out [capacity] f32 = -(sum_h relu(s) * scale * (w * H^-0.5)) on the valid prefix,
+ *   +inf behind it.  32 <= H <= 64.
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  const float* scores;
+  const void* weights_raw;
+  int32_t w_dtype;
+  const int32_t* params;
+  float* out;
+  int32_t H;
+  int64_t capacity;
+  float scale;
+} mxb_score_tail_args;
+
+int mxb_score_tail(const mxb_score_tail_args* a, void* stream);
+
+/* ------------------------------------------------------------------------ *
  * Top-k selection.
  * Replaces  mx.argpartition(-scores, k-1)[..., :k] + mx.sort
  *           src/moespresso/runtime/deepseek_v4/model.py:1003-1005,1057,1442-1451,

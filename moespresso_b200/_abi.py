@@ -41,6 +41,17 @@ class TopkArgs(C.Structure):
     ]
 
 
+class IndexerQatArgs(C.Structure):
+    _fields_ = [("x", _p), ("x_dtype", _i32), ("out", _p), ("n_rows", _i64), ("width", _i32)]
+
+
+class ScoreTailArgs(C.Structure):
+    _fields_ = [
+        ("scores", _p), ("weights_raw", _p), ("w_dtype", _i32), ("params", _p), ("out", _p), ("H", _i32),
+        ("capacity", _i64), ("scale", C.c_float),
+    ]
+
+
 class SparseAttnArgs(C.Structure):
     _fields_ = [
         ("q", _p), ("q_dtype", _i32), ("q_stride_b", _i64), ("q_stride_h", _i64), ("q_stride_t", _i64),
@@ -81,6 +92,8 @@ EXPORTS = {
     "mxb_last_error": (C.c_char_p, []),
     "mxb_kernel_launches": (C.c_int64, []),
     "mxb_indexer_scores": (C.c_int, [C.POINTER(IndexerScoresArgs), _p]),
+    "mxb_indexer_qat": (C.c_int, [C.POINTER(IndexerQatArgs), _p]),
+    "mxb_score_tail": (C.c_int, [C.POINTER(ScoreTailArgs), _p]),
     "mxb_topk_workspace_bytes": (_i64, [_i32, _i64, _i32]),
     "mxb_topk_select": (C.c_int, [C.POINTER(TopkArgs), _p]),
     "mxb_topk_select_static": (C.c_int, [C.POINTER(TopkArgs), _p]),

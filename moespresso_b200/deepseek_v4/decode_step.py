@@ -82,9 +82,16 @@ class SparseDecodePlan:
         dev = cache.kv.device
         B = cache.batch
         self.cache, self.k, self.scale, self.d_v, self.sinks, self.out_dtype = cache, int(k), float(scale), int(d_v), sinks, out_dtype
-        self.q = torch.zeros((B, heads, d_qk), dtype=q_dtype, device=dev)
-        self.idx_q = torch.zeros((B, idx_heads, idx_dim), dtype=q_dtype, device=dev)
-        self.idx_w = torch.zeros((B, idx_heads), dtype=torch.float32, device=dev)
+        # one device buffer behind the three inputs, so that a caller who keeps its step inputs in one pinned
+        # host buffer of the same layout (``host_views``) pays for a single host->device copy per step
+        esz = torch.empty((), dtype=q_dtype).element_size()
+        nq, niq, nw = B * heads * d_qk * esz, B * idx_heads * idx_dim * esz, B * idx_heads * 4
+        self._offs = (0, (nq + 255) // 256 * 256, ((nq + 255) // 256 * 256) + (niq + 255) // 256 * 256)
+        self._sizes = (nq, niq, nw)
+        self._shapes = ((B, heads, d_qk), (B, idx_heads, idx_dim), (B, idx_heads))
+        self._dtypes = (q_dtype, q_dtype, torch.float32)
+        self.packed = torch.zeros(self._offs[2] + (nw + 255) // 256 * 256, dtype=torch.uint8, device=dev)
+        self.q, self.idx_q, self.idx_w = self._views(self.packed)
         self.graph = None
         self.out = None
         self.ids = None
@@ -100,6 +107,20 @@ class SparseDecodePlan:
             with torch.cuda.graph(g):
                 self.out, self.ids = self._step()
             self.graph = g
+
+    def _views(self, buf):
+        return tuple(buf[o:o + n].view(dt).view(sh)
+                     for o, n, sh, dt in zip(self._offs, self._sizes, self._shapes, self._dtypes))
+
+    def host_buffer(self):
+        """A pinned host buffer with the plan's input layout and its (q, idx_q, idx_w) views.  Fill the views,
+        then ``run_packed(buffer)``: one host->device copy instead of three."""
+        buf = torch.zeros(self.packed.numel(), dtype=torch.uint8).pin_memory()
+        return buf, self._views(buf)
+
+    def run_packed(self, host_buf):
+        self.packed.copy_(host_buf, non_blocking=True)
+        return self.launch()
 
     def _step(self):
         return sparse_decode_step(self.q, self.idx_q, self.idx_w, self.cache, k=self.k, scale=self.scale,

@@ -251,6 +251,21 @@ def banded_prefill_attention_live(q, raw_kv, comp_kv, topk, sinks, *, pos0: int,
                            route="banded")
 
 
+def indexer_q_qat_live(q):
+    """Hadamard-128 + e2m1 round trip of live BHLD query rows (reference: indexed_attention_kernel.py:1989-2027).
+    q float32 ``[batch, n_heads, tokens, 128]`` -> float32 of the same shape."""
+    if q.ndim != 4:
+        raise ValueError("q must have shape [batch, n_heads, tokens, 128]")
+    if int(q.shape[0]) <= 0 or int(q.shape[2]) <= 0:
+        raise ValueError("q must contain at least one batch and token")
+    if int(q.shape[3]) != 128:
+        raise ValueError("DS4 indexer QAT probe requires head_dim=128")
+    if q.dtype != torch.float32:
+        raise ValueError("q must be float32")
+    from .indexer_score_kernel import indexer_qat_rows
+    return indexer_qat_rows(q)
+
+
 def indexer_score_operands(q, index_comp):
     """Operand form the score kernel wants (reference: indexed_attention_kernel.py:51-59):
     16-bit operands are used as they are, anything else is widened to float32."""

@@ -89,3 +89,11 @@ def test_plan_matches_eager_step(graph):
     out = plan.run(q.cpu().pin_memory(), iq.cpu().pin_memory(), iw.cpu().pin_memory())
     torch.cuda.synchronize()
     assert torch.equal(out, eager)
+    plan.packed.zero_()
+    host, (qv, iqv, iwv) = plan.host_buffer()
+    qv.copy_(q.cpu())
+    iqv.copy_(iq.cpu())
+    iwv.copy_(iw.cpu())
+    out = plan.run_packed(host)
+    torch.cuda.synchronize()
+    assert torch.equal(out, eager)
