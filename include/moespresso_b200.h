@@ -134,6 +134,42 @@ typedef struct {
 int mxb_score_tail(const mxb_score_tail_args* a, void* stream);
 
 /* ------------------------------------------------------------------------ *
+ * Cache-row formats.
+ * mxb_fp8_kv_rows replaces  fp8_kv_prefix_rows
+ *           src/moespresso/runtime/deepseek_v4/decode_attention_kernel.py:587-619 (helpers :149-176),
+ *           composed _deepseek_v4_fp8_kv_roundtrip  src/moespresso/runtime/deepseek_v4/model.py:560-609:
+ *   x [n_rows, 512] f32 -> out [n_rows, 512] f32, E4M3FN round trip of dims [0, 448) in 64-blocks,
+ *   dims [448, 512) copied.
+ * mxb_quantize_kv_int8 has no counterpart in the reference: the per-token int8 quantiser that writes
+ *   the int8 + fp16-scale latent cache the sparse decode operators read.
+ *   x [n_rows, width] f32 | f16 | bf16 -> q int8 [n_rows, width], scales fp16 [n_rows].
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  const float* x;
+  float* out;
+  int64_t n_rows;
+  int32_t width; /* must be 512 */
+  int32_t mode;  /* MXB_FP8KV_SERVED | MXB_FP8KV_REPLAY */
+} mxb_fp8_kv_rows_args;
+
+#define MXB_FP8KV_SERVED 0 /* the served kernel: float32 log / ceil / exp block scale, ties to the lower magnitude */
+#define MXB_FP8KV_REPLAY 1 /* _fp8_kv_round of src/moespresso/correctness/deepseek_v4/compressor_diff.py:74-86:
+                              exact power-of-two block scale, ties to the even code */
+
+int mxb_fp8_kv_rows(const mxb_fp8_kv_rows_args* a, void* stream);
+
+typedef struct {
+  const void* x;
+  int32_t x_dtype;
+  int8_t* q;
+  void* scales; /* fp16 [n_rows] */
+  int64_t n_rows;
+  int32_t width;
+} mxb_quantize_kv_int8_args;
+
+int mxb_quantize_kv_int8(const mxb_quantize_kv_int8_args* a, void* stream);
+
+/* ------------------------------------------------------------------------ *
  * Top-k selection.
  * Replaces  mx.argpartition(-scores, k-1)[..., :k] + mx.sort
  *           src/moespresso/runtime/deepseek_v4/model.py:1003-1005,1057,1442-1451,

@@ -52,6 +52,14 @@ class ScoreTailArgs(C.Structure):
     ]
 
 
+class Fp8KvRowsArgs(C.Structure):
+    _fields_ = [("x", _p), ("out", _p), ("n_rows", _i64), ("width", _i32), ("mode", _i32)]
+
+
+class QuantizeKvInt8Args(C.Structure):
+    _fields_ = [("x", _p), ("x_dtype", _i32), ("q", _p), ("scales", _p), ("n_rows", _i64), ("width", _i32)]
+
+
 class SparseAttnArgs(C.Structure):
     _fields_ = [
         ("q", _p), ("q_dtype", _i32), ("q_stride_b", _i64), ("q_stride_h", _i64), ("q_stride_t", _i64),
@@ -94,6 +102,8 @@ EXPORTS = {
     "mxb_indexer_scores": (C.c_int, [C.POINTER(IndexerScoresArgs), _p]),
     "mxb_indexer_qat": (C.c_int, [C.POINTER(IndexerQatArgs), _p]),
     "mxb_score_tail": (C.c_int, [C.POINTER(ScoreTailArgs), _p]),
+    "mxb_fp8_kv_rows": (C.c_int, [C.POINTER(Fp8KvRowsArgs), _p]),
+    "mxb_quantize_kv_int8": (C.c_int, [C.POINTER(QuantizeKvInt8Args), _p]),
     "mxb_topk_workspace_bytes": (_i64, [_i32, _i64, _i32]),
     "mxb_topk_select": (C.c_int, [C.POINTER(TopkArgs), _p]),
     "mxb_topk_select_static": (C.c_int, [C.POINTER(TopkArgs), _p]),

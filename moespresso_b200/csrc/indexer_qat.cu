@@ -69,16 +69,12 @@ __global__ void __launch_bounds__(128) indexer_qat_kernel(QatParams p) {
   for (int j = 0; j < 4; ++j) x[j] = __fmul_rn(x[j], kHadamardScale);
 
   // e2m1 round trip over groups of 32 elements = 8 lanes
+  // the maximum skips NaN elements (fmax), as the reference kernel's does; a group of nothing but NaN keeps NaN
   float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
-  bool any_nan = isnan(x[0]) || isnan(x[1]) || isnan(x[2]) || isnan(x[3]);
 #pragma unroll
-  for (int m = 1; m <= 4; m <<= 1) {
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
-    any_nan = any_nan || (__shfl_xor_sync(0xffffffffu, any_nan ? 1 : 0, m) != 0);
-  }
+  for (int m = 1; m <= 4; m <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
   const float kAmaxFloor = 7.052966104933725e-38f;
-  if (any_nan) amax = __int_as_float(0x7fc00000);   // a NaN anywhere in the group poisons its maximum
-  else if (!(amax > kAmaxFloor)) amax = kAmaxFloor;
+  if (!isnan(amax) && !(amax > kAmaxFloor)) amax = kAmaxFloor;
   const float kLn2 = 0.6931471805599453f;           // ln 2 rounded to float32, as the float32 chain sees it
   const float ratio = __fdiv_rn(amax, 6.0f);
   const float lg = (float)log((double)ratio);        // correctly rounded float32 log

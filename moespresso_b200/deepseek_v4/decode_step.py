@@ -40,6 +40,27 @@ class LatentCache:
         return int(self.row_start.numel())
 
 
+def quantize_kv_int8(rows):
+    """Per-token int8 quantisation of latent KV rows ``[n, width]`` (float32 / float16 / bfloat16): returns
+    ``(q int8 [n, width], scales float16 [n])`` with ``rows ~= q * scales[:, None]`` — the cache format the sparse
+    decode operators read through ``kv_scales``."""
+    from .. import _abi
+    from .. import _torchabi as _t
+    if rows.ndim != 2 or rows.shape[0] == 0 or rows.shape[1] == 0:
+        raise ValueError("rows must be a non-empty [n, width] matrix")
+    if rows.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise ValueError("rows must be float32, float16, or bfloat16")
+    dev = _t.require_cuda(rows)
+    rows = rows.contiguous()
+    q = torch.empty(rows.shape, dtype=torch.int8, device=dev)
+    scales = torch.empty((rows.shape[0],), dtype=torch.float16, device=dev)
+    a = _abi.QuantizeKvInt8Args()
+    a.x, a.x_dtype, a.q, a.scales = _t.ptr(rows), _t.dtype_code(rows), _t.ptr(q), _t.ptr(scales)
+    a.n_rows, a.width = int(rows.shape[0]), int(rows.shape[1])
+    _abi.check(_t.launch("quantize_kv_int8", _abi.load().mxb_quantize_kv_int8, a))
+    return q, scales
+
+
 def sparse_decode_step(q, idx_q, idx_w, cache: LatentCache, *, k: int, scale: float, d_v: int,
                        sinks=None, out_dtype=torch.float32, exact_fp32: bool = False, partial: bool = False,
                        return_ids: bool = False, return_scores: bool = False):

@@ -128,3 +128,24 @@ def test_e4m3_round_trip():
     x = np.random.default_rng(1).normal(size=4096) * 3
     t = torch.tensor(x, dtype=torch.float32).to(torch.float8_e4m3fn)
     np.testing.assert_array_equal(t.view(torch.uint8).numpy(), ds4.e4m3_encode(x.astype(np.float32)))
+
+
+def _fp8kv_golden():
+    import os
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "fp8kv_golden.npz"))
+
+
+def test_fp8_kv_replay_form_matches_reference_vectors():
+    """oracle.ds4.fp8_kv_round_replay / e4m3fn_dequant against outputs of the reference's own NumPy functions
+    (tests/golden/make_golden_fp8kv.py)."""
+    g = _fp8kv_golden()
+    np.testing.assert_array_equal(ds4.E4M3FN_VALUES, g["table"])
+    np.testing.assert_array_equal(ds4.e4m3fn_dequant(g["dequant_in"]).view(np.uint32), g["dequant_out"].view(np.uint32))
+    np.testing.assert_array_equal(ds4.fp8_kv_round_replay(g["rows"]).view(np.uint32), g["rounded"].view(np.uint32))
+
+
+def test_fp8_kv_served_form_stays_within_scale_rounding_of_the_replay_form():
+    g = _fp8kv_golden()
+    served = ds4.fp8_kv_prefix_rows(g["rows"])
+    np.testing.assert_array_equal(served[:, 448:], g["rows"][:, 448:])            # rotary tail untouched
+    np.testing.assert_allclose(served, g["rounded"], rtol=1e-6, atol=0)          # float32 exp(k ln 2) vs 2**k
