@@ -170,6 +170,27 @@ typedef struct {
 int mxb_quantize_kv_int8(const mxb_quantize_kv_int8_args* a, void* stream);
 
 /* ------------------------------------------------------------------------ *
+ * Partial rotary embedding of the last rope_dim channels (interleaved pairs), forward or inverse.
+ * Replaces  apply_rope_tail  src/moespresso/runtime/deepseek_v4/attention.py:114-156 and the in-kernel
+ *           rope prologue / inverse-rope epilogue of fused_decode_sdpa
+ *           src/moespresso/runtime/deepseek_v4/decode_attention_kernel.py:398-422, 504-521.
+ *   x, out [n_rows, width] f32 | f16 | bf16 (out may alias x); row r has position
+ *   positions[r % seq_len]; inv_freq [rope_dim / 2] f64 (rope_inverse_frequencies, host side).
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  const void* x;
+  void* out;
+  int32_t x_dtype;
+  const int64_t* positions; /* [seq_len] */
+  const double* inv_freq;   /* [rope_dim / 2] */
+  int64_t n_rows;
+  int32_t seq_len, width, rope_dim;
+  int32_t inverse;
+} mxb_rope_tail_args;
+
+int mxb_rope_tail(const mxb_rope_tail_args* a, void* stream);
+
+/* ------------------------------------------------------------------------ *
  * Top-k selection.
  * Replaces  mx.argpartition(-scores, k-1)[..., :k] + mx.sort
  *           src/moespresso/runtime/deepseek_v4/model.py:1003-1005,1057,1442-1451,

@@ -60,6 +60,13 @@ class QuantizeKvInt8Args(C.Structure):
     _fields_ = [("x", _p), ("x_dtype", _i32), ("q", _p), ("scales", _p), ("n_rows", _i64), ("width", _i32)]
 
 
+class RopeTailArgs(C.Structure):
+    _fields_ = [
+        ("x", _p), ("out", _p), ("x_dtype", _i32), ("positions", _p), ("inv_freq", _p), ("n_rows", _i64),
+        ("seq_len", _i32), ("width", _i32), ("rope_dim", _i32), ("inverse", _i32),
+    ]
+
+
 class SparseAttnArgs(C.Structure):
     _fields_ = [
         ("q", _p), ("q_dtype", _i32), ("q_stride_b", _i64), ("q_stride_h", _i64), ("q_stride_t", _i64),
@@ -104,6 +111,7 @@ EXPORTS = {
     "mxb_score_tail": (C.c_int, [C.POINTER(ScoreTailArgs), _p]),
     "mxb_fp8_kv_rows": (C.c_int, [C.POINTER(Fp8KvRowsArgs), _p]),
     "mxb_quantize_kv_int8": (C.c_int, [C.POINTER(QuantizeKvInt8Args), _p]),
+    "mxb_rope_tail": (C.c_int, [C.POINTER(RopeTailArgs), _p]),
     "mxb_topk_workspace_bytes": (_i64, [_i32, _i64, _i32]),
     "mxb_topk_select": (C.c_int, [C.POINTER(TopkArgs), _p]),
     "mxb_topk_select_static": (C.c_int, [C.POINTER(TopkArgs), _p]),

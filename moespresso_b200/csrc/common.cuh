@@ -93,6 +93,14 @@ __device__ __forceinline__ void store_elem(void* p, int64_t i, float x) {
   else reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(x);
 }
 
+// one rounding from float64 to the element type
+template <int DT>
+__device__ __forceinline__ void store_elem_f64(void* p, int64_t i, double x) {
+  if constexpr (DT == MXB_F32) reinterpret_cast<float*>(p)[i] = __double2float_rn(x);
+  else if constexpr (DT == MXB_F16) reinterpret_cast<__half*>(p)[i] = __double2half(x);
+  else reinterpret_cast<__nv_bfloat16*>(p)[i] = __double2bfloat16(x);
+}
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));

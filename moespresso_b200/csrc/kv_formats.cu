@@ -150,3 +150,63 @@ extern "C" int mxb_quantize_kv_int8(const mxb_quantize_kv_int8_args* a, void* st
   MXB_CUDA_OK(cudaGetLastError());
   return MXB_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Partial rotary embedding of the last `rope_dim` channels of every row (interleaved pairs), forward or
+// inverse: the seam either side of the attention call
+// (src/moespresso/runtime/deepseek_v4/attention.py:114-156; in-kernel forms
+//  src/moespresso/runtime/deepseek_v4/decode_attention_kernel.py:398-422, 504-521).
+// Row r sits at sequence index r % seq_len (the sequence axis is the second-to-last).  Angles are
+// position * inverse frequency in float64, as in the NumPy definition; the result is rounded once to
+// the row type.  Leading channels are copied.
+// ---------------------------------------------------------------------------------------------
+namespace mxb {
+
+template <int XT>
+__global__ void __launch_bounds__(128) rope_tail_kernel(const void* __restrict__ x, void* __restrict__ out,
+                                                        const int64_t* __restrict__ positions,
+                                                        const double* __restrict__ inv_freq, int64_t n_rows,
+                                                        int seq_len, int width, int rope_dim, int inverse) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= n_rows) return;
+  const int64_t base = row * width;
+  const int lead = width - rope_dim;
+  if (x != out)
+    for (int i = lane; i < lead; i += 32) store_elem<XT>(out, base + i, load_elem<XT>(x, base + i));
+  const double pos = (double)positions[row % seq_len];
+  for (int pr = lane; pr < rope_dim / 2; pr += 32) {
+    double s, c;
+    sincos(pos * inv_freq[pr], &s, &c);
+    if (inverse) s = -s;
+    const double x0 = (double)load_elem<XT>(x, base + lead + 2 * pr);
+    const double x1 = (double)load_elem<XT>(x, base + lead + 2 * pr + 1);
+    store_elem_f64<XT>(out, base + lead + 2 * pr, x0 * c - x1 * s);
+    store_elem_f64<XT>(out, base + lead + 2 * pr + 1, x0 * s + x1 * c);
+  }
+}
+
+}  // namespace mxb
+
+extern "C" int mxb_rope_tail(const mxb_rope_tail_args* a, void* stream) {
+  MXB_REQUIRE(a != nullptr, MXB_ERR_INVALID, "rope: null args");
+  MXB_REQUIRE(a->n_rows > 0 && a->seq_len > 0 && a->n_rows % a->seq_len == 0, MXB_ERR_INVALID,
+              "x must have at least sequence and feature dimensions");
+  MXB_REQUIRE(a->rope_dim > 0 && a->rope_dim % 2 == 0, MXB_ERR_INVALID, "rope_dim must be a positive even integer");
+  MXB_REQUIRE(a->width >= a->rope_dim, MXB_ERR_INVALID, "rope_dim cannot exceed the feature dimension");
+  MXB_REQUIRE(a->x && a->out && a->positions && a->inv_freq, MXB_ERR_INVALID, "rope: null tensor");
+  MXB_REQUIRE(a->x_dtype == MXB_F32 || a->x_dtype == MXB_F16 || a->x_dtype == MXB_BF16, MXB_ERR_INVALID,
+              "rope rows must be float32, float16, or bfloat16");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const unsigned grid = (unsigned)ceil_div(a->n_rows, 4);
+#define MXB_ROPE(XT)                                                                                          \
+  rope_tail_kernel<XT><<<grid, 128, 0, st>>>(a->x, a->out, a->positions, a->inv_freq, a->n_rows, a->seq_len, \
+                                             a->width, a->rope_dim, a->inverse)
+  if (a->x_dtype == MXB_F32) MXB_ROPE(MXB_F32);
+  else if (a->x_dtype == MXB_F16) MXB_ROPE(MXB_F16);
+  else MXB_ROPE(MXB_BF16);
+#undef MXB_ROPE
+  note_launch();
+  MXB_CUDA_OK(cudaGetLastError());
+  return MXB_OK;
+}

@@ -127,3 +127,80 @@ def topk_select_static(scores, k: int, out, *, valid=None, row_start=None, n=Non
     a.out_ids = ptr(out); a.rows = rows; a.n = n_; a.k = int(k)
     _abi.check(_t.launch("topk_select_static", lib.mxb_topk_select_static, a))
     return out
+
+
+# --------------------------------------------------------------------------- #
+# partial rotary embedding (reference: src/moespresso/runtime/deepseek_v4/attention.py:20-31, 71-156)
+# --------------------------------------------------------------------------- #
+DS4_ROPE_DIM = 64
+DS4_SWA_ROPE_BASE = 10000.0
+DS4_COMPRESS_ROPE_BASE = 160000.0
+DS4_YARN = {"factor": 16.0, "original_seq_len": 65536.0, "beta_fast": 32.0, "beta_slow": 1.0}
+
+
+def rope_inverse_frequencies(dim: int, base: float, yarn=None):
+    """RoPE inverse frequencies in float64 (host side), including DS4's pure-frequency YaRN variant
+    (reference: attention.py:71-101).  Returns a NumPy array ``[dim / 2]``."""
+    import math
+
+    import numpy as np
+    if dim <= 0 or dim % 2:
+        raise ValueError("RoPE dim must be a positive even integer")
+    freqs = 1.0 / (float(base) ** (np.arange(0, dim, 2, dtype=np.float64) / dim))
+    if not yarn:
+        return freqs
+    factor, original = float(yarn["factor"]), float(yarn["original_seq_len"])
+    beta_fast, beta_slow = float(yarn.get("beta_fast", 32.0)), float(yarn.get("beta_slow", 1.0))
+    if factor <= 1.0 or original <= 0:
+        return freqs
+
+    def correction_dim(n: float) -> float:
+        return dim * math.log(original / (n * 2.0 * math.pi)) / (2.0 * math.log(base))
+
+    low = max(math.floor(correction_dim(beta_fast)), 0)
+    high = min(math.ceil(correction_dim(beta_slow)), dim - 1)
+    if low == high:
+        high += 0.001
+    smooth = 1.0 - np.clip((np.arange(dim // 2, dtype=np.float64) - low) / (high - low), 0.0, 1.0)
+    return freqs / factor * (1.0 - smooth) + freqs * smooth
+
+
+def apply_rope_tail(x, positions, *, base: float, yarn=None, rope_dim: int = DS4_ROPE_DIM, inverse: bool = False,
+                    out=None):
+    """DS4 partial RoPE on only the final ``rope_dim`` channels (interleaved pairs); the sequence axis is the
+    second-to-last axis; leading channels are copied (reference: attention.py:114-156).
+
+    x: CUDA tensor ``[..., seq, features]`` float32 / float16 / bfloat16; positions: ``seq`` integers (sequence,
+    NumPy array or tensor).  Angles are formed in float64 and the result is rounded once to ``x.dtype``.
+    ``out=x`` rotates in place."""
+    import numpy as np
+    if x.ndim < 2:
+        raise ValueError("x must have at least sequence and feature dimensions")
+    if rope_dim <= 0 or rope_dim % 2:
+        raise ValueError("rope_dim must be a positive even integer")
+    if int(x.shape[-1]) < rope_dim:
+        raise ValueError("rope_dim cannot exceed the feature dimension")
+    dev = require_cuda(x)
+    if isinstance(positions, torch.Tensor):
+        pos = positions.reshape(-1).to(device=dev, dtype=torch.int64)
+    else:
+        pos = torch.as_tensor(np.asarray(positions).reshape(-1).astype(np.int64), device=dev)
+    if int(x.shape[-2]) != int(pos.numel()):
+        raise ValueError("positions length must match x.shape[-2]")
+    if x.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise ValueError("x must be float32, float16, or bfloat16")
+    x = x.contiguous()
+    if out is None:
+        out = torch.empty_like(x)
+    elif out.shape != x.shape or out.dtype != x.dtype or not out.is_contiguous():
+        raise ValueError("out must be a contiguous tensor with x's shape and dtype")
+    inv = torch.as_tensor(rope_inverse_frequencies(rope_dim, base, yarn), dtype=torch.float64, device=dev)
+    a = _abi.RopeTailArgs()
+    a.x, a.out, a.x_dtype = ptr(x), ptr(out), _t.dtype_code(x)
+    a.positions, a.inv_freq = ptr(pos), ptr(inv)
+    a.n_rows = int(x.numel() // x.shape[-1])
+    a.seq_len, a.width, a.rope_dim, a.inverse = int(x.shape[-2]), int(x.shape[-1]), int(rope_dim), 1 if inverse else 0
+    if a.n_rows == 0:
+        return out
+    _abi.check(_t.launch("rope_tail", _abi.load().mxb_rope_tail, a))
+    return out

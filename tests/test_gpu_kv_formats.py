@@ -82,3 +82,34 @@ def test_quantize_kv_int8(dtype):
     back = q.float() * s.float()[:, None]
     assert torch.all((back - x.float()).abs() <= 0.5 * s.float()[:, None] * 1.001 + 1e-30)
     # the decode operators read this format: a one-row sanity check through sparse attention happens elsewhere
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-7), (torch.bfloat16, 0.0), (torch.float16, 0.0)])
+def test_rope_tail_against_reference_vectors(dtype, tol):
+    """apply_rope_tail through the CUDA kernel against outputs of the reference's NumPy function."""
+    need_gpu()
+    from moespresso_b200.deepseek_v4 import attention as pkg
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "rope_golden.npz"))
+    x = dev(g["x"]).to(dtype)
+    fwd = pkg.apply_rope_tail(x, g["pos"], base=pkg.DS4_COMPRESS_ROPE_BASE, yarn=pkg.DS4_YARN)
+    assert fwd.dtype == dtype and fwd.shape == x.shape
+    if dtype == torch.float32:
+        np.testing.assert_allclose(fwd.cpu().numpy(), g["fwd_yarn"], rtol=0, atol=tol * 8)
+        inv = pkg.apply_rope_tail(fwd, torch.as_tensor(g["pos"]), base=pkg.DS4_COMPRESS_ROPE_BASE, yarn=pkg.DS4_YARN,
+                                  inverse=True)
+        np.testing.assert_allclose(inv.cpu().numpy(), g["x"], rtol=0, atol=1e-5)
+        swa = pkg.apply_rope_tail(x, g["pos"], base=pkg.DS4_SWA_ROPE_BASE)
+        np.testing.assert_allclose(swa.cpu().numpy(), g["fwd_swa"], rtol=0, atol=tol * 8)
+    else:
+        exp = ds4.apply_rope_tail(x.float().cpu().numpy(), g["pos"], base=pkg.DS4_COMPRESS_ROPE_BASE, yarn=pkg.DS4_YARN)
+        exp = torch.from_numpy(exp).to(dtype)                         # one rounding from float64 math
+        diff = (fwd.float().cpu() - exp.float()).abs().max().item()
+        assert diff <= 2 ** -7 * 8                                    # at most one unit in the last place of the 16-bit type
+    np.testing.assert_array_equal(fwd[..., :448].float().cpu().numpy(), x[..., :448].float().cpu().numpy())
+    same = x.clone()
+    pkg.apply_rope_tail(same, g["pos"], base=pkg.DS4_COMPRESS_ROPE_BASE, yarn=pkg.DS4_YARN, out=same)   # in place
+    assert torch.equal(same, fwd)
+    with pytest.raises(ValueError, match="positions length"):
+        pkg.apply_rope_tail(x, g["pos"][:3], base=10000.0)
+    with pytest.raises(ValueError, match="positive even"):
+        pkg.apply_rope_tail(x, g["pos"], base=10000.0, rope_dim=3)

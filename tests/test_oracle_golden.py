@@ -149,3 +149,24 @@ def test_fp8_kv_served_form_stays_within_scale_rounding_of_the_replay_form():
     served = ds4.fp8_kv_prefix_rows(g["rows"])
     np.testing.assert_array_equal(served[:, 448:], g["rows"][:, 448:])            # rotary tail untouched
     np.testing.assert_allclose(served, g["rounded"], rtol=1e-6, atol=0)          # float32 exp(k ln 2) vs 2**k
+
+
+def test_rope_matches_reference_vectors():
+    """oracle.ds4 rope functions and the host-side frequency helper of the package against outputs of the
+    reference's NumPy functions (tests/golden/make_golden_rope.py)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "rope_golden.npz"))
+    yarn = {"factor": float(g["yarn_factor"]), "original_seq_len": float(g["yarn_original_seq_len"]),
+            "beta_fast": float(g["yarn_beta_fast"]), "beta_slow": float(g["yarn_beta_slow"])}
+    np.testing.assert_array_equal(ds4.rope_inverse_frequencies(64, float(g["swa_base"])), g["inv_freq_swa"])
+    np.testing.assert_array_equal(ds4.rope_inverse_frequencies(64, float(g["compress_base"]), yarn), g["inv_freq_yarn"])
+    np.testing.assert_array_equal(ds4.apply_rope_tail(g["x"], g["pos"], base=float(g["compress_base"]), yarn=yarn),
+                                  g["fwd_yarn"])
+    np.testing.assert_array_equal(ds4.apply_rope_tail(g["fwd_yarn"], g["pos"], base=float(g["compress_base"]),
+                                                      yarn=yarn, inverse=True), g["inv_yarn"])
+    np.testing.assert_array_equal(ds4.apply_rope_tail(g["x"], g["pos"], base=float(g["swa_base"])), g["fwd_swa"])
+    from moespresso_b200.deepseek_v4 import attention as pkg
+    np.testing.assert_array_equal(pkg.rope_inverse_frequencies(64, pkg.DS4_COMPRESS_ROPE_BASE, pkg.DS4_YARN),
+                                  g["inv_freq_yarn"])
+    np.testing.assert_array_equal(pkg.rope_inverse_frequencies(64, pkg.DS4_SWA_ROPE_BASE), g["inv_freq_swa"])
+    assert pkg.DS4_YARN == yarn
