@@ -186,6 +186,8 @@ typedef struct {
   int64_t n_rows;
   int32_t seq_len, width, rope_dim;
   int32_t inverse;
+  int32_t half_chain; /* float16 rows only: float32 angle, cos / sin and every product / sum rounded to float16,
+                         as the fused decode kernels rotate (0 = float64 angles, one rounding) */
 } mxb_rope_tail_args;
 
 int mxb_rope_tail(const mxb_rope_tail_args* a, void* stream);

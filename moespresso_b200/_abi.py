@@ -63,7 +63,7 @@ class QuantizeKvInt8Args(C.Structure):
 class RopeTailArgs(C.Structure):
     _fields_ = [
         ("x", _p), ("out", _p), ("x_dtype", _i32), ("positions", _p), ("inv_freq", _p), ("n_rows", _i64),
-        ("seq_len", _i32), ("width", _i32), ("rope_dim", _i32), ("inverse", _i32),
+        ("seq_len", _i32), ("width", _i32), ("rope_dim", _i32), ("inverse", _i32), ("half_chain", _i32),
     ]
 
 

@@ -166,7 +166,8 @@ template <int XT>
 __global__ void __launch_bounds__(128) rope_tail_kernel(const void* __restrict__ x, void* __restrict__ out,
                                                         const int64_t* __restrict__ positions,
                                                         const double* __restrict__ inv_freq, int64_t n_rows,
-                                                        int seq_len, int width, int rope_dim, int inverse) {
+                                                        int seq_len, int width, int rope_dim, int inverse,
+                                                        int half_chain) {
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (row >= n_rows) return;
@@ -175,6 +176,26 @@ __global__ void __launch_bounds__(128) rope_tail_kernel(const void* __restrict__
   if (x != out)
     for (int i = lane; i < lead; i += 32) store_elem<XT>(out, base + i, load_elem<XT>(x, base + i));
   const double pos = (double)positions[row % seq_len];
+  if constexpr (XT == MXB_F16) {
+    if (half_chain) {
+      // the fused decode kernels' float16 form: float32 angle, cos / sin rounded to float16, every product and
+      // sum rounded to float16 (decode_attention_kernel.py:120-147, 398-422)
+      const int64_t ipos = positions[row % seq_len];
+      for (int pr = lane; pr < rope_dim / 2; pr += 32) {
+        const float theta = __fmul_rn((float)ipos, (float)inv_freq[pr]);
+        const __half c = __float2half_rn((float)cos((double)theta));
+        __half s = __float2half_rn((float)sin((double)theta));
+        if (inverse) s = __hneg(s);
+        const __half x0 = reinterpret_cast<const __half*>(x)[base + lead + 2 * pr];
+        const __half x1 = reinterpret_cast<const __half*>(x)[base + lead + 2 * pr + 1];
+        // the _rn forms are never contracted into a fused multiply-add: every product is rounded on its own
+        const __half m0 = __hmul_rn(x0, c), m1 = __hmul_rn(x1, s), m2 = __hmul_rn(x0, s), m3 = __hmul_rn(x1, c);
+        reinterpret_cast<__half*>(out)[base + lead + 2 * pr] = __hsub_rn(m0, m1);
+        reinterpret_cast<__half*>(out)[base + lead + 2 * pr + 1] = __hadd_rn(m2, m3);
+      }
+      return;
+    }
+  }
   for (int pr = lane; pr < rope_dim / 2; pr += 32) {
     double s, c;
     sincos(pos * inv_freq[pr], &s, &c);
@@ -197,11 +218,12 @@ extern "C" int mxb_rope_tail(const mxb_rope_tail_args* a, void* stream) {
   MXB_REQUIRE(a->x && a->out && a->positions && a->inv_freq, MXB_ERR_INVALID, "rope: null tensor");
   MXB_REQUIRE(a->x_dtype == MXB_F32 || a->x_dtype == MXB_F16 || a->x_dtype == MXB_BF16, MXB_ERR_INVALID,
               "rope rows must be float32, float16, or bfloat16");
+  MXB_REQUIRE(!a->half_chain || a->x_dtype == MXB_F16, MXB_ERR_INVALID, "the float16 rope chain takes float16 rows");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const unsigned grid = (unsigned)ceil_div(a->n_rows, 4);
 #define MXB_ROPE(XT)                                                                                          \
   rope_tail_kernel<XT><<<grid, 128, 0, st>>>(a->x, a->out, a->positions, a->inv_freq, a->n_rows, a->seq_len, \
-                                             a->width, a->rope_dim, a->inverse)
+                                             a->width, a->rope_dim, a->inverse, a->half_chain)
   if (a->x_dtype == MXB_F32) MXB_ROPE(MXB_F32);
   else if (a->x_dtype == MXB_F16) MXB_ROPE(MXB_F16);
   else MXB_ROPE(MXB_BF16);

@@ -165,14 +165,16 @@ def rope_inverse_frequencies(dim: int, base: float, yarn=None):
     return freqs / factor * (1.0 - smooth) + freqs * smooth
 
 
-def apply_rope_tail(x, positions, *, base: float, yarn=None, rope_dim: int = DS4_ROPE_DIM, inverse: bool = False,
-                    out=None):
+def apply_rope_tail(x, positions, *, base: float = None, yarn=None, rope_dim: int = DS4_ROPE_DIM,
+                    inverse: bool = False, out=None, inv_freq=None, half_chain: bool = False):
     """DS4 partial RoPE on only the final ``rope_dim`` channels (interleaved pairs); the sequence axis is the
     second-to-last axis; leading channels are copied (reference: attention.py:114-156).
 
     x: CUDA tensor ``[..., seq, features]`` float32 / float16 / bfloat16; positions: ``seq`` integers (sequence,
     NumPy array or tensor).  Angles are formed in float64 and the result is rounded once to ``x.dtype``.
-    ``out=x`` rotates in place."""
+    ``out=x`` rotates in place.  ``inv_freq`` (``rope_dim / 2`` values) replaces ``base`` / ``yarn``;
+    ``half_chain=True`` (float16 rows) rotates the way the fused decode kernels do: float32 angle, cos / sin and
+    every product and sum rounded to float16."""
     import numpy as np
     if x.ndim < 2:
         raise ValueError("x must have at least sequence and feature dimensions")
@@ -194,12 +196,22 @@ def apply_rope_tail(x, positions, *, base: float, yarn=None, rope_dim: int = DS4
         out = torch.empty_like(x)
     elif out.shape != x.shape or out.dtype != x.dtype or not out.is_contiguous():
         raise ValueError("out must be a contiguous tensor with x's shape and dtype")
-    inv = torch.as_tensor(rope_inverse_frequencies(rope_dim, base, yarn), dtype=torch.float64, device=dev)
+    if inv_freq is None:
+        if base is None:
+            raise ValueError("either base or inv_freq must be given")
+        inv = torch.as_tensor(rope_inverse_frequencies(rope_dim, base, yarn), dtype=torch.float64, device=dev)
+    else:
+        inv = torch.as_tensor(inv_freq).reshape(-1).to(device=dev, dtype=torch.float64)
+        if int(inv.numel()) != rope_dim // 2:
+            raise ValueError("inv_freq must hold rope_dim / 2 values")
+    if half_chain and x.dtype != torch.float16:
+        raise ValueError("half_chain takes float16 rows")
     a = _abi.RopeTailArgs()
     a.x, a.out, a.x_dtype = ptr(x), ptr(out), _t.dtype_code(x)
     a.positions, a.inv_freq = ptr(pos), ptr(inv)
     a.n_rows = int(x.numel() // x.shape[-1])
     a.seq_len, a.width, a.rope_dim, a.inverse = int(x.shape[-2]), int(x.shape[-1]), int(rope_dim), 1 if inverse else 0
+    a.half_chain = 1 if half_chain else 0
     if a.n_rows == 0:
         return out
     _abi.check(_t.launch("rope_tail", _abi.load().mxb_rope_tail, a))
