@@ -1,18 +1,24 @@
 // Causal GQA flash prefill, head_dim 256, 16-bit operands, fp32 accumulation, with the
 // sigmoid-gate epilogue fused:  out = softmax(scale * Q K^T + causal) V * sigmoid(gate).
 //
-// One CTA = 128 query rows of one query head.  Seven warps:
-//   warps 0-3  softmax + epilogue; thread r owns query row r = TMEM lane r
-//   warp  4    issues the S = Q K^T MMAs (one lane)
-//   warp  5    TMA producer (one lane)
-//   warp  6    issues the O += P V MMAs (one lane)
-// Per 64-key tile:  S = Q K^T (M128 x N64 x K256) into one of two TMEM buffers;
+// One CTA = 128 query rows of one query head.  Twelve warps:
+//   warps 0-7  softmax + epilogue; warp w owns query rows 32 * (w % 4) .. (= its TMEM lanes) and keys
+//              32 * (w / 4) .. of every 64-key tile; the two halves of a row swap maxima and sums through
+//              shared memory
+//   warp  8    issues the first half of the S = Q K^T MMAs (feature slabs 0-1, one lane)
+//   warp  9    TMA producer (one lane)
+//   warp 10    issues the O += P V MMAs (one lane)
+//   warp 11    issues the second half of the S MMAs (feature slabs 2-3) into a second accumulator
+// Per 64-key tile:  S = Q K^T (M128 x N64 x K256) into one of two TMEM buffers, each made of two
+// accumulators that the softmax adds (one thread sustains only one tcgen05.mma per ~85 cycles, so
+// the 16 MMAs of a tile are split between two issuers);
 // the softmax warps read S from TMEM, keep a running maximum with lazy rescaling of
 // the TMEM-resident O (only when the maximum grew by more than 2^8), write P as a
-// 16-bit K-major swizzled tile to shared memory; O += P V (M128 x N256 x K64) with V
-// read from a pre-transposed copy (keys contiguous) so that every operand is K-major.
-// S of tile j+1 is issued before P of tile j is consumed, so the tensor pipe overlaps
-// the softmax.  TMEM: S0 [0,64) S1 [64,128) O [128,384).
+// 16-bit K-major swizzled tile to one of two shared-memory buffers; O += P V (M128 x N256 x K64)
+// with V read from a pre-transposed copy (keys contiguous) so that every operand is K-major.
+// S of tile j+1 is issued before P of tile j is consumed and P of tile j+1 is written while P V of
+// tile j runs, so the tensor pipe overlaps the softmax.
+// TMEM: S0a [0,64) S0b [64,128) S1a [128,192) S1b [192,256) O [256,512).
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
@@ -24,9 +30,10 @@ struct FlashSmem {
   static constexpr int q_off = 0;                       // 4 slabs x [128 x 128 B]
   static constexpr int k_off = q_off + 4 * 16384;       // 2 stages x 4 slabs x [64 x 128 B]
   static constexpr int v_off = k_off + 2 * 32768;       // 2 stages x [256 x 128 B]
-  static constexpr int p_off = v_off + 2 * 32768;       // [128 x 128 B]
-  static constexpr int bar_off = p_off + 16384;
-  static constexpr int total = bar_off + 256;
+  static constexpr int p_off = v_off + 2 * 32768;       // 2 buffers x [128 x 128 B]
+  static constexpr int bar_off = p_off + 2 * 16384;
+  static constexpr int rowmax_off = bar_off + 256;      // [2 tiles][2 halves][128 rows] bf16 (1 KB); reused for the row sums
+  static constexpr int total = rowmax_off + 1024;
 };
 
 struct FlashParams {
@@ -66,6 +73,12 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&v);
   }
 }
+__device__ __forceinline__ float fast_ex2(float x) {   // 2^x, x <= 0 here; -inf -> 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <bool BF16>
 __device__ __forceinline__ float2 unpack2(uint32_t u) {
   if constexpr (BF16) return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
@@ -73,7 +86,7 @@ __device__ __forceinline__ float2 unpack2(uint32_t u) {
 }
 
 template <bool BF16>
-__global__ void __launch_bounds__(224, 1) flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
+__global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
                                                                const __grid_constant__ CUtensorMap tm_k,
                                                                const __grid_constant__ CUtensorMap tm_vt,
                                                                FlashParams p) {
@@ -85,16 +98,17 @@ __global__ void __launch_bounds__(224, 1) flash_prefill_kernel(const __grid_cons
   uint8_t* v_s = smem + L::v_off;
   uint8_t* p_s = smem + L::p_off;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::bar_off);
+  uint16_t* rowmax_s = reinterpret_cast<uint16_t*>(smem + L::rowmax_off);
   uint64_t* q_full = bars + 0;
   uint64_t* k_full = bars + 1;   // [2]
   uint64_t* k_empty = bars + 3;  // [2]
   uint64_t* v_full = bars + 5;   // [2]
   uint64_t* v_empty = bars + 7;  // [2]
   uint64_t* s_ready = bars + 9;  // [2]
-  uint64_t* p_ready = bars + 11;
-  uint64_t* pv_done = bars + 12;
-  uint64_t* s_free = bars + 13;  // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* p_ready = bars + 11;  // [2], one per P buffer (the softmax warps may be a tile apart)
+  uint64_t* pv_done = bars + 13;  // [2], one per P buffer
+  uint64_t* s_free = bars + 15;   // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -111,15 +125,15 @@ __global__ void __launch_bounds__(224, 1) flash_prefill_kernel(const __grid_cons
     ptx::mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(&k_full[i], 1);
-      ptx::mbar_init(&k_empty[i], 1);
+      ptx::mbar_init(&k_empty[i], 2);   // both S issuers release a K stage
       ptx::mbar_init(&v_full[i], 1);
       ptx::mbar_init(&v_empty[i], 1);
-      ptx::mbar_init(&s_ready[i], 1);
+      ptx::mbar_init(&s_ready[i], 2);   // both halves of S
+      ptx::mbar_init(&pv_done[i], 1);
+      ptx::mbar_init(&p_ready[i], 256);
     }
-    ptx::mbar_init(p_ready, 128);
-    ptx::mbar_init(pv_done, 1);
-    ptx::mbar_init(&s_free[0], 128);
-    ptx::mbar_init(&s_free[1], 128);
+    ptx::mbar_init(&s_free[0], 256);
+    ptx::mbar_init(&s_free[1], 256);
     *abort_flag = 0;
     ptx::mbar_fence_init();
   }
@@ -132,9 +146,9 @@ __global__ void __launch_bounds__(224, 1) flash_prefill_kernel(const __grid_cons
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_o = tmem_base + 128;
+  const uint32_t tmem_o = tmem_base + 256;
 
-  if (warp == 5) {
+  if (warp == 9) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       ptx::tma_prefetch_desc(&tm_q);
@@ -156,11 +170,12 @@ __global__ void __launch_bounds__(224, 1) flash_prefill_kernel(const __grid_cons
         ptx::tma_load_3d(v_s + s * 32768, &tm_vt, &v_full[s], j * FB_N, 0, kvh);
       }
     }
-  } else if (warp == 4) {
-    // ------------------------------------------------------------ S = Q K^T issuer
-    // Issuing one tcgen05.mma costs a thread ~80 cycles; S (16 MMAs per tile) and P V (4 MMAs) write
-    // different TMEM columns, so they are issued by two threads in two warps and neither waits for the other.
+  } else if (warp == 8 || warp == 11) {
+    // ------------------------------------------------------------ S = Q K^T issuers
+    // Warp 4 accumulates feature slabs 0-1 into S(s)a, warp 7 slabs 2-3 into S(s)b; P V (4 MMAs) is a third
+    // issuer.  All write different TMEM columns, so none waits for another.
     if (lane == 0) {
+      const int half = warp == 8 ? 0 : 1;
       constexpr uint32_t fmt = BF16 ? ptx::kFmtBF16 : ptx::kFmtF16;
       const uint32_t idesc_s = ptx::idesc_f16(fmt, fmt, FB_M, FB_N, 0, 0);
       const uint64_t q_desc = ptx::smem_desc_sw128(ptx::smem_u32(q_s), 16, 1024);
@@ -171,19 +186,21 @@ __global__ void __launch_bounds__(224, 1) flash_prefill_kernel(const __grid_cons
         ptx::mbar_wait(&k_full[s], (uint32_t)((j >> 1) & 1), abort_flag);
         if (j >= 2) ptx::mbar_wait(&s_free[s], (uint32_t)(((j >> 1) - 1) & 1), abort_flag);  // softmax read S(j-2)
         ptx::tc_fence_after_sync();
-        const uint32_t d = tmem_base + (uint32_t)(s * FB_N);
+        const uint32_t d = tmem_base + (uint32_t)(s * 2 * FB_N + half * FB_N);
         const uint64_t kd = ptx::desc_advance(k_desc, s * 32768);
 #pragma unroll
-        for (int kb = 0; kb < 4; ++kb)
+        for (int kb2 = 0; kb2 < 2; ++kb2) {
+          const int kb = half * 2 + kb2;
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
             ptx::mma_f16_ss(d, ptx::desc_advance(q_desc, kb * 16384 + ks * 32),
-                            ptx::desc_advance(kd, kb * 8192 + ks * 32), idesc_s, (kb | ks) ? 1u : 0u);
+                            ptx::desc_advance(kd, kb * 8192 + ks * 32), idesc_s, (kb2 | ks) ? 1u : 0u);
+        }
         ptx::mma_commit(&s_ready[s]);
         ptx::mma_commit(&k_empty[s]);
       }
     }
-  } else if (warp == 6) {
+  } else if (warp == 10) {
     // ------------------------------------------------------------ O += P V issuer
     if (lane == 0) {
       constexpr uint32_t fmt = BF16 ? ptx::kFmtBF16 : ptx::kFmtF16;
@@ -192,42 +209,63 @@ __global__ void __launch_bounds__(224, 1) flash_prefill_kernel(const __grid_cons
       const uint64_t p_desc = ptx::smem_desc_sw128(ptx::smem_u32(p_s), 16, 1024);
       for (int j = 0; j < ntiles; ++j) {
         const int s = j & 1;
-        ptx::mbar_wait(p_ready, (uint32_t)(j & 1), abort_flag);
+        ptx::mbar_wait(&p_ready[s], (uint32_t)((j >> 1) & 1), abort_flag);
         ptx::mbar_wait(&v_full[s], (uint32_t)((j >> 1) & 1), abort_flag);
         ptx::tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          ptx::mma_f16_ss(tmem_o, ptx::desc_advance(p_desc, ks * 32), ptx::desc_advance(v_desc, s * 32768 + ks * 32),
-                          idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
-        ptx::mma_commit(pv_done);
+          ptx::mma_f16_ss(tmem_o, ptx::desc_advance(p_desc, s * 16384 + ks * 32),
+                          ptx::desc_advance(v_desc, s * 32768 + ks * 32), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+        ptx::mma_commit(&pv_done[s]);
         ptx::mma_commit(&v_empty[s]);
       }
     }
   } else {
-    // ------------------------------------------------------------ softmax + epilogue
-    const int row = tid;             // 0..127
-    const int qi = m0 + row;         // query row
-    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    // ------------------------------------------------------------ softmax + epilogue (warps 0-7)
+    // Thread = (query row, half of the tile's 64 keys): warps 0-3 take keys 0-31, warps 4-7 keys 32-63 of the
+    // same 128 rows (a warp reaches the TMEM lanes 32 * (warp % 4) ..).  The two halves of a row swap their
+    // maxima through shared memory, so both keep the same running reference; each rescales and writes out its
+    // half of the 256 output features.
+    const int quad = warp & 3, half = warp >> 2;
+    const int row = quad * 32 + lane;   // 0..127
+    const int qi = m0 + row;            // query row
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     float m_used = -INFINITY, l = 0.f;
     for (int j = 0; j < ntiles; ++j) {
       const int s = j & 1;
       ptx::mbar_wait(&s_ready[s], (uint32_t)((j >> 1) & 1), abort_flag);
       ptx::tc_fence_after_sync();
-      uint32_t sv[64];
-      ptx::tmem_ld32(tmem_base + lane_off + (uint32_t)(s * FB_N), sv);
-      ptx::tmem_ld32(tmem_base + lane_off + (uint32_t)(s * FB_N + 32), sv + 32);
-      ptx::tmem_ld_wait();
+      uint32_t sv[32];
+      {
+        uint32_t sb[32];
+        const uint32_t sa = tmem_base + lane_off + (uint32_t)(s * 2 * FB_N + half * 32);
+        ptx::tmem_ld32(sa, sv);
+        ptx::tmem_ld32(sa + FB_N, sb);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) sv[c] = __float_as_uint(__uint_as_float(sv[c]) + __uint_as_float(sb[c]));
+      }
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(&s_free[s]);
-      const int key0 = j * FB_N;
-      const bool need_mask = key0 + FB_N - 1 > m0 + past;  // tile reaches past the first row's diagonal
+      const int key0 = j * FB_N + half * 32;
+      const bool need_mask = j * FB_N + FB_N - 1 > m0 + past;  // tile reaches past the first row's diagonal
       float tmax = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
+      for (int c = 0; c < 32; ++c) {
         float x = __uint_as_float(sv[c]) * p.scale_log2;
         if (need_mask && key0 + c > qi + past) x = -INFINITY;
         sv[c] = __float_as_uint(x);
         tmax = fmaxf(tmax, x);
+      }
+      // Both halves of a row must use the SAME reference, and any upper bound of the tile's maximum will do:
+      // each half publishes its maximum rounded UP to bfloat16 and both take the larger of the two rounded values.
+      {
+        const uint32_t tb = __float_as_uint(tmax);
+        const uint16_t up = (uint16_t)(((tb >> 31) ? tb : tb + 0xFFFFu) >> 16);   // toward +inf; -inf stays -inf
+        rowmax_s[(s * 2 + half) * FB_M + row] = up;
+        asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight softmax warps
+        const uint16_t other = rowmax_s[(s * 2 + (half ^ 1)) * FB_M + row];
+        tmax = fmaxf(__uint_as_float((uint32_t)up << 16), __uint_as_float((uint32_t)other << 16));
       }
       float factor = 1.f;
       bool grow = false;
@@ -236,17 +274,19 @@ __global__ void __launch_bounds__(224, 1) flash_prefill_kernel(const __grid_cons
       } else {
         grow = tmax > m_used + 8.f;
       }
+      // P buffer s is free once P V of tile j-2 has read it
+      if (j >= 2) ptx::mbar_wait(&pv_done[s], (uint32_t)(((j >> 1) - 1) & 1), abort_flag);
       if (j > 0) {
-        // P buffer and O are free / final only after the previous P.V finished
-        ptx::mbar_wait(pv_done, (uint32_t)((j - 1) & 1), abort_flag);
-        ptx::tc_fence_after_sync();
-        if (__any_sync(0xffffffffu, grow)) {
+        if (__any_sync(0xffffffffu, grow)) {   // the same answer in both warps of a row quarter
+          // O is final only after the previous P V finished
+          ptx::mbar_wait(&pv_done[(j - 1) & 1], (uint32_t)(((j - 1) >> 1) & 1), abort_flag);
+          ptx::tc_fence_after_sync();
           if (grow) {
             factor = exp2f(m_used - tmax);
             m_used = tmax;
           }
 #pragma unroll 1
-          for (int c0 = 0; c0 < FB_D; c0 += 32) {
+          for (int c0 = half * (FB_D / 2); c0 < (half + 1) * (FB_D / 2); c0 += 32) {
             uint32_t ov[32];
             ptx::tmem_ld32(tmem_o + lane_off + (uint32_t)c0, ov);
             ptx::tmem_ld_wait();
@@ -259,26 +299,31 @@ __global__ void __launch_bounds__(224, 1) flash_prefill_kernel(const __grid_cons
         }
       }
       float psum = 0.f;
-      uint8_t* prow = p_s + row * 128;
+      uint8_t* prow = p_s + s * 16384 + row * 128;
 #pragma unroll
-      for (int c8 = 0; c8 < 8; ++c8) {
+      for (int c8 = 0; c8 < 4; ++c8) {
         uint32_t w[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float a = exp2f(__uint_as_float(sv[c8 * 8 + 2 * i]) - m_used);
-          const float b = exp2f(__uint_as_float(sv[c8 * 8 + 2 * i + 1]) - m_used);
+          const float a = fast_ex2(__uint_as_float(sv[c8 * 8 + 2 * i]) - m_used);
+          const float b = fast_ex2(__uint_as_float(sv[c8 * 8 + 2 * i + 1]) - m_used);
           psum += a + b;
           w[i] = pack2<BF16>(a, b);
         }
-        *reinterpret_cast<uint4*>(prow + ((c8 ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(prow + (((half * 4 + c8) ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
       l += psum;
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(p_ready);
+      ptx::mbar_arrive(&p_ready[s]);
     }
-    // epilogue
-    ptx::mbar_wait(pv_done, (uint32_t)((ntiles - 1) & 1), abort_flag);
+    // epilogue: the row sum over both halves, then each half writes its 128 output features
+    float* rowsum_s = reinterpret_cast<float*>(rowmax_s);   // [2 halves][128 rows]
+    asm volatile("bar.sync 1, 256;" ::: "memory");           // every maximum of the last tile has been read
+    rowsum_s[half * FB_M + row] = l;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    l += rowsum_s[(half ^ 1) * FB_M + row];
+    ptx::mbar_wait(&pv_done[(ntiles - 1) & 1], (uint32_t)(((ntiles - 1) >> 1) & 1), abort_flag);
     ptx::tc_fence_after_sync();
     const float inv_l = l > 0.f ? 1.f / l : 0.f;
     const bool row_ok = qi < p.S;
@@ -286,7 +331,7 @@ __global__ void __launch_bounds__(224, 1) flash_prefill_kernel(const __grid_cons
                                   : nullptr;
     uint16_t* optr = reinterpret_cast<uint16_t*>(p.out) + (int64_t)qi * p.o_ss + (int64_t)head * p.o_sh;
 #pragma unroll 1
-    for (int c0 = 0; c0 < FB_D; c0 += 32) {
+    for (int c0 = half * (FB_D / 2); c0 < (half + 1) * (FB_D / 2); c0 += 32) {
       uint32_t ov[32];
       ptx::tmem_ld32(tmem_o + lane_off + (uint32_t)c0, ov);
       ptx::tmem_ld_wait();
@@ -407,11 +452,11 @@ extern "C" int mxb_flash_prefill(const mxb_flash_prefill_args* a, void* stream) 
   dim3 grid((unsigned)ceil_div(a->S, FB_M), (unsigned)a->Hq);
   if (a->dtype == MXB_BF16) {
     MXB_CUDA_OK(cudaFuncSetAttribute(flash_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    flash_prefill_kernel<true><<<grid, 224, smem, st>>>(tq, tk, tv, p);
+    flash_prefill_kernel<true><<<grid, 384, smem, st>>>(tq, tk, tv, p);
     note_launch();
   } else {
     MXB_CUDA_OK(cudaFuncSetAttribute(flash_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    flash_prefill_kernel<false><<<grid, 224, smem, st>>>(tq, tk, tv, p);
+    flash_prefill_kernel<false><<<grid, 384, smem, st>>>(tq, tk, tv, p);
     note_launch();
   }
   MXB_CUDA_OK(cudaGetLastError());
