@@ -1,0 +1,78 @@
+"""Parity at the full sizes of the benchmark configurations, through checks whose cost does not grow with the
+size: the selection property of top-k over every row, and the oracle on a sample of rows / sequences / heads."""
+import numpy as np
+import pytest
+import torch
+
+from moespresso_b200 import synth
+from moespresso_b200.deepseek_v4.decode_step import LatentCache, sparse_decode_step
+from moespresso_b200.qwen.full_attention import sdpa_fa_prefill
+from oracle import ds4
+from tests.gpu_util import dev, fp8_from_bits, max_abs, need_gpu
+
+pytestmark = pytest.mark.gpu
+
+
+def test_batched_decode_step_at_full_size():
+    """Batch 32, contexts U[32K, 128K], top-k 2048, int8 KV + FP8 index keys: 2.6 M rows."""
+    need_gpu()
+    c = synth.config3(seed=1)
+    B, k = int(c["lens"].size), int(c["k"])
+    cache = LatentCache(kv=dev(c["kv"]), kv_scales=dev(c["kv_scales"]), idx_keys=fp8_from_bits(c["idx_key_bits"]),
+                        row_start=dev(c["row_start"]), row_count=dev(c["lens"].astype(np.int32)),
+                        max_rows=int(c["lens"].max()))
+    out, ids, scores = sparse_decode_step(dev(c["q"], torch.bfloat16), dev(c["idx_q"], torch.bfloat16),
+                                          dev(c["idx_w"]), cache, k=k, scale=c["scale"], d_v=c["d_v"],
+                                          return_ids=True, return_scores=True)
+    # --- top-k over EVERY row, on the device: ascending distinct valid ids, and nothing left out beats anything taken
+    rs, ln = dev(c["row_start"]), dev(c["lens"])
+    assert ids.dtype == torch.int32 and tuple(ids.shape) == (B, k)
+    assert torch.all(ids[:, 1:] > ids[:, :-1]) and torch.all(ids >= 0) and torch.all(ids < ln[:, None])
+    taken = torch.gather(scores, 0, (rs[:, None] + ids.long()).reshape(-1)).reshape(B, k)
+    for b in range(B):
+        row = scores[int(rs[b]): int(rs[b]) + int(ln[b])].clone()
+        kth = taken[b].min()
+        row[ids[b].long()] = -float("inf")
+        rest = row.max()
+        assert rest <= kth
+        if rest == kth:   # a tie at the boundary goes to the lower id
+            tied_out = torch.nonzero(row == kth).reshape(-1)
+            tied_in = ids[b][taken[b] == kth]
+            assert tied_in.max() < tied_out.min()
+    # --- scores and attention of a sample of sequences against the oracle
+    keys = None
+    sc = scores.cpu().numpy()
+    idn = ids.cpu().numpy()
+    for b in (0, B // 2, B - 1):
+        s, n = int(c["row_start"][b]), int(c["lens"][b])
+        kb = synth.e4m3_bits_to_f32(c["idx_key_bits"][s:s + n])
+        ref_scores = ds4.indexer_scores(c["idx_q"][b][None], kb, c["idx_w"][b][None])[0]
+        np.testing.assert_allclose(sc[s:s + n], ref_scores, rtol=2e-4, atol=2e-3)
+        sel = idn[b].astype(np.int64)
+        ref = ds4.indexed_mixed_attention_decode(c["q"][b], None, c["kv"][s:s + n][sel], np.arange(k), None, pos0=0,
+                                                 window=0, ratio=0, scale=c["scale"], d_v=c["d_v"],
+                                                 kv_scales=c["kv_scales"][s:s + n][sel])
+        assert max_abs(out[b], ref) <= 2e-2
+
+
+def test_qwen_prefill_at_full_size():
+    """S = 8192, 16 query heads over 2 KV heads, head_dim 256, bf16: three query tiles of three heads against a
+    float64 evaluation of those rows."""
+    need_gpu()
+    c = synth.config2()
+    t = lambda x: torch.from_numpy(x).cuda().to(torch.bfloat16)  # noqa: E731
+    q, k, v, g = t(c["q"]), t(c["k"]), t(c["v"]), t(c["gate"])
+    out = sdpa_fa_prefill(q, k, v, c["scale"], gate=g, layout="lhd").float().cpu().numpy()
+    S, Hq, D = c["q"].shape
+    group = Hq // c["k"].shape[1]
+    for h in (0, 7, 15):
+        kk = c["k"][:, h // group].astype(np.float64)
+        vv = c["v"][:, h // group].astype(np.float64)
+        for r0 in (0, 4032, S - 128):
+            rows = np.arange(r0, r0 + 128)
+            s = (c["q"][rows, h].astype(np.float64) @ kk.T) * c["scale"]
+            s[np.arange(S)[None, :] > rows[:, None]] = -np.inf
+            p = np.exp(s - s.max(axis=1, keepdims=True))
+            ref = (p @ vv) / p.sum(axis=1, keepdims=True)
+            ref = ref / (1.0 + np.exp(-c["gate"][rows, h].astype(np.float64)))
+            assert np.abs(out[rows, h] - ref).max() <= 2e-2
