@@ -76,3 +76,33 @@ def test_qwen_prefill_at_full_size():
             ref = (p @ vv) / p.sum(axis=1, keepdims=True)
             ref = ref / (1.0 + np.exp(-c["gate"][rows, h].astype(np.float64)))
             assert np.abs(out[rows, h] - ref).max() <= 2e-2
+
+
+def test_chunked_sparse_prefill_at_full_size():
+    """One 4096-token chunk at the end of a 131072-token context over 32768 ratio-4 compressed rows, top-k 2048 per
+    token, bf16: a sample of tokens against the oracle (scores -> selection -> attention)."""
+    need_gpu()
+    from moespresso_b200.deepseek_v4.prefill_step import sparse_prefill_step
+    c = synth.config4()
+    T, H, Dqk = c["q"].shape
+    R, k = c["kv"].shape[0], int(c["k"])
+    bf = lambda x: torch.from_numpy(x).cuda().to(torch.bfloat16)  # noqa: E731
+    out, ids = sparse_prefill_step(bf(c["q"]), bf(c["kv"]), bf(c["idx_q"]), bf(c["idx_keys"]), dev(c["idx_w"]),
+                                   pos0=int(c["pos0"]), ratio=int(c["ratio"]), k=k, scale=c["scale"], d_v=c["d_v"],
+                                   window=0, return_ids=True)
+    assert tuple(out.shape) == (T, H, c["d_v"]) and tuple(ids.shape) == (T, k)
+    vis = (int(c["pos0"]) + torch.arange(T, device="cuda") + 1) // int(c["ratio"])
+    assert torch.all(ids[:, 1:] > ids[:, :-1]) and torch.all(ids >= 0) and torch.all(ids < vis[:, None])
+    ids_n = ids.cpu().numpy()
+    for t in (0, 1, T // 2 + 3, T - 1):
+        v = int(vis[t])
+        ref_scores = ds4.indexer_scores(c["idx_q"][t][None], c["idx_keys"][:v], c["idx_w"][t][None])[0]
+        ref_ids = ds4.topk_ids(ref_scores, k)[0]
+        diff = np.setxor1d(ids_n[t], ref_ids)
+        if diff.size:   # the two sides round the scores differently: only near-ties of the k-th score may swap
+            kth = np.sort(ref_scores)[::-1][k - 1]
+            assert np.all(np.abs(ref_scores[diff] - kth) <= 2e-3 * max(1.0, abs(kth)))
+        sel = ids_n[t].astype(np.int64)
+        ref = ds4.indexed_mixed_attention_decode(c["q"][t], None, c["kv"][sel], np.arange(k), None, pos0=0, window=0,
+                                                 ratio=0, scale=c["scale"], d_v=c["d_v"])
+        assert max_abs(out[t], ref) <= 2e-2
