@@ -51,6 +51,9 @@ const char* mxb_last_error(void);
 /* Kernels this library has enqueued so far in this process (launches recorded into a CUDA graph count once,
  * when captured).  For benchmarks and tests that want to see that the device path ran. */
 int64_t mxb_kernel_launches(void);
+/* cudaMemcpyAsync(host -> device) on `stream`, for hosts that feed an operator's inputs from pinned memory on a
+ * side stream without a CUDA binding of their own (the decode plan copies q this way while the selection runs). */
+int mxb_copy_h2d_async(void* dst_device, const void* src_host, int64_t bytes, void* stream);
 
 /* ------------------------------------------------------------------------ *
  * Indexer score.

@@ -106,6 +106,7 @@ EXPORTS = {
     "mxb_abi_version": (C.c_int, []),
     "mxb_last_error": (C.c_char_p, []),
     "mxb_kernel_launches": (C.c_int64, []),
+    "mxb_copy_h2d_async": (C.c_int, [_p, _p, _i64, _p]),
     "mxb_indexer_scores": (C.c_int, [C.POINTER(IndexerScoresArgs), _p]),
     "mxb_indexer_qat": (C.c_int, [C.POINTER(IndexerQatArgs), _p]),
     "mxb_score_tail": (C.c_int, [C.POINTER(ScoreTailArgs), _p]),

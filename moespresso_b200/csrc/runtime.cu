@@ -86,5 +86,12 @@ void note_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 }  // namespace mxb
 
 extern "C" int64_t mxb_kernel_launches(void) { return mxb::g_launches.load(std::memory_order_relaxed); }
+extern "C" int mxb_copy_h2d_async(void* dst_device, const void* src_host, int64_t bytes, void* stream) {
+  MXB_REQUIRE(dst_device && src_host && bytes >= 0, MXB_ERR_INVALID, "copy: null pointer or negative size");
+  MXB_CUDA_OK(cudaMemcpyAsync(dst_device, src_host, (size_t)bytes, cudaMemcpyHostToDevice,
+                              reinterpret_cast<cudaStream_t>(stream)));
+  return MXB_OK;
+}
+
 extern "C" int mxb_abi_version(void) { return MXB_ABI_VERSION; }
 extern "C" const char* mxb_last_error(void) { return mxb::g_err; }

@@ -128,6 +128,18 @@ class SparseDecodePlan:
             with torch.cuda.graph(g):
                 self.out, self.ids = self._step()
             self.graph = g
+            # the same step as two graphs (select, attend): a host-fed step copies q on a second stream while the
+            # selection runs, because only the attention reads q
+            g1, g2 = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g1):
+                self._ids2 = self._select()
+            with torch.cuda.graph(g2):
+                self._out2 = self._attend(self._ids2)
+            self._graph_select, self._graph_attend = g1, g2
+        self._copy_stream = torch.cuda.Stream(device=dev)
+        self._q_copied = torch.cuda.Event()
+        self._attend_done = torch.cuda.Event()
+        self._attend_done.record(torch.cuda.current_stream(dev))
 
     def _views(self, buf):
         return tuple(buf[o:o + n].view(dt).view(sh)
@@ -140,8 +152,38 @@ class SparseDecodePlan:
         return buf, self._views(buf)
 
     def run_packed(self, host_buf):
-        self.packed.copy_(host_buf, non_blocking=True)
-        return self.launch()
+        """One step fed from a pinned host buffer laid out like ``host_buffer()``.  The small selection inputs are
+        copied first; q (97 % of the bytes) travels on a second stream while the scores and the top-k run, and the
+        attention waits for it.  Returns out [B,H,d_v] (asynchronously, on the current stream)."""
+        main = torch.cuda.current_stream(self.packed.device)
+        nq = self._offs[1]
+        if self.graph is None:
+            self.packed.copy_(host_buf, non_blocking=True)
+            return self.launch()
+        from .. import _abi
+        self.packed[nq:].copy_(host_buf[nq:], non_blocking=True)       # selection inputs first: the device starts at once
+        self._graph_select.replay()
+        self._copy_stream.wait_event(self._attend_done)                # the previous step's attention has read q
+        _abi.check(_abi.load().mxb_copy_h2d_async(self.packed.data_ptr(), host_buf.data_ptr(), nq,
+                                                  self._copy_stream.cuda_stream))
+        self._q_copied.record(self._copy_stream)
+        main.wait_event(self._q_copied)
+        self._graph_attend.replay()
+        self._attend_done.record(main)
+        return self._out2
+
+    def _select(self):
+        scores = indexer_scores(self.idx_q[:, :, None, :], self.idx_w[:, None, :].contiguous(), self.cache.idx_keys,
+                                n_rows=self.cache.max_rows, row_start=self.cache.row_start,
+                                row_count=self.cache.row_count)
+        return topk_select(scores, self.k, valid=self.cache.row_count, row_start=self.cache.row_start,
+                           n=self.cache.max_rows)
+
+    def _attend(self, ids):
+        return sparse_attention(self.q[:, :, None, :], self.cache.kv, ids[:, None, :], self.sinks, pos0=0, window=0,
+                                ratio=0, scale=self.scale, d_v=self.d_v, kv_scales=self.cache.kv_scales,
+                                comp_row_start=self.cache.row_start, comp_row_count=self.cache.row_count,
+                                n_comp=self.cache.max_rows, out_dtype=self.out_dtype)[:, :, 0, :]
 
     def _step(self):
         return sparse_decode_step(self.q, self.idx_q, self.idx_w, self.cache, k=self.k, scale=self.scale,
