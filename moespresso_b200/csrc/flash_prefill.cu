@@ -250,13 +250,16 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
       const int key0 = j * FB_N + half * 32;
       const bool need_mask = j * FB_N + FB_N - 1 > m0 + past;  // tile reaches past the first row's diagonal
       float tmax = -INFINITY;
+      // sv keeps the raw dot products; the (positive) scale is applied once to the maximum here and inside the
+      // exponent's fused multiply-add below
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
-        float x = __uint_as_float(sv[c]) * p.scale_log2;
+        float x = __uint_as_float(sv[c]);
         if (need_mask && key0 + c > qi + past) x = -INFINITY;
         sv[c] = __float_as_uint(x);
         tmax = fmaxf(tmax, x);
       }
+      tmax *= p.scale_log2;
       // Both halves of a row must use the SAME reference, and any upper bound of the tile's maximum will do:
       // each half publishes its maximum rounded UP to bfloat16 and both take the larger of the two rounded values.
       {
@@ -305,8 +308,8 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
         uint32_t w[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float a = fast_ex2(__uint_as_float(sv[c8 * 8 + 2 * i]) - m_used);
-          const float b = fast_ex2(__uint_as_float(sv[c8 * 8 + 2 * i + 1]) - m_used);
+          const float a = fast_ex2(fmaf(__uint_as_float(sv[c8 * 8 + 2 * i]), p.scale_log2, -m_used));
+          const float b = fast_ex2(fmaf(__uint_as_float(sv[c8 * 8 + 2 * i + 1]), p.scale_log2, -m_used));
           psum += a + b;
           w[i] = pack2<BF16>(a, b);
         }
@@ -440,6 +443,7 @@ extern "C" int mxb_flash_prefill(const mxb_flash_prefill_args* a, void* stream) 
     if (rc != MXB_OK) return rc;
   }
 
+  MXB_REQUIRE(a->scale > 0.f, MXB_ERR_INVALID, "flash prefill: scale must be positive");
   FlashParams p{};
   p.gate = a->gate; p.g_ss = a->gate_stride_s; p.g_sh = a->gate_stride_h;
   p.out = a->out; p.o_ss = a->out_stride_s; p.o_sh = a->out_stride_h;
