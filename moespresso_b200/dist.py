@@ -89,15 +89,11 @@ def _all_gather(t: torch.Tensor, group=None) -> torch.Tensor:
     return torch.stack(out)
 
 
-def range_sharded_decode_step(q, idx_q, idx_w, shard: RangeShard, *, k: int, scale: float, d_v: int, sinks=None,
-                              ops=None, group=None, return_ids: bool = False):
-    """One decode step of ONE sequence whose rows are range-sharded over the ranks of
-    `group`.  q [H,Dqk], idx_q [Hi,Di], idx_w [Hi] are replicated.  Every rank returns the
-    full output [H,d_v] (and, on request, the global ids this rank attended)."""
-    ops = ops or CudaOps()
+def range_step_candidates(idx_q, idx_w, shard: RangeShard, *, k: int, ops):
+    """Steps 1-2 of the range-sharded decode step on one rank: local scores and the local exact top-k as
+    (score, global id) candidates, ascending by id, padded with (-inf, -1)."""
     rows_local = int(shard.idx_keys.shape[0])
-    dev = q.device
-    # 1-2: local scores and local exact top-k (ascending local ids, -1 padded)
+    dev = idx_q.device
     if rows_local > 0:
         scores = ops.scores(idx_q, idx_w, shard.idx_keys)
         local_ids = ops.topk(scores, k).long()
@@ -107,29 +103,47 @@ def range_sharded_decode_step(q, idx_q, idx_w, shard: RangeShard, *, k: int, sca
     else:
         cand_scores = torch.full((k,), float("-inf"), device=dev)
         cand_ids = torch.full((k,), -1, dtype=torch.int64, device=dev)
-    # 3: exchange candidates.  Rank order == ascending global id order (range sharding), and
-    #    each rank's list is ascending, so position order == global id order.
-    all_scores = _all_gather(cand_scores.float(), group).reshape(-1)
-    all_ids = _all_gather(cand_ids, group).reshape(-1)
-    # 4: the same exact selection on every rank; ties go to the lower position == lower global id
-    pos = ops.topk(all_scores, k).long()
-    chosen = torch.where(pos >= 0, all_ids[pos.clamp(min=0)], torch.full_like(pos, -1))
+    return cand_scores.float(), cand_ids
+
+
+def range_step_partial(q, shard: RangeShard, all_scores, all_ids, *, k: int, scale: float, d_v: int, ops):
+    """Steps 4-5 on one rank, given every rank's candidates concatenated in rank order: the same exact global
+    selection on every rank (ties go to the lower position == lower global id, because ranks own ascending row
+    ranges and each list is ascending), then partial attention over the rows this rank owns.
+    Returns (o [H,d_v], ml [H,2], global ids attended here)."""
+    rows_local = int(shard.idx_keys.shape[0])
+    dev = q.device
+    pos = ops.topk(all_scores.reshape(-1), k).long()
+    chosen = torch.where(pos >= 0, all_ids.reshape(-1)[pos.clamp(min=0)], torch.full_like(pos, -1))
     hi = shard.row_lo + rows_local
     mine = (chosen >= shard.row_lo) & (chosen < hi)
     my_ids = torch.where(mine, chosen - shard.row_lo, torch.full_like(chosen, -1)).to(torch.int32)
-    # 5: partial attention over the rows this rank owns (none -> m = -inf, l = 0)
     if rows_local > 0:
         o, ml = ops.attend_partial(q, shard.kv, shard.kv_scales, my_ids, scale, d_v)
-    else:
+    else:   # no rows here: m = -inf, l = 0
         H = int(q.shape[0])
         o = torch.zeros((H, d_v), dtype=torch.float32, device=dev)
         ml = torch.stack([torch.full((H,), float("-inf"), device=dev), torch.zeros(H, device=dev)], dim=1)
+    return o.float(), ml.float(), chosen[mine]
+
+
+def range_sharded_decode_step(q, idx_q, idx_w, shard: RangeShard, *, k: int, scale: float, d_v: int, sinks=None,
+                              ops=None, group=None, return_ids: bool = False):
+    """One decode step of ONE sequence whose rows are range-sharded over the ranks of
+    `group`.  q [H,Dqk], idx_q [Hi,Di], idx_w [Hi] are replicated.  Every rank returns the
+    full output [H,d_v] (and, on request, the global ids this rank attended)."""
+    ops = ops or CudaOps()
+    # 1-2: local scores and local exact top-k
+    cand_scores, cand_ids = range_step_candidates(idx_q, idx_w, shard, k=k, ops=ops)
+    # 3: exchange candidates (k (score, id) pairs per rank)
+    all_scores = _all_gather(cand_scores, group)
+    all_ids = _all_gather(cand_ids, group)
+    # 4-5: identical global selection, local partial attention
+    o, ml, attended = range_step_partial(q, shard, all_scores, all_ids, k=k, scale=scale, d_v=d_v, ops=ops)
     # 6-7: exchange partials, merge in rank order, sink joins once
-    o_parts = _all_gather(o.float(), group)
-    ml_parts = _all_gather(ml.float(), group)
-    out = ops.merge(o_parts, ml_parts, sinks)
+    out = ops.merge(_all_gather(o, group), _all_gather(ml, group), sinks)
     if return_ids:
-        return out, chosen[mine]
+        return out, attended
     return out
 
 
