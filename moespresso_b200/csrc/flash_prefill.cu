@@ -25,6 +25,16 @@
 namespace mxb {
 
 constexpr int FB_M = 128, FB_N = 64, FB_D = 256;
+#ifndef MXB_FLASH_POLY
+#define MXB_FLASH_POLY 2
+#endif
+constexpr int kPolyOf2 = MXB_FLASH_POLY;   // of every four exponentials, this many (0, 1 or 2) run on the FMA pipe
+
+#ifdef MXB_TRACE_FL   // development aid: cycle stamps of one CTA's roles over 16 tiles, written behind `status`
+#define TRF(k, j) do { if (tr_cta && (j) >= 32 && (j) < 48) tr[(k) * 16 + (j) - 32] = clock64(); } while (0)
+#else
+#define TRF(k, j)
+#endif
 
 struct FlashSmem {
   static constexpr int q_off = 0;                       // 4 slabs x [128 x 128 B]
@@ -79,6 +89,21 @@ __device__ __forceinline__ float fast_ex2(float x) {   // 2^x, x <= 0 here; -inf
   return y;
 }
 
+// 2^x on the FMA pipe for x <= ~8: round-to-nearest split x = n + f with the 1.5 * 2^23 trick, a cubic for 2^f on
+// [-0.5, 0.5] (relative error 7.5e-5, below the rounding of a 16-bit P), n added into the exponent field.  Half of
+// a tile's exponentials go this way because the special-function unit (16 results per clock per SM) would otherwise
+// bound the softmax.  Inputs below -126 (masked keys) give 2^-126 instead of 0.
+__device__ __forceinline__ float poly_ex2(float x) {
+  x = fmaxf(x, -126.f);
+  const float kMagic = 12582912.f;
+  const float xr = x + kMagic;
+  const float f = x - (xr - kMagic);
+  float r = fmaf(0.0551716685295105f, f, 0.2426111251115799f);
+  r = fmaf(r, f, 0.6932609677314758f);
+  r = fmaf(r, f, 0.9999280571937561f);
+  return __int_as_float(__float_as_int(r) + (__float_as_int(xr) << 23));
+}
+
 template <bool BF16>
 __device__ __forceinline__ float2 unpack2(uint32_t u) {
   if constexpr (BF16) return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
@@ -103,7 +128,6 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
   uint64_t* k_full = bars + 1;   // [2]
   uint64_t* k_empty = bars + 3;  // [2]
   uint64_t* v_full = bars + 5;   // [2]
-  uint64_t* v_empty = bars + 7;  // [2]
   uint64_t* s_ready = bars + 9;  // [2]
   uint64_t* p_ready = bars + 11;  // [2], one per P buffer (the softmax warps may be a tile apart)
   uint64_t* pv_done = bars + 13;  // [2], one per P buffer
@@ -120,6 +144,10 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
   int kv_end = m0 + FB_M + past;
   if (kv_end > p.Skv) kv_end = p.Skv;
   const int ntiles = (kv_end + FB_N - 1) / FB_N;
+#ifdef MXB_TRACE_FL
+  long long* tr = reinterpret_cast<long long*>(p.status);
+  const bool tr_cta = p.status && blockIdx.x == 0 && blockIdx.y == 0 && (tid & 31) == 0;
+#endif
 
   if (tid == 0) {
     ptx::mbar_init(q_full, 1);
@@ -127,7 +155,6 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
       ptx::mbar_init(&k_full[i], 1);
       ptx::mbar_init(&k_empty[i], 2);   // both S issuers release a K stage
       ptx::mbar_init(&v_full[i], 1);
-      ptx::mbar_init(&v_empty[i], 1);
       ptx::mbar_init(&s_ready[i], 2);   // both halves of S
       ptx::mbar_init(&pv_done[i], 1);
       ptx::mbar_init(&p_ready[i], 256);
@@ -153,21 +180,17 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
     if (lane == 0) {
       ptx::tma_prefetch_desc(&tm_q);
       ptx::tma_prefetch_desc(&tm_k);
-      ptx::tma_prefetch_desc(&tm_vt);
       ptx::mbar_expect_tx(q_full, 4 * 16384);
       for (int kb = 0; kb < 4; ++kb)
         ptx::tma_load_3d(q_s + kb * 16384, &tm_q, q_full, kb * 64, p.q_head_inner ? head : m0,
                          p.q_head_inner ? m0 : head);
-      for (int j = 0; j < ntiles; ++j) {
+      for (int j = 0; j < ntiles; ++j) {   // K tiles only: V is fetched by the P V issuer, behind its own MMAs
         const int s = j & 1, u = j >> 1;
         if (j >= 2) ptx::mbar_wait(&k_empty[s], (uint32_t)((u - 1) & 1), abort_flag);
         ptx::mbar_expect_tx(&k_full[s], 32768);
         for (int kb = 0; kb < 4; ++kb)
           ptx::tma_load_3d(k_s + s * 32768 + kb * 8192, &tm_k, &k_full[s], kb * 64, p.k_head_inner ? kvh : j * FB_N,
                            p.k_head_inner ? j * FB_N : kvh);
-        if (j >= 2) ptx::mbar_wait(&v_empty[s], (uint32_t)((u - 1) & 1), abort_flag);
-        ptx::mbar_expect_tx(&v_full[s], 32768);
-        ptx::tma_load_3d(v_s + s * 32768, &tm_vt, &v_full[s], j * FB_N, 0, kvh);
       }
     }
   } else if (warp == 8 || warp == 11) {
@@ -186,6 +209,7 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
         ptx::mbar_wait(&k_full[s], (uint32_t)((j >> 1) & 1), abort_flag);
         if (j >= 2) ptx::mbar_wait(&s_free[s], (uint32_t)(((j >> 1) - 1) & 1), abort_flag);  // softmax read S(j-2)
         ptx::tc_fence_after_sync();
+        TRF(half ? 2 : 0, j);
         const uint32_t d = tmem_base + (uint32_t)(s * 2 * FB_N + half * FB_N);
         const uint64_t kd = ptx::desc_advance(k_desc, s * 32768);
 #pragma unroll
@@ -198,6 +222,7 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
         }
         ptx::mma_commit(&s_ready[s]);
         ptx::mma_commit(&k_empty[s]);
+        TRF(half ? 3 : 1, j);
       }
     }
   } else if (warp == 10) {
@@ -207,17 +232,31 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
       const uint32_t idesc_o = ptx::idesc_f16(fmt, fmt, FB_M, FB_D, 0, 0);
       const uint64_t v_desc = ptx::smem_desc_sw128(ptx::smem_u32(v_s), 16, 1024);
       const uint64_t p_desc = ptx::smem_desc_sw128(ptx::smem_u32(p_s), 16, 1024);
+      ptx::tma_prefetch_desc(&tm_vt);
+      auto load_v = [&](int j) {
+        const int s = j & 1;
+        ptx::mbar_expect_tx(&v_full[s], 32768);
+        ptx::tma_load_3d(v_s + s * 32768, &tm_vt, &v_full[s], j * FB_N, 0, kvh);
+      };
+      load_v(0);
+      if (ntiles > 1) load_v(1);
       for (int j = 0; j < ntiles; ++j) {
         const int s = j & 1;
         ptx::mbar_wait(&p_ready[s], (uint32_t)((j >> 1) & 1), abort_flag);
         ptx::mbar_wait(&v_full[s], (uint32_t)((j >> 1) & 1), abort_flag);
         ptx::tc_fence_after_sync();
+        TRF(4, j);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
           ptx::mma_f16_ss(tmem_o, ptx::desc_advance(p_desc, s * 16384 + ks * 32),
                           ptx::desc_advance(v_desc, s * 32768 + ks * 32), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
         ptx::mma_commit(&pv_done[s]);
-        ptx::mma_commit(&v_empty[s]);
+        TRF(5, j);
+        // V of the next tile goes where P V of the previous tile read; that one was issued a whole tile ago
+        if (j >= 1 && j + 1 < ntiles) {
+          ptx::mbar_wait(&pv_done[s ^ 1], (uint32_t)(((j - 1) >> 1) & 1), abort_flag);
+          load_v(j + 1);
+        }
       }
     }
   } else {
@@ -233,8 +272,13 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
     float m_used = -INFINITY, l = 0.f;
     for (int j = 0; j < ntiles; ++j) {
       const int s = j & 1;
+#ifdef MXB_TRACE_FL
+      const int tk = warp == 0 ? 6 : (warp == 4 ? 12 : 18);
+#endif
+      TRF(tk + 0, j);
       ptx::mbar_wait(&s_ready[s], (uint32_t)((j >> 1) & 1), abort_flag);
       ptx::tc_fence_after_sync();
+      TRF(tk + 1, j);
       uint32_t sv[32];
       {
         uint32_t sb[32];
@@ -247,26 +291,31 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
       }
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(&s_free[s]);
+      TRF(tk + 2, j);
       const int key0 = j * FB_N + half * 32;
       const bool need_mask = j * FB_N + FB_N - 1 > m0 + past;  // tile reaches past the first row's diagonal
-      float tmax = -INFINITY;
       // sv keeps the raw dot products; the (positive) scale is applied once to the maximum here and inside the
       // exponent's fused multiply-add below
+      if (need_mask) {
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        float x = __uint_as_float(sv[c]);
-        if (need_mask && key0 + c > qi + past) x = -INFINITY;
-        sv[c] = __float_as_uint(x);
-        tmax = fmaxf(tmax, x);
+        for (int c = 0; c < 32; ++c)
+          if (key0 + c > qi + past) sv[c] = 0xff800000u;   // -inf
       }
-      tmax *= p.scale_log2;
+      float tm4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four independent chains
+#pragma unroll
+      for (int c = 0; c < 32; c += 4) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) tm4[i] = fmaxf(tm4[i], __uint_as_float(sv[c + i]));
+      }
+      float tmax = fmaxf(fmaxf(tm4[0], tm4[1]), fmaxf(tm4[2], tm4[3])) * p.scale_log2;
       // Both halves of a row must use the SAME reference, and any upper bound of the tile's maximum will do:
       // each half publishes its maximum rounded UP to bfloat16 and both take the larger of the two rounded values.
       {
         const uint32_t tb = __float_as_uint(tmax);
         const uint16_t up = (uint16_t)(((tb >> 31) ? tb : tb + 0xFFFFu) >> 16);   // toward +inf; -inf stays -inf
         rowmax_s[(s * 2 + half) * FB_M + row] = up;
-        asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight softmax warps
+        asm volatile("bar.sync %0, 64;" ::"r"(quad + 1) : "memory");   // the two warps that share these rows
+        TRF(tk + 3, j);
         const uint16_t other = rowmax_s[(s * 2 + (half ^ 1)) * FB_M + row];
         tmax = fmaxf(__uint_as_float((uint32_t)up << 16), __uint_as_float((uint32_t)other << 16));
       }
@@ -301,6 +350,7 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
           l *= factor;
         }
       }
+      TRF(tk + 4, j);
       float psum = 0.f;
       uint8_t* prow = p_s + s * 16384 + row * 128;
 #pragma unroll
@@ -308,8 +358,10 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
         uint32_t w[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float a = fast_ex2(fmaf(__uint_as_float(sv[c8 * 8 + 2 * i]), p.scale_log2, -m_used));
-          const float b = fast_ex2(fmaf(__uint_as_float(sv[c8 * 8 + 2 * i + 1]), p.scale_log2, -m_used));
+          const float xa = fmaf(__uint_as_float(sv[c8 * 8 + 2 * i]), p.scale_log2, -m_used);
+          const float xb = fmaf(__uint_as_float(sv[c8 * 8 + 2 * i + 1]), p.scale_log2, -m_used);
+          const float a = fast_ex2(xa);
+          const float b = ((i & 1) < kPolyOf2) ? poly_ex2(xb) : fast_ex2(xb);
           psum += a + b;
           w[i] = pack2<BF16>(a, b);
         }
@@ -319,12 +371,13 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(&p_ready[s]);
+      TRF(tk + 5, j);
     }
     // epilogue: the row sum over both halves, then each half writes its 128 output features
     float* rowsum_s = reinterpret_cast<float*>(rowmax_s);   // [2 halves][128 rows]
-    asm volatile("bar.sync 1, 256;" ::: "memory");           // every maximum of the last tile has been read
+    asm volatile("bar.sync 5, 256;" ::: "memory");   // all eight warps: every maximum of the last tile has been read
     rowsum_s[half * FB_M + row] = l;
-    asm volatile("bar.sync 1, 256;" ::: "memory");
+    asm volatile("bar.sync %0, 64;" ::"r"(quad + 1) : "memory");
     l += rowsum_s[(half ^ 1) * FB_M + row];
     ptx::mbar_wait(&pv_done[(ntiles - 1) & 1], (uint32_t)(((ntiles - 1) >> 1) & 1), abort_flag);
     ptx::tc_fence_after_sync();

@@ -48,8 +48,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // time instead of hanging the device.  Returns false when it gave up.
 constexpr uint32_t kSpinLimit = 1u << 22;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return !*abort_flag;   // the common case: one probe, flag read off the critical path
   if (*abort_flag) return false;
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+  for (uint32_t i = 1; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 1023u) == 1023u && *abort_flag) return false;
   }
