@@ -32,8 +32,10 @@ constexpr int kPolyOf2 = MXB_FLASH_POLY;   // of every four exponentials, this m
 
 #ifdef MXB_TRACE_FL   // development aid: cycle stamps of one CTA's roles over 16 tiles, written behind `status`
 #define TRF(k, j) do { if (tr_cta && (j) >= 32 && (j) < 48) tr[(k) * 16 + (j) - 32] = clock64(); } while (0)
+#define TRX(i) do { if (tr_cta && warp == 0) tr[18 * 16 + (i)] = clock64() - c_begin; } while (0)
 #else
 #define TRF(k, j)
+#define TRX(i)
 #endif
 
 struct FlashSmem {
@@ -147,6 +149,14 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
 #ifdef MXB_TRACE_FL
   long long* tr = reinterpret_cast<long long*>(p.status);
   const bool tr_cta = p.status && blockIdx.x == 0 && blockIdx.y == 0 && (tid & 31) == 0;
+  long long* tr_all = tr + 24 * 16 + (blockIdx.y * gridDim.x + blockIdx.x) * 4;   // per CTA: start ns, end ns, cycles, SM
+  const long long c_begin = clock64();
+  if (p.status && tid == 0) {
+    unsigned long long ns; unsigned sm;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+    tr_all[0] = (long long)ns; tr_all[3] = sm;
+  }
 #endif
 
   if (tid == 0) {
@@ -174,6 +184,7 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_o = tmem_base + 256;
+  TRX(0);
 
   if (warp == 9) {
     // ------------------------------------------------------------ TMA producer
@@ -279,6 +290,9 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
       ptx::mbar_wait(&s_ready[s], (uint32_t)((j >> 1) & 1), abort_flag);
       ptx::tc_fence_after_sync();
       TRF(tk + 1, j);
+      if (j == 0) TRX(1);
+      if (j == 1) TRX(2);
+      if (j == ntiles - 1) TRX(3);
       uint32_t sv[32];
       {
         uint32_t sb[32];
@@ -374,6 +388,17 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
       TRF(tk + 5, j);
     }
     // epilogue: the row sum over both halves, then each half writes its 128 output features
+    TRX(4);
+    // The gate values of this thread's half row (16 x 16 bytes) are requested first, all at once: they travel
+    // while the last P V finishes and the row sums are exchanged (one load per use would put 16 round trips
+    // to L2 on the drain's critical path).
+    const bool row_ok = qi < p.S;
+    const uint16_t* gptr = (p.gate && row_ok) ? reinterpret_cast<const uint16_t*>(p.gate) + (int64_t)qi * p.g_ss +
+                                                    (int64_t)head * p.g_sh + half * (FB_D / 2)
+                                              : nullptr;
+    uint4 gv[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) gv[i] = gptr ? __ldg(reinterpret_cast<const uint4*>(gptr) + i) : make_uint4(0, 0, 0, 0);
     float* rowsum_s = reinterpret_cast<float*>(rowmax_s);   // [2 halves][128 rows]
     asm volatile("bar.sync 5, 256;" ::: "memory");   // all eight warps: every maximum of the last tile has been read
     rowsum_s[half * FB_M + row] = l;
@@ -381,44 +406,51 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
     l += rowsum_s[(half ^ 1) * FB_M + row];
     ptx::mbar_wait(&pv_done[(ntiles - 1) & 1], (uint32_t)(((ntiles - 1) >> 1) & 1), abort_flag);
     ptx::tc_fence_after_sync();
+    TRX(5);
     const float inv_l = l > 0.f ? 1.f / l : 0.f;
-    const bool row_ok = qi < p.S;
-    const uint16_t* gptr = p.gate ? reinterpret_cast<const uint16_t*>(p.gate) + (int64_t)qi * p.g_ss + (int64_t)head * p.g_sh
-                                  : nullptr;
-    uint16_t* optr = reinterpret_cast<uint16_t*>(p.out) + (int64_t)qi * p.o_ss + (int64_t)head * p.o_sh;
-#pragma unroll 1
-    for (int c0 = half * (FB_D / 2); c0 < (half + 1) * (FB_D / 2); c0 += 32) {
+    uint16_t* optr = reinterpret_cast<uint16_t*>(p.out) + (int64_t)qi * p.o_ss + (int64_t)head * p.o_sh + half * (FB_D / 2);
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) {
       uint32_t ov[32];
-      ptx::tmem_ld32(tmem_o + lane_off + (uint32_t)c0, ov);
+      ptx::tmem_ld32(tmem_o + lane_off + (uint32_t)(half * (FB_D / 2) + cc * 32), ov);
       ptx::tmem_ld_wait();
       if (row_ok) {
 #pragma unroll
         for (int c8 = 0; c8 < 4; ++c8) {
-          uint4 g = make_uint4(0, 0, 0, 0);
-          if (gptr) g = __ldg(reinterpret_cast<const uint4*>(gptr + c0 + c8 * 8));
+          const uint4 g = gv[cc * 4 + c8];
           const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
           uint32_t w[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             float a = __uint_as_float(ov[c8 * 8 + 2 * i]) * inv_l;
             float b = __uint_as_float(ov[c8 * 8 + 2 * i + 1]) * inv_l;
-            if (gptr) {
+            if (p.gate) {
               const float2 gg = unpack2<BF16>(gw[i]);
-              a *= 1.f / (1.f + __expf(-gg.x));
-              b *= 1.f / (1.f + __expf(-gg.y));
+              a = __fdividef(a, 1.f + __expf(-gg.x));
+              b = __fdividef(b, 1.f + __expf(-gg.y));
             }
             w[i] = pack2<BF16>(a, b);
           }
-          *reinterpret_cast<uint4*>(optr + c0 + c8 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(optr + cc * 32 + c8 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
     }
+    TRX(6);
     ptx::tc_fence_before_sync();
   }
 
   __syncthreads();
+  TRX(7);
   if (warp == 0) ptx::tmem_dealloc(tmem_base, 512);
+#ifdef MXB_TRACE_FL
+  if (p.status && tid == 0) {
+    unsigned long long ns;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+    tr_all[1] = (long long)ns; tr_all[2] = clock64() - c_begin;
+  }
+#else
   if (tid == 0 && *abort_flag && p.status) atomicExch(p.status, 1);
+#endif
 }
 
 }  // namespace mxb
