@@ -90,6 +90,19 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// Row gather: four rows (y0..y3, any order, each checked against the map's bounds on its own: a row outside them,
+// e.g. -1, arrives as zeros) of a 2-D tensor, `box` columns starting at x, land as four consecutive rows of the
+// destination.  The map is encoded with a box of {columns, 1}.  Counts 4 * box bytes on the barrier.
+__device__ __forceinline__ void tma_gather4_2d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int32_t x,
+                                               int32_t y0, int32_t y1, int32_t y2, int32_t y3) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y0), "r"(y1),
+        "r"(y2), "r"(y3)
+      : "memory");
+}
+
 // Untiled bulk copy of `bytes` contiguous bytes (multiple of 16, both addresses 16-byte aligned).
 __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
   asm volatile(

@@ -31,6 +31,7 @@ struct SparseParams {
   int32_t window, ratio;
   int32_t nsplit;
   int32_t* status;
+  int32_t tma_rows;   // 16-bit tables: rows are gathered by TMA (tensor maps passed beside these parameters)
 };
 
 // tcgen05 path (16-bit / int8 KV).  Returns MXB_ERR_UNSUPPORTED when the shape is outside its range.

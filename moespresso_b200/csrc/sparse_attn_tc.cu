@@ -80,7 +80,7 @@ struct TcMisc {
   uint32_t row_ref[3][TC_ROWS];  // two tiles ahead, so that the loads of the next tile can be issued as soon as the
                                  // registers that carry them are free.  row_ref: kNoRow, or row index within its
                                  // table (< 2^31) with bit 31 set for the raw table
-  uint64_t bar_s, bar_o;
+  uint64_t bar_s, bar_o, bar_t;
   uint32_t tmem_slot;
   int abort_flag;
   int keff;
@@ -155,7 +155,8 @@ __device__ __forceinline__ int float_order(float x) {
 __device__ __forceinline__ float order_float(int i) { return __int_as_float(i ^ ((i >> 31) & 0x7fffffff)); }
 
 template <int KVT, int QT, int OT>
-__global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) {
+__global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_comp,
+                                                                const __grid_constant__ CUtensorMap tm_raw) {
   constexpr bool BF16 = (KVT == MXB_BF16);
   constexpr int EB = ElemBytes<KVT>::v;
   extern __shared__ uint8_t smem_raw[];
@@ -205,6 +206,7 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
   if (tid == 0) {
     ptx::mbar_init(&mi->bar_s, 1);
     ptx::mbar_init(&mi->bar_o, (uint32_t)(p.Dv / 128));
+    ptx::mbar_init(&mi->bar_t, 1);
     mi->abort_flag = 0;
     mi->keff = p.k;
     ptx::mbar_fence_init();
@@ -419,6 +421,61 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
       }
     }
   };
+  // 16-bit tables need no widening, so their rows can bypass the registers: TMA row gathers (four rows x one
+  // 128-byte slab per instruction, swizzled on the way in) write the operand layout directly.  Warp w fetches rows
+  // 16w .. 16w+15; a lane owns (group of four rows, slab) pairs.  Rows without data are fetched from row -1 (zeros).
+  // A group of four that holds rows of BOTH tables (at most one per token, where the raw window ends) is fetched
+  // from the compressed table and its raw rows are patched in with plain loads once the tile has landed.
+  const bool tma_rows = KVT != MXB_I8 && p.tma_rows != 0;
+  auto group_refs = [&](int mbuf, int r0, uint32_t* ref, bool& any_raw, bool& any_comp) {
+    any_raw = any_comp = false;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      ref[j] = mi->row_ref[mbuf][r0 + j];
+      if (ref[j] != kNoRow) {
+        if (ref[j] >> 31) any_raw = true;
+        else any_comp = true;
+      }
+    }
+  };
+  auto issue_tma = [&](int T) {
+    const int mbuf = T % 3;
+    if (tid == 0) ptx::mbar_expect_tx(&mi->bar_t, (uint32_t)(TC_ROWS * p.Dqk * 2));
+    for (int i = lane; i < 4 * nslab; i += 32) {
+      const int g = i / nslab, sl = i % nslab;
+      const int r0 = warp * 16 + g * 4;
+      uint32_t ref[4];
+      bool any_raw, any_comp;
+      group_refs(mbuf, r0, ref, any_raw, any_comp);
+      const bool from_raw = any_raw && !any_comp;
+      int32_t y[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        y[j] = (ref[j] != kNoRow && (ref[j] >> 31) == (from_raw ? 1u : 0u)) ? (int32_t)(ref[j] & 0x7FFFFFFFu) : -1;
+      ptx::tma_gather4_2d(tile + (size_t)sl * 16384 + (size_t)r0 * 128, from_raw ? &tm_raw : &tm_comp, &mi->bar_t,
+                          sl * 64, y[0], y[1], y[2], y[3]);
+    }
+  };
+  auto patch_mixed = [&](int T) {
+    const int mbuf = T % 3;
+    for (int i = lane; i < 4 * nslab; i += 32) {
+      const int g = i / nslab, sl = i % nslab;
+      const int r0 = warp * 16 + g * 4;
+      uint32_t ref[4];
+      bool any_raw, any_comp;
+      group_refs(mbuf, r0, ref, any_raw, any_comp);
+      if (!(any_raw && any_comp)) continue;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (ref[j] == kNoRow || !(ref[j] >> 31)) continue;
+        const int rr = r0 + j;
+        const uint4* src = reinterpret_cast<const uint4*>(row_address(ref[j]) + (size_t)sl * 128);
+        uint8_t* drow = tile + (size_t)sl * 16384 + (size_t)rr * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(drow + ((c ^ (rr & 7)) << 4)) = __ldg(src + c);
+      }
+    }
+  };
   if (ntiles > 0) {
     // prime the pipeline: tiles 0 and 1 published, tile 2 through stage B, tile 3 through stage A
     const int32_t i0 = fetch_id(0), i1 = fetch_id(1), i2 = fetch_id(2);
@@ -433,7 +490,8 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
     TRS(12, 4);
     __syncthreads();
     TRS(12, 5);
-    issue_loads(0, 0);
+    if (tma_rows) issue_tma(0);
+    else issue_loads(0, 0);
     TRS(12, 6);
   }
 
@@ -441,10 +499,15 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
     TRS(0, it);
     // ---------------------------------------------------------------- rows of this tile -> operand layout
     const int mb = it % 3;   // metadata buffer of this tile (filled two tiles ago, or before the loop)
-    store_loaded(0);
-    for (int cg0 = 9; cg0 < ncg; cg0 += 9) {   // rows wider than 9 chunk groups (16-bit tables): the rest, in place
-      issue_loads(mb, cg0);
-      store_loaded(cg0);
+    if (tma_rows) {
+      ptx::mbar_wait(&mi->bar_t, (uint32_t)(it & 1), abort_flag);
+      patch_mixed(it);
+    } else {
+      store_loaded(0);
+      for (int cg0 = 9; cg0 < ncg; cg0 += 9) {   // rows wider than 9 chunk groups (16-bit tables): the rest, in place
+        issue_loads(mb, cg0);
+        store_loaded(cg0);
+      }
     }
     ptx::fence_proxy_async_smem();
     ptx::tc_fence_before_sync();
@@ -470,9 +533,9 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
       }
       ptx::mma_commit(&mi->bar_s);
       TRS(2, it);
-      if (it + 1 < ntiles) issue_loads((it + 1) % 3, 0);
+      if (!tma_rows && it + 1 < ntiles) issue_loads((it + 1) % 3, 0);
     } else {
-      if (it + 1 < ntiles) issue_loads((it + 1) % 3, 0);
+      if (!tma_rows && it + 1 < ntiles) issue_loads((it + 1) % 3, 0);
     }
     ptx::mbar_wait(&mi->bar_s, (uint32_t)(it & 1), abort_flag);
     ptx::tc_fence_after_sync();
@@ -586,6 +649,7 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_tc_kernel(SparseParams p) 
     ptx::mbar_wait(&mi->bar_o, (uint32_t)(it & 1), abort_flag);  // the single row tile is rewritten next
     ptx::tc_fence_after_sync();
     TRS(6, it);
+    if (tma_rows && it + 1 < ntiles) issue_tma(it + 1);   // the tile is free: the next rows start travelling
   }
 
   // ------------------------------------------------------------------ reduce l over the 128 rows
@@ -703,15 +767,37 @@ int sparse_tc_splits(int B, int T, int H, int k, int raw_cap, int requested) {
   return (int)want;
 }
 
+// Tensor map over a [rows, Dqk] table of 16-bit values for row gathers: box = one 128-byte slab of one row.  The
+// row extent is left open (the caller's ids are what bounds the reads); row -1 is the zero row.
+static int row_gather_map(CUtensorMap* out, const void* table, int Dqk, bool bf16) {
+  const uint64_t dims[2] = {(uint64_t)Dqk, (uint64_t)0x7FFFFFFF};
+  const uint64_t strides[1] = {(uint64_t)Dqk * 2};
+  const uint32_t box[2] = {64, 1};
+  return make_tensor_map(out, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, table, dims,
+                         strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
 template <int KVT, int QT>
 static int launch_tc_typed(SparseParams& p, int out_dtype, cudaStream_t st) {
   const int smem = tc_layout(p.Dqk, p.Dv).total + 1024;
+  CUtensorMap tm_comp, tm_raw;
+  memset(&tm_comp, 0, sizeof(tm_comp));
+  memset(&tm_raw, 0, sizeof(tm_raw));
+  p.tma_rows = 0;
+  if (KVT != MXB_I8 && p.comp_kv && (reinterpret_cast<uintptr_t>(p.comp_kv) & 15) == 0 &&
+      (!p.raw_kv || (reinterpret_cast<uintptr_t>(p.raw_kv) & 15) == 0)) {
+    int rc = row_gather_map(&tm_comp, p.comp_kv, p.Dqk, KVT == MXB_BF16);
+    if (rc != MXB_OK) return rc;
+    rc = row_gather_map(&tm_raw, p.raw_kv ? p.raw_kv : p.comp_kv, p.Dqk, KVT == MXB_BF16);
+    if (rc != MXB_OK) return rc;
+    p.tma_rows = 1;
+  }
   dim3 grid((unsigned)p.nsplit, 1, (unsigned)(p.B * p.T));
 #define MXB_TC(OT)                                                                                   \
   {                                                                                                  \
     auto kern = sparse_attn_tc_kernel<KVT, QT, OT>;                                                  \
     MXB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));      \
-    kern<<<grid, 256, smem, st>>>(p);                                                                \
+    kern<<<grid, 256, smem, st>>>(p, tm_comp, tm_raw);                                                \
   }
   if (out_dtype == MXB_F32 || p.nsplit > 1 || p.partial_ml) MXB_TC(MXB_F32)
   else if (out_dtype == MXB_BF16) MXB_TC(MXB_BF16)
