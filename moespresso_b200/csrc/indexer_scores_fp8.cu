@@ -107,7 +107,8 @@ indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
   uint8_t* a16_buf = smem + C::a16_off;
   uint8_t* b_buf = smem + C::b_off;
   float* w_s = reinterpret_cast<float*>(b_buf + p.b_bytes);              // [<= 256]
-  uint64_t* raw_full = reinterpret_cast<uint64_t*>(w_s + 256);           // [8]
+  int32_t* vis_s = reinterpret_cast<int32_t*>(w_s + 256);                // [<= 256] rows visible to each token
+  uint64_t* raw_full = reinterpret_cast<uint64_t*>(vis_s + 256);         // [8]
   uint64_t* raw_empty = raw_full + 8;                                    // [8]
   uint64_t* a_full = raw_empty + 8;                                      // [4]
   uint64_t* a_empty = a_full + 4;                                        // [4]
@@ -214,6 +215,15 @@ indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
       }
     }
     if (lane == 0) w_s[r] = (t < nt) ? ldexpf(p.weights[((int64_t)b * p.T + t0 + t) * H + h], -a) : 0.f;
+  }
+  // rows a token may see (causal mask over compressed rows), once per token instead of once per score
+  for (int t = tid; t < nt; t += C::kThreads) {
+    int64_t v = count;
+    if (p.ratio > 0) {
+      v = (p.pos0 + t0 + t + 1) / p.ratio;
+      if (v > count) v = count;
+    }
+    vis_s[t] = (int32_t)v;
   }
   ptx::fence_proxy_async_smem();
   ptx::tc_fence_before_sync();
@@ -365,7 +375,9 @@ indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
       if (quad == 0) TR(4, i);
       const int64_t r = row0 + (int64_t)i * 128 + rloc;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * p.acc_stride);
-      for (int t = t_lo; t < t_hi; ++t) {
+      const bool r_ok = r < count;
+      float* sp = p.scores + sbase + (int64_t)(t0 + t_lo) * p.s_st + r;
+      for (int t = t_lo; t < t_hi; ++t, sp += p.s_st) {
         float sum = 0.f;
         for (int c0 = 0; c0 < H; c0 += 16) {
           uint32_t v1[16];
@@ -380,19 +392,17 @@ indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
             ptx::tmem_ld16(taddr + (uint32_t)(t * H + c0), v1);
             ptx::tmem_ld_wait();
           }
+          const float4* w4 = reinterpret_cast<const float4*>(w_s + t * H + c0);   // H is a multiple of 16
 #pragma unroll
-          for (int j = 0; j < 16; ++j) sum = fmaf(w_s[t * H + c0 + j], fmaxf(__uint_as_float(v1[j]), 0.f), sum);
-        }
-        if (r < count) {
-          const int tok = t0 + t;
-          bool vis = true;
-          if (p.ratio > 0) {
-            int64_t v = (p.pos0 + tok + 1) / p.ratio;
-            if (v > count) v = count;
-            vis = r < v;
+          for (int j4 = 0; j4 < 4; ++j4) {
+            const float4 w = w4[j4];
+            sum = fmaf(w.x, fmaxf(__uint_as_float(v1[4 * j4 + 0]), 0.f), sum);
+            sum = fmaf(w.y, fmaxf(__uint_as_float(v1[4 * j4 + 1]), 0.f), sum);
+            sum = fmaf(w.z, fmaxf(__uint_as_float(v1[4 * j4 + 2]), 0.f), sum);
+            sum = fmaf(w.w, fmaxf(__uint_as_float(v1[4 * j4 + 3]), 0.f), sum);
           }
-          p.scores[sbase + (int64_t)tok * p.s_st + r] = vis ? sum : -INFINITY;
         }
+        if (r_ok) *sp = r < (int64_t)vis_s[t] ? sum : -INFINITY;
       }
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(&acc_empty[a]);
@@ -428,7 +438,7 @@ static int launch_fp8_d(Fp8Params& p, const mxb_indexer_scores_args* a, cudaStre
   p.b_bytes = (int)round_up((int64_t)p.N * D * (DIRECT ? 1 : 2), 1024);
   const int64_t t_tiles = ceil_div(p.T, t_tile);
   const int64_t tiles = ceil_div(p.n_rows, 128);
-  const int smem = C::b_off + p.b_bytes + 256 * 4 + 56 * 8 + 64 + 1024;
+  const int smem = C::b_off + p.b_bytes + 256 * 4 + 256 * 4 + 56 * 8 + 64 + 1024;
   const int ctas_per_sm = smem <= 113 * 1024 ? 2 : 1;
   // static chunks of rows per CTA, several per resident slot so that ragged sequences balance
   int64_t want_ctas = (int64_t)sm_count() * ctas_per_sm * 6;
