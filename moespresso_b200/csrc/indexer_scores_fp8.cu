@@ -158,8 +158,30 @@ indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
     ptx::tmem_relinquish();
   }
 
-  // ---- query -> B operand.  One warp per (token, head) row; lane owns D/32 features.
-  for (int r = warp; r < p.t_tile * H; r += C::kThreads / 32) {
+  // ---- query -> B operand.
+  // 16-bit keys: q has the keys' type and is used as it is, so the operand is a plain copy, one 16-byte chunk
+  // (8 features of one (token, head) column) per thread and step, all loads independent.
+  const bool q_copy = K16 && ((reinterpret_cast<uintptr_t>(p.q) & 15) == 0) && p.q_sb % 8 == 0 && p.q_sh % 8 == 0 &&
+                      p.q_st % 8 == 0;
+  if (q_copy) {
+    constexpr int CPRq = D / 8;   // chunks per column
+    for (int i = tid; i < p.t_tile * H * CPRq; i += C::kThreads) {
+      const int n = i / CPRq, cq = i % CPRq;   // column = t * H + h
+      const int t = n / H, h = n % H;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (t < nt)
+        v = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.q) + (int64_t)b * p.q_sb +
+                                                 (int64_t)h * p.q_sh + (int64_t)(t0 + t) * p.q_st) + cq);
+      const int kb = cq >> 3, c = cq & 7;
+      *reinterpret_cast<uint4*>(b_buf + (size_t)kb * N * 128 + (size_t)n * 128 + ((c ^ (n & 7)) << 4)) = v;
+    }
+    for (int n = tid; n < p.t_tile * H; n += C::kThreads) {
+      const int t = n / H, h = n % H;
+      w_s[n] = (t < nt) ? p.weights[((int64_t)b * p.T + t0 + t) * H + h] : 0.f;
+    }
+  }
+  // Otherwise one warp per (token, head) row; lane owns D/32 features.
+  for (int r = warp; !q_copy && r < p.t_tile * H; r += C::kThreads / 32) {
     const int t = r / H, h = r % H;
     constexpr int EPL = D / 32;
     float x[EPL];
@@ -377,22 +399,55 @@ indexer_fp8_kernel(const __grid_constant__ CUtensorMap tmap, Fp8Params p) {
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * p.acc_stride);
       const bool r_ok = r < count;
       float* sp = p.scores + sbase + (int64_t)(t0 + t_lo) * p.s_st + r;
-      for (int t = t_lo; t < t_hi; ++t, sp += p.s_st) {
+      // two tokens per step: their TMEM loads travel together and their two head sums (each in head order) are
+      // independent chains, so the loop is no longer one load latency plus one dependent chain per token
+      auto load_tok = [&](int t, int c0, uint32_t* v) {
+        if constexpr (DIRECT) {
+          uint32_t v2[16];
+          ptx::tmem_ld16(taddr + (uint32_t)(t * 2 * H + c0), v);
+          ptx::tmem_ld16(taddr + (uint32_t)(t * 2 * H + H + c0), v2);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(fmaf(__uint_as_float(v2[j]), 0.0625f, __uint_as_float(v[j])));
+        } else {
+          ptx::tmem_ld16(taddr + (uint32_t)(t * H + c0), v);
+        }
+      };
+      int t = t_lo;
+      for (; t + 1 < t_hi; t += 2, sp += 2 * p.s_st) {
+        float sum0 = 0.f, sum1 = 0.f;
+        for (int c0 = 0; c0 < H; c0 += 16) {
+          uint32_t va[16], vb[16];
+          load_tok(t, c0, va);
+          load_tok(t + 1, c0, vb);
+          ptx::tmem_ld_wait();
+          const float4* wa = reinterpret_cast<const float4*>(w_s + t * H + c0);   // H is a multiple of 16
+          const float4* wb = reinterpret_cast<const float4*>(w_s + (t + 1) * H + c0);
+#pragma unroll
+          for (int j4 = 0; j4 < 4; ++j4) {
+            const float4 x = wa[j4], y = wb[j4];
+            sum0 = fmaf(x.x, fmaxf(__uint_as_float(va[4 * j4 + 0]), 0.f), sum0);
+            sum1 = fmaf(y.x, fmaxf(__uint_as_float(vb[4 * j4 + 0]), 0.f), sum1);
+            sum0 = fmaf(x.y, fmaxf(__uint_as_float(va[4 * j4 + 1]), 0.f), sum0);
+            sum1 = fmaf(y.y, fmaxf(__uint_as_float(vb[4 * j4 + 1]), 0.f), sum1);
+            sum0 = fmaf(x.z, fmaxf(__uint_as_float(va[4 * j4 + 2]), 0.f), sum0);
+            sum1 = fmaf(y.z, fmaxf(__uint_as_float(vb[4 * j4 + 2]), 0.f), sum1);
+            sum0 = fmaf(x.w, fmaxf(__uint_as_float(va[4 * j4 + 3]), 0.f), sum0);
+            sum1 = fmaf(y.w, fmaxf(__uint_as_float(vb[4 * j4 + 3]), 0.f), sum1);
+          }
+        }
+        if (r_ok) {
+          sp[0] = r < (int64_t)vis_s[t] ? sum0 : -INFINITY;
+          sp[p.s_st] = r < (int64_t)vis_s[t + 1] ? sum1 : -INFINITY;
+        }
+      }
+      if (t < t_hi) {
         float sum = 0.f;
         for (int c0 = 0; c0 < H; c0 += 16) {
           uint32_t v1[16];
-          if constexpr (DIRECT) {
-            uint32_t v2[16];
-            ptx::tmem_ld16(taddr + (uint32_t)(t * 2 * H + c0), v1);
-            ptx::tmem_ld16(taddr + (uint32_t)(t * 2 * H + H + c0), v2);
-            ptx::tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 16; ++j) v1[j] = __float_as_uint(fmaf(__uint_as_float(v2[j]), 0.0625f, __uint_as_float(v1[j])));
-          } else {
-            ptx::tmem_ld16(taddr + (uint32_t)(t * H + c0), v1);
-            ptx::tmem_ld_wait();
-          }
-          const float4* w4 = reinterpret_cast<const float4*>(w_s + t * H + c0);   // H is a multiple of 16
+          load_tok(t, c0, v1);
+          ptx::tmem_ld_wait();
+          const float4* w4 = reinterpret_cast<const float4*>(w_s + t * H + c0);
 #pragma unroll
           for (int j4 = 0; j4 < 4; ++j4) {
             const float4 w = w4[j4];
