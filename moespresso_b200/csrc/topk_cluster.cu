@@ -409,8 +409,13 @@ int topk_cluster_size(int32_t rows, int64_t n) {
 #else
   if (n > (int64_t)kCMaxCluster * kCPartMax) return 0;
   if (n > kSmemRowMax) return kCMaxCluster;
-  // shorter rows: clusters only while single CTAs would leave most of the machine idle
-  if (n >= 16384 && (int64_t)rows * 2 <= sm_count()) return kCMaxCluster;
+  // Rows that one CTA could hold.  Few rows: wide clusters, or most of the machine idles.  Many rows of 24 K
+  // keys and more (prefill): pairs of CTAs, each with half a row, finish a batch of rows sooner than one full-row
+  // CTA per SM (256 x 32768: 43 us against 61; 1024 x 32768: 142 against 254); below that the one-CTA kernel wins.
+  const int64_t sms = sm_count();
+  if (n >= 16384 && (int64_t)rows * 4 <= sms) return kCMaxCluster;
+  if (n >= 24576) return (int64_t)rows * 2 <= sms ? 4 : 2;
+  if (n >= 16384 && (int64_t)rows * 2 <= sms) return kCMaxCluster;
   return 0;
 #endif
 }

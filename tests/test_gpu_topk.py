@@ -62,6 +62,15 @@ def test_kernel_boundaries(n, k, rows):
     _check(s, k)
 
 
+@pytest.mark.parametrize("n,k,rows", [(32768, 2048, 160), (24576, 512, 150), (45056, 2048, 80), (30001, 2048, 60),
+                                      (32768, 1, 75), (40000, 4096, 38)])
+def test_many_rows_small_clusters(n, k, rows):
+    """Row batches that run as clusters of two or four CTAs: random rows, then rows made of a few distinct values."""
+    rng = np.random.default_rng(n + rows)
+    _check(rng.standard_normal((rows, n)).astype(np.float32), k)
+    _check(np.round(rng.standard_normal((rows, n)) * 2).astype(np.float32), k)
+
+
 def test_long_rows_ties():
     need_gpu()
     rng = np.random.default_rng(4)
