@@ -255,6 +255,44 @@ def test_tensor_core_kernel_decode(kvkind, qkind, Dqk, Dv, H):
     assert max_abs(outs[0], exact) <= tol
 
 
+@pytest.mark.parametrize("kvkind", ["bf16", "f16", "int8"])
+@pytest.mark.parametrize("window,raw_cap", [(101, 128), (6, 128), (128, 127), (63, 64)])
+def test_tensor_core_kernel_raw_window_boundary(kvkind, window, raw_cap):
+    """Raw windows whose length is not a multiple of four: with 16-bit tables a group of four gathered rows then
+    holds rows of both tables (fetched from the compressed one, raw rows patched in afterwards)."""
+    need_gpu()
+    Dqk, Dv, H, R, k = 576, 512, 64, 2000, 515
+    rng = np.random.default_rng(window * 131 + raw_cap)
+    q = bf16_round(rng.standard_normal((H, Dqk)))
+    sinks = rng.standard_normal(H).astype(np.float32)
+    ids = np.sort(rng.choice(R, size=k, replace=False)).astype(np.int32)
+    ids[0] = -1; ids[2] = -1; ids[77] = -1
+    if kvkind == "int8":
+        comp = rng.integers(-127, 128, size=(R, Dqk), dtype=np.int8)
+        raw = rng.integers(-127, 128, size=(raw_cap, Dqk), dtype=np.int8)
+        cs = np.exp(rng.uniform(np.log(1e-3), np.log(1e-1), size=R)).astype(np.float16)
+        rs = np.exp(rng.uniform(np.log(1e-3), np.log(1e-1), size=raw_cap)).astype(np.float16)
+        comp_t, raw_t, cs_t, rs_t = dev(comp), dev(raw), dev(cs), dev(rs)
+        okw = dict(kv_scales=cs, raw_scales=rs)
+        qt, scale = torch.bfloat16, Dqk ** -0.5 * 20.0
+    else:
+        rnd = f16_round if kvkind == "f16" else bf16_round
+        kt = torch.float16 if kvkind == "f16" else torch.bfloat16
+        comp, raw = rnd(rng.standard_normal((R, Dqk))), rnd(rng.standard_normal((raw_cap, Dqk)))
+        comp_t, raw_t, cs_t, rs_t = dev(comp, kt), dev(raw, kt), None, None
+        okw = {}
+        qt, scale = kt, Dqk ** -0.5
+        q = rnd(q)
+    pos0 = 128 + R * 4 - 1
+    ref = ds4.indexed_mixed_attention_decode(q, raw, comp, ids, sinks, pos0=pos0, window=window, ratio=4, raw_start=11,
+                                             scale=scale, d_v=Dv, **okw)
+    for ns in (1, 2, 5):
+        o = iak.sparse_attention(dev(q, qt)[None, :, None, :], comp_t, dev(ids)[None, None], dev(sinks), pos0=pos0,
+                                 window=window, ratio=4, raw_kv=raw_t[None], raw_start=11, scale=scale, d_v=Dv,
+                                 kv_scales=cs_t, raw_scales=rs_t, n_splits=ns, check=True)[0, :, 0]
+        assert max_abs(o, ref) <= (2e-3 if kvkind == "f16" else TOL_16), (ns, max_abs(o, ref))
+
+
 def test_tensor_core_kernel_peaked_softmax_and_empty_tiles():
     """Logits spread over hundreds of units force reference-maximum updates and O rescales;
     a list with long runs of skipped ids gives tiles without any valid row."""
