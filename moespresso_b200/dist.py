@@ -106,7 +106,8 @@ def range_step_candidates(idx_q, idx_w, shard: RangeShard, *, k: int, ops):
     return cand_scores.float(), cand_ids
 
 
-def range_step_partial(q, shard: RangeShard, all_scores, all_ids, *, k: int, scale: float, d_v: int, ops):
+def range_step_partial(q, shard: RangeShard, all_scores, all_ids, *, k: int, scale: float, d_v: int, ops,
+                       want_ids: bool = True):
     """Steps 4-5 on one rank, given every rank's candidates concatenated in rank order: the same exact global
     selection on every rank (ties go to the lower position == lower global id, because ranks own ascending row
     ranges and each list is ascending), then partial attention over the rows this rank owns.
@@ -124,7 +125,8 @@ def range_step_partial(q, shard: RangeShard, all_scores, all_ids, *, k: int, sca
         H = int(q.shape[0])
         o = torch.zeros((H, d_v), dtype=torch.float32, device=dev)
         ml = torch.stack([torch.full((H,), float("-inf"), device=dev), torch.zeros(H, device=dev)], dim=1)
-    return o.float(), ml.float(), chosen[mine]
+    # the list of attended ids has a data-dependent length (a device-to-host round trip): only on request
+    return o.float(), ml.float(), (chosen[mine] if want_ids else None)
 
 
 def range_sharded_decode_step(q, idx_q, idx_w, shard: RangeShard, *, k: int, scale: float, d_v: int, sinks=None,
@@ -145,6 +147,81 @@ def range_sharded_decode_step(q, idx_q, idx_w, shard: RangeShard, *, k: int, sca
     if return_ids:
         return out, attended
     return out
+
+
+class RangeDecodePlan:
+    """The range-sharded decode step of one sequence with everything between the collectives captured as CUDA
+    graphs: per step three graph launches and two ``all_gather`` calls (candidates: 8 bytes x k per rank; partials:
+    (d_v + 2) floats per head per rank), no allocation and no device-to-host round trip.  Results are those of
+    ``range_sharded_decode_step`` bit for bit.  The shard's tensors are captured by address."""
+
+    def __init__(self, shard: RangeShard, *, heads: int, d_qk: int, idx_heads: int, idx_dim: int, k: int,
+                 scale: float, d_v: int, q_dtype=torch.bfloat16, sinks=None, group=None, ops=None,
+                 graph: bool = True):
+        dev = shard.kv.device
+        self.shard, self.k, self.scale, self.d_v, self.sinks = shard, int(k), float(scale), int(d_v), sinks
+        self.group, self.ops = group, ops or CudaOps()
+        world = dist.get_world_size(group)
+        self.q = torch.zeros((heads, d_qk), dtype=q_dtype, device=dev)
+        self.idx_q = torch.zeros((idx_heads, idx_dim), dtype=q_dtype, device=dev)
+        self.idx_w = torch.zeros((idx_heads,), dtype=torch.float32, device=dev)
+        # candidates travel as one tensor: row 0 = the float32 scores' bits, row 1 = global row ids (< 2^31)
+        self.cand = torch.empty((2, self.k), dtype=torch.int32, device=dev)
+        self.all_cand = torch.empty((world, 2, self.k), dtype=torch.int32, device=dev)
+        # partials travel as one tensor: [H, d_v] un-normalised output, then (m, l)
+        self.part = torch.empty((heads, self.d_v + 2), dtype=torch.float32, device=dev)
+        self.all_part = torch.empty((world, heads, self.d_v + 2), dtype=torch.float32, device=dev)
+        self.out = None
+        self._graphs = None
+        if graph:
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    self._candidates()
+                    self.all_cand.copy_(self.cand[None].expand_as(self.all_cand))
+                    self._partial()
+                    self.all_part.copy_(self.part[None].expand_as(self.all_part))
+                    self._merge()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            torch.cuda.synchronize(dev)
+            graphs = []
+            for phase in (self._candidates, self._partial, self._merge):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    phase()
+                graphs.append(g)
+            self._graphs = graphs
+
+    def _candidates(self):
+        cs, ci = range_step_candidates(self.idx_q, self.idx_w, self.shard, k=self.k, ops=self.ops)
+        self.cand[0].copy_(cs.contiguous().view(torch.int32))
+        self.cand[1].copy_(ci)
+
+    def _partial(self):
+        o, ml, _ = range_step_partial(self.q, self.shard, self.all_cand[:, 0].contiguous().view(torch.float32),
+                                      self.all_cand[:, 1].long(), k=self.k, scale=self.scale, d_v=self.d_v,
+                                      ops=self.ops, want_ids=False)
+        self.part[:, :self.d_v].copy_(o)
+        self.part[:, self.d_v:].copy_(ml)
+
+    def _merge(self):
+        self.out = self.ops.merge(self.all_part[:, :, :self.d_v].contiguous(),
+                                  self.all_part[:, :, self.d_v:].contiguous(), self.sinks)
+
+    def step(self, q, idx_q, idx_w):
+        """One decode step; q [H,Dqk], idx_q [Hi,Di], idx_w [Hi] replicated on every rank.  Returns out [H,d_v]
+        (the plan's own buffer when graphs are in use: consume it before the next step)."""
+        self.q.copy_(q, non_blocking=True)
+        self.idx_q.copy_(idx_q, non_blocking=True)
+        self.idx_w.copy_(idx_w, non_blocking=True)
+        phases = self._graphs and [g.replay for g in self._graphs] or [self._candidates, self._partial, self._merge]
+        phases[0]()
+        dist.all_gather_into_tensor(self.all_cand, self.cand, group=self.group)
+        phases[1]()
+        dist.all_gather_into_tensor(self.all_part, self.part, group=self.group)
+        phases[2]()
+        return self.out
 
 
 def numpy_lens_to_tables(c: dict, seqs: list[int]) -> dict:

@@ -115,3 +115,45 @@ def test_range_sharded_step_nccl_ranks(tmp_path):
     for o in outs[1:]:
         np.testing.assert_array_equal(o, outs[0])          # every rank holds the same merged output
     _check(c, scores_ref, ids, outs[0])
+
+
+def _plan_worker(rank, world, port, R, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    torch.distributed.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        c, _ = _case(R, seed=5)
+        lo, hi = mdist.row_range(R, world, rank, align=128)
+        shard = _shard(c, lo, hi, dev)
+        H, Dqk = c["q"][0].shape
+        Hi, Di = c["idx_q"][0].shape
+        plan = mdist.RangeDecodePlan(shard, heads=H, d_qk=Dqk, idx_heads=Hi, idx_dim=Di, k=int(c["k"]),
+                                     scale=c["scale"], d_v=c["d_v"])
+        rng = np.random.default_rng(3)
+        same = True
+        for step in range(3):   # fresh inputs every step: the graphs must read the plan's buffers, not stale copies
+            q = torch.from_numpy(synth.to_bf16_f32(rng.standard_normal((H, Dqk), dtype=np.float32))).to(dev).to(torch.bfloat16)
+            iq = torch.from_numpy(synth.to_bf16_f32(rng.standard_normal((Hi, Di), dtype=np.float32))).to(dev).to(torch.bfloat16)
+            iw = torch.from_numpy((rng.standard_normal(Hi) / 4).astype(np.float32)).to(dev)
+            eager = mdist.range_sharded_decode_step(q, iq, iw, shard, k=int(c["k"]), scale=c["scale"], d_v=c["d_v"])
+            got = plan.step(q, iq, iw).clone()
+            torch.cuda.synchronize()
+            same = same and bool(torch.equal(got, eager))
+        with open(os.path.join(out_dir, f"same{rank}.txt"), "w") as f:
+            f.write("1" if same else "0")
+    finally:
+        torch.distributed.destroy_process_group()
+
+
+def test_range_plan_matches_eager_step(tmp_path):
+    """The graph-captured plan (three graphs, two collectives per step) returns the eager driver's result bit for
+    bit, over several steps with new inputs; one NCCL rank per GPU, a single rank when there is one GPU."""
+    need_gpu()
+    world = min(torch.cuda.device_count(), 2)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    torch.multiprocessing.spawn(_plan_worker, args=(world, port, 50000, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert (tmp_path / f"same{r}.txt").read_text() == "1"
