@@ -138,8 +138,12 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int qt = gridDim.x - 1 - blockIdx.x;  // heavy (late) tiles first
-  const int head = blockIdx.y;
+  // One-dimensional grid in longest-first order: every head's latest (heaviest) query tile, then the next tile of
+  // every head, ..., so that the CTAs that start last are the 2-tile ones and the SMs finish together.  CTAs that
+  // run at the same time share their K/V stream across the query heads of a KV head.
+  const int n_qt = (p.S + FB_M - 1) / FB_M;
+  const int qt = n_qt - 1 - (int)blockIdx.x / p.Hq;
+  const int head = (int)blockIdx.x % p.Hq;
   const int kvh = head / (p.Hq / p.Hkv);
   const int m0 = qt * FB_M;
   const int past = p.Skv - p.S;
@@ -148,8 +152,8 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
   const int ntiles = (kv_end + FB_N - 1) / FB_N;
 #ifdef MXB_TRACE_FL
   long long* tr = reinterpret_cast<long long*>(p.status);
-  const bool tr_cta = p.status && blockIdx.x == 0 && blockIdx.y == 0 && (tid & 31) == 0;
-  long long* tr_all = tr + 24 * 16 + (blockIdx.y * gridDim.x + blockIdx.x) * 4;   // per CTA: start ns, end ns, cycles, SM
+  const bool tr_cta = p.status && blockIdx.x == 0 && (tid & 31) == 0;
+  long long* tr_all = tr + 24 * 16 + (head * n_qt + (n_qt - 1 - qt)) * 4;   // per CTA: start ns, end ns, cycles, SM
   const long long c_begin = clock64();
   if (p.status && tid == 0) {
     unsigned long long ns; unsigned sm;
@@ -538,7 +542,7 @@ extern "C" int mxb_flash_prefill(const mxb_flash_prefill_args* a, void* stream) 
   p.q_head_inner = q_hin ? 1 : 0;
   p.k_head_inner = k_hin ? 1 : 0;
   const int smem = FlashSmem::total + 1024;
-  dim3 grid((unsigned)ceil_div(a->S, FB_M), (unsigned)a->Hq);
+  dim3 grid((unsigned)(ceil_div(a->S, FB_M) * a->Hq));
   if (a->dtype == MXB_BF16) {
     MXB_CUDA_OK(cudaFuncSetAttribute(flash_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     flash_prefill_kernel<true><<<grid, 384, smem, st>>>(tq, tk, tv, p);
