@@ -500,6 +500,14 @@ static int launch_fp8_d(Fp8Params& p, const mxb_indexer_scores_args* a, cudaStre
   int64_t per = ceil_div(tiles * p.B * t_tiles, want_ctas);
   if (per < 16) per = 16;
   if (per > tiles) per = tiles;
+  // Equal-length sequences (one prefill chunk): all CTAs cost the same, so a grid of 1.7 waves wastes the
+  // difference to 2.  Cut the rows so that one wave holds everything when that leaves enough tiles per CTA.
+  const int64_t slots = (int64_t)sm_count() * (p.tmem_cols > 256 ? 1 : ctas_per_sm);   // 512 TMEM columns: one CTA per SM
+  if (!p.row_count && p.B * t_tiles <= slots) {
+    const int64_t gx = slots / (p.B * t_tiles);
+    const int64_t one_wave = ceil_div(tiles, gx);
+    if (one_wave >= 8) per = one_wave;
+  }
   p.rows_per_cta = (int)(per * 128);
 
   CUtensorMap tmap;
