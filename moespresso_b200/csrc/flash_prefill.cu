@@ -56,6 +56,8 @@ struct FlashParams {
   int32_t S, Skv, Hq, Hkv;
   float scale_log2;  // scale * log2(e)
   int32_t q_head_inner, k_head_inner;  // tensor-map dimension order: (D, head, row) instead of (D, row, head)
+  int32_t g_head_inner, o_head_inner;
+  int32_t tma_drain;   // gate tile in and output tile out by TMA through the (then idle) Q buffer
   int32_t* status;
 };
 
@@ -106,6 +108,12 @@ __device__ __forceinline__ float poly_ex2(float x) {
   return __int_as_float(__float_as_int(r) + (__float_as_int(xr) << 23));
 }
 
+__device__ __forceinline__ float fast_tanh(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <bool BF16>
 __device__ __forceinline__ float2 unpack2(uint32_t u) {
   if constexpr (BF16) return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
@@ -116,6 +124,8 @@ template <bool BF16>
 __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
                                                                const __grid_constant__ CUtensorMap tm_k,
                                                                const __grid_constant__ CUtensorMap tm_vt,
+                                                               const __grid_constant__ CUtensorMap tm_g,
+                                                               const __grid_constant__ CUtensorMap tm_o,
                                                                FlashParams p) {
   using L = FlashSmem;
   extern __shared__ uint8_t smem_raw[];
@@ -134,7 +144,8 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
   uint64_t* p_ready = bars + 11;  // [2], one per P buffer (the softmax warps may be a tile apart)
   uint64_t* pv_done = bars + 13;  // [2], one per P buffer
   uint64_t* s_free = bars + 15;   // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  uint64_t* g_full = bars + 17;   // gate tile landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -173,6 +184,7 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
       ptx::mbar_init(&pv_done[i], 1);
       ptx::mbar_init(&p_ready[i], 256);
     }
+    ptx::mbar_init(g_full, 1);
     ptx::mbar_init(&s_free[0], 256);
     ptx::mbar_init(&s_free[1], 256);
     *abort_flag = 0;
@@ -297,6 +309,14 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
       if (j == 0) TRX(1);
       if (j == 1) TRX(2);
       if (j == ntiles - 1) TRX(3);
+      if (j == ntiles - 1 && p.tma_drain && p.gate && tid == 0) {
+        // the last S has been computed, so nothing reads Q any more: its buffer receives the gate tile
+        // ([128 rows x 256] as four 64-feature slabs, swizzled like an operand) while the last tile is finished
+        ptx::mbar_expect_tx(g_full, 4 * 16384);
+        for (int kb = 0; kb < 4; ++kb)
+          ptx::tma_load_3d(q_s + kb * 16384, &tm_g, g_full, kb * 64, p.g_head_inner ? head : m0,
+                           p.g_head_inner ? m0 : head);
+      }
       uint32_t sv[32];
       {
         uint32_t sb[32];
@@ -393,49 +413,102 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
     }
     // epilogue: the row sum over both halves, then each half writes its 128 output features
     TRX(4);
-    // The gate values of this thread's half row (16 x 16 bytes) are requested first, all at once: they travel
-    // while the last P V finishes and the row sums are exchanged (one load per use would put 16 round trips
-    // to L2 on the drain's critical path).
-    const bool row_ok = qi < p.S;
-    const uint16_t* gptr = (p.gate && row_ok) ? reinterpret_cast<const uint16_t*>(p.gate) + (int64_t)qi * p.g_ss +
-                                                    (int64_t)head * p.g_sh + half * (FB_D / 2)
-                                              : nullptr;
-    uint4 gv[16];
+    if (p.tma_drain) {
+      // Drain through shared memory so that global memory sees whole tiles: the gate tile arrived by TMA in the Q
+      // buffer; each thread turns the 16-byte chunks of its half row into output chunks in place; one TMA store
+      // per slab writes the tile (rows past the end of the sequence are clipped by the tensor map).
+      float* rowsum_s = reinterpret_cast<float*>(rowmax_s);   // [2 halves][128 rows]
+      asm volatile("bar.sync 5, 256;" ::: "memory");   // all eight warps: every maximum of the last tile has been read
+      rowsum_s[half * FB_M + row] = l;
+      asm volatile("bar.sync %0, 64;" ::"r"(quad + 1) : "memory");
+      l += rowsum_s[(half ^ 1) * FB_M + row];
+      ptx::mbar_wait(&pv_done[(ntiles - 1) & 1], (uint32_t)(((ntiles - 1) >> 1) & 1), abort_flag);
+      if (p.gate) ptx::mbar_wait(g_full, 0, abort_flag);
+      ptx::tc_fence_after_sync();
+      TRX(5);
+      const float inv_l = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) gv[i] = gptr ? __ldg(reinterpret_cast<const uint4*>(gptr) + i) : make_uint4(0, 0, 0, 0);
-    float* rowsum_s = reinterpret_cast<float*>(rowmax_s);   // [2 halves][128 rows]
-    asm volatile("bar.sync 5, 256;" ::: "memory");   // all eight warps: every maximum of the last tile has been read
-    rowsum_s[half * FB_M + row] = l;
-    asm volatile("bar.sync %0, 64;" ::"r"(quad + 1) : "memory");
-    l += rowsum_s[(half ^ 1) * FB_M + row];
-    ptx::mbar_wait(&pv_done[(ntiles - 1) & 1], (uint32_t)(((ntiles - 1) >> 1) & 1), abort_flag);
-    ptx::tc_fence_after_sync();
-    TRX(5);
-    const float inv_l = l > 0.f ? 1.f / l : 0.f;
-    uint16_t* optr = reinterpret_cast<uint16_t*>(p.out) + (int64_t)qi * p.o_ss + (int64_t)head * p.o_sh + half * (FB_D / 2);
-#pragma unroll
-    for (int cc = 0; cc < 4; ++cc) {
-      uint32_t ov[32];
-      ptx::tmem_ld32(tmem_o + lane_off + (uint32_t)(half * (FB_D / 2) + cc * 32), ov);
-      ptx::tmem_ld_wait();
-      if (row_ok) {
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t ov[32];
+        ptx::tmem_ld32(tmem_o + lane_off + (uint32_t)(half * (FB_D / 2) + cc * 32), ov);
+        ptx::tmem_ld_wait();
 #pragma unroll
         for (int c8 = 0; c8 < 4; ++c8) {
-          const uint4 g = gv[cc * 4 + c8];
-          const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+          const int chunk = half * 16 + cc * 4 + c8;   // 16-byte chunk of the 512-byte row
+          uint4* cell = reinterpret_cast<uint4*>(q_s + (chunk >> 3) * 16384 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
           uint32_t w[4];
+          if (p.gate) {
+            const uint4 g = *cell;
+            const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            float a = __uint_as_float(ov[c8 * 8 + 2 * i]) * inv_l;
-            float b = __uint_as_float(ov[c8 * 8 + 2 * i + 1]) * inv_l;
-            if (p.gate) {
+            for (int i = 0; i < 4; ++i) {
               const float2 gg = unpack2<BF16>(gw[i]);
-              a = __fdividef(a, 1.f + __expf(-gg.x));
-              b = __fdividef(b, 1.f + __expf(-gg.y));
+              // sigmoid(g) = 0.5 + 0.5 * tanh(g / 2): one special-function result per element
+              const float sa = fmaf(0.5f, fast_tanh(0.5f * gg.x), 0.5f), sb = fmaf(0.5f, fast_tanh(0.5f * gg.y), 0.5f);
+              w[i] = pack2<BF16>(__uint_as_float(ov[c8 * 8 + 2 * i]) * inv_l * sa,
+                                 __uint_as_float(ov[c8 * 8 + 2 * i + 1]) * inv_l * sb);
             }
-            w[i] = pack2<BF16>(a, b);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              w[i] = pack2<BF16>(__uint_as_float(ov[c8 * 8 + 2 * i]) * inv_l, __uint_as_float(ov[c8 * 8 + 2 * i + 1]) * inv_l);
           }
-          *reinterpret_cast<uint4*>(optr + cc * 32 + c8 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          *cell = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      ptx::fence_proxy_async_smem();
+      asm volatile("bar.sync 5, 256;" ::: "memory");
+      if (tid == 0) {
+        for (int kb = 0; kb < 4; ++kb)
+          ptx::tma_store_3d(&tm_o, q_s + kb * 16384, kb * 64, p.o_head_inner ? head : m0, p.o_head_inner ? m0 : head);
+        ptx::tma_store_commit();
+        ptx::tma_store_wait_read();
+      }
+    } else {
+    // The gate values of this thread's half row (16 x 16 bytes) are requested first, all at once: they travel
+      // while the last P V finishes and the row sums are exchanged (one load per use would put 16 round trips
+      // to L2 on the drain's critical path).
+      const bool row_ok = qi < p.S;
+      const uint16_t* gptr = (p.gate && row_ok) ? reinterpret_cast<const uint16_t*>(p.gate) + (int64_t)qi * p.g_ss +
+                                                      (int64_t)head * p.g_sh + half * (FB_D / 2)
+                                                : nullptr;
+      uint4 gv[16];
+  #pragma unroll
+      for (int i = 0; i < 16; ++i) gv[i] = gptr ? __ldg(reinterpret_cast<const uint4*>(gptr) + i) : make_uint4(0, 0, 0, 0);
+      float* rowsum_s = reinterpret_cast<float*>(rowmax_s);   // [2 halves][128 rows]
+      asm volatile("bar.sync 5, 256;" ::: "memory");   // all eight warps: every maximum of the last tile has been read
+      rowsum_s[half * FB_M + row] = l;
+      asm volatile("bar.sync %0, 64;" ::"r"(quad + 1) : "memory");
+      l += rowsum_s[(half ^ 1) * FB_M + row];
+      ptx::mbar_wait(&pv_done[(ntiles - 1) & 1], (uint32_t)(((ntiles - 1) >> 1) & 1), abort_flag);
+      ptx::tc_fence_after_sync();
+      TRX(5);
+      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+      uint16_t* optr = reinterpret_cast<uint16_t*>(p.out) + (int64_t)qi * p.o_ss + (int64_t)head * p.o_sh + half * (FB_D / 2);
+  #pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t ov[32];
+        ptx::tmem_ld32(tmem_o + lane_off + (uint32_t)(half * (FB_D / 2) + cc * 32), ov);
+        ptx::tmem_ld_wait();
+        if (row_ok) {
+  #pragma unroll
+          for (int c8 = 0; c8 < 4; ++c8) {
+            const uint4 g = gv[cc * 4 + c8];
+            const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+            uint32_t w[4];
+  #pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              float a = __uint_as_float(ov[c8 * 8 + 2 * i]) * inv_l;
+              float b = __uint_as_float(ov[c8 * 8 + 2 * i + 1]) * inv_l;
+              if (p.gate) {
+                const float2 gg = unpack2<BF16>(gw[i]);
+                a = __fdividef(a, 1.f + __expf(-gg.x));
+                b = __fdividef(b, 1.f + __expf(-gg.y));
+              }
+              w[i] = pack2<BF16>(a, b);
+            }
+            *reinterpret_cast<uint4*>(optr + cc * 32 + c8 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
         }
       }
     }
@@ -532,8 +605,26 @@ extern "C" int mxb_flash_prefill(const mxb_flash_prefill_args* a, void* stream) 
     if (rc != MXB_OK) return rc;
   }
 
+  // gate and output tiles travel by TMA when their layouts allow a tensor map (rows and heads at distinct,
+  // 16-byte aligned strides); otherwise the kernel reads and writes them with per-thread accesses
+  CUtensorMap tg, to;
+  memset(&tg, 0, sizeof(tg));
+  memset(&to, 0, sizeof(to));
+  const bool g_hin = a->gate_stride_h < a->gate_stride_s, o_hin = a->out_stride_h < a->out_stride_s;
+  auto tile_map = [&](CUtensorMap* m, const void* base, int64_t ss, int64_t sh, bool hin) -> bool {
+    if (ss <= 0 || sh <= 0 || ss == sh) return false;
+    uint64_t dims[3] = {(uint64_t)a->D, (uint64_t)(hin ? a->Hq : a->S), (uint64_t)(hin ? a->S : a->Hq)};
+    uint64_t str[2] = {(uint64_t)(hin ? sh : ss) * 2, (uint64_t)(hin ? ss : sh) * 2};
+    uint32_t box[3] = {64, hin ? 1u : (uint32_t)FB_M, hin ? (uint32_t)FB_M : 1u};
+    if (str[0] > str[1] || str[1] % str[0] != 0) return false;   // plain nested layouts only
+    return make_tensor_map(m, dt, 3, base, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B) == MXB_OK;
+  };
+  bool tma_drain = tile_map(&to, a->out, a->out_stride_s, a->out_stride_h, o_hin);
+  if (tma_drain && a->gate) tma_drain = tile_map(&tg, a->gate, a->gate_stride_s, a->gate_stride_h, g_hin);
+
   MXB_REQUIRE(a->scale > 0.f, MXB_ERR_INVALID, "flash prefill: scale must be positive");
   FlashParams p{};
+  p.g_head_inner = g_hin ? 1 : 0; p.o_head_inner = o_hin ? 1 : 0; p.tma_drain = tma_drain ? 1 : 0;
   p.gate = a->gate; p.g_ss = a->gate_stride_s; p.g_sh = a->gate_stride_h;
   p.out = a->out; p.o_ss = a->out_stride_s; p.o_sh = a->out_stride_h;
   p.S = a->S; p.Skv = a->Skv; p.Hq = a->Hq; p.Hkv = a->Hkv;
@@ -545,11 +636,11 @@ extern "C" int mxb_flash_prefill(const mxb_flash_prefill_args* a, void* stream) 
   dim3 grid((unsigned)(ceil_div(a->S, FB_M) * a->Hq));
   if (a->dtype == MXB_BF16) {
     MXB_CUDA_OK(cudaFuncSetAttribute(flash_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    flash_prefill_kernel<true><<<grid, 384, smem, st>>>(tq, tk, tv, p);
+    flash_prefill_kernel<true><<<grid, 384, smem, st>>>(tq, tk, tv, tg, to, p);
     note_launch();
   } else {
     MXB_CUDA_OK(cudaFuncSetAttribute(flash_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    flash_prefill_kernel<false><<<grid, 384, smem, st>>>(tq, tk, tv, p);
+    flash_prefill_kernel<false><<<grid, 384, smem, st>>>(tq, tk, tv, tg, to, p);
     note_launch();
   }
   MXB_CUDA_OK(cudaGetLastError());

@@ -90,6 +90,18 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// Tile store, shared -> global, 3-D map; rows outside the tensor are not written.  Bulk-group completion:
+// commit, then wait until the source has been read before the shared memory is reused or the CTA exits.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* smem_src, int32_t x, int32_t y,
+                                             int32_t z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
 // Row gather: four rows (y0..y3, any order, each checked against the map's bounds on its own: a row outside them,
 // e.g. -1, arrives as zeros) of a 2-D tensor, `box` columns starting at x, land as four consecutive rows of the
 // destination.  The map is encoded with a box of {columns, 1}.  Counts 4 * box bytes on the barrier.
