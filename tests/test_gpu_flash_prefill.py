@@ -42,6 +42,25 @@ def test_matches_oracle(S, past, Hq, Hkv, dt):
     assert max_abs(out_ng, qwen.causal_gqa_prefill(q, k, v, None, scale=1.0 / 16.0, past_len=past)) <= 2e-2
 
 
+def test_gate_layout_without_tensor_map():
+    """A gate whose row stride is not a multiple of its head stride cannot be described by a tensor map: the drain
+    then reads the gate and writes the output with per-thread accesses.  Same result as the tiled drain."""
+    need_gpu()
+    rng = np.random.default_rng(9)
+    S, Hq, Hkv, D = 300, 4, 2, 256
+    q, k, v, g = _inputs(rng, S, 0, Hq, Hkv, bf16_round)
+    tq, tk, tv = (dev(x, torch.bfloat16) for x in (q, k, v))
+    row = Hq * (D + 8) + 8
+    store = torch.zeros(S * row, dtype=torch.bfloat16, device="cuda")
+    tg = store.as_strided((S, Hq, D), (row, D + 8, 1))
+    tg.copy_(dev(g, torch.bfloat16))
+    odd = fa.sdpa_fa_prefill(tq, tk, tv, 1.0 / 16.0, gate=tg, layout="lhd", check=True)
+    tiled = fa.sdpa_fa_prefill(tq, tk, tv, 1.0 / 16.0, gate=dev(g, torch.bfloat16), layout="lhd", check=True)
+    ref = qwen.causal_gqa_prefill(q, k, v, g, scale=1.0 / 16.0, past_len=0)
+    assert max_abs(odd, ref) <= 2e-2 and max_abs(tiled, ref) <= 2e-2
+    assert (odd.float() - tiled.float()).abs().max().item() <= 1e-2
+
+
 def test_bhld_layout_and_peaked_softmax():
     """[1,H,L,D] operands as the reference wrapper passes them; large logits exercise the
     running-maximum rescale."""
