@@ -26,9 +26,9 @@ namespace mxb {
 
 constexpr int FB_M = 128, FB_N = 64, FB_D = 256;
 #ifndef MXB_FLASH_POLY
-#define MXB_FLASH_POLY 2
+#define MXB_FLASH_POLY 1
 #endif
-constexpr int kPolyOf2 = MXB_FLASH_POLY;   // of every four exponentials, this many (0, 1 or 2) run on the FMA pipe
+constexpr int kPolyOf8 = MXB_FLASH_POLY;   // of every eight exponentials, this many (0 .. 4) run on the FMA pipe
 
 #ifdef MXB_TRACE_FL   // development aid: cycle stamps of one CTA's roles over 16 tiles, written behind `status`
 #define TRF(k, j) do { if (tr_cta && (j) >= 32 && (j) < 48) tr[(k) * 16 + (j) - 32] = clock64(); } while (0)
@@ -94,8 +94,8 @@ __device__ __forceinline__ float fast_ex2(float x) {   // 2^x, x <= 0 here; -inf
 }
 
 // 2^x on the FMA pipe for x <= ~8: round-to-nearest split x = n + f with the 1.5 * 2^23 trick, a cubic for 2^f on
-// [-0.5, 0.5] (relative error 7.5e-5, below the rounding of a 16-bit P), n added into the exponent field.  Half of
-// a tile's exponentials go this way because the special-function unit (16 results per clock per SM) would otherwise
+// [-0.5, 0.5] (relative error 7.5e-5, below the rounding of a 16-bit P), n added into the exponent field.  One in eight of
+// a tile's exponentials goes this way (measured best among 0, 1, 2, 3 and 4 in eight) because the special-function unit (16 results per clock per SM) would otherwise
 // bound the softmax.  Inputs below -126 (masked keys) give 2^-126 instead of 0.
 __device__ __forceinline__ float poly_ex2(float x) {
   x = fmaxf(x, -126.f);
@@ -399,7 +399,8 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
           const float xa = fmaf(__uint_as_float(sv[c8 * 8 + 2 * i]), p.scale_log2, -m_used);
           const float xb = fmaf(__uint_as_float(sv[c8 * 8 + 2 * i + 1]), p.scale_log2, -m_used);
           const float a = fast_ex2(xa);
-          const float b = ((i & 1) < kPolyOf2) ? poly_ex2(xb) : fast_ex2(xb);
+          const bool on_fma = kPolyOf8 == 1 ? i == 0 : kPolyOf8 == 2 ? (i & 1) == 0 : kPolyOf8 == 3 ? i < 3 : kPolyOf8 >= 4;
+          const float b = on_fma ? poly_ex2(xb) : fast_ex2(xb);
           psum += a + b;
           w[i] = pack2<BF16>(a, b);
         }
