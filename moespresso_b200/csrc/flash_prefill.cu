@@ -94,9 +94,9 @@ __device__ __forceinline__ float fast_ex2(float x) {   // 2^x, x <= 0 here; -inf
 }
 
 // 2^x on the FMA pipe for x <= ~8: round-to-nearest split x = n + f with the 1.5 * 2^23 trick, a cubic for 2^f on
-// [-0.5, 0.5] (relative error 7.5e-5, below the rounding of a 16-bit P), n added into the exponent field.  One in eight of
-// a tile's exponentials goes this way (measured best among 0, 1, 2, 3 and 4 in eight) because the special-function unit (16 results per clock per SM) would otherwise
-// bound the softmax.  Inputs below -126 (masked keys) give 2^-126 instead of 0.
+// [-0.5, 0.5] (relative error 7.5e-5, below the rounding of a 16-bit P), n added into the exponent field.  One in
+// eight of a tile's exponentials goes this way (measured best among 0 to 4 in eight): it takes the edge off the
+// special-function unit's 16 results per clock per SM.  Inputs below -126 (masked keys) give 2^-126 instead of 0.
 __device__ __forceinline__ float poly_ex2(float x) {
   x = fmaxf(x, -126.f);
   const float kMagic = 12582912.f;
