@@ -330,7 +330,7 @@ typedef struct {
   int32_t dtype;    /* BF16 | F16, all five tensors */
   int32_t S, Skv, Hq, Hkv, D;
   float scale;
-  void* workspace;
+  void* workspace;            /* unused: the kernel needs no scratch (the size query returns 0) */
   int64_t workspace_bytes;
   int32_t* status;
 } mxb_flash_prefill_args;

@@ -15,7 +15,7 @@
 // the softmax warps read S from TMEM, keep a running maximum with lazy rescaling of
 // the TMEM-resident O (only when the maximum grew by more than 2^8), write P as a
 // 16-bit K-major swizzled tile to one of two shared-memory buffers; O += P V (M128 x N256 x K64)
-// with V read from a pre-transposed copy (keys contiguous) so that every operand is K-major.
+// with V read in place as an MN-major B operand (no transposed copy).
 // S of tile j+1 is issued before P of tile j is consumed and P of tile j+1 is written while P V of
 // tile j runs, so the tensor pipe overlaps the softmax.
 // TMEM: S0a [0,64) S0b [64,128) S1a [128,192) S1b [192,256) O [256,512).
@@ -56,26 +56,10 @@ struct FlashParams {
   int32_t S, Skv, Hq, Hkv;
   float scale_log2;  // scale * log2(e)
   int32_t q_head_inner, k_head_inner;  // tensor-map dimension order: (D, head, row) instead of (D, row, head)
-  int32_t g_head_inner, o_head_inner;
+  int32_t g_head_inner, o_head_inner, v_head_inner;
   int32_t tma_drain;   // gate tile in and output tile out by TMA through the (then idle) Q buffer
   int32_t* status;
 };
-
-__global__ void transpose_v_kernel(const uint16_t* __restrict__ v, int64_t v_ss, int64_t v_sh, uint16_t* __restrict__ vt,
-                                   int Skv, int Skv_pad, int D) {
-  __shared__ uint16_t tile[32][33];
-  const int hk = blockIdx.z;
-  const int s0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
-  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
-    const int s = s0 + r, d = d0 + threadIdx.x;
-    tile[r][threadIdx.x] = (s < Skv && d < D) ? v[(int64_t)s * v_ss + (int64_t)hk * v_sh + d] : (uint16_t)0;
-  }
-  __syncthreads();
-  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
-    const int d = d0 + r, s = s0 + threadIdx.x;
-    if (d < D && s < Skv_pad) vt[((int64_t)hk * D + d) * Skv_pad + s] = tile[threadIdx.x][r];
-  }
-}
 
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
@@ -256,14 +240,18 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
     // ------------------------------------------------------------ O += P V issuer
     if (lane == 0) {
       constexpr uint32_t fmt = BF16 ? ptx::kFmtBF16 : ptx::kFmtF16;
-      const uint32_t idesc_o = ptx::idesc_f16(fmt, fmt, FB_M, FB_D, 0, 0);
-      const uint64_t v_desc = ptx::smem_desc_sw128(ptx::smem_u32(v_s), 16, 1024);
+      // V is read as it lies in memory ([key][feature]): as the B operand that is MN-major, four 64-feature slabs of
+      // [64 keys x 128 B] (8 KB apart = LBO), groups of 8 keys 1 KB apart (SBO), 16 keys per K step
+      const uint32_t idesc_o = ptx::idesc_f16(fmt, fmt, FB_M, FB_D, 0, 1);
+      const uint64_t v_desc = ptx::smem_desc_sw128(ptx::smem_u32(v_s), 8192, 1024);
       const uint64_t p_desc = ptx::smem_desc_sw128(ptx::smem_u32(p_s), 16, 1024);
       ptx::tma_prefetch_desc(&tm_vt);
       auto load_v = [&](int j) {
         const int s = j & 1;
         ptx::mbar_expect_tx(&v_full[s], 32768);
-        ptx::tma_load_3d(v_s + s * 32768, &tm_vt, &v_full[s], j * FB_N, 0, kvh);
+        for (int kb = 0; kb < 4; ++kb)
+          ptx::tma_load_3d(v_s + s * 32768 + kb * 8192, &tm_vt, &v_full[s], kb * 64, p.v_head_inner ? kvh : j * FB_N,
+                           p.v_head_inner ? j * FB_N : kvh);
       };
       load_v(0);
       if (ntiles > 1) load_v(1);
@@ -276,7 +264,7 @@ __global__ void __launch_bounds__(384, 1) flash_prefill_kernel(const __grid_cons
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
           ptx::mma_f16_ss(tmem_o, ptx::desc_advance(p_desc, s * 16384 + ks * 32),
-                          ptx::desc_advance(v_desc, s * 32768 + ks * 32), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+                          ptx::desc_advance(v_desc, s * 32768 + ks * 2048), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
         ptx::mma_commit(&pv_done[s]);
         TRF(5, j);
         // V of the next tile goes where P V of the previous tile read; that one was issued a whole tile ago
@@ -548,35 +536,19 @@ static int flash_validate(const mxb_flash_prefill_args* a) {
 }
 
 extern "C" int64_t mxb_flash_prefill_workspace_bytes(const mxb_flash_prefill_args* a) {
-  if (!a || a->Skv <= 0 || a->Hkv <= 0 || a->D <= 0) return 0;
-  return (int64_t)a->Hkv * a->D * round_up(a->Skv, 64) * 2;
+  (void)a;
+  return 0;   // V is read in place (MN-major operand): no scratch
 }
 
 extern "C" int mxb_flash_prefill(const mxb_flash_prefill_args* a, void* stream) {
   int rc = flash_validate(a);
   if (rc != MXB_OK) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const int64_t need = mxb_flash_prefill_workspace_bytes(a);
-  MXB_REQUIRE(a->workspace && a->workspace_bytes >= need, MXB_ERR_WORKSPACE,
-              "flash prefill: workspace of %lld bytes required", (long long)need);
-  MXB_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 255) == 0, MXB_ERR_INVALID,
-              "flash prefill: workspace must be 256-byte aligned");
   MXB_REQUIRE((reinterpret_cast<uintptr_t>(a->out) & 15) == 0 && a->out_stride_s % 8 == 0 && a->out_stride_h % 8 == 0,
               MXB_ERR_INVALID, "out must be 16-byte aligned with strides that are multiples of 8 elements");
   MXB_REQUIRE(!a->gate || ((reinterpret_cast<uintptr_t>(a->gate) & 15) == 0 && a->gate_stride_s % 8 == 0 &&
                            a->gate_stride_h % 8 == 0),
               MXB_ERR_INVALID, "gate must be 16-byte aligned with strides that are multiples of 8 elements");
-  const int Skv_pad = (int)round_up(a->Skv, 64);
-
-  {
-    dim3 blk(32, 8);
-    dim3 grd((unsigned)ceil_div(Skv_pad, 32), (unsigned)ceil_div(a->D, 32), (unsigned)a->Hkv);
-    note_launch();
-    transpose_v_kernel<<<grd, blk, 0, st>>>(reinterpret_cast<const uint16_t*>(a->v), a->v_stride_s, a->v_stride_h,
-                                            reinterpret_cast<uint16_t*>(a->workspace), a->Skv, Skv_pad, a->D);
-    MXB_CUDA_OK(cudaGetLastError());
-  }
-
   const CUtensorMapDataType dt = a->dtype == MXB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUtensorMap tq, tk, tv;
   // cuTensorMapEncodeTiled wants ascending strides: put the head axis before the row axis when its
@@ -598,11 +570,13 @@ extern "C" int mxb_flash_prefill(const mxb_flash_prefill_args* a, void* stream) 
     rc = make_tensor_map(&tk, dt, 3, a->k, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != MXB_OK) return rc;
   }
+  const bool v_hin = a->v_stride_h < a->v_stride_s;
   {
-    uint64_t dims[3] = {(uint64_t)Skv_pad, (uint64_t)a->D, (uint64_t)a->Hkv};
-    uint64_t str[2] = {(uint64_t)Skv_pad * 2, (uint64_t)a->D * Skv_pad * 2};
-    uint32_t box[3] = {64, FB_D, 1};
-    rc = make_tensor_map(&tv, dt, 3, a->workspace, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    uint64_t dims[3] = {(uint64_t)a->D, (uint64_t)(v_hin ? a->Hkv : a->Skv), (uint64_t)(v_hin ? a->Skv : a->Hkv)};
+    uint64_t str[2] = {(uint64_t)(v_hin ? a->v_stride_h : a->v_stride_s) * 2,
+                       (uint64_t)(v_hin ? a->v_stride_s : a->v_stride_h) * 2};
+    uint32_t box[3] = {64, v_hin ? 1u : (uint32_t)FB_N, v_hin ? (uint32_t)FB_N : 1u};
+    rc = make_tensor_map(&tv, dt, 3, a->v, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != MXB_OK) return rc;
   }
 
@@ -626,6 +600,7 @@ extern "C" int mxb_flash_prefill(const mxb_flash_prefill_args* a, void* stream) 
   MXB_REQUIRE(a->scale > 0.f, MXB_ERR_INVALID, "flash prefill: scale must be positive");
   FlashParams p{};
   p.g_head_inner = g_hin ? 1 : 0; p.o_head_inner = o_hin ? 1 : 0; p.tma_drain = tma_drain ? 1 : 0;
+  p.v_head_inner = v_hin ? 1 : 0;
   p.gate = a->gate; p.g_ss = a->gate_stride_s; p.g_sh = a->gate_stride_h;
   p.out = a->out; p.o_ss = a->out_stride_s; p.o_sh = a->out_stride_h;
   p.S = a->S; p.Skv = a->Skv; p.Hq = a->Hq; p.Hkv = a->Hkv;
