@@ -1,13 +1,14 @@
 // Causal GQA flash prefill, head_dim 256, 16-bit operands, fp32 accumulation, with the
 // sigmoid-gate epilogue fused:  out = softmax(scale * Q K^T + causal) V * sigmoid(gate).
 //
-// One CTA = 128 query rows of one query head.  Twelve warps:
-//   warps 0-7  softmax + epilogue; warp w owns query rows 32 * (w % 4) .. (= its TMEM lanes) and keys
+// One CTA = 128 query rows of one query head; the grid is one-dimensional in longest-first order (every head's
+// latest query tile first), because causal tiles differ 64-fold in length.  Twelve warps:
+//   warps 0-7  softmax + drain; warp w owns query rows 32 * (w % 4) .. (= its TMEM lanes) and keys
 //              32 * (w / 4) .. of every 64-key tile; the two halves of a row swap maxima and sums through
-//              shared memory
+//              shared memory behind a 64-thread barrier
 //   warp  8    issues the first half of the S = Q K^T MMAs (feature slabs 0-1, one lane)
-//   warp  9    TMA producer (one lane)
-//   warp 10    issues the O += P V MMAs (one lane)
+//   warp  9    TMA producer for Q and K (one lane)
+//   warp 10    issues the O += P V MMAs and fetches the next V tile behind them (one lane)
 //   warp 11    issues the second half of the S MMAs (feature slabs 2-3) into a second accumulator
 // Per 64-key tile:  S = Q K^T (M128 x N64 x K256) into one of two TMEM buffers, each made of two
 // accumulators that the softmax adds (one thread sustains only one tcgen05.mma per ~85 cycles, so
@@ -18,6 +19,8 @@
 // with V read in place as an MN-major B operand (no transposed copy).
 // S of tile j+1 is issued before P of tile j is consumed and P of tile j+1 is written while P V of
 // tile j runs, so the tensor pipe overlaps the softmax.
+// Drain: the gate tile arrives by TMA in the Q buffer during the last tile; each thread normalises its half row,
+// applies the sigmoid and writes the output chunks in place; TMA stores write the tile.
 // TMEM: S0a [0,64) S0b [64,128) S1a [128,192) S1b [192,256) O [256,512).
 #include "common.cuh"
 #include "ptx_sm100.cuh"
@@ -41,7 +44,7 @@ constexpr int kPolyOf8 = MXB_FLASH_POLY;   // of every eight exponentials, this 
 struct FlashSmem {
   static constexpr int q_off = 0;                       // 4 slabs x [128 x 128 B]
   static constexpr int k_off = q_off + 4 * 16384;       // 2 stages x 4 slabs x [64 x 128 B]
-  static constexpr int v_off = k_off + 2 * 32768;       // 2 stages x [256 x 128 B]
+  static constexpr int v_off = k_off + 2 * 32768;       // 2 stages x 4 slabs x [64 keys x 128 B]
   static constexpr int p_off = v_off + 2 * 32768;       // 2 buffers x [128 x 128 B]
   static constexpr int bar_off = p_off + 2 * 16384;
   static constexpr int rowmax_off = bar_off + 256;      // [2 tiles][2 halves][128 rows] bf16 (1 KB); reused for the row sums
