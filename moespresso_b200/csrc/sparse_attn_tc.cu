@@ -8,13 +8,14 @@
 //                                                                 MN-major: dims contiguous)
 //
 // so one staged copy of the rows (128-byte-swizzled 64-feature slabs) feeds both
-// contractions and nothing is transposed.  Rows are gathered with 16-byte vector loads;
-// int8 rows are widened to fp16 integers (exact) while staging and their per-row scale is
+// contractions and nothing is transposed.  16-bit rows are gathered by TMA (tile::gather4: four rows x one slab
+// per instruction, swizzled on the way in, row -1 = zeros for padding).  int8 rows are gathered with 16-byte
+// vector loads through registers, widened to fp16 integers (exact) while staging, and their per-row scale is
 // folded into the logit (s = scale_j * q.int_j) and into P (p_j * scale_j), so the tensor
 // core multiplies exact values.  Thread = row for the softmax (TMEM lane), with a lazily
 // updated per-head reference maximum held in shared memory: the cross-row maximum is
-// reduced only when some logit exceeds the reference by more than 2^8, the
-// O accumulator in TMEM is rescaled only then.  The row sum uses the ROUNDED 16-bit P
+// reduced only when some logit exceeds the reference by more than a gap (2^15 for fp16 operands, 2^60 for bf16),
+// the O accumulator in TMEM is rescaled only then.  The row sum uses the ROUNDED 16-bit P
 // values, so out = sum(p~ v) / sum(p~) is an exactly normalised average.  Splits over the
 // row list emit (o, m, l) partials for the log-sum-exp merge kernel.
 //
