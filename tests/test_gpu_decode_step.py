@@ -97,3 +97,29 @@ def test_plan_matches_eager_step(graph):
     out = plan.run_packed(host)
     torch.cuda.synchronize()
     assert torch.equal(out, eager)
+
+
+def test_plan_with_16bit_cache():
+    """bf16 latent cache: the attention kernel gathers rows by TMA (tensor maps passed as kernel parameters); the
+    captured graph must replay to the eager step's bits and stay within the 16-bit bound of the oracle."""
+    need_gpu()
+    from moespresso_b200.deepseek_v4.decode_step import SparseDecodePlan
+    lens = [3000, 2500, 6000]
+    c = synth.config3(seed=4, lens=lens)
+    kv = synth.to_bf16_f32(c["kv"].astype(np.float32) * c["kv_scales"].astype(np.float32)[:, None])   # dequantised rows
+    cache = LatentCache(kv=dev(kv, torch.bfloat16), kv_scales=None, idx_keys=fp8_from_bits(c["idx_key_bits"]),
+                        row_start=dev(c["row_start"]), row_count=dev(c["lens"].astype(np.int32)), max_rows=6000)
+    q, iq, iw = dev(c["q"], torch.bfloat16), dev(c["idx_q"], torch.bfloat16), dev(c["idx_w"])
+    eager, ids = sparse_decode_step(q, iq, iw, cache, k=c["k"], scale=c["scale"], d_v=c["d_v"], return_ids=True)
+    plan = SparseDecodePlan(cache, heads=64, d_qk=576, idx_heads=16, idx_dim=64, k=c["k"], scale=c["scale"],
+                            d_v=c["d_v"], q_dtype=torch.bfloat16)
+    for _ in range(2):
+        out = plan.run(q, iq, iw)
+        torch.cuda.synchronize()
+        assert torch.equal(out, eager)
+    ids = ids.cpu().numpy()
+    for b, n in enumerate(lens):
+        s = int(c["row_start"][b])
+        ref = ds4.indexed_mixed_attention_decode(c["q"][b], None, kv[s:s + n], ids[b], None, pos0=0, window=0, ratio=0,
+                                                 scale=c["scale"], d_v=c["d_v"])
+        assert max_abs(eager[b], ref) <= 2e-2
