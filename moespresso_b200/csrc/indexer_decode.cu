@@ -270,7 +270,9 @@ static int launch_decode_d(DecodeIdxParams& p, cudaStream_t st) {
 
 bool indexer_decode_eligible(const mxb_indexer_scores_args* a) {
   const bool q16 = a->q_dtype == MXB_F16 || a->q_dtype == MXB_BF16;
-  return a->T == 1 && a->B <= kDecMaxBatch && a->key_dtype == MXB_F8E4M3 && q16 &&
+  // the scan applies no causal row mask: a single-token call that asks for one (ratio > 0) goes to the tiled
+  // kernel, which reads the per-token visibility table
+  return a->T == 1 && a->ratio == 0 && a->B <= kDecMaxBatch && a->key_dtype == MXB_F8E4M3 && q16 &&
          (a->H == 8 || a->H == 16 || a->H == 32 || a->H == 64) &&
          !(a->flags & (MXB_INDEXER_EXACT_FP32 | MXB_INDEXER_FP8_MMA));
 }

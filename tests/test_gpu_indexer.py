@@ -46,6 +46,7 @@ def test_exact_fp32_matches_oracle(B, H, T, D, R, pos0, ratio):
     (2, 16, 40, 64, 1000, 3000, 4),      # token tiles (16 tokens x 16 heads = 256 columns), ragged last tile
     (1, 64, 7, 128, 700, 2500, 4),       # D = 128 (two swizzle slabs), 64 heads
     (3, 32, 1, 64, 129, 0, 0),
+    (2, 16, 1, 64, 1000, 1500, 4),       # one token WITH the causal row mask: rows >= (1500 + 1) // 4 are -inf
 ])
 def test_tensor_core_path_matches_oracle(form, B, H, T, D, R, pos0, ratio):
     need_gpu()

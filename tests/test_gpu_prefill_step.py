@@ -39,3 +39,35 @@ def test_prefill_step_bf16(T, R, k, chunk):
                                               scale=Dqk ** -0.5, d_v=Dv)
     assert out.shape == (T, H, Dv)
     assert max_abs(out, ref) <= 2e-2
+
+
+def test_prefill_step_fp8_keys_one_token_tail_chunk():
+    """FP8 index keys and T % token_chunk == 1: the last score launch holds a single token and must still carry
+    the causal row mask (rows >= (pos + 1) // ratio never selected)."""
+    need_gpu()
+    from moespresso_b200 import synth
+    from tests.gpu_util import fp8_from_bits
+    rng = np.random.default_rng(5)
+    T, R, k, chunk = 17, 600, 64, 16
+    H, Dqk, Dv, Hi, Di, ratio = 64, 576, 512, 16, 64, 4
+    pos0 = 1200                      # visible rows 300 .. 304 of 600: half of the pool is masked
+    q = bf16_round(rng.standard_normal((T, H, Dqk)))
+    kv = bf16_round(rng.standard_normal((R, Dqk)))
+    iq = bf16_round(rng.standard_normal((T, Hi, Di)))
+    bits = synth.to_e4m3_bits(rng.standard_normal((R, Di)).astype(np.float32))
+    ik = synth.e4m3_bits_to_f32(bits)
+    iw = (rng.standard_normal((T, Hi)) / 4).astype(np.float32)
+    bf = torch.bfloat16
+    out, ids = sparse_prefill_step(dev(q, bf), dev(kv, bf), dev(iq, bf), fp8_from_bits(bits), dev(iw), pos0=pos0,
+                                   ratio=ratio, k=k, scale=Dqk ** -0.5, d_v=Dv, window=0, token_chunk=chunk,
+                                   return_ids=True)
+    ids = ids.cpu().numpy()
+    for t in range(T):
+        vis = (pos0 + t + 1) // ratio
+        assert ids[t].max() < vis and ids[t].min() >= 0
+    ref = ds4.indexed_mixed_attention_prefill(q, None, kv, ids, None, pos0=pos0, window=0, ratio=ratio,
+                                              scale=Dqk ** -0.5, d_v=Dv)
+    assert max_abs(out, ref) <= 2e-2
+    scores = ds4.indexer_scores(iq, ik, iw, pos0=pos0, ratio=ratio)
+    for t in range(T):               # t = T - 1 is the one-token launch
+        assert np.all(np.isfinite(scores[t][ids[t]]))
