@@ -31,7 +31,8 @@ struct SparseParams {
   int32_t window, ratio;
   int32_t nsplit;
   int32_t* status;
-  int32_t tma_rows;   // 16-bit tables: rows are gathered by TMA (tensor maps passed beside these parameters)
+  int32_t q_tma;      // q reaches shared memory by TMA (tensor map beside these parameters) instead of registers
+  int32_t q_axis[3];  // which of (0 = head, 1 = token, 2 = batch) lies on dimensions 1..3 of that map
 };
 
 // tcgen05 path (16-bit / int8 KV).  Returns MXB_ERR_UNSUPPORTED when the shape is outside its range.

@@ -118,8 +118,12 @@ def test_plan_with_16bit_cache():
         torch.cuda.synchronize()
         assert torch.equal(out, eager)
     ids = ids.cpu().numpy()
+    # The 2e-2 bound is stated for unit-scale values.  These rows reach |v| = 12.7 (int8 x scale), where bf16 itself
+    # resolves 0.0625 and the bf16 softmax weights (8 significant bits) move an output by up to |v| * 2^-9: the
+    # bound scales with the table's magnitude.
+    tol = 2e-2 * max(1.0, float(np.abs(kv).max()) / 4.0)
     for b, n in enumerate(lens):
         s = int(c["row_start"][b])
         ref = ds4.indexed_mixed_attention_decode(c["q"][b], None, kv[s:s + n], ids[b], None, pos0=0, window=0, ratio=0,
                                                  scale=c["scale"], d_v=c["d_v"])
-        assert max_abs(eager[b], ref) <= 2e-2
+        assert max_abs(eager[b], ref) <= tol
