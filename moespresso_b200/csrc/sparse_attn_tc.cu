@@ -4,37 +4,44 @@
 // gathered row.  The row list (raw window rows, then the selected compressed rows) is cut into UNITS of 64
 // rows.  The gathered rows sit on the MMA M axis:
 //
-//   S^T[64 rows  x 64 heads]  = Kunit[64 x Dqk] . Q^T             (M = 64:  A = operand buffer, K-major)
-//   O^T[Dv dims  x 64 heads] += Vunit^T[Dv x 64] . P^T            (M = 128: A = the SAME buffer read MN-major)
+//   S^T[64 rows  x 64 heads]  = Kunit[64 x Dqk] . Q^T             (M = 64)
+//   O^T[Dv dims  x 64 heads] += Vunit^T[Dv x 64] . P^T            (M = 128, A read MN-major)
 //
-// so one staged copy of the rows (128-byte-swizzled 64-feature slabs of [64 rows x 128 B]) feeds both
-// contractions and nothing is transposed.  Warp roles:
+// Twenty warps:
 //   warps 0-7    softmax, one unit at a time.  An M = 64 accumulator occupies lanes 0-15 of each 32-lane
 //                quarter of TMEM; thread = (row, 16 heads)
-//   next 2 or 4  issue S^T, each into an accumulator of its own for its share of the feature slabs (measured: a
-//                thread issues one tcgen05.mma per ~105 cycles whatever its shape, four threads together one per
-//                ~37 (M = 64) or ~53 (M = 128) cycles); the softmax adds the accumulators
-//   next 4       issue O^T += V^T P^T, one 128-feature value block each
-//   last 8       producers: resolve list entries to rows ahead of time and bring the rows in.
-// 16-bit tables: two operand buffers alternate; TMA row gathers (tile::gather4: four rows x one 128-byte slab per
-// instruction, swizzled on the way in, row -1 = zeros) fill one while the other is multiplied, slab by slab, and
-// the logit MMAs of a slab start as soon as it has landed.
-// int8 tables: the rows of units u + 1 and u + 2 travel by bulk copies (one 576-byte copy per row) into a ring of
-// two int8 staging buffers while unit u is processed; the producers widen a landed unit to exact 16-bit integers
-// into the ONE operand buffer (shared memory cannot hold two beside the staging ring) and the per-row scale is
-// folded into the logit and into P, so the tensor core multiplies exact values.  Loads through registers are not
-// used for rows: measured, an SM sustains ~5 bytes per clock of gathered row pieces that way whatever their
-// source, against 16-19 through its bulk-copy engine.
-// Operand type: bf16 for bf16 tables, fp16 otherwise (q is rounded to fp16, as the reference kernels do; a bf16
-// q over int8 rows lands by TMA and is converted in place).
+//   warps 8, 9   issue S^T (measured: a thread issues one tcgen05.mma per ~105 cycles whatever its shape; four
+//                threads together reach one per ~37 cycles for M = 64, ~53 for M = 128)
+//   warps 10, 11 issue O^T += V^T P^T for the value blocks 0-1 / 2-3; every 128-feature block has a barrier of its
+//                own, so that its two slabs can be refilled while the other blocks are still being multiplied
+//   warps 12-19  (int8 tables: 12-15) resolve list entries to rows ahead of time and bring the rows in by TMA row
+//                gathers (tile::gather4: four rows x one slab per instruction, swizzled on the way in, row -1 =
+//                zeros).  Loads through registers are not used for rows: measured, an SM sustains ~5 bytes per
+//                clock of gathered row pieces that way whatever their source, several times that through TMA.
+//   warps 16-19  int8 tables only: widen the value features of a landed unit
+//
+// 16-bit tables: two operand buffers (64-feature slabs of [64 rows x 128 B]) alternate; one staged copy of a
+// unit feeds both contractions (K-major for the logits, MN-major for the values) and nothing is transposed.  The
+// two logit issuers split the slabs, each into an accumulator of its own that the softmax adds, and multiply a
+// slab as soon as it has landed.
+//
+// int8 tables: the logits run on the int8 tensor-core path (kind::i8, int32 accumulation) straight from the rows as
+// they are stored.  The gathers land the int8 rows in operand layout (128-feature slabs, two buffers); q is held
+// as two int8 digit planes of a per-head 15-bit fixed-point number, q = (256 hi + lo) step_h, stacked on the MMA N
+// axis (N = 128), so S^T = step_h (256 S_hi + S_lo) is exact integer arithmetic and q is never rounded to fp16.
+// Only the values need 16-bit operands: the producers widen the first Dv features of a landed unit to exact fp16
+// integers into ONE value buffer, block by block behind the previous unit's P V and in parallel with the softmax
+// of this one; the per-row scale is folded into the logit and into P.
+// Operand type of the 16-bit contractions: bf16 for bf16 tables, fp16 otherwise (16-bit tables: q rounded to the
+// table's type, as the reference kernels round it to fp16).
 //
 // The softmax keeps one per-head reference maximum m_ref in shared memory, moved only when a logit exceeds it by
 // more than a gap (2^15 for fp16 operands, 2^60 for bf16); O^T in TMEM is rescaled only then, after the previous
 // unit's P V has completed.  The row sum uses the ROUNDED 16-bit P values, so out = sum(p~ v) / sum(p~) is an
 // exactly normalised average.  Splits over the row list emit (o, m, l) partials for the log-sum-exp merge kernel.
 //
-// TMEM columns: four S^T accumulators of 64 columns at [0,256) (16-bit tables: two per operand buffer; int8:
-// four issuers on the one buffer), O^T at [256, 256 + Dv/2).
+// TMEM columns: S^T of even units [0,128), of odd units [128,256) (two accumulators of 64 columns, or the hi and
+// lo planes), O^T at [256, 256 + Dv/2).
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 #include "sparse_attn.cuh"
@@ -42,20 +49,18 @@
 namespace mxb {
 
 #ifdef MXB_TRACE_SP   // development aid: cycle stamps of CTA 0's roles for its first 16 units, written behind `status`
-#define TRS(k, i) do { if (tr_on && (i) < 16) tr[(k) * 16 + (i)] = clock64(); } while (0)
+#define TRS(k, i) do { if (tr_on && (i) < 16) tr[(k) * 16 + (i)] = clock64(); } while (0)   // needs 16 x 16 slots
 #else
 #define TRS(k, i)
 #endif
 
 constexpr int WS_UNIT = 64;       // gathered rows per unit
-constexpr int WS_HEADS = 64;      // MMA N
+constexpr int WS_HEADS = 64;      // heads per CTA (MMA N; two planes of 64 for int8 tables)
 constexpr int WS_MAX_SLABS = 9;   // Dqk <= 576
 constexpr int WS_SLAB = 8192;     // [64 rows or heads] x 128 B
-constexpr int kWsMiscBytes = 5120;
-constexpr int kRing = 4;          // units of row metadata kept in shared memory
-// warps: 8 softmax, NQK logit issuers, 4 value issuers (one per 128-feature block), 8 producers
-__host__ __device__ constexpr int ws_nqk(bool i8) { return i8 ? 4 : 2; }
-__host__ __device__ constexpr int ws_threads(bool i8) { return (8 + ws_nqk(i8) + 4 + 8) * 32; }
+constexpr int WS_THREADS = 640;   // 20 warps
+constexpr int kWsMiscBytes = 7168;
+constexpr int kRing = 8;          // units of row metadata kept in shared memory (a slot is rewritten six units later)
 // P = 2^(s - m_ref) may be as large as 2^gap.  bf16 operands have fp32's range; fp16 operands top out at 65504,
 // and the int8 path folds the row's dequantisation scale into P, so its gap shrinks by log2(scale) when positive.
 constexpr float kRescaleGapF16 = 15.f;
@@ -63,12 +68,13 @@ constexpr float kRescaleGapBF16 = 60.f;
 constexpr uint32_t kNoRow = 0xFFFFFFFFu;
 
 struct WsLayout {
-  int nslab;        // Dqk / 64
-  int q_off;        // q operand: nslab slabs of [64 heads x 128 B]
-  int ub_off[2];    // operand buffers: nslab slabs of [64 rows x 128 B] each (int8 tables: only the first)
+  int nslab;        // Dqk / 64: 64-feature slabs of 16-bit operands
+  int n128, tail;   // int8 operands: full 128-feature slabs, and 64 tail features (0 or 64) in a 64-byte-swizzled slab
+  int q_off;        // q operand.  16-bit: nslab slabs of [64 heads x 128 B]; int8: [128 rows x 128 B] slabs (+ [128 x 64 B])
+  int ub_off[2];    // 16-bit operand buffers of a unit (int8 tables: one value buffer of Dv / 64 slabs)
   int pt_off[2];    // P^T of the unit in buffer b: [64 heads x 128 B] (64 rows of 16 bits)
-  int st_off[2];    // int8 tables: staging ring, 64 rows of st_stride bytes each
-  int st_stride;    // Dqk + 16: consecutive rows start in different 16-byte bank groups
+  int kb_off[2];    // int8 tables: the two int8 row buffers, n128 slabs of [64 rows x 128 B] (+ [64 x 64 B])
+  int qtmp_off;     // int8 tables: where a 16-bit q lands before it is turned into digit planes (-1: no room)
   int misc_off;
   int total;
 };
@@ -76,29 +82,34 @@ struct WsLayout {
 __host__ __device__ inline WsLayout ws_layout(int Dqk, int Dv, bool i8) {
   WsLayout L;
   L.nslab = Dqk / 64;
+  L.n128 = Dqk / 128;
+  L.tail = Dqk % 128;
   L.q_off = 0;
-  L.ub_off[0] = L.nslab * WS_SLAB;
-  L.ub_off[1] = 2 * L.nslab * WS_SLAB;
-  L.st_stride = Dqk + 16;
-  L.st_off[0] = L.st_off[1] = 0;
+  L.qtmp_off = -1;
+  L.kb_off[0] = L.kb_off[1] = 0;
   int end;
   if (i8) {
-    L.ub_off[1] = L.ub_off[0];
-    L.st_off[0] = 2 * L.nslab * WS_SLAB;
-    L.st_off[1] = L.st_off[0] + WS_UNIT * L.st_stride;
-    end = L.st_off[1] + WS_UNIT * L.st_stride;
+    const int q_bytes = L.n128 * 2 * WS_SLAB + (L.tail ? WS_SLAB : 0);
+    const int k_bytes = WS_UNIT * Dqk;
+    L.kb_off[0] = q_bytes;
+    L.kb_off[1] = q_bytes + k_bytes;
+    L.ub_off[0] = L.ub_off[1] = (q_bytes + 2 * k_bytes + 1023) & ~1023;
+    L.pt_off[0] = L.pt_off[1] = L.ub_off[0] + (Dv / 64) * WS_SLAB;
+    end = L.pt_off[0] + WS_SLAB;
+    if (end - L.ub_off[0] >= L.nslab * WS_SLAB) L.qtmp_off = L.ub_off[0];   // value buffer + P^T hold a 16-bit q
   } else {
+    L.ub_off[0] = L.nslab * WS_SLAB;
+    L.ub_off[1] = 2 * L.nslab * WS_SLAB;
     end = 3 * L.nslab * WS_SLAB;
-  }
-  if (Dqk - Dv >= 64) {
-    // the last slab feeds only the logits: it is free once S^T of its unit is complete
-    L.pt_off[0] = L.ub_off[0] + (L.nslab - 1) * WS_SLAB;
-    L.pt_off[1] = L.ub_off[1] + (L.nslab - 1) * WS_SLAB;
-  } else {
-    end = (end + 1023) & ~1023;
-    L.pt_off[0] = end;
-    L.pt_off[1] = i8 ? end : end + WS_SLAB;
-    end += i8 ? WS_SLAB : 2 * WS_SLAB;
+    if (Dqk - Dv >= 64) {
+      // the last slab feeds only the logits: it is free once S^T of its unit is complete
+      L.pt_off[0] = L.ub_off[0] + (L.nslab - 1) * WS_SLAB;
+      L.pt_off[1] = L.ub_off[1] + (L.nslab - 1) * WS_SLAB;
+    } else {
+      L.pt_off[0] = end;
+      L.pt_off[1] = end + WS_SLAB;
+      end += 2 * WS_SLAB;
+    }
   }
   L.misc_off = (end + 15) & ~15;
   L.total = L.misc_off + kWsMiscBytes;
@@ -110,11 +121,16 @@ struct WsMisc {
   float factor[WS_HEADS];          // of the latest move of m_ref; the output factors at the end
   float l_tot[WS_HEADS];
   float colmax[4][WS_HEADS];       // per row quarter; reused for the row sums at the end
+  float q_step[WS_HEADS];          // int8 tables: q[h, :] = (256 hi + lo) * q_step[h]
+  uint32_t q_amax[WS_HEADS];       // bits of max |q[h, :]|
   uint32_t row_ref[kRing][WS_UNIT];   // kNoRow, or row index within its table (< 2^31), bit 31 set for the raw table
   float row_scale[kRing][WS_UNIT];
-  // full: operand slabs ready for the logit MMAs (16-bit tables: [buffer][slab], completed by the row gathers;
-  // int8 tables: [0][issuer], completed by the widening warps); st_full: an int8 staging buffer has landed
-  uint64_t q_full, q_ready, full[2][WS_MAX_SLABS], st_full[2], s_ready[2], s_free[2], p_ready[2];
+  uint64_t q_full, q_ready;
+  uint64_t full[2][WS_MAX_SLABS];  // a slab of the unit in row buffer b has landed
+  uint64_t v_full[4];              // int8 tables: a 128-feature block of the value buffer has been widened
+  uint64_t k_free[2];              // int8 tables: the widening warps have read row buffer b
+  uint64_t meta_ready;             // int8 tables: the scales of units 0 and 1 have been published
+  uint64_t s_ready[2], s_free[2], p_ready[2];
   uint64_t pv_blk[2][4];           // P V of one 128-feature block of the unit in buffer b has completed: its two slabs are free
   uint32_t tmem_slot;
   int abort_flag;
@@ -135,26 +151,6 @@ __device__ __forceinline__ void widen_i8x16_f16(const uint4& in, uint4& lo, uint
     __half2 hb = __hsub2(*reinterpret_cast<__half2*>(&b), bias);
     o[2 * i] = *reinterpret_cast<uint32_t*>(&ha);
     o[2 * i + 1] = *reinterpret_cast<uint32_t*>(&hb);
-  }
-  lo = make_uint4(o[0], o[1], o[2], o[3]);
-  hi = make_uint4(o[4], o[5], o[6], o[7]);
-}
-
-// 16 int8 -> 16 bf16 integers (exact).  bf16 carries 7 mantissa bits: the low 7 bits u7 of the biased byte go into
-// the mantissa of 128.0 (giving 128 + u7), and 128 (byte >= 128, value >= 0) or 256 (value < 0) is subtracted.
-__device__ __forceinline__ uint32_t i8pair_to_bf16x2(uint32_t a) {   // a = [u0][0x43][u1][0x43]
-  uint32_t hi = a & 0xFF7FFF7Fu;
-  uint32_t sub = 0x43804380u ^ (a & 0x00800080u);
-  __nv_bfloat162 r = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&hi), *reinterpret_cast<__nv_bfloat162*>(&sub));
-  return *reinterpret_cast<uint32_t*>(&r);
-}
-__device__ __forceinline__ void widen_i8x16_bf16(const uint4& in, uint4& lo, uint4& hi) {
-  const uint32_t w[4] = {in.x ^ 0x80808080u, in.y ^ 0x80808080u, in.z ^ 0x80808080u, in.w ^ 0x80808080u};
-  uint32_t o[8];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    o[2 * i] = i8pair_to_bf16x2(__byte_perm(w[i], 0x43434343u, 0x4140));
-    o[2 * i + 1] = i8pair_to_bf16x2(__byte_perm(w[i], 0x43434343u, 0x4342));
   }
   lo = make_uint4(o[0], o[1], o[2], o[3]);
   hi = make_uint4(o[4], o[5], o[6], o[7]);
@@ -211,15 +207,12 @@ __device__ __forceinline__ bool __syncthreads_or_256(bool pred) {
 }
 
 template <int KVT, int QT, int OT>
-__global__ void __launch_bounds__(ws_threads(KVT == MXB_I8), 1)
+__global__ void __launch_bounds__(WS_THREADS, 1)
 sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_comp,
-                      const __grid_constant__ CUtensorMap tm_raw, const __grid_constant__ CUtensorMap tm_q) {
+                      const __grid_constant__ CUtensorMap tm_raw, const __grid_constant__ CUtensorMap tm_comp_tail,
+                      const __grid_constant__ CUtensorMap tm_raw_tail, const __grid_constant__ CUtensorMap tm_q) {
   constexpr bool I8 = (KVT == MXB_I8);
-  constexpr bool BF16 = (KVT == MXB_BF16);       // operand type: bf16 for bf16 tables, fp16 otherwise
-  constexpr bool Q_CONVERT = I8 && QT == MXB_BF16;   // q lands by TMA as bf16 and is turned into fp16 in place
-  constexpr int NQK = ws_nqk(I8);
-  constexpr int THREADS = ws_threads(I8);
-  constexpr int W_PV = 8 + NQK, W_PROD = W_PV + 4;   // first warp of the value issuers / of the producers
+  constexpr bool BF16 = (KVT == MXB_BF16);       // type of the 16-bit operands: bf16 for bf16 tables, fp16 otherwise
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const WsLayout L = ws_layout(p.Dqk, p.Dv, I8);
@@ -233,25 +226,23 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
   const int b = bt / p.T, t = bt % p.T;
   const int nslab = L.nslab;
   const int n_mt = p.Dv / 128;
-  // Operand / S^T / P^T buffer of unit u and the parity of that buffer's barriers for it: 16-bit tables alternate
-  // two buffers, int8 tables reuse the one.  `prev_use(u)` is the unit that had the buffer before (< 0: none).
-  auto xbuf = [](int u) { return I8 ? 0 : (u & 1); };
-  auto xphase = [](int u) { return (uint32_t)((I8 ? u : (u >> 1)) & 1); };
-  auto prev_use = [](int u) { return I8 ? u - 1 : u - 2; };
-  // slabs [slab_lo(j), slab_lo(j + 1)) go to logit issuer j.  16-bit tables: two halves (9 slabs: 5 + 4).  int8
-  // tables: the last issuer gets one slab, so that little is left to multiply when the widening ends (9: 3 + 3 + 2 + 1)
-  auto slab_lo = [&](int j) {
-    if (!I8 || nslab < 5) return (nslab * j + NQK - 1) / NQK;
-    return j >= NQK ? nslab : ((nslab - 1) * j + NQK - 2) / (NQK - 1);
-  };
-  // P V of unit u: one barrier per 128-feature block, so that the two slabs of a block can be refilled as soon
-  // as that block has been multiplied.  The slabs beyond the value width (the rotary slab, where P^T lives) are
-  // free when every block is done.
-  auto wait_pv_block = [&](int u, int mt) { ptx::mbar_wait(&mi->pv_blk[xbuf(u)][mt], xphase(u), abort_flag); };
+  // Row buffers and S^T alternate with the unit's parity.  The value operand (and P^T) of a unit: 16-bit tables
+  // read it from the unit's own row buffer, int8 tables have one value buffer.
+  auto sbuf = [](int u) { return u & 1; };
+  auto sphase = [](int u) { return (uint32_t)((u >> 1) & 1); };
+  auto pbuf = [](int u) { return I8 ? 0 : (u & 1); };
+  auto pphase = [](int u) { return (uint32_t)((I8 ? u : (u >> 1)) & 1); };
+  // slabs of a row buffer: 16-bit tables nslab slabs of 64 features, int8 tables n128 slabs of 128 features and
+  // the 64-feature tail; [slab_lo(j), slab_lo(j + 1)) go to logit issuer j of the 16-bit path
+  const int nrs = I8 ? L.n128 + (L.tail ? 1 : 0) : nslab;
+  auto slab_lo = [&](int j) { return (nslab * j + 1) / 2; };
+  // P V of unit u: one barrier per 128-feature block.  The slabs beyond the value width (the rotary slab of a
+  // 16-bit unit, where P^T lives) are free when every block is done.
+  auto wait_pv_block = [&](int u, int mt) { ptx::mbar_wait(&mi->pv_blk[pbuf(u)][mt], pphase(u), abort_flag); };
   auto wait_pv_all = [&](int u) {
     for (int mt = 0; mt < n_mt; ++mt) wait_pv_block(u, mt);
   };
-  auto wait_pv_slab = [&](int u, int slab) {   // before slab `slab` of the buffer that unit u used is overwritten
+  auto wait_pv_slab = [&](int u, int slab) {   // before 16-bit slab `slab` of the buffer that unit u used is overwritten
     if (slab < 2 * n_mt) wait_pv_block(u, slab >> 1);
     else wait_pv_all(u);
   };
@@ -290,13 +281,16 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
     ptx::mbar_init(&mi->q_full, 1);
     ptx::mbar_init(&mi->q_ready, 256);
     for (int i = 0; i < 2; ++i) {
-      for (int kb = 0; kb < WS_MAX_SLABS; ++kb) ptx::mbar_init(&mi->full[i][kb], I8 ? 8u : 1u);
-      ptx::mbar_init(&mi->st_full[i], (uint32_t)WS_UNIT);
-      ptx::mbar_init(&mi->s_ready[i], (uint32_t)NQK);
+      for (int kb = 0; kb < WS_MAX_SLABS; ++kb) ptx::mbar_init(&mi->full[i][kb], 1);
+      ptx::mbar_init(&mi->s_ready[i], I8 ? 1u : 2u);
       ptx::mbar_init(&mi->s_free[i], 256);
       ptx::mbar_init(&mi->p_ready[i], 256);
       for (int mt = 0; mt < 4; ++mt) ptx::mbar_init(&mi->pv_blk[i][mt], 1);
     }
+    for (int mt = 0; mt < 4; ++mt) ptx::mbar_init(&mi->v_full[mt], 4);
+    ptx::mbar_init(&mi->k_free[0], 4);
+    ptx::mbar_init(&mi->k_free[1], 4);
+    ptx::mbar_init(&mi->meta_ready, (uint32_t)WS_UNIT);
     mi->abort_flag = 0;
     mi->keff = p.k;
     ptx::mbar_fence_init();
@@ -305,6 +299,7 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
     mi->m_ref[tid] = -INFINITY;
     mi->factor[tid] = 1.f;
     mi->l_tot[tid] = 0.f;
+    mi->q_amax[tid] = 0u;
   }
   __syncwarp();
   if (warp == 0) {
@@ -317,9 +312,11 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
   const uint32_t tmem_base = mi->tmem_slot;
   const uint32_t tmem_o = tmem_base + 256;
 
-  // ------------------------------------------------------------------ q -> B operand of S^T, and the list scan
-  // [64 heads x Dqk] K-major, 128-byte swizzle, in the operand type.  By TMA when q is a 16-bit tensor that a
-  // tensor map can describe (heads beyond H arrive as zeros); through registers (rounded) otherwise.
+  // ------------------------------------------------------------------ q on its way, and the list scan
+  // A 16-bit q that a tensor map can describe lands by TMA as 64-feature slabs of [64 heads x 128 B] (heads beyond
+  // H arrive as zeros): in place as the B operand for 16-bit tables, in a scratch region (the value buffer) for
+  // int8 tables, where it is turned into digit planes.  Otherwise q goes through registers.
+  uint8_t* q_land = I8 ? smem + (L.qtmp_off >= 0 ? L.qtmp_off : 0) : q_s;
   if (p.q_tma) {
     if (tid == 256) {
       ptx::tma_prefetch_desc(&tm_q);
@@ -327,56 +324,44 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
       int32_t c[3];
 #pragma unroll
       for (int i = 0; i < 3; ++i) c[i] = p.q_axis[i] == 0 ? 0 : (p.q_axis[i] == 1 ? t : b);
-      for (int kb = 0; kb < nslab; ++kb) ptx::tma_load_4d(q_s + kb * WS_SLAB, &tm_q, &mi->q_full, kb * 64, c[0], c[1], c[2]);
+      for (int kb = 0; kb < nslab; ++kb) ptx::tma_load_4d(q_land + kb * WS_SLAB, &tm_q, &mi->q_full, kb * 64, c[0], c[1], c[2]);
     }
   }
   const bool q_vec = ((reinterpret_cast<uintptr_t>(p.q) & 15) == 0) && (p.q_sb % 8 == 0) && (p.q_sh % 8 == 0) &&
                      (p.q_st % 8 == 0);
-  const int n_items = WS_HEADS * (p.Dqk / 8);
-  auto store_q_item = [&](int i, const float* f) {
-    // item i = (head i % 64, 16-byte chunk i / 64): a warp writes 32 different rows, conflict-free stores
+  const int n_items = WS_HEADS * (p.Dqk / 8);   // item i = (head i % 64, 8 features i / 64)
+  // eight consecutive features of q as floats: from the landed copy, or from global memory
+  auto load_q_item = [&](int i, float* f) {
     const int h = i & (WS_HEADS - 1), c = i >> 6;
-    uint32_t w[4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      float b0, b1;
-      w[e] = pack_op16x2<BF16>(f[2 * e], f[2 * e + 1], b0, b1);
-    }
-    const int kb = c >> 3, cc = c & 7;
-    *reinterpret_cast<uint4*>(q_s + (size_t)kb * WS_SLAB + (size_t)h * 128 + ((cc ^ (h & 7)) << 4)) =
-        make_uint4(w[0], w[1], w[2], w[3]);
-  };
-  constexpr int kQB = 9;   // 16-bit q, vector path: this many 16-byte loads in flight per thread and pass
-  const bool q_regs = !p.q_tma && warp < 8;
-  const bool q_fast = q_regs && q_vec && QT != MXB_F32;
-  uint4 qraw[kQB];
-  auto load_q_pass = [&](int pass) {
+    for (int e = 0; e < 8; ++e) f[e] = 0.f;
+    if (p.q_tma) {
+      if constexpr (QT != MXB_F32) {
+        const uint4 u4 = *reinterpret_cast<const uint4*>(q_land + (size_t)(c >> 3) * WS_SLAB + (size_t)h * 128 +
+                                                         (((c & 7) ^ (h & 7)) << 4));
+        unpack16<QT>(u4, f);
+      }
+    } else if (h < p.H) {
+      const int64_t base = (int64_t)b * p.q_sb + (int64_t)h * p.q_sh + (int64_t)t * p.q_st + c * 8;
+      if (q_vec) {
+        if constexpr (QT == MXB_F32) {
+          const float4 a = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + base));
+          const float4 bq = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + base) + 1);
+          f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = bq.x; f[5] = bq.y; f[6] = bq.z; f[7] = bq.w;
+        } else {
+          const uint4 u4 = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.q) + base));
+          unpack16<QT>(u4, f);
+        }
+      } else {
 #pragma unroll
-    for (int j = 0; j < kQB; ++j) {
-      const int i = tid + (pass * kQB + j) * 256;
-      const int h = i & (WS_HEADS - 1), c = i >> 6;
-      qraw[j] = make_uint4(0, 0, 0, 0);
-      if (i < n_items && h < p.H)
-        qraw[j] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.q) + (int64_t)b * p.q_sb +
-                                                       (int64_t)h * p.q_sh + (int64_t)t * p.q_st + c * 8));
-    }
-  };
-  auto store_q_pass = [&](int pass) {
-#pragma unroll
-    for (int j = 0; j < kQB; ++j) {
-      const int i = tid + (pass * kQB + j) * 256;
-      if (i < n_items) {
-        float f[8];
-        if constexpr (QT != MXB_F32) unpack16<QT>(qraw[j], f);
-        store_q_item(i, f);
+        for (int e = 0; e < 8; ++e) f[e] = load_elem<QT>(p.q, base + e);
       }
     }
   };
-  if (q_fast) load_q_pass(0);
-  {  // first list entry that ends the walk (its loads overlap the q loads above)
+  {  // first list entry that ends the walk
     int mine = p.k;
 #pragma unroll 4
-    for (int j = tid; j < p.k; j += THREADS) {   // no early exit: the loads stay independent
+    for (int j = tid; j < p.k; j += WS_THREADS) {   // no early exit: the loads stay independent
       const int64_t v = ids[j];
       if (v >= visible && j < mine) mine = j;
     }
@@ -394,14 +379,15 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
   constexpr uint32_t fmt = BF16 ? ptx::kFmtBF16 : ptx::kFmtF16;
   const float scale_log2 = p.scale * 1.4426950408889634f;
 
-  if (warp >= W_PROD) {
-    // ================================================================ producers (8 warps)
-    const int pt = tid - W_PROD * 32, pw = warp - W_PROD;
-    const bool resolver = pt < WS_UNIT;   // thread pt resolves entry pt of every unit
+  constexpr int NG = I8 ? 4 : 8;   // gather warps (int8 tables: the other four producer warps widen the values)
+  if (warp >= 12 && warp < 12 + NG) {
+    // ================================================================ row gathers
+    const int pt = tid - 384;             // threads 0-63 resolve entry pt of every unit
+    const bool resolver = pt < WS_UNIT;
     // Row metadata (list id -> row -> dequantisation scale) is a chain of dependent global loads, run as a
     // pipeline, one stage per unit, so that nobody waits on it: stage A fetches the list id, stage B turns it
     // into the row and fetches the scale; the last stage publishes both in shared memory two units before they
-    // are needed (and, for int8 tables, starts the row's copy).
+    // are needed.
     auto fetch_id = [&](int U) -> int32_t {   // -1: no compressed row behind this slot
       if (!resolver || U >= nunits) return -1;
       const int e = e_lo + U * WS_UNIT + pt;
@@ -433,26 +419,12 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
       if (resolver && U < nunits) mi->row_ref[U & (kRing - 1)][pt] = ref;
     };
     auto publish_scale = [&](int U, float rs) {
-      if (resolver && U < nunits) mi->row_scale[U & (kRing - 1)][pt] = rs;
+      if (I8 && resolver && U < nunits) mi->row_scale[U & (kRing - 1)][pt] = rs;
     };
-    // int8 tables: one bulk copy brings this thread's row of unit U into the staging ring (nothing to bring:
-    // a plain arrival, and the widening warps write zeros)
-    auto start_copy = [&](int U, uint32_t ref) {
-      if (!resolver || U >= nunits) return;
-      uint64_t* bar = &mi->st_full[U & 1];
-      if (ref != kNoRow) {
-        const uint8_t* src = reinterpret_cast<const uint8_t*>((ref >> 31) ? p.raw_kv : p.comp_kv) +
-                             (int64_t)(ref & 0x7FFFFFFFu) * p.Dqk;
-        ptx::mbar_expect_tx(bar, (uint32_t)p.Dqk);
-        ptx::bulk_load_1d(smem + L.st_off[U & 1] + (size_t)pt * L.st_stride, src, (uint32_t)p.Dqk, bar);
-      } else {
-        ptx::mbar_arrive(bar);
-      }
-    };
-    int32_t id_a = -1;          // stage A result: list id of this thread's entry of unit u + 3
-    uint32_t src_b = kNoRow;    // stage B result: row and scale of this thread's entry of unit u + 2
+    int32_t id_a = -1;          // stage A result: list id of this thread's entry of unit v + 3
+    uint32_t src_b = kNoRow;    // stage B result: row and scale of this thread's entry of unit v + 2
     float rs_b = 1.f;
-    float rs0 = 1.f, rs1 = 1.f;   // scales of units 0 and 1: published inside the first step, behind the row traffic
+    float rs0 = 1.f, rs1 = 1.f;   // scales of units 0 and 1: published behind the first gathers
     if (pt == 0) TRS(14, 0);
     if (nunits > 0) {
       const int32_t i0 = fetch_id(0), i1 = fetch_id(1), i2 = fetch_id(2);
@@ -460,160 +432,203 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
       uint32_t s0, s1;
       fetch_row(0, i0, s0, rs0);
       fetch_row(1, i1, s1, rs1);
-      if (I8) {
-        start_copy(0, s0);
-        start_copy(1, s1);
-      }
-      if (pt == 0) TRS(14, 1);
       fetch_row(2, i2, src_b, rs_b);
       publish_ref(0, s0);
       publish_ref(1, s1);
     }
-    if (pt == 0) TRS(14, 2);
-    group_sync(3, 256);
+    group_sync(5, NG * 32);
     if (pt == 0) TRS(14, 3);
-
+    for (int v = 0; v < nunits; ++v) {
+      const int buf = v & 1, slot = v & (kRing - 1);
+      if (pt == 0) TRS(0, v);
+      if (I8 && v >= 2) {
+        // row buffer `buf` is free once the widening warps and the logit MMAs of unit v - 2 have read it
+        ptx::mbar_wait(&mi->k_free[buf], sphase(v - 2), abort_flag);
+        ptx::mbar_wait(&mi->s_ready[buf], sphase(v - 2), abort_flag);
+      }
+      if (pt == 0) TRS(1, v);
+      // Unit v into row buffer v & 1, slab by slab (so that the logit MMAs of the first slabs can start while the
+      // later ones travel); a thread owns (slab, group of four rows) pairs; rows without data are fetched from
+      // row -1 (zeros).
+      uint8_t* rb = smem + (I8 ? L.kb_off[buf] : L.ub_off[buf]);
+      if (pt == 0)
+        for (int sl = 0; sl < nrs; ++sl)
+          ptx::mbar_expect_tx(&mi->full[buf][sl], (uint32_t)((I8 && sl == L.n128) ? WS_UNIT * 64 : WS_SLAB));
+      // (One TMA operation per instruction, a lane at a time, was measured three times slower: the operations of
+      // one warp-wide instruction pipeline, separate instructions of a warp do not.)
+      for (int i = pt; i < 16 * nrs; i += NG * 32) {
+        const int sl = i >> 4, r0 = (i & 15) * 4;
+        if (!I8 && v >= 2) wait_pv_slab(v - 2, sl);   // this slab has been multiplied by P V of unit v - 2
+        uint32_t ref[4];
+        bool from_raw = false;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          ref[j] = mi->row_ref[slot][r0 + j];
+          if (ref[j] != kNoRow && (ref[j] >> 31)) from_raw = true;
+        }
+        int32_t y[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) y[j] = ref[j] != kNoRow ? (int32_t)(ref[j] & 0x7FFFFFFFu) : -1;
+        if (I8 && sl == L.n128)
+          ptx::tma_gather4_2d(rb + (size_t)sl * WS_SLAB + (size_t)r0 * 64, from_raw ? &tm_raw_tail : &tm_comp_tail,
+                              &mi->full[buf][sl], sl * 128, y[0], y[1], y[2], y[3]);
+        else
+          ptx::tma_gather4_2d(rb + (size_t)sl * WS_SLAB + (size_t)r0 * 128, from_raw ? &tm_raw : &tm_comp,
+                              &mi->full[buf][sl], I8 ? sl * 128 : sl * 64, y[0], y[1], y[2], y[3]);
+      }
+      if (pt == 0) TRS(2, v);
+      if (I8 && v == 0 && resolver) {
+        publish_scale(0, rs0);
+        publish_scale(1, rs1);
+        ptx::mbar_arrive(&mi->meta_ready);
+      }
+      // a metadata slot is rewritten six units after its unit: that unit's softmax is long over, because the
+      // buffer wait above implies that the softmax of unit v - 4 has started
+      publish_ref(v + 2, src_b);
+      publish_scale(v + 2, rs_b);
+      fetch_row(v + 3, id_a, src_b, rs_b);
+      id_a = fetch_id(v + 4);
+      group_sync(5, NG * 32);
+    }
+  } else if (warp >= 12 + NG) {
+    // ================================================================ widening (warps 16-19, int8 tables)
+    // The int8 rows land in operand layout and feed the logit MMAs as they are; only the values need 16-bit
+    // operands.  An item = 8 rows x the 64 features of one fp16 slab = one warp instruction of 16-byte chunks
+    // (lane = row % 8 + 8 * chunk): the rows have 8 different swizzle phases, so the 128-bit shared-memory loads
+    // and stores are conflict-free.  Warp cw takes the items cw, cw + 4, ... in slab order, eight at a time (a
+    // half of the value width); a 128-feature block is announced as soon as every warp has stored its items of
+    // it, and may be overwritten as soon as the previous unit's P V has multiplied it.
     if constexpr (I8) {
-      // Widening, staging ring -> operand buffer.  One warp instruction covers 8 rows x 4 consecutive 16-byte
-      // chunks (lane = row % 8 + 8 * chunk) = the 64 features of one operand slab: the staging rows are
-      // Dqk + 16 bytes apart and the operand rows have 8 different swizzle phases, so the 128-bit shared-memory
-      // loads and stores are conflict-free.  Warp pw takes rows 8 pw .. 8 pw + 7, nine chunks per lane for a
-      // 576-byte row.  The slabs of a logit issuer are announced as soon as every warp has stored them.
-      const int nch = p.Dqk / 16;
+      const int cw = warp - (12 + NG);
       const int r8 = lane & 7, cl = lane >> 3;
-      const int rr = pw * 8 + r8;
-      uint8_t* drow = smem + L.ub_off[0] + (size_t)rr * 128;
+      const int nitems = (p.Dv / 64) * 8;   // (fp16 slab, group of 8 rows), slab-major
+      ptx::mbar_wait(&mi->q_ready, 0, abort_flag);   // q's scratch copy (in the value buffer) has been consumed
       for (int u = 0; u < nunits; ++u) {
-        const int slot = u & 1;
-        if (pt == 0) TRS(0, u);
-        ptx::mbar_wait(&mi->st_full[slot], (uint32_t)((u >> 1) & 1), abort_flag);      // the rows have landed
-        if (pt == 0) TRS(1, u);
-        if (u == 0) {
-          publish_scale(0, rs0);
-          publish_scale(1, rs1);
-        }
-        const bool valid = mi->row_ref[u & (kRing - 1)][rr] != kNoRow;
-        const uint8_t* srow = smem + L.st_off[slot] + (size_t)rr * L.st_stride;
-        uint4 v[WS_MAX_SLABS];   // this lane's chunks, read while the previous unit's P V still owns the operand buffer
+        const int buf = u & 1;
+        for (int sl = 0; sl < n_mt; ++sl) ptx::mbar_wait(&mi->full[buf][sl], sphase(u), abort_flag);   // the value features have landed
+        if (cw == 0) TRS(13, u);
+        for (int it0 = 0; it0 < nitems; it0 += 32) {
+          uint4 v[8];
+          if (cw == 0) TRS(16 + (it0 >> 5) * 4, u);
 #pragma unroll
-        for (int i = 0; i < WS_MAX_SLABS; ++i) {
-          const int c = i * 4 + cl;
-          v[i] = make_uint4(0, 0, 0, 0);
-          if (valid && c < nch) v[i] = *reinterpret_cast<const uint4*>(srow + c * 16);
-        }
-        int grp = 0;
+          for (int j = 0; j < 8; ++j) {
+            const int it = it0 + cw + 4 * j;
+            v[j] = make_uint4(0, 0, 0, 0);
+            if (it < nitems) {
+              const int i = it >> 3, rr = (it & 7) * 8 + r8;
+              v[j] = *reinterpret_cast<const uint4*>(smem + L.kb_off[buf] + (size_t)(i >> 1) * WS_SLAB + (size_t)rr * 128 +
+                                                     ((((i & 1) * 4 + cl) ^ r8) << 4));
+            }
+          }
+          if (it0 + 32 >= nitems) {
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&mi->k_free[buf]);   // this warp has read what it needs of the row buffer
+          }
+          if (cw == 0) TRS(17 + (it0 >> 5) * 4, u);
 #pragma unroll
-        for (int i = 0; i < WS_MAX_SLABS; ++i) {
-          if (i < nslab) {
-            if (u >= 1 && (i == 2 * n_mt || (i < 2 * n_mt && (i & 1) == 0))) wait_pv_slab(u - 1, i);   // slab pair free
-            if (pt == 0 && i == 0) TRS(13, u);
-            uint4 lo, hi;
-            widen_i8x16_f16(v[i], lo, hi);   // zero bytes (no row) widen to 0.0
-            uint8_t* d = drow + (size_t)i * WS_SLAB;
-            *reinterpret_cast<uint4*>(d + (((2 * cl) ^ r8) << 4)) = lo;
-            *reinterpret_cast<uint4*>(d + (((2 * cl + 1) ^ r8) << 4)) = hi;
-            while (grp < NQK && i + 1 == slab_lo(grp + 1)) {   // the last slab of issuer grp (empty shares pass through)
-              if (slab_lo(grp + 1) > slab_lo(grp)) {
+          for (int j = 0; j < 8; ++j) {
+            const int it = it0 + cw + 4 * j;
+            if (it < nitems) {
+              const int i = it >> 3, rr = (it & 7) * 8 + r8, blk = i >> 1;
+              // once per block (this warp's items of a block are consecutive): the previous unit's P V has read it
+              if (u >= 1 && (it - 4 < 0 || ((it - 4) >> 4) != blk)) wait_pv_block(u - 1, blk);
+              uint4 lo, hi;
+              widen_i8x16_f16(v[j], lo, hi);   // zero rows (no data) widen to 0.0
+              uint8_t* d = smem + L.ub_off[0] + (size_t)i * WS_SLAB + (size_t)rr * 128;
+              *reinterpret_cast<uint4*>(d + (((2 * cl) ^ r8) << 4)) = lo;
+              *reinterpret_cast<uint4*>(d + (((2 * cl + 1) ^ r8) << 4)) = hi;
+              const int nxt = it + 4;
+              if (nxt >= nitems || (nxt >> 4) != blk) {   // this warp's last item of the block
+                if (cw == 0) TRS(24 + blk, u);
                 ptx::fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(&mi->full[0][grp]);
+                if (lane == 0) ptx::mbar_arrive(&mi->v_full[blk]);
+                if (cw == 0) TRS(18 + (blk & 1) + (blk >> 1) * 4, u);
               }
-              ++grp;
             }
           }
         }
-        if (pt == 0) TRS(2, u);
-        group_sync(3, 256);   // every warp is done with the staging buffer: the rows of unit u + 2 may land in it
-        publish_ref(u + 2, src_b);
-        publish_scale(u + 2, rs_b);
-        start_copy(u + 2, src_b);
-        fetch_row(u + 3, id_a, src_b, rs_b);
-        id_a = fetch_id(u + 4);
-      }
-    } else {
-      // 16-bit tables need no widening: TMA row gathers write the operand layout directly.  A thread owns
-      // (slab, group of four rows) pairs, slab by slab, so that the logit MMAs of the first slabs can start
-      // while the later ones travel; rows without data are fetched from row -1 (zeros).
-      for (int u = 0; u < nunits; ++u) {
-        const int buf = u & 1, slot = u & (kRing - 1);
-        uint8_t* ub = smem + L.ub_off[buf];
-        if (pt == 0) TRS(0, u);
-        // the row metadata slot written below was last read for unit u - 2, whose softmax is over once its first
-        // value block has been multiplied
-        if (u >= 2) wait_pv_block(u - 2, 0);
-        if (pt == 0) TRS(1, u);
-        publish_ref(u + 2, src_b);
-        fetch_row(u + 3, id_a, src_b, rs_b);
-        id_a = fetch_id(u + 4);
-        if (pt == 0)
-          for (int kb = 0; kb < nslab; ++kb) ptx::mbar_expect_tx(&mi->full[buf][kb], (uint32_t)WS_SLAB);
-        for (int i = pt; i < 16 * nslab; i += 256) {
-          const int sl = i >> 4, r0 = (i & 15) * 4;
-          if (u >= 2) wait_pv_slab(u - 2, sl);   // this slab of the buffer has been multiplied by P V of unit u - 2
-          uint32_t ref[4];
-          bool from_raw = false;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            ref[j] = mi->row_ref[slot][r0 + j];
-            if (ref[j] != kNoRow && (ref[j] >> 31)) from_raw = true;
-          }
-          int32_t y[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) y[j] = ref[j] != kNoRow ? (int32_t)(ref[j] & 0x7FFFFFFFu) : -1;
-          ptx::tma_gather4_2d(ub + (size_t)sl * WS_SLAB + (size_t)r0 * 128, from_raw ? &tm_raw : &tm_comp,
-                              &mi->full[buf][sl], sl * 64, y[0], y[1], y[2], y[3]);
-        }
-        if (pt == 0) TRS(2, u);
-        group_sync(3, 256);
+        if (cw == 0) TRS(15, u);
       }
     }
-  } else if (warp >= 8 && warp < W_PV) {
+  } else if (warp == 8 || warp == 9) {
     // ================================================================ S^T = Kunit . Q^T issuers
-    // Issuer j accumulates its share of the feature slabs into an accumulator of its own; the softmax adds them.
     if (lane == 0) {
       const int j = warp - 8;
-      const int kb_lo = slab_lo(j), kb_hi = slab_lo(j + 1);
-      const uint32_t idesc_s = ptx::idesc_f16(fmt, fmt, WS_UNIT, WS_HEADS, 0, 0);
-      const uint64_t q_desc = ptx::smem_desc_sw128(ptx::smem_u32(q_s), 16, 1024);
       ptx::mbar_wait(&mi->q_ready, 0, abort_flag);   // also when there is no unit: q has landed before the CTA exits
-      for (int u = 0; u < nunits; ++u) {
-        const int buf = xbuf(u);
-        const uint64_t k_desc = ptx::smem_desc_sw128(ptx::smem_u32(smem + L.ub_off[buf]), 16, 1024);
-        const uint32_t d = tmem_base + (uint32_t)((I8 ? 0 : buf * 128) + j * WS_HEADS);
-        if (prev_use(u) >= 0) ptx::mbar_wait(&mi->s_free[buf], xphase(prev_use(u)), abort_flag);   // S^T has been read
-        if (I8 && kb_hi > kb_lo) ptx::mbar_wait(&mi->full[0][j], xphase(u), abort_flag);
-        for (int kb = kb_lo; kb < kb_hi; ++kb) {
-          if (!I8) ptx::mbar_wait(&mi->full[buf][kb], xphase(u), abort_flag);   // each slab as soon as it has landed
-          ptx::tc_fence_after_sync();
-          if (kb == kb_lo && j == 0) TRS(3, u);
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            ptx::mma_f16_ss(d, ptx::desc_advance(k_desc, kb * WS_SLAB + ks * 32),
-                            ptx::desc_advance(q_desc, kb * WS_SLAB + ks * 32), idesc_s, (kb > kb_lo || ks) ? 1u : 0u);
+      if constexpr (I8) {
+        // int8 x int8 -> int32, K = 32 per instruction, N = 128 = the hi and lo planes of q.  Issuer j takes the
+        // units of parity j, whole.
+        const uint32_t idesc_s = ptx::idesc_i8(WS_UNIT, 2 * WS_HEADS, 1, 1);
+        const uint32_t q_addr = ptx::smem_u32(q_s), k_addr = ptx::smem_u32(smem + L.kb_off[j]);
+        const uint32_t d = tmem_base + (uint32_t)(j * 128);
+        for (int u = j; u < nunits; u += 2) {
+          if (u >= 2) ptx::mbar_wait(&mi->s_free[j], sphase(u - 2), abort_flag);   // S^T(u - 2) has been read
+          for (int sl = 0; sl < nrs; ++sl) {
+            ptx::mbar_wait(&mi->full[j][sl], sphase(u), abort_flag);   // each slab as soon as it has landed
+            ptx::tc_fence_after_sync();
+            if (sl == 0) TRS(3, u);
+            const bool tail = sl == L.n128;
+            const uint64_t ka = tail ? ptx::smem_desc(k_addr + sl * WS_SLAB, 16, 512, 4)
+                                     : ptx::smem_desc_sw128(k_addr + sl * WS_SLAB, 16, 1024);
+            const uint64_t qb = tail ? ptx::smem_desc(q_addr + sl * 2 * WS_SLAB, 16, 512, 4)
+                                     : ptx::smem_desc_sw128(q_addr + sl * 2 * WS_SLAB, 16, 1024);
+            for (int ks = 0; ks < (tail ? 2 : 4); ++ks)
+              ptx::mma_i8_ss(d, ptx::desc_advance(ka, ks * 32), ptx::desc_advance(qb, ks * 32), idesc_s,
+                             (sl | ks) ? 1u : 0u);
+          }
+          ptx::mma_commit(&mi->s_ready[j]);
+          TRS(4, u);
         }
-        ptx::mma_commit(&mi->s_ready[buf]);
-        if (j == 0) TRS(4, u);
+      } else {
+        // Issuer j accumulates its half of the feature slabs of every unit into an accumulator of its own.
+        const int kb_lo = slab_lo(j), kb_hi = slab_lo(j + 1);
+        const uint32_t idesc_s = ptx::idesc_f16(fmt, fmt, WS_UNIT, WS_HEADS, 0, 0);
+        const uint64_t q_desc = ptx::smem_desc_sw128(ptx::smem_u32(q_s), 16, 1024);
+        for (int u = 0; u < nunits; ++u) {
+          const int buf = sbuf(u);
+          const uint64_t k_desc = ptx::smem_desc_sw128(ptx::smem_u32(smem + L.ub_off[buf]), 16, 1024);
+          const uint32_t d = tmem_base + (uint32_t)(buf * 128 + j * WS_HEADS);
+          if (u >= 2) ptx::mbar_wait(&mi->s_free[buf], sphase(u - 2), abort_flag);   // S^T(u - 2) has been read
+          for (int kb = kb_lo; kb < kb_hi; ++kb) {
+            ptx::mbar_wait(&mi->full[buf][kb], sphase(u), abort_flag);   // each slab as soon as it has landed
+            ptx::tc_fence_after_sync();
+            if (kb == kb_lo && j == 0) TRS(3, u);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+              ptx::mma_f16_ss(d, ptx::desc_advance(k_desc, kb * WS_SLAB + ks * 32),
+                              ptx::desc_advance(q_desc, kb * WS_SLAB + ks * 32), idesc_s, (kb > kb_lo || ks) ? 1u : 0u);
+          }
+          ptx::mma_commit(&mi->s_ready[buf]);
+          if (j == 0) TRS(4, u);
+        }
       }
     }
-  } else if (warp >= W_PV && warp < W_PROD) {
+  } else if (warp == 10 || warp == 11) {
     // ================================================================ O^T += Vunit^T . P^T issuers
-    const int mt = warp - W_PV;
-    if (lane == 0 && mt < n_mt) {
+    const int mt0 = (warp - 10) * 2;
+    if (lane == 0 && mt0 < n_mt) {
       const uint32_t idesc_o = ptx::idesc_f16(fmt, fmt, 128, WS_HEADS, 1, 0);   // A read MN-major
       for (int u = 0; u < nunits; ++u) {
-        const int buf = xbuf(u);
+        const int buf = pbuf(u);
         // A, MN-major: 64-feature blocks 8 KB apart (LBO), 8-row groups 1 KB apart (SBO); 16 rows per K step
         const uint64_t v_desc = ptx::smem_desc_sw128(ptx::smem_u32(smem + L.ub_off[buf]), WS_SLAB, 1024);
         const uint64_t pt_desc = ptx::smem_desc_sw128(ptx::smem_u32(smem + L.pt_off[buf]), 16, 1024);
-        ptx::mbar_wait(&mi->p_ready[buf], xphase(u), abort_flag);
+        ptx::mbar_wait(&mi->p_ready[buf], pphase(u), abort_flag);
         ptx::tc_fence_after_sync();
-        if (warp == W_PV) TRS(9, u);
+        if (warp == 10) TRS(9, u);
+        for (int mt = mt0; mt < mt0 + 2 && mt < n_mt; ++mt) {
+          if (I8) {
+            ptx::mbar_wait(&mi->v_full[mt], (uint32_t)(u & 1), abort_flag);   // this block has been widened
+            ptx::tc_fence_after_sync();
+          }
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          ptx::mma_f16_ss(tmem_o + (uint32_t)(mt * WS_HEADS), ptx::desc_advance(v_desc, (2 * mt) * WS_SLAB + ks * 2048),
-                          ptx::desc_advance(pt_desc, ks * 32), idesc_o, (u > 0 || ks > 0) ? 1u : 0u);
-        ptx::mma_commit(&mi->pv_blk[buf][mt]);
-        if (warp == W_PV) TRS(10, u);
+          for (int ks = 0; ks < 4; ++ks)
+            ptx::mma_f16_ss(tmem_o + (uint32_t)(mt * WS_HEADS), ptx::desc_advance(v_desc, (2 * mt) * WS_SLAB + ks * 2048),
+                            ptx::desc_advance(pt_desc, ks * 32), idesc_o, (u > 0 || ks > 0) ? 1u : 0u);
+          ptx::mma_commit(&mi->pv_blk[buf][mt]);
+        }
+        if (warp == 10) TRS(10, u);
       }
     }
   } else {
@@ -627,97 +642,103 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
     const int col0 = cset * 32 + ch * 16;      // first head of this thread
     const uint32_t lane_off = (uint32_t)(wq * 32) << 16;
 
-    // q: finish the operand (register path: convert and store; TMA path: wait, convert in place if needed)
-    if (q_regs) {
-      if (q_fast) {
-        store_q_pass(0);
-        for (int pass = 1; pass * kQB * 256 < n_items; ++pass) {
-          load_q_pass(pass);
-          store_q_pass(pass);
+    // ---- q: finish the operand
+    if (p.q_tma) ptx::mbar_wait(&mi->q_full, 0, abort_flag);
+    if constexpr (I8) {
+      // Per head h: step_h = 2^(e - 13) with 2^e <= max |q[h, :]| < 2^(e + 1); Q = round(q / step_h), |Q| <= 2^14;
+      // Q = 256 hi + lo with lo in [-128, 127].  Rows h (hi) and 64 + h (lo) of the B operand: 128-feature slabs of
+      // [128 rows x 128 B] with the 128-byte swizzle, the 64 tail features in [128 rows x 64 B] with the 64-byte one.
+      float amax = 0.f;
+      for (int i = tid; i < n_items; i += 256) {   // i % 64 = tid % 64: one head per thread
+        float f[8];
+        load_q_item(i, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+      }
+      atomicMax(&mi->q_amax[tid & (WS_HEADS - 1)], __float_as_uint(amax));
+      group_sync(4, 256);
+      const uint32_t abits = mi->q_amax[tid & (WS_HEADS - 1)];
+      const int ex = (int)(abits >> 23) - 127;   // floor(log2(max)); zeros and denormals: a harmless tiny step
+      const float step = abits == 0u ? 1.f : __uint_as_float((uint32_t)(max(ex - 13, -126) + 127) << 23);
+      const float inv_step = 1.f / step;
+      if (tid < WS_HEADS) mi->q_step[tid] = step;
+      for (int i = tid; i < n_items; i += 256) {
+        const int h = i & (WS_HEADS - 1), c = i >> 6;
+        float f[8];
+        load_q_item(i, f);
+        uint32_t hi_w[2] = {0u, 0u}, lo_w[2] = {0u, 0u};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          int Q = __float2int_rn(f[e] * inv_step);
+          Q = max(-16384, min(16384, Q));
+          const int hi = (Q + 128) >> 8;
+          const int lo = Q - (hi << 8);
+          hi_w[e >> 2] |= (uint32_t)(hi & 0xff) << (8 * (e & 3));
+          lo_w[e >> 2] |= (uint32_t)(lo & 0xff) << (8 * (e & 3));
         }
-      } else {
-        for (int i = tid; i < n_items; i += 256) {   // fp32 q, unaligned q
-          const int h = i & (WS_HEADS - 1), c = i >> 6;
-          float f[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] = 0.f;
-          if (h < p.H) {
-            const int64_t base = (int64_t)b * p.q_sb + (int64_t)h * p.q_sh + (int64_t)t * p.q_st + c * 8;
-            if (q_vec) {
-              if constexpr (QT == MXB_F32) {
-                const float4 a = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + base));
-                const float4 bq = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + base) + 1);
-                f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = bq.x; f[5] = bq.y; f[6] = bq.z; f[7] = bq.w;
-              } else {
-                const uint4 u4 = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.q) + base));
-                unpack16<QT>(u4, f);
-              }
-            } else {
-#pragma unroll
-              for (int e = 0; e < 8; ++e) f[e] = load_elem<QT>(p.q, base + e);
-            }
-          }
-          store_q_item(i, f);
+        const int f0 = c * 8;
+        if (f0 < L.n128 * 128) {
+          uint8_t* base = q_s + (size_t)(f0 >> 7) * 2 * WS_SLAB + (f0 & 8);
+          const int ck = (f0 & 127) >> 4;
+          *reinterpret_cast<uint2*>(base + (size_t)h * 128 + ((ck ^ (h & 7)) << 4)) = make_uint2(hi_w[0], hi_w[1]);
+          *reinterpret_cast<uint2*>(base + (size_t)(64 + h) * 128 + ((ck ^ (h & 7)) << 4)) = make_uint2(lo_w[0], lo_w[1]);
+        } else {
+          const int bb = f0 - L.n128 * 128;
+          uint8_t* base = q_s + (size_t)L.n128 * 2 * WS_SLAB + (bb & 8);
+          const int ck = bb >> 4;
+          *reinterpret_cast<uint2*>(base + (size_t)h * 64 + ((ck ^ ((h >> 1) & 3)) << 4)) = make_uint2(hi_w[0], hi_w[1]);
+          *reinterpret_cast<uint2*>(base + (size_t)(64 + h) * 64 + ((ck ^ (((64 + h) >> 1) & 3)) << 4)) =
+              make_uint2(lo_w[0], lo_w[1]);
         }
       }
-    } else {
-      ptx::mbar_wait(&mi->q_full, 0, abort_flag);
-      if constexpr (Q_CONVERT) {
-        // bf16 -> fp16 in place, element by element (the swizzled position of a chunk does not change);
-        // exact for magnitudes in [2^-14, 65504], which is where the reference's fp16 q lives as well
-        for (int i = tid; i < nslab * (WS_SLAB / 16); i += 256) {
-          uint4* cell = reinterpret_cast<uint4*>(q_s) + i;
-          uint4 x = *cell;
-          uint32_t* w = reinterpret_cast<uint32_t*>(&x);
+    } else if (!p.q_tma) {
+      // [64 heads x Dqk] K-major, 128-byte swizzle, rounded to the operand type; a warp writes 32 different rows
+      for (int i = tid; i < n_items; i += 256) {
+        const int h = i & (WS_HEADS - 1), c = i >> 6;
+        float f[8];
+        load_q_item(i, f);
+        uint32_t w[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&w[e]));
-            const __half2 h2 = __floats2half2_rn(f.x, f.y);
-            w[e] = *reinterpret_cast<const uint32_t*>(&h2);
-          }
-          *cell = x;
+        for (int e = 0; e < 4; ++e) {
+          float b0, b1;
+          w[e] = pack_op16x2<BF16>(f[2 * e], f[2 * e + 1], b0, b1);
         }
+        *reinterpret_cast<uint4*>(q_s + (size_t)(c >> 3) * WS_SLAB + (size_t)h * 128 + (((c & 7) ^ (h & 7)) << 4)) =
+            make_uint4(w[0], w[1], w[2], w[3]);
       }
     }
     ptx::fence_proxy_async_smem();
     ptx::mbar_arrive(&mi->q_ready);
+    float qs[16];   // int8 tables: the fixed-point steps of this thread's heads
+    if constexpr (I8) {
+      ptx::mbar_wait(&mi->q_ready, 0, abort_flag);   // every step has been written
+#pragma unroll
+      for (int c = 0; c < 16; ++c) qs[c] = mi->q_step[col0 + c];
+    }
 
     float l1 = 0.f;   // row sum of head col0 + li over this warp's rows of all units
     for (int u = 0; u < nunits; ++u) {
-      const int buf = xbuf(u), slot = u & (kRing - 1);
-      ptx::mbar_wait(&mi->s_ready[buf], xphase(u), abort_flag);
+      const int sb_i = sbuf(u), pb_i = pbuf(u), slot = u & (kRing - 1);
+      ptx::mbar_wait(&mi->s_ready[sb_i], sphase(u), abort_flag);
       ptx::tc_fence_after_sync();
       if (warp == 0) TRS(5, u);
       uint32_t sv[16];
       {
-        // add the issuers' accumulators, two loads in flight at a time (issuers without a slab leave theirs untouched)
-        const uint32_t sa = tmem_base + lane_off + (uint32_t)((I8 ? 0 : buf * 128) + cset * 32);
+        // two accumulators per unit: the halves of the feature slabs (16-bit tables), or the digit planes of q
+        const uint32_t sa = tmem_base + lane_off + (uint32_t)(sb_i * 128 + cset * 32);
         uint32_t sb[16];
-        const bool has1 = slab_lo(2) > slab_lo(1);
         ptx::tmem_ld_16x32bx2_x16(sa, sv);
-        if (has1) ptx::tmem_ld_16x32bx2_x16(sa + (uint32_t)WS_HEADS, sb);
+        ptx::tmem_ld_16x32bx2_x16(sa + (uint32_t)WS_HEADS, sb);
         ptx::tmem_ld_wait();
-        if (has1) {
 #pragma unroll
-          for (int c = 0; c < 16; ++c) sv[c] = __float_as_uint(__uint_as_float(sv[c]) + __uint_as_float(sb[c]));
-        }
-        if constexpr (NQK == 4) {
-          const bool has2 = slab_lo(3) > slab_lo(2), has3 = slab_lo(4) > slab_lo(3);
-          uint32_t sc[16];
-          if (has2) ptx::tmem_ld_16x32bx2_x16(sa + (uint32_t)(2 * WS_HEADS), sb);
-          if (has3) ptx::tmem_ld_16x32bx2_x16(sa + (uint32_t)(3 * WS_HEADS), sc);
-          ptx::tmem_ld_wait();
-#pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            float x = __uint_as_float(sv[c]);
-            if (has2) x += __uint_as_float(sb[c]);
-            if (has3) x += __uint_as_float(sc[c]);
-            sv[c] = __float_as_uint(x);
-          }
+        for (int c = 0; c < 16; ++c) {
+          if constexpr (I8) sv[c] = __float_as_uint(fmaf((float)(int)sv[c], 256.f, (float)(int)sb[c]) * qs[c]);
+          else sv[c] = __float_as_uint(__uint_as_float(sv[c]) + __uint_as_float(sb[c]));
         }
       }
       ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(&mi->s_free[buf]);
+      ptx::mbar_arrive(&mi->s_free[sb_i]);
+      if (I8 && u == 0) ptx::mbar_wait(&mi->meta_ready, 0, abort_flag);   // the first scales are published behind the gathers
       const bool ok = mi->row_ref[slot][row] != kNoRow;
       const float rs = I8 ? mi->row_scale[slot][row] : 1.f;
       const float mul = scale_log2 * rs;
@@ -784,9 +805,10 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
       }
       if (warp == 0) TRS(7, u);
       // ---- P^T (16-bit, K-major, swizzled) and the row sums
+      if (I8 && u >= 1) wait_pv_all(u - 1);   // the one P^T buffer has been read by the previous unit's P V
       {
         const float inv = I8 ? __frcp_rn(rs) : 1.f;
-        uint8_t* pbase = smem + L.pt_off[buf] + (row & 7) * 2;
+        uint8_t* pbase = smem + L.pt_off[pb_i] + (row & 7) * 2;
         const int cj = row >> 3;
 #pragma unroll
         for (int c = 0; c < 16; c += 2) {   // two heads per step: one packed conversion each way
@@ -809,7 +831,7 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
       if (warp == 0) TRS(12, u);
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(&mi->p_ready[buf]);
+      ptx::mbar_arrive(&mi->p_ready[pb_i]);
       if (warp == 0) TRS(8, u);
       // Sum over the 16 rows of this half warp, behind the hand-off: at each step a lane keeps half of its
       // columns and hands the other half to its partner, so 15 shuffles leave lane li with column li.
@@ -935,14 +957,18 @@ int sparse_tc_splits(int B, int T, int H, int k, int raw_cap, int requested) {
   return (int)want;
 }
 
-// Tensor map over a [rows, Dqk] table of 16-bit values for row gathers: box = one 128-byte slab of one row.  The
-// row extent is left open (the caller's ids are what bounds the reads); row -1 is the zero row.
-static int row_gather_map(CUtensorMap* out, const void* table, int Dqk, bool bf16) {
+// Tensor map over a [rows, Dqk] table for row gathers: box = `box_elems` features of one row (one shared-memory
+// slab row).  The row extent is left open (the caller's ids are what bounds the reads); row -1 is the zero row.
+static int row_gather_map(CUtensorMap* out, const void* table, int Dqk, int kv_dtype, int box_elems) {
+  const int esz = kv_dtype == MXB_I8 ? 1 : 2;
   const uint64_t dims[2] = {(uint64_t)Dqk, (uint64_t)0x7FFFFFFF};
-  const uint64_t strides[1] = {(uint64_t)Dqk * 2};
-  const uint32_t box[2] = {64, 1};
-  return make_tensor_map(out, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, table, dims,
-                         strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  const uint64_t strides[1] = {(uint64_t)Dqk * esz};
+  const uint32_t box[2] = {(uint32_t)box_elems, 1};
+  const CUtensorMapDataType dt = kv_dtype == MXB_I8     ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : kv_dtype == MXB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                        : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  return make_tensor_map(out, dt, 2, table, dims, strides, box,
+                         box_elems * esz == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
 }
 
 // Tensor map over q [B, H, T, Dqk] (any strides on the first three axes) whose box is the 64 heads x 64 features
@@ -988,24 +1014,33 @@ static bool q_tile_map(CUtensorMap* out, SparseParams& p, bool bf16) {
 template <int KVT, int QT>
 static int launch_tc_typed(SparseParams& p, int out_dtype, cudaStream_t st) {
   constexpr bool I8 = (KVT == MXB_I8);
-  const int smem = ws_layout(p.Dqk, p.Dv, I8).total + 1024;
-  CUtensorMap tm_comp, tm_raw, tm_q;
+  const WsLayout L = ws_layout(p.Dqk, p.Dv, I8);
+  const int smem = L.total + 1024;
+  CUtensorMap tm_comp, tm_raw, tm_comp_tail, tm_raw_tail, tm_q;
   memset(&tm_comp, 0, sizeof(tm_comp));
   memset(&tm_raw, 0, sizeof(tm_raw));
+  memset(&tm_comp_tail, 0, sizeof(tm_comp_tail));
+  memset(&tm_raw_tail, 0, sizeof(tm_raw_tail));
   memset(&tm_q, 0, sizeof(tm_q));
-  if (!I8) {
-    const void* comp = p.comp_kv ? p.comp_kv : p.raw_kv;
-    MXB_REQUIRE(comp != nullptr || p.k + p.raw_cap == 0, MXB_ERR_INVALID, "sparse attention: no KV table");
-    if (comp) {
-      int rc = row_gather_map(&tm_comp, comp, p.Dqk, KVT == MXB_BF16);
+  const void* comp = p.comp_kv ? p.comp_kv : p.raw_kv;
+  const void* raw = p.raw_kv ? p.raw_kv : comp;
+  MXB_REQUIRE(comp != nullptr || p.k + p.raw_cap == 0, MXB_ERR_INVALID, "sparse attention: no KV table");
+  if (comp) {
+    const int box = I8 ? 128 : 64;   // one 128-byte slab row
+    int rc = row_gather_map(&tm_comp, comp, p.Dqk, KVT, I8 && p.Dqk < 128 ? 64 : box);
+    if (rc != MXB_OK) return rc;
+    rc = row_gather_map(&tm_raw, raw, p.Dqk, KVT, I8 && p.Dqk < 128 ? 64 : box);
+    if (rc != MXB_OK) return rc;
+    if (I8 && L.tail) {
+      rc = row_gather_map(&tm_comp_tail, comp, p.Dqk, KVT, 64);
       if (rc != MXB_OK) return rc;
-      rc = row_gather_map(&tm_raw, p.raw_kv ? p.raw_kv : comp, p.Dqk, KVT == MXB_BF16);
+      rc = row_gather_map(&tm_raw_tail, raw, p.Dqk, KVT, 64);
       if (rc != MXB_OK) return rc;
     }
   }
-  // a 16-bit q lands by TMA: as it is when it has the operand type, converted in place for a bf16 q over int8 rows
+  // a 16-bit q lands by TMA (int8 tables: into the value buffer, when that is large enough to hold it)
   p.q_tma = 0;
-  if (QT == MXB_BF16 || QT == MXB_F16) p.q_tma = q_tile_map(&tm_q, p, QT == MXB_BF16) ? 1 : 0;
+  if ((QT == MXB_BF16 || QT == MXB_F16) && (!I8 || L.qtmp_off >= 0)) p.q_tma = q_tile_map(&tm_q, p, QT == MXB_BF16) ? 1 : 0;
   const int64_t ctas = (int64_t)p.B * p.T * p.nsplit;
   MXB_REQUIRE(ctas <= 0x7FFFFFFFll, MXB_ERR_INVALID, "sparse attention: too many (batch, token, split) items");
   dim3 grid((unsigned)ctas);
@@ -1013,7 +1048,7 @@ static int launch_tc_typed(SparseParams& p, int out_dtype, cudaStream_t st) {
   {                                                                                                  \
     auto kern = sparse_attn_tc_kernel<KVT, QT, OT>;                                                  \
     MXB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));      \
-    kern<<<grid, ws_threads(I8), smem, st>>>(p, tm_comp, tm_raw, tm_q);                                  \
+    kern<<<grid, WS_THREADS, smem, st>>>(p, tm_comp, tm_raw, tm_comp_tail, tm_raw_tail, tm_q);       \
   }
   if (out_dtype == MXB_F32 || p.nsplit > 1 || p.partial_ml) MXB_TC(MXB_F32)
   else if (out_dtype == MXB_BF16) MXB_TC(MXB_BF16)
