@@ -1,26 +1,35 @@
 #!/usr/bin/env python
 """Benchmark of the sparse-decode attention hot path (and, as extras, the other configurations).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload ...]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Headline workload (N = 1): the batched DS-V4-shaped sparse decode step — batch 32,
-context ~ U[32K, 128K] per sequence, top-k 2048, bf16 queries over an int8 latent KV
-cache with per-token fp16 scales, FP8-E4M3 index keys, 64 heads x 576 (V = first 512),
-indexer 16 heads x 64, seed 1.  One "step" = indexer score -> top-k -> indexed sparse
-attention for the whole batch (one decoded token per sequence), so tokens/s = batch /
-step time.  With N > 1 every rank holds its own batch of 32 sequences (sequence
-sharding, no collective on the data path): weak scaling.
+Headline workload: the batched DS-V4-shaped sparse decode step — batch 32, context ~ U[32K, 128K] per
+sequence, top-k 2048, bf16 queries over an int8 latent KV cache with per-token fp16 scales, FP8-E4M3 index
+keys, 64 heads x 576 (V = first 512), indexer 16 heads x 64, seed 1.  One "step" = indexer score -> top-k ->
+indexed sparse attention for the whole batch (one decoded token per sequence), so tokens/s = batch / step
+time.  With N > 1 every rank holds its own batch of 32 sequences (sequence sharding, no collective on the
+data path): weak scaling.
 
-Prints ONE JSON line on rank 0.  `value` is timed with the inputs resident in HBM;
-`e2e` goes through the public Python operator with the step's inputs in pinned host
-memory and the result read back to the host inside the timed region.  The latent KV
-and index-key tables are the decode cache (state that lives on the device between
-steps, like weights); the per-step inputs are the queries, indexer queries and
-head weights.
+Prints ONE JSON line on rank 0.
+* `value` is timed with the inputs resident in HBM: windows of K steps (one CUDA graph per step) between two
+  CUDA events, repeated until the timed region is at least 250 ms; the median window is reported (the minimum
+  beside it), the maximum over ranks of every window.
+* `e2e` goes through the public Python operator with the step's inputs in pinned host memory and the result
+  read back to the host inside the timed region.  The latent KV and index-key tables are the decode cache
+  (state that lives on the device between steps, like weights); the per-step inputs are the queries, indexer
+  queries and head weights.
+* `roofline` describes the whole step: the bytes the step has to move (index keys once, the selected rows,
+  queries in, outputs out; scores are not counted because a fused selection need not materialise them) over
+  the step time, against the measured and the nominal HBM bandwidth; `extras.kernels` breaks it down.
+* `extras.c5a` / `extras.c5b` are the multi-GPU configurations: 256 sequences of 131072 rows dealt to the
+  ranks (strong scaling of one fixed batch, no collective), and one sequence of 1,048,576 rows range-sharded
+  over the ranks (two NCCL all-gathers and a log-sum-exp merge per step), checked bit for bit against the
+  single-GPU selection on rank 0.
 """
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import subprocess
@@ -36,6 +45,8 @@ sys.path.insert(0, ROOT)
 METRIC = "sparse_decode_attn_tokens_per_s"
 UNIT = "tokens/s"
 WORKLOAD = "c3_batched_sparse_decode_b32_ctx32k-128k_topk2048_int8kv_fp8idx"
+H, DQK, DV, HI, DI = 64, 576, 512, 16, 64
+MIN_TIMED_MS = 250.0
 
 
 def measured_peaks():
@@ -45,6 +56,22 @@ def measured_peaks():
             d = json.load(f)
         return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
     return 6650.0, 1590.0, "fallback"
+
+
+def workload_config(batch: int, rows_total: int, topk: int, world: int) -> dict:
+    """The `config` object; both arms print the same keys."""
+    return {"workload": WORKLOAD, "batch_per_gpu": batch, "rows_total_per_gpu": rows_total, "topk": topk,
+            "heads": H, "d_qk": DQK, "d_v": DV, "indexer": "16x64 fp8-e4m3 keys", "kv": "int8 + fp16 per-token scale",
+            "parallelism": f"sequence-sharded x{world}, no collective",
+            "l2": "inputs (1.7 GB per GPU) exceed L2, no flush needed"}
+
+
+def step_bytes(lens, k: int) -> int:
+    """Bytes one decode step has to move: every index key once, the selected int8 rows with their scales,
+    q and the indexer q in, the bf16 output out.  Scores are not counted (a fused selection keeps them on chip)."""
+    lens = np.asarray(lens, dtype=np.int64)
+    per_seq = lens * DI + min(k, int(lens.max())) * (DQK + 2) + H * DQK * 2 + H * DV * 2 + HI * DI * 2
+    return int(per_seq.sum())
 
 
 class ClockSampler:
@@ -61,7 +88,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -70,9 +97,10 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+            self.rows.append((time.time(), [x.strip() for x in line.split(",")]))
 
-    def stop(self) -> dict:
+    def stop(self, t_lo: float | None = None, t_hi: float | None = None) -> dict:
+        """Summary of the samples taken in [t_lo, t_hi] (all samples if the window holds none)."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -80,8 +108,10 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
+        inside = [r for ts, r in self.rows if t_lo is not None and t_lo <= ts <= t_hi]
+        rows = inside or [r for _, r in self.rows]
         sm, smax, reasons = [], [], set()
-        for r in self.rows:
+        for r in rows:
             try:
                 sm.append(float(r[1])); smax.append(float(r[2]))
             except Exception:
@@ -90,7 +120,7 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "samples_inside_timed_region": len(inside)}
 
 
 # --------------------------------------------------------------------------- #
@@ -131,9 +161,9 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "batch": B, "topk": int(c["k"]), "rows_total": int(c["lens"].sum())},
+        "config": workload_config(B, int(c["lens"].sum()), int(c["k"]), max(1, args.gpus)),
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": f"all {B} sequences of the batch per step, NumPy float32 (BLAS threads = {cores})"},
+                         "sample": f"all {B} sequences of one rank's batch per step, NumPy float32 (BLAS threads = {cores})"},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -150,7 +180,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-extras", action="store_true", help="skip the secondary workloads (c1, c2)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the secondary workloads (c1, c2, c4, c5)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of as a CUDA graph")
     ap.add_argument("--small", action="store_true", help="reduced sizes (for profiling captures only)")
@@ -164,21 +194,22 @@ def main():
 
     from moespresso_b200 import _abi, synth
     from moespresso_b200.deepseek_v4.attention import topk_select
-    from moespresso_b200.deepseek_v4.decode_step import LatentCache
+    from moespresso_b200.deepseek_v4.decode_step import LatentCache, SparseDecodePlan, sparse_decode_step
     from moespresso_b200.deepseek_v4.indexed_attention_kernel import indexer_scores, sparse_attention
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU path for the product kernels")
-    _abi.load()
+    lib = _abi.load()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     W = max(args.warmup, 3)
-    K = args.steps
+    K = max(args.steps, 1)
 
     if args.small:
         # 8 long sequences: index keys (~133 MB) still exceed L2, everything on the device stays under 2 GB
@@ -197,12 +228,9 @@ def main():
     iq_h = torch.from_numpy(c["idx_q"]).to(torch.bfloat16).pin_memory()
     iw_h = torch.from_numpy(c["idx_w"]).pin_memory()
     q_d, iq_d, iw_d = q_h.to(dev), iq_h.to(dev), iw_h.to(dev)
-    out_h = torch.empty((B, 64, d_v), dtype=torch.bfloat16).pin_memory()   # the step's result in the activation type
+    out_h = torch.empty((B, H, d_v), dtype=torch.bfloat16).pin_memory()   # the step's result in the activation type
 
-    from moespresso_b200 import _torchabi
-    from moespresso_b200.deepseek_v4.decode_step import SparseDecodePlan, sparse_decode_step
-
-    plan = SparseDecodePlan(cache, heads=64, d_qk=576, idx_heads=16, idx_dim=64, k=kk, scale=scale, d_v=d_v,
+    plan = SparseDecodePlan(cache, heads=H, d_qk=DQK, idx_heads=HI, idx_dim=DI, k=kk, scale=scale, d_v=d_v,
                             q_dtype=torch.bfloat16, out_dtype=torch.bfloat16, graph=not args.no_graph)
     plan.load_inputs(q_d, iq_d, iw_d)
 
@@ -211,30 +239,49 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def max_over_ranks(x: float) -> float:
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+    def max_over_ranks(xs):
+        t = torch.tensor(list(xs), dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(x) for x in t.tolist()]
+
+    def timed_windows(step, k_steps: int, min_ms: float, max_windows: int = 400):
+        """Windows of `k_steps` calls of `step` between two events, repeated until `min_ms` of timed region;
+        every rank runs the same number of windows.  Returns ms per step of every window (max over ranks)."""
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        ev[0].record()
+        for _ in range(k_steps):
+            step()
+        ev[1].record()
+        torch.cuda.synchronize()
+        first = max_over_ranks([ev[0].elapsed_time(ev[1])])[0]
+        n = int(min(max_windows, max(1, np.ceil(min_ms / max(first, 1e-3)))))
+        events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+        barrier()
+        for a, b in events:
+            a.record()
+            for _ in range(k_steps):
+                step()
+            b.record()
+        barrier()
+        return [x / k_steps for x in max_over_ranks([a.elapsed_time(b) for a, b in events])]
 
     sampler = ClockSampler(local)
     sampler.start()
     for _ in range(W):
         plan.launch()
     barrier()
-    # ---- timed region: K steps, inputs resident in HBM
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(K):
-        plan.launch()
-    e1.record()
-    barrier()
-    ms_step = max_over_ranks(e0.elapsed_time(e1) / K)
+    # ---- timed region: windows of K steps, inputs resident in HBM
+    t_lo = time.time()
+    windows = timed_windows(plan.launch, K, MIN_TIMED_MS)
+    t_hi = time.time()
+    ms_step = float(np.median(windows))
+    ms_min = float(np.min(windows))
 
-    # ---- per-stage device time: each entry point captured as its own CUDA graph and replayed K times between two
-    # events (no host gaps inside the timed region; the 167 MB key table alone exceeds L2 between replays)
-    lib = _abi.load()
+    # ---- per-stage device time: each entry point captured as its own CUDA graph and replayed between two events
+    # (no host gaps inside the timed region).  The index keys (167 MB) exceed L2 between replays; the attention
+    # stage replays the same ids, so its 38 MB of gathered rows stay L2-resident across replays, whereas inside
+    # the real step the key scan evicts them: stage times add up to a little less than the step.
     launches0 = int(lib.mxb_kernel_launches())
     out_e, ids_e, sc_e = sparse_decode_step(q_d, iq_d, iw_d, cache, k=kk, scale=scale, d_v=d_v, return_ids=True,
                                             return_scores=True, out_dtype=torch.bfloat16)
@@ -257,11 +304,11 @@ def main():
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        for _ in range(K):
+        for _ in range(5 * K):
             g.replay()
         b.record()
         torch.cuda.synchronize()
-        return a.elapsed_time(b) / K * 1e3
+        return a.elapsed_time(b) / (5 * K) * 1e3
 
     stage = {
         "indexer_scores": stage_us(lambda: indexer_scores(
@@ -280,64 +327,81 @@ def main():
     qv.copy_(q_h)
     iqv.copy_(iq_h)
     iwv.copy_(iw_h)
-    for _ in range(2):
-        out_h.copy_(plan.run_packed(in_h), non_blocking=True)
-    barrier()
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    f0.record()
-    for _ in range(K):
+
+    def e2e_step():
         out_h.copy_(plan.run_packed(in_h), non_blocking=True)
         torch.cuda.current_stream().synchronize()   # the caller consumes the result of every step
-    f1.record()
-    barrier()
-    ms_e2e = max_over_ranks(f0.elapsed_time(f1) / K)
-    # keep the device busy with the same step until the clock sampler has seen it under load
-    t_end = time.time() + 1.5
-    while time.time() < t_end and len(sampler.rows) < 8:
-        for _ in range(50):
-            plan.launch()
-        torch.cuda.synchronize()
-    clocks = sampler.stop()
-    if K * ms_step < 500:
-        clocks["note"] = ("timed region shorter than the 100 ms sampling period: samples span warm-up, the timed "
-                          "region and an untimed repeat of the same step")
+
+    for _ in range(2):
+        e2e_step()
+    e2e_windows = timed_windows(e2e_step, K, MIN_TIMED_MS)
+    ms_e2e = float(np.median(e2e_windows))
+    clocks = sampler.stop(t_lo, t_hi)
 
     hbm, tf, which = measured_peaks()
-    # algorithmic bytes of the dominant kernel (indexer score scan): FP8 keys read once, fp32 scores written once
-    idx_bytes = total * 64 + total * 4 + B * (16 * 64 * 2 + 16 * 4)
-    achieved = idx_bytes / (stage["indexer_scores"] * 1e-6) / 1e9
-    # DRAM traffic of the same kernel from one ncu capture on the --small case (profiles/): 65.0 B read and
-    # 4.8 B written per key row against 68 B algorithmic; scaled to this launch by its row count
-    traffic = total * (65.0 + 4.8)
-    step_bytes = idx_bytes + total * 4 + B * (kk * (576 + 2) + 64 * 576 * 2 + 64 * d_v * 2 + kk * 4 * 2)
+    # ---- roofline of the whole step (HBM-bound: key scan + row gather); per-kernel figures beside it
+    alg_bytes = step_bytes(c["lens"], kk)
+    achieved = alg_bytes / (ms_step * 1e-3) / 1e9
+    kbytes = {
+        # FP8 keys read once, fp32 scores written once
+        "indexer_scores": total * DI + total * 4 + B * (HI * DI * 2 + HI * 4),
+        # scores read once, ids written
+        "topk_select": total * 4 + B * kk * 4,
+        # selected int8 rows + scales, ids, q in, bf16 output out
+        "sparse_attn": B * (kk * (DQK + 2) + kk * 4 + H * DQK * 2 + H * d_v * 2),
+    }
+    kernels = {name: {"us": stage[name], "algorithmic_bytes": kbytes[name],
+                      "GBs": kbytes[name] / (stage[name] * 1e-6) / 1e9,
+                      "frac_of_measured_hbm": kbytes[name] / (stage[name] * 1e-6) / 1e9 / hbm}
+               for name in stage}
+    dominant = max(stage, key=stage.get)
+    kernel_names = {"indexer_scores": "indexer_decode_kernel<64, 16 heads>", "topk_select": "topk_cluster_kernel",
+                    "sparse_attn": "sparse_attn_tc_kernel<int8 kv, bf16 q> + merge_kernel"}
+    # DRAM traffic from ncu captures on the --small case (profiles/), scaled by the units each launch processes:
+    # the key scan reads 65.0 B and writes 4.8 B per key row; the attention kernel reads 787 B per gathered row
+    # (576-byte rows start at any 64-byte offset: sector rounding) plus q; the selection re-reads the scores
+    traffic = total * (65.0 + 4.8) + total * 4.0 + B * (kk * 787.0 + H * DQK * 2 + H * d_v * 2)
 
     line = {
         "metric": METRIC, "value": world * B / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K,
         "warmup": W, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD if not args.small else WORKLOAD + "_SMALL", "batch_per_gpu": B,
-                   "rows_total_per_gpu": total, "topk": kk, "heads": 64, "d_qk": 576, "d_v": d_v,
-                   "indexer": "16x64 fp8-e4m3 keys", "kv": "int8 + fp16 per-token scale",
-                   "parallelism": f"sequence-sharded x{world}, no collective",
-                   "l2": "inputs (1.7 GB per GPU) exceed L2, no flush needed"},
+        "config": workload_config(B, total, kk, world),
+        "timing": {"windows": len(windows), "steps_per_window": K, "timed_region_ms": float(np.sum(windows)) * K,
+                   "ms_per_step_median": ms_step, "ms_per_step_min": ms_min},
         "e2e": {"value": world * B / (ms_e2e * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": int(in_h.numel()),
-                "d2h_bytes_per_step": int(out_h.numel() * out_h.element_size()), "ms_per_step": ms_e2e},
-        "gpu_launches": kernels_per_step * K,
+                "d2h_bytes_per_step": int(out_h.numel() * out_h.element_size()), "ms_per_step": ms_e2e,
+                "windows": len(e2e_windows)},
+        "gpu_launches": kernels_per_step * K * len(windows),
         "launch": (f"one CUDA graph per step ({kernels_per_step} kernels of this library)" if not args.no_graph
                    else f"eager ({kernels_per_step} kernels of this library per step)"),
         "stage_us": stage,
-        "roofline": {"bound": "hbm", "kernel": "indexer_decode_kernel<64, 16 heads>", "achieved": achieved, "peak": hbm,
-                     "unit": "GB/s", "frac": achieved / hbm, "peak_source": which, "traffic": traffic,
-                     "algorithmic_bytes": idx_bytes, "launch_us": stage["indexer_scores"],
-                     "frac_of_nominal_8TBs": achieved / 8000.0,
-                     "whole_step_GBs": step_bytes / (ms_step * 1e-3) / 1e9},
+        "roofline": {"bound": "hbm", "kernel": kernel_names[dominant], "scope": "whole decode step",
+                     "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm, "peak_source": which,
+                     "traffic": traffic, "algorithmic_bytes": alg_bytes, "launch_us": ms_step * 1e3,
+                     "frac_of_nominal_8TBs": achieved / 8000.0},
         "clocks": clocks,
     }
+    if args.small:
+        line["config"]["workload"] = WORKLOAD + "_SMALL"
 
-    if rank == 0 and world == 1 and not args.no_extras and not args.small:
-        line["extras"] = run_extras(torch, dev, tf)
-    if rank == 0 and world == 1 and not args.no_cpu:
+    extras = {"kernels": kernels}
+    if not args.no_extras and not args.small:
+        del plan, cache
+        torch.cuda.empty_cache()
+        if rank == 0:
+            extras.update(run_extras(torch, dev, tf))
+        try:
+            extras["c5a"] = run_c5a(torch, dist, dev, rank, world, hbm, barrier, max_over_ranks)
+        except Exception as e:   # report, do not hide
+            extras["c5a_error"] = repr(e)
+        try:
+            extras["c5b"] = run_c5b(torch, dist, dev, rank, world, barrier, max_over_ranks)
+        except Exception as e:
+            extras["c5b_error"] = repr(e)
+    line["extras"] = extras
+    if rank == 0 and not args.no_cpu:
         cores = len(os.sched_getaffinity(0))
         seqs = list(range(B))
         t = cpu_decode_batch(c, seqs)
@@ -349,8 +413,134 @@ def main():
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------- #
+# multi-GPU configurations (also run at N = 1)
+# --------------------------------------------------------------------------- #
+
+def _device_tables(torch, dev, n_rows: int, seed: int):
+    """int8 latent rows, fp16 scales (log-uniform in [1e-3, 1e-1]) and FP8 index keys, generated on the device."""
+    g = torch.Generator(device=dev).manual_seed(seed)
+    kv = torch.randint(-127, 128, (n_rows, DQK), generator=g, device=dev, dtype=torch.int8)
+    u = torch.rand(n_rows, generator=g, device=dev)
+    scales = torch.exp(u * (np.log(1e-1) - np.log(1e-3)) + np.log(1e-3)).to(torch.float16)
+    keys = torch.empty((n_rows, DI), dtype=torch.float8_e4m3fn, device=dev)
+    step = 1 << 22
+    for lo in range(0, n_rows, step):   # in pieces: the fp32 normal draw of all keys at once would take 8.6 GB
+        hi = min(lo + step, n_rows)
+        keys[lo:hi] = torch.randn((hi - lo, DI), generator=g, device=dev).to(torch.float8_e4m3fn)
+    return kv, scales, keys
+
+
+def run_c5a(torch, dist, dev, rank, world, hbm, barrier, max_over_ranks) -> dict:
+    """256 sequences x 131072 rows, seed 3, dealt to the ranks by context length: one fixed batch, no collective
+    (strong scaling).  Every rank generates and holds only its own sequences."""
+    from moespresso_b200 import dist as mdist
+    from moespresso_b200.deepseek_v4.decode_step import LatentCache, SparseDecodePlan
+    Bt, L, kk = 256, 131072, 2048
+    mine = mdist.assign_sequences([L] * Bt, world)[rank]
+    nb = len(mine)
+    kv, scales, keys = _device_tables(torch, dev, nb * L, 3000 + rank)
+    cache = LatentCache(kv=kv, kv_scales=scales, idx_keys=keys,
+                        row_start=torch.arange(nb, device=dev, dtype=torch.int64) * L,
+                        row_count=torch.full((nb,), L, dtype=torch.int32, device=dev), max_rows=L)
+    g = torch.Generator(device=dev).manual_seed(3)
+    q = torch.randn((Bt, H, DQK), generator=g, device=dev).to(torch.bfloat16)[mine]
+    iq = torch.randn((Bt, HI, DI), generator=g, device=dev).to(torch.bfloat16)[mine]
+    iw = (torch.randn((Bt, HI), generator=g, device=dev) / 4)[mine]
+    plan = SparseDecodePlan(cache, heads=H, d_qk=DQK, idx_heads=HI, idx_dim=DI, k=kk, scale=DQK ** -0.5, d_v=DV,
+                            q_dtype=torch.bfloat16, out_dtype=torch.bfloat16)
+    plan.load_inputs(q, iq, iw)
+    for _ in range(3):
+        plan.launch()
+    barrier()
+    reps = 10
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        plan.launch()
+    b.record()
+    barrier()
+    ms = max_over_ranks([a.elapsed_time(b) / reps])[0]
+    per_gpu_bytes = step_bytes([L] * nb, kk)
+    out = {"batch": Bt, "rows_per_sequence": L, "sequences_on_this_rank": nb, "topk": kk, "scaling": "strong",
+           "collective": "none", "us_per_step": ms * 1e3, "tokens_per_s": Bt / (ms * 1e-3),
+           "per_gpu_GBs": per_gpu_bytes / (ms * 1e-3) / 1e9,
+           "per_gpu_frac_of_measured_hbm": per_gpu_bytes / (ms * 1e-3) / 1e9 / hbm}
+    del plan, cache, kv, scales, keys
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_c5b(torch, dist, dev, rank, world, barrier, max_over_ranks) -> dict:
+    """One sequence of 1,048,576 rows, seed 3, range-sharded over the ranks: local scores and top-k, all-gather of
+    the candidates, identical global selection, local partial attention, all-gather of the partials, merge.
+    Every rank draws the same table and keeps its own range; rank 0 also runs the single-GPU step on the whole
+    table and the results are compared (selection bit for bit)."""
+    from moespresso_b200 import dist as mdist
+    from moespresso_b200.deepseek_v4.decode_step import LatentCache, sparse_decode_step
+    R, kk = 1 << 20, 2048
+    kv, scales, keys = _device_tables(torch, dev, R, 3)          # the same draw on every rank
+    g = torch.Generator(device=dev).manual_seed(33)
+    q = torch.randn((H, DQK), generator=g, device=dev).to(torch.bfloat16)
+    iq = torch.randn((HI, DI), generator=g, device=dev).to(torch.bfloat16)
+    iw = torch.randn((HI,), generator=g, device=dev) / 4
+    lo, hi = mdist.row_range(R, world, rank, align=128)
+    shard = mdist.RangeShard(kv=kv[lo:hi], kv_scales=scales[lo:hi], idx_keys=keys[lo:hi], row_lo=lo)
+    out = {"rows": R, "topk": kk, "rows_on_this_rank": hi - lo, "collective": "2 x all_gather (NCCL) per step"
+           if world > 1 else "none (one rank)"}
+    if world == 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29541")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev,
+                                timeout=datetime.timedelta(seconds=180))
+        own_group = True
+    else:
+        own_group = False
+    # correctness against the single-GPU step (eager driver, which can report the attended ids)
+    res, attended = mdist.range_sharded_decode_step(q, iq, iw, shard, k=kk, scale=DQK ** -0.5, d_v=DV, return_ids=True)
+    counts = [torch.zeros(1, dtype=torch.int64, device=dev) for _ in range(world)]
+    dist.all_gather(counts, torch.tensor([attended.numel()], dtype=torch.int64, device=dev))
+    padded = torch.full((kk,), -1, dtype=torch.int64, device=dev)
+    padded[:attended.numel()] = attended
+    gathered = [torch.empty_like(padded) for _ in range(world)]
+    dist.all_gather(gathered, padded)
+    if rank == 0:
+        cache = LatentCache(kv=kv, kv_scales=scales, idx_keys=keys, row_start=torch.zeros(1, dtype=torch.int64, device=dev),
+                            row_count=torch.tensor([R], dtype=torch.int32, device=dev), max_rows=R)
+        ref, ref_ids = sparse_decode_step(q[None], iq[None], iw[None], cache, k=kk, scale=DQK ** -0.5, d_v=DV,
+                                          return_ids=True)
+        got = torch.cat([t[:int(n.item())] for t, n in zip(gathered, counts)])
+        out["ids_equal_single_gpu"] = bool(got.numel() == kk and
+                                           torch.equal(torch.sort(got)[0].to(torch.int32), ref_ids[0]))
+        out["max_abs_vs_single_gpu"] = float((res.float() - ref[0].float()).abs().max().item())
+    plan = mdist.RangeDecodePlan(shard, heads=H, d_qk=DQK, idx_heads=HI, idx_dim=DI, k=kk, scale=DQK ** -0.5, d_v=DV)
+    for _ in range(5):
+        plan.step(q, iq, iw)
+    barrier()
+    reps = 20
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        plan.step(q, iq, iw)
+    b.record()
+    barrier()
+    out["us_per_step"] = max_over_ranks([a.elapsed_time(b) / reps])[0] * 1e3
+    phases = plan.timed_step(q, iq, iw, reps=reps)   # device time of the three local phases and the two collectives
+    for name, us in zip(("candidates_us", "allgather_candidates_us", "partial_attention_us", "allgather_partials_us",
+                         "merge_us"), max_over_ranks(phases)):
+        out[name] = us
+    if rank == 0:
+        out["plan_max_abs_vs_eager"] = float((plan.out.float() - res.float()).abs().max().item())
+    if own_group:
+        dist.destroy_process_group()
+    del plan, shard, kv, scales, keys
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_extras(torch, dev, tf_peak) -> dict:
-    """Secondary workloads, single GPU: config 1 (fp32 decode, latency) and config 2 (Qwen prefill)."""
+    """Secondary workloads, single GPU: config 1 (fp32 decode, latency), config 2 (Qwen prefill), config 4 (chunk of
+    sparse prefill)."""
     from moespresso_b200 import synth
     from moespresso_b200.deepseek_v4.decode_step import LatentCache, sparse_decode_step
     from moespresso_b200.qwen.full_attention import sdpa_fa_prefill
@@ -396,13 +586,13 @@ def run_extras(torch, dev, tf_peak) -> dict:
         # Inputs are generated on the device (same shapes and N(0,1) distributions as synth.config4).
         from moespresso_b200 import _torchabi
         from moespresso_b200.deepseek_v4.prefill_step import sparse_prefill_step
-        T, R, H, Dqk, Dv, Hi, Di, kk = 4096, 32768, 64, 576, 512, 16, 64, 2048
+        T, R, kk = 4096, 32768, 2048
         g = torch.Generator(device=dev).manual_seed(2)
         rn = lambda *sh: torch.randn(*sh, generator=g, device=dev, dtype=torch.float32)
-        kv, q = rn(R, Dqk).to(torch.bfloat16), rn(T, H, Dqk).to(torch.bfloat16)
-        iq, ik, iw = rn(T, Hi, Di).to(torch.bfloat16), rn(R, Di).to(torch.bfloat16), rn(T, Hi) / 4
-        run = lambda: sparse_prefill_step(q, kv, iq, ik, iw, pos0=131072 - T, ratio=4, k=kk, scale=Dqk ** -0.5,
-                                          d_v=Dv, window=0)
+        kv, q = rn(R, DQK).to(torch.bfloat16), rn(T, H, DQK).to(torch.bfloat16)
+        iq, ik, iw = rn(T, HI, DI).to(torch.bfloat16), rn(R, DI).to(torch.bfloat16), rn(T, HI) / 4
+        run = lambda: sparse_prefill_step(q, kv, iq, ik, iw, pos0=131072 - T, ratio=4, k=kk, scale=DQK ** -0.5,
+                                          d_v=DV, window=0)
         run(); torch.cuda.synchronize()
         _torchabi.TIMER = {}
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -412,10 +602,12 @@ def run_extras(torch, dev, tf_peak) -> dict:
         ex["c4_chunk_ms"] = a.elapsed_time(b)
         ex["c4_entry_point_ms"] = tot
         if tot.get("indexer_scores"):
-            ex["c4_indexer_tflops"] = 2.0 * T * Hi * Di * R / (tot["indexer_scores"] * 1e-3) / 1e12
+            ex["c4_indexer_tflops"] = 2.0 * T * HI * DI * R / (tot["indexer_scores"] * 1e-3) / 1e12
+            ex["c4_indexer_frac_of_bf16_peak"] = ex["c4_indexer_tflops"] / tf_peak
         if tot.get("sparse_attn"):
-            ex["c4_sparse_attn_tflops"] = 2.0 * T * H * kk * (Dqk + Dv) / (tot["sparse_attn"] * 1e-3) / 1e12
-            ex["c4_gathered_GBs"] = T * kk * Dqk * 2 / (tot["sparse_attn"] * 1e-3) / 1e9
+            ex["c4_sparse_attn_tflops"] = 2.0 * T * H * kk * (DQK + DV) / (tot["sparse_attn"] * 1e-3) / 1e12
+            ex["c4_sparse_attn_frac_of_bf16_peak"] = ex["c4_sparse_attn_tflops"] / tf_peak
+            ex["c4_gathered_GBs"] = T * kk * DQK * 2 / (tot["sparse_attn"] * 1e-3) / 1e9
     except Exception as e:
         ex["c4_error"] = repr(e)
     return ex

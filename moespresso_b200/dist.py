@@ -223,6 +223,30 @@ class RangeDecodePlan:
         phases[2]()
         return self.out
 
+    def timed_step(self, q, idx_q, idx_w, reps: int = 20) -> list[float]:
+        """Device time of the five parts of a step, in microseconds, averaged over ``reps`` steps: local candidates,
+        all-gather of the candidates, local partial attention, all-gather of the partials, merge.  CUDA events on
+        the current stream (the collectives run on NCCL's stream; the events bracket the waits for them)."""
+        phases = self._graphs and [g.replay for g in self._graphs] or [self._candidates, self._partial, self._merge]
+        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(6)] for _ in range(reps)]
+        for e in evs:
+            self.q.copy_(q, non_blocking=True)
+            self.idx_q.copy_(idx_q, non_blocking=True)
+            self.idx_w.copy_(idx_w, non_blocking=True)
+            e[0].record()
+            phases[0]()
+            e[1].record()
+            dist.all_gather_into_tensor(self.all_cand, self.cand, group=self.group)
+            e[2].record()
+            phases[1]()
+            e[3].record()
+            dist.all_gather_into_tensor(self.all_part, self.part, group=self.group)
+            e[4].record()
+            phases[2]()
+            e[5].record()
+        torch.cuda.synchronize(self.q.device)
+        return [sum(e[i].elapsed_time(e[i + 1]) for e in evs) / reps * 1e3 for i in range(5)]
+
 
 def numpy_lens_to_tables(c: dict, seqs: list[int]) -> dict:
     """Slice a synthetic batch (moespresso_b200.synth.config3 layout) down to `seqs`,

@@ -113,3 +113,80 @@ def test_numpy_lens_to_tables():
     np.testing.assert_array_equal(sub["kv"][:30], c["kv"][30:60])
     np.testing.assert_array_equal(sub["kv"][30:], c["kv"][:10])
     assert sub["q"].shape[0] == 2
+
+
+def test_all_winners_in_one_shard(tmp_path):
+    """Every one of the k best rows lies in rank 0's range: the other ranks attend nothing and contribute
+    (m = -inf, l = 0) partials; selection and output still equal the single-device result."""
+    world, R = 3, 900
+    c = _case(seed=5, R=R, k=64)
+    lo, hi = mdist.row_range(R, world, 0, align=128)
+    c["idx_keys"][hi:] *= 1e-3                       # rows outside rank 0's range score ~0 ...
+    c["idx_keys"][lo:lo + 200] = np.abs(c["idx_keys"][lo:lo + 200]) + 1.0
+    c["idx_q"] = np.abs(c["idx_q"]) + 0.5            # ... rows inside it score high (all weights positive)
+    c["idx_w"] = np.abs(c["idx_w"]) + 0.1
+    mp.spawn(_worker, args=(world, _free_port(), c, str(tmp_path)), nprocs=world, join=True)
+    scores = ds4.indexer_scores(c["idx_q"][None], c["idx_keys"], c["idx_w"][None])[0].astype(np.float32)
+    ref_ids = ds4.topk_ids(scores, c["k"])[0]
+    assert ref_ids.max() < hi
+    assert np.load(tmp_path / "ids1.npy").size == 0 and np.load(tmp_path / "ids2.npy").size == 0
+    np.testing.assert_array_equal(np.sort(np.load(tmp_path / "ids0.npy")), ref_ids)
+    ref = ds4.indexed_mixed_attention_decode(c["q"], None, c["kv"], ref_ids, c["sinks"], pos0=0, window=0, ratio=0,
+                                             scale=c["scale"], d_v=c["d_v"])
+    for r in range(world):
+        np.testing.assert_allclose(np.load(tmp_path / f"out{r}.npy"), ref, rtol=1e-4, atol=1e-5)
+
+
+def _failing_worker(rank, world, port, c, out_dir, bad_rank, timeout_s):
+    """One rank raises before the candidate exchange; the others must get an error out of the collective (not
+    hang) within the process group's timeout, and record it."""
+    import datetime
+    import time
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=timeout_s))
+    R = c["kv"].shape[0]
+    lo, hi = mdist.row_range(R, world, rank, align=128)
+    shard = mdist.RangeShard(kv=torch.from_numpy(c["kv"][lo:hi]), kv_scales=None,
+                             idx_keys=torch.from_numpy(c["idx_keys"][lo:hi]), row_lo=lo)
+
+    class Ops(OracleOps):
+        def scores(self, idx_q, idx_w, keys):
+            if rank == bad_rank:
+                raise RuntimeError("injected failure before the candidate exchange")
+            return super().scores(idx_q, idx_w, keys)
+
+    t0 = time.time()
+    try:
+        mdist.range_sharded_decode_step(torch.from_numpy(c["q"]), torch.from_numpy(c["idx_q"]),
+                                        torch.from_numpy(c["idx_w"]), shard, k=c["k"], scale=c["scale"], d_v=c["d_v"],
+                                        ops=Ops())
+        msg = "completed"
+    except Exception as e:   # noqa: BLE001 - the kind of error is the backend's business
+        msg = f"error after {time.time() - t0:.1f}s: {type(e).__name__}"
+    with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
+        f.write(msg)
+    os._exit(1 if rank == bad_rank else 0)   # no clean shutdown of a broken group
+
+
+def test_rank_failure_surfaces_as_error_on_the_survivors(tmp_path):
+    import time
+    world, bad, timeout_s = 3, 1, 8
+    c = _case(seed=9, R=600)
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_worker, args=(r, world, port, c, str(tmp_path), bad, timeout_s))
+             for r in range(world)]
+    t0 = time.time()
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=90)
+    hung = [p for p in procs if p.is_alive()]
+    for p in hung:
+        p.kill()
+    assert not hung, "a surviving rank hung instead of failing"
+    assert time.time() - t0 < 80
+    for r in range(world):
+        text = (tmp_path / f"rank{r}.txt").read_text()
+        assert text.startswith("error"), (r, text)
