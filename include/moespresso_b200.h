@@ -173,6 +173,57 @@ typedef struct {
 int mxb_quantize_kv_int8(const mxb_quantize_kv_int8_args* a, void* stream);
 
 /* ------------------------------------------------------------------------ *
+ * Affine 8-bit rows, group size 64: the format of the Qwen full-attention KV cache.
+ * Replaces  mx.quantize / mx.dequantize(group_size=64, bits=8) as used on the cache and on the self chunk
+ *           src/moespresso/runtime/qwen/full_attention.py:364-369 (round trip of the fresh chunk),
+ *           mlx-lm QuantizedKVCache.update_and_fetch (:316, :352)
+ * Per group of 64 features: bias = min, scale = (max - min) / 255, element = round((w - bias) / scale) in
+ * [0, 255], w ~= element * scale + bias; four elements per uint32 (lowest byte first); scales and biases in
+ * the rows' floating type.  Parity unpinned: MLX's source is not part of the reference tree.
+ *   quantize:   x [n_rows, width] (row stride x_row_stride elements) -> packed, scales, biases
+ *   dequantize: packed, scales, biases -> x [n_rows, width] (row stride x_row_stride; x is written)
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  const void* x;        /* rows; the OUTPUT of mxb_affine_q8_dequantize */
+  int32_t x_dtype;      /* MXB_F32 | MXB_F16 | MXB_BF16 */
+  int64_t x_row_stride; /* elements */
+  void* packed;         /* uint32 [n_rows, width / 4] */
+  void* scales;         /* [n_rows, width / 64] */
+  void* biases;         /* [n_rows, width / 64] */
+  int32_t sb_dtype;     /* type of scales and biases (quantize: must equal x_dtype) */
+  int64_t n_rows;
+  int32_t width;        /* multiple of 64 */
+} mxb_affine_q8_args;
+
+int mxb_affine_q8_quantize(const mxb_affine_q8_args* a, void* stream);
+int mxb_affine_q8_dequantize(const mxb_affine_q8_args* a, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * One decode token over the affine-q8 cache, head_dim 256, split over the keys.
+ * Replaces  mlx_kquant.sdpa_decode_q8(queries, *q_keys, *q_values, scale, group_size=64, bits=8, splits=128, ...)
+ *           call site src/moespresso/runtime/qwen/full_attention.py:323-335 (eligibility :238-275)
+ *   q [Hq, 256]; keys / values as (packed u32 [Hkv, cap, 64], scales [Hkv, cap, 4], biases [Hkv, cap, 4]) with
+ *   the first P rows of every head valid and head_stride_rows = cap; q head h reads kv head h / (Hq / Hkv).
+ *   Writes per-split partials o_parts [n_splits, Hq, 256] f32 and ml_parts [n_splits, Hq, 2] f32 (max in natural
+ *   log units, sum); mxb_merge_partials (P = n_splits, B = T = 1) finishes.  Parity unpinned (third-party kernel).
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  const void* q;
+  int32_t q_dtype;
+  const void* k_packed; const void* k_scales; const void* k_biases;
+  const void* v_packed; const void* v_scales; const void* v_biases;
+  int32_t sb_dtype;
+  int64_t head_stride_rows;
+  int32_t P, Hq, Hkv, D;
+  float scale;
+  int32_t n_splits;
+  float* o_parts;
+  float* ml_parts;
+} mxb_sdpa_decode_q8_args;
+
+int mxb_sdpa_decode_q8(const mxb_sdpa_decode_q8_args* a, void* stream);
+
+/* ------------------------------------------------------------------------ *
  * Partial rotary embedding of the last rope_dim channels (interleaved pairs), forward or inverse.
  * Replaces  apply_rope_tail  src/moespresso/runtime/deepseek_v4/attention.py:114-156 and the in-kernel
  *           rope prologue / inverse-rope epilogue of fused_decode_sdpa
@@ -230,8 +281,10 @@ int mxb_topk_select(const mxb_topk_args* a, void* stream);
  * allocator's callback).  `workspace` / `workspace_bytes` are ignored; the candidate
  * scratch is an 8 MiB array built into the library (2^20 entries), so rows * n must not
  * exceed 2^20.  Calls nothing that allocates.  The first call on each device looks up the
- * array's device address: make it before any stream capture.  All calls share the array:
- * calls whose kernels could overlap on the GPU must be ordered (same stream). */
+ * array's device address: make it before any stream capture.  The address is kept for the
+ * life of the device's primary context: after a cudaDeviceReset in the same process the
+ * library must be reloaded.  All calls share the array: calls whose kernels could overlap
+ * on the GPU must be ordered (same stream). */
 int mxb_topk_select_static(const mxb_topk_args* a, void* stream);
 
 /* ------------------------------------------------------------------------ *

@@ -60,6 +60,18 @@ class QuantizeKvInt8Args(C.Structure):
     _fields_ = [("x", _p), ("x_dtype", _i32), ("q", _p), ("scales", _p), ("n_rows", _i64), ("width", _i32)]
 
 
+class AffineQ8Args(C.Structure):
+    _fields_ = [("x", _p), ("x_dtype", _i32), ("x_row_stride", _i64), ("packed", _p), ("scales", _p), ("biases", _p),
+                ("sb_dtype", _i32), ("n_rows", _i64), ("width", _i32)]
+
+
+class SdpaDecodeQ8Args(C.Structure):
+    _fields_ = [("q", _p), ("q_dtype", _i32), ("k_packed", _p), ("k_scales", _p), ("k_biases", _p),
+                ("v_packed", _p), ("v_scales", _p), ("v_biases", _p), ("sb_dtype", _i32), ("head_stride_rows", _i64),
+                ("P", _i32), ("Hq", _i32), ("Hkv", _i32), ("D", _i32), ("scale", C.c_float), ("n_splits", _i32),
+                ("o_parts", _p), ("ml_parts", _p)]
+
+
 class RopeTailArgs(C.Structure):
     _fields_ = [
         ("x", _p), ("out", _p), ("x_dtype", _i32), ("positions", _p), ("inv_freq", _p), ("n_rows", _i64),
@@ -113,6 +125,9 @@ EXPORTS = {
     "mxb_fp8_kv_rows": (C.c_int, [C.POINTER(Fp8KvRowsArgs), _p]),
     "mxb_quantize_kv_int8": (C.c_int, [C.POINTER(QuantizeKvInt8Args), _p]),
     "mxb_rope_tail": (C.c_int, [C.POINTER(RopeTailArgs), _p]),
+    "mxb_affine_q8_quantize": (C.c_int, [C.POINTER(AffineQ8Args), _p]),
+    "mxb_affine_q8_dequantize": (C.c_int, [C.POINTER(AffineQ8Args), _p]),
+    "mxb_sdpa_decode_q8": (C.c_int, [C.POINTER(SdpaDecodeQ8Args), _p]),
     "mxb_topk_workspace_bytes": (_i64, [_i32, _i64, _i32]),
     "mxb_topk_select": (C.c_int, [C.POINTER(TopkArgs), _p]),
     "mxb_topk_select_static": (C.c_int, [C.POINTER(TopkArgs), _p]),

@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmoespresso_b200.so")
 STAMP = os.path.join(HERE, "build", "stamp.txt")
-SOURCES = ["runtime.cu", "indexer_scores.cu", "indexer_scores_fp8.cu", "indexer_decode.cu", "indexer_qat.cu", "kv_formats.cu", "topk_select.cu", "topk_multi.cu", "topk_cluster.cu", "sparse_attn.cu", "sparse_attn_tc.cu", "flash_prefill.cu"]
+SOURCES = ["runtime.cu", "indexer_scores.cu", "indexer_scores_fp8.cu", "indexer_decode.cu", "indexer_qat.cu", "kv_formats.cu", "qwen_q8.cu", "topk_select.cu", "topk_multi.cu", "topk_cluster.cu", "sparse_attn.cu", "sparse_attn_tc.cu", "flash_prefill.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v",

@@ -52,6 +52,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   if (*abort_flag) return false;
   for (uint32_t i = 1; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+#ifdef MXB_MBAR_BACKOFF_NS
+    __nanosleep(MXB_MBAR_BACKOFF_NS);   // waiting warps leave the memory-instruction queue to the working ones
+#endif
     if ((i & 1023u) == 1023u && *abort_flag) return false;
   }
   *abort_flag = 1;

@@ -358,7 +358,8 @@ extern "C" int mxb_topk_select(const mxb_topk_args* a, void* stream) {
 // The array's name is only a host-side handle here; the kernel needs the device address,
 // which cudaGetSymbolAddress returns for the CURRENT device.  It is looked up once per
 // device, on the first call made with that device current — make that first call before
-// any stream capture.  Every call shares the array (it keeps the previous call's
+// any stream capture — and kept for the life of that device's primary context (a
+// cudaDeviceReset inside the process invalidates it).  Every call shares the array (it keeps the previous call's
 // candidates; nothing in it has to start at zero because the kernel's counters live in
 // shared memory), so two calls whose kernels overlap on the GPU race on it: keep calls on
 // one stream, or otherwise ordered.  rows * n above kStaticCandEntries is rejected.

@@ -3,9 +3,12 @@
 
 ``fp8_kv_prefix_rows``   E4M3FN round trip of the non-rotary prefix of 512-wide compressed-KV rows (:587-619)
 
-The attention part of ``fused_decode_sdpa`` (:733) and the score + select part of ``fused_decode_prep`` (:669) are
-``indexed_attention_kernel.indexed_mixed_attention_decode`` and ``decode_step.sparse_decode_step``; their rotary
-prologue / epilogue is not part of this package.
+``fused_decode_prep``    QAT of q, scores, exact top-k, and the prepared KV row (rope tail + FP8 round trip) (:669-730)
+``fused_decode_sdpa``    rope on q, attention over the window (with the prepared row) and the selected rows, sink,
+                         inverse rope (:733-786)
+
+The two fused operators are compositions of this package's kernels (the reference runs each as one Metal launch);
+``params`` is read on the device, so neither synchronises with the host and both can be captured in a CUDA graph.
 """
 from __future__ import annotations
 
@@ -43,8 +46,9 @@ _MAX_HEADS = 64
 _ROPE_DIM = 64
 
 
-def _position(params) -> int:
-    return int(params.reshape(-1)[0].item())
+def _position(params):
+    """The token position as a one-element int64 device tensor (no host round trip)."""
+    return params.reshape(-1)[0:1].to(torch.int64)
 
 
 def fused_decode_prep(q_idx, pooled_qat, weights, kv_row, inv_freq, params, *, scale, topk):
@@ -84,7 +88,7 @@ def fused_decode_prep(q_idx, pooled_qat, weights, kv_row, inv_freq, params, *, s
     sel = topk_select(scores[None], topk)[0]
     # the round trip touches dims [0, 448), the rope dims [448, 512): they commute
     row = fp8_kv_prefix_rows(kv_row.float()[None])[0].to(torch.float16)
-    roped = apply_rope_tail(kv_row.reshape(1, 1, _HEAD_DIM), [_position(params)], inv_freq=inv_freq, half_chain=True)
+    roped = apply_rope_tail(kv_row.reshape(1, 1, _HEAD_DIM), _position(params), inv_freq=inv_freq, half_chain=True)
     row[_HEAD_DIM - _ROPE_DIM:] = roped.reshape(-1)[_HEAD_DIM - _ROPE_DIM:]
     return sel, row, scores
 
@@ -118,17 +122,18 @@ def fused_decode_sdpa(q, window, row, pooled, sel, sinks, inv_freq, params, *, s
     if int(inv_freq.shape[-1]) != _ROPE_DIM // 2 or inv_freq.dtype != torch.float32:
         raise ValueError("inv_freq must be float32 [32]")
     require_cuda(q, window, row, pooled, sel, sinks, inv_freq, params)
-    p = params.reshape(-1)
-    pos, write_idx = int(p[0].item()), int(p[1].item())
+    pos = _position(params)
+    write_idx = params.reshape(-1)[1:2].to(torch.int64)
     window_rows = int(window.shape[0])
-    qr = apply_rope_tail(q.reshape(1, n_heads, _HEAD_DIM).transpose(0, 1).contiguous(), [pos], inv_freq=inv_freq,
+    qr = apply_rope_tail(q.reshape(1, n_heads, _HEAD_DIM).transpose(0, 1).contiguous(), pos, inv_freq=inv_freq,
                          half_chain=True)                                   # [H, 1, 512]
-    win = window.clone()
-    if 0 <= write_idx < window_rows:
-        win[write_idx] = row
+    # the prepared row replaces window[write_idx] (an index outside the window replaces nothing), on the device
+    slot = torch.arange(window_rows, device=window.device, dtype=torch.int64)[:, None] == write_idx
+    win = torch.where(slot, row[None], window)
     # all window rows are keys: place the window so that its last row is the newest position and nothing is clipped
+    pos0 = torch.clamp(pos, min=window_rows - 1)
     out = sparse_attention(qr.reshape(1, n_heads, 1, _HEAD_DIM), pooled, sel.reshape(1, 1, -1), sinks.float(),
-                           pos0=max(pos, window_rows - 1), window=0, ratio=0, raw_kv=win[None], raw_start=0,
+                           pos0=0, pos0_dev=pos0, window=0, ratio=0, raw_kv=win[None], raw_start=0,
                            scale=float(scale), d_v=_HEAD_DIM, out_dtype=torch.float16)
     out = out.reshape(n_heads, 1, _HEAD_DIM)
-    return apply_rope_tail(out, [pos], inv_freq=inv_freq, inverse=True, half_chain=True).reshape(n_heads, _HEAD_DIM)
+    return apply_rope_tail(out, pos, inv_freq=inv_freq, inverse=True, half_chain=True).reshape(n_heads, _HEAD_DIM)

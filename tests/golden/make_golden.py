@@ -2,7 +2,7 @@
 
 Run once in a container that has the reference checkout:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path to the reference checkout>
 
 It imports ``moespresso.runtime.deepseek_v4.attention`` and
 ``moespresso.correctness.deepseek_v4.attention_diff`` from the reference tree
@@ -81,4 +81,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python " + sys.argv[0] + " <path to the reference checkout>")
+    main(sys.argv[1])

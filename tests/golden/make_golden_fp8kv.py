@@ -2,7 +2,7 @@
 
 Run once in a container that has the reference checkout:
 
-    python tests/golden/make_golden_fp8kv.py /root/reference
+    python tests/golden/make_golden_fp8kv.py <path to the reference checkout>
 
 It imports ``moespresso.correctness.deepseek_v4.compressor_diff`` from the reference tree (imports without
 MLX) and stores seeded 512-wide rows with the output of its ``_fp8_kv_round`` and, for the value table,
@@ -44,4 +44,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python " + sys.argv[0] + " <path to the reference checkout>")
+    main(sys.argv[1])

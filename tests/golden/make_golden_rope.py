@@ -1,6 +1,6 @@
 """Generate ``rope_golden.npz`` by RUNNING the reference's own pure-NumPy RoPE functions.
 
-    python tests/golden/make_golden_rope.py /root/reference
+    python tests/golden/make_golden_rope.py <path to the reference checkout>
 
 Imports ``moespresso.runtime.deepseek_v4.attention`` from the reference tree (no MLX needed) and stores the
 inverse frequencies (plain and YaRN), and seeded rows before and after ``apply_rope_tail`` (forward and inverse).
@@ -43,4 +43,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python " + sys.argv[0] + " <path to the reference checkout>")
+    main(sys.argv[1])

@@ -78,33 +78,40 @@ def test_bhld_layout_and_peaked_softmax():
     assert max_abs(out, ref) <= 4e-2      # |V| is 4x the benchmark's amplitude here
 
 
+class _Inner(torch.nn.Module):
+    """A stand-in for the stock attention module the wrapper decorates (Linear projections, identity norms and rope)."""
+
+    def __init__(self, Hq, Hkv, D, E):
+        super().__init__()
+        mk = lambda o: torch.nn.Linear(E, o, bias=False, dtype=torch.bfloat16, device="cuda")
+        self.q_proj, self.k_proj, self.v_proj = mk(Hq * 2 * D), mk(Hkv * D), mk(Hkv * D)
+        self.o_proj = torch.nn.Linear(Hq * D, E, bias=False, dtype=torch.bfloat16, device="cuda")
+        self.q_norm = self.k_norm = torch.nn.Identity()
+        self.num_attention_heads, self.num_key_value_heads, self.head_dim, self.scale = Hq, Hkv, D, D ** -0.5
+        self.stock_calls = 0
+
+    def rope(self, x, offset):
+        return x
+
+    def forward(self, x, mask=None, cache=None):   # the stock path: only counted here
+        self.stock_calls += 1
+        return torch.zeros_like(x)
+
+
 @torch.no_grad()
-def test_wrapper_module_counts_and_rejects():
+def test_wrapper_module_routes_counts_and_delegates():
     need_gpu()
     torch.manual_seed(0)
     Hq, Hkv, D, E = 4, 2, 256, 128
-
-    class Inner(torch.nn.Module):
-        def __init__(self):
-            super().__init__()
-            mk = lambda o: torch.nn.Linear(E, o, bias=False, dtype=torch.bfloat16, device="cuda")
-            self.q_proj, self.k_proj, self.v_proj = mk(Hq * 2 * D), mk(Hkv * D), mk(Hkv * D)
-            self.o_proj = torch.nn.Linear(Hq * D, E, bias=False, dtype=torch.bfloat16, device="cuda")
-            self.q_norm = self.k_norm = torch.nn.Identity()
-            self.num_attention_heads, self.num_key_value_heads, self.head_dim, self.scale = Hq, Hkv, D, D ** -0.5
-
-        def rope(self, x, offset):
-            return x
-
-    inner = Inner()
+    inner = _Inner(Hq, Hkv, D, E)
     model = type("M", (), {})()
     model.layers = [type("L", (), {"self_attn": inner})()]
     assert fa.install_flash_prefill_attention(model) == 1
     attn = model.layers[0].self_attn
     x = torch.randn(1, 200, E, dtype=torch.bfloat16, device="cuda") * 0.5
-    cache = {}
+    cache = fa.DenseKVCache(Hkv, D, 512)
     y = attn(x, mask="causal", cache=cache)
-    assert y.shape == (1, 200, E) and cache["offset"] == 200 and cache["keys"].shape == (1, Hkv, 200, D)
+    assert y.shape == (1, 200, E) and cache.offset == 200
     # composed fp32 reference of the same module
     qg = inner.q_proj(x).reshape(1, 200, Hq, 2 * D).float()
     qq, gg = qg[..., :D], qg[..., D:]
@@ -116,10 +123,13 @@ def test_wrapper_module_counts_and_rejects():
     yref = inner.o_proj(ref)
     rel = float((y.float() - yref.float()).norm() / yref.float().norm())
     assert rel < 2e-2
-    with pytest.raises(ValueError):
-        attn(x[:, :1], mask="causal", cache=None)
-    with pytest.raises(ValueError):
-        attn(x, mask=None, cache=None)
+    # a second chunk appends in place and attends over the first
+    y2 = attn(x[:, :100], mask="causal", cache=cache)
+    assert y2.shape == (1, 100, E) and cache.offset == 300
+    # calls the routes do not take go to the wrapped module, as the reference falls back to the stock path
+    attn(x[:, :1], mask="causal", cache=None)
+    attn(x, mask=None, cache=None)
+    assert inner.stock_calls == 2
     st = fa.flash_prefill_attention_stats(model)
-    assert st["layers"] == 1 and st["flash_calls"] == 1
+    assert st["layers"] == 1 and st["dense_flash_calls"] == 2 and st["flash_calls"] == 0
     assert st["rejected"]["single_token"] == 1 and st["rejected"]["mask"] == 1

@@ -293,6 +293,44 @@ def test_tensor_core_kernel_raw_window_boundary(kvkind, window, raw_cap):
         assert max_abs(o, ref) <= (2e-3 if kvkind == "f16" else TOL_16), (ns, max_abs(o, ref))
 
 
+@pytest.mark.parametrize("H,kvkind", [(8, "f32"), (64, "bf16"), (64, "int8")])
+@pytest.mark.parametrize("pos0,T", [(40, 1), (0, 1), (100, 20)])
+def test_raw_buffer_that_is_not_full_yet(H, kvkind, pos0, T):
+    """pos0 + T < raw_cap: outside the reference's domain (its uint32 first_raw_pos wraps and it attends no raw row;
+    its callers pass the rows held, not the capacity).  Pinned here: the valid rows are the last pos0 + T slots in
+    ring order.  Both the scalar kernel (H = 8, float32) and the tensor-core kernel take this path."""
+    need_gpu()
+    Dqk, Dv, R, k, raw_cap = 576, 512, 600, 32, 128
+    rng = np.random.default_rng(pos0 * 7 + T + H)
+    sinks = rng.standard_normal(H).astype(np.float32)
+    # few compressed rows are visible this early ((qpos + 1) // 4): ids beyond them end the walk
+    ids = np.stack([np.sort(rng.choice(40, size=k, replace=False)) for _ in range(T)]).astype(np.int32)
+    cs_t, rs_t = None, None
+    if kvkind == "int8":
+        comp = rng.integers(-127, 128, size=(R, Dqk), dtype=np.int8)
+        raw = rng.integers(-127, 128, size=(raw_cap, Dqk), dtype=np.int8)
+        cs = np.exp(rng.uniform(np.log(1e-3), np.log(1e-1), size=R)).astype(np.float16)
+        rs = np.exp(rng.uniform(np.log(1e-3), np.log(1e-1), size=raw_cap)).astype(np.float16)
+        comp_t, raw_t, cs_t, rs_t = dev(comp), dev(raw), dev(cs), dev(rs)
+        comp, raw = ds4.dequant_rows(comp, cs), ds4.dequant_rows(raw, rs)
+        q, qt, scale, tol = bf16_round(rng.standard_normal((H, T, Dqk))), torch.bfloat16, Dqk ** -0.5 * 20.0, TOL_16
+    elif kvkind == "bf16":
+        comp, raw = bf16_round(rng.standard_normal((R, Dqk))), bf16_round(rng.standard_normal((raw_cap, Dqk)))
+        comp_t, raw_t = dev(comp, torch.bfloat16), dev(raw, torch.bfloat16)
+        q, qt, scale, tol = bf16_round(rng.standard_normal((H, T, Dqk))), torch.bfloat16, Dqk ** -0.5, TOL_16
+    else:
+        comp = rng.standard_normal((R, Dqk)).astype(np.float32)
+        raw = rng.standard_normal((raw_cap, Dqk)).astype(np.float32)
+        comp_t, raw_t = dev(comp), dev(raw)
+        q, qt, scale, tol = rng.standard_normal((H, T, Dqk)).astype(np.float32), torch.float32, Dqk ** -0.5, TOL_F32
+    ref = ds4.indexed_mixed_attention_prefill(q.transpose(1, 0, 2), raw, comp, ids, sinks, pos0=pos0, window=128,
+                                              ratio=4, raw_start=5, scale=scale, d_v=Dv)
+    o = iak.sparse_attention(dev(q, qt)[None], comp_t, dev(ids)[None], dev(sinks), pos0=pos0, window=128, ratio=4,
+                             raw_kv=raw_t[None], raw_start=5, scale=scale, d_v=Dv, kv_scales=cs_t, raw_scales=rs_t,
+                             check=True)[0]
+    assert max_abs(o.permute(1, 0, 2), ref) <= tol
+
+
 def test_tensor_core_kernel_peaked_softmax_and_empty_tiles():
     """Logits spread over hundreds of units force reference-maximum updates and O rescales;
     a list with long runs of skipped ids gives tiles without any valid row."""

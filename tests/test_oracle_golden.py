@@ -170,3 +170,19 @@ def test_rope_matches_reference_vectors():
                                   g["inv_freq_yarn"])
     np.testing.assert_array_equal(pkg.rope_inverse_frequencies(64, pkg.DS4_SWA_ROPE_BASE), g["inv_freq_swa"])
     assert pkg.DS4_YARN == yarn
+
+
+def test_raw_rows_of_a_buffer_that_is_not_full_yet():
+    """Pinned convention outside the reference's domain.  The reference's kernels take n_raw = the rows the buffer
+    holds and compute first_raw_pos = last_pos + 1 - n_raw in uint32 (indexed_attention_kernel.py:120-130,
+    :243-251): with n_raw > last_pos + 1 that wraps and no raw row is attended, so its callers never pass it.  Here
+    raw_cap may exceed last_pos + 1 (a pre-allocated ring that is still filling): the valid rows are the LAST
+    last_pos + 1 slots in ring order, position p at (raw_start + p + raw_cap - last_pos - 1) mod raw_cap."""
+    raw_cap, raw_start, last_pos = 128, 11, 40
+    rows, comp = ds4._visit_rows(raw_cap, 0, [], qpos=40, last_pos=last_pos, window=128, ratio=4, raw_start=raw_start)
+    assert rows == [(raw_start + p + raw_cap - last_pos - 1) % raw_cap for p in range(41)] and comp == []
+    rows, _ = ds4._visit_rows(raw_cap, 0, [], qpos=30, last_pos=last_pos, window=8, ratio=4, raw_start=raw_start)
+    assert rows == [(raw_start + p + raw_cap - last_pos - 1) % raw_cap for p in range(23, 31)]
+    # inside the reference's domain (raw_cap <= last_pos + 1) the same formula is the reference's own
+    rows, _ = ds4._visit_rows(16, 0, [], qpos=40, last_pos=40, window=0, ratio=4, raw_start=3)
+    assert rows == [(3 + i) % 16 for i in range(16)]
