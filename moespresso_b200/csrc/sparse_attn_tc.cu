@@ -122,6 +122,7 @@ struct WsMisc {
   float l_tot[WS_HEADS];
   float colmax[4][WS_HEADS];       // per row quarter; reused for the row sums at the end
   float q_step[WS_HEADS];          // int8 tables: q[h, :] = (256 hi + lo) * q_step[h]
+  float v_bias[WS_HEADS];          // int8 tables: kValueBias x (sum of the fp16 weights), taken off O^T at the end
   uint32_t q_amax[WS_HEADS];       // bits of max |q[h, :]|
   uint32_t row_ref[kRing][WS_UNIT];   // kNoRow, or row index within its table (< 2^31), bit 31 set for the raw table
   float row_scale[kRing][WS_UNIT];
@@ -138,22 +139,33 @@ struct WsMisc {
 };
 static_assert(sizeof(WsMisc) <= kWsMiscBytes, "WsMisc must fit the bytes the layout reserves for it");
 
-// 16 int8 -> 16 fp16 integers (exact): bytes biased by 128 are dropped into the mantissa of 1024.0
+// 16 int8 -> 16 fp16 values v + kValueBias (exact): the byte, biased by 128, is dropped into the mantissa of
+// 1024.0.  The bias stays in the operand: O^T accumulates sum P (v + bias), and bias x sum P (the sum of the very
+// fp16 weights the MMA reads) is taken off once, in the epilogue.  The products are exact in fp32 and the bias
+// term is at most ~9 x the value term, so the cancellation costs about three of the accumulator's 24 bits.
+constexpr float kValueBias = 1152.f;
 __device__ __forceinline__ void widen_i8x16_f16(const uint4& in, uint4& lo, uint4& hi) {
   const uint32_t w[4] = {in.x ^ 0x80808080u, in.y ^ 0x80808080u, in.z ^ 0x80808080u, in.w ^ 0x80808080u};
-  uint32_t o[8];
-  const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
+  lo = make_uint4(__byte_perm(w[0], 0x64646464u, 0x4140), __byte_perm(w[0], 0x64646464u, 0x4342),
+                  __byte_perm(w[1], 0x64646464u, 0x4140), __byte_perm(w[1], 0x64646464u, 0x4342));
+  hi = make_uint4(__byte_perm(w[2], 0x64646464u, 0x4140), __byte_perm(w[2], 0x64646464u, 0x4342),
+                  __byte_perm(w[3], 0x64646464u, 0x4140), __byte_perm(w[3], 0x64646464u, 0x4342));
+}
+
+// Sums a[c] over the 16 lanes of a half warp: at each step a lane keeps half of its columns and hands the other
+// half to its partner, so 15 shuffles leave lane li with column li in a[0].
+__device__ __forceinline__ float half_warp_column_sum(float (&a)[16], int li) {
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    uint32_t a = __byte_perm(w[i], 0x64646464u, 0x4140);
-    uint32_t b = __byte_perm(w[i], 0x64646464u, 0x4342);
-    __half2 ha = __hsub2(*reinterpret_cast<__half2*>(&a), bias);
-    __half2 hb = __hsub2(*reinterpret_cast<__half2*>(&b), bias);
-    o[2 * i] = *reinterpret_cast<uint32_t*>(&ha);
-    o[2 * i + 1] = *reinterpret_cast<uint32_t*>(&hb);
+  for (int step = 8; step >= 1; step >>= 1) {
+    const bool upper = (li & step) != 0;
+#pragma unroll
+    for (int c = 0; c < step; ++c) {
+      const float send = upper ? a[c] : a[c + step];
+      const float keep = upper ? a[c + step] : a[c];
+      a[c] = keep + __shfl_xor_sync(0xffffffffu, send, step);
+    }
   }
-  lo = make_uint4(o[0], o[1], o[2], o[3]);
-  hi = make_uint4(o[4], o[5], o[6], o[7]);
+  return a[0];
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -217,6 +229,10 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const WsLayout L = ws_layout(p.Dqk, p.Dv, I8);
   uint8_t* q_s = smem + L.q_off;
+  // buffer b of a pair sits at first + b * stride (no run-time index into L: that would push it to local memory)
+  const int ub0 = L.ub_off[0], ub_st = L.ub_off[1] - L.ub_off[0];
+  const int pt0 = L.pt_off[0], pt_st = L.pt_off[1] - L.pt_off[0];
+  const int kb0 = L.kb_off[0], kb_st = L.kb_off[1] - L.kb_off[0];
   WsMisc* mi = reinterpret_cast<WsMisc*>(smem + L.misc_off);
   volatile int* abort_flag = &mi->abort_flag;
 
@@ -450,7 +466,7 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
       // Unit v into row buffer v & 1, slab by slab (so that the logit MMAs of the first slabs can start while the
       // later ones travel); a thread owns (slab, group of four rows) pairs; rows without data are fetched from
       // row -1 (zeros).
-      uint8_t* rb = smem + (I8 ? L.kb_off[buf] : L.ub_off[buf]);
+      uint8_t* rb = smem + (I8 ? (kb0 + (buf) * kb_st) : (ub0 + (buf) * ub_st));
       if (pt == 0)
         for (int sl = 0; sl < nrs; ++sl)
           ptx::mbar_expect_tx(&mi->full[buf][sl], (uint32_t)((I8 && sl == L.n128) ? WS_UNIT * 64 : WS_SLAB));
@@ -495,56 +511,57 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
     // The int8 rows land in operand layout and feed the logit MMAs as they are; only the values need 16-bit
     // operands.  An item = 8 rows x the 64 features of one fp16 slab = one warp instruction of 16-byte chunks
     // (lane = row % 8 + 8 * chunk): the rows have 8 different swizzle phases, so the 128-bit shared-memory loads
-    // and stores are conflict-free.  Warp cw takes the items cw, cw + 4, ... in slab order, eight at a time (a
-    // half of the value width); a 128-feature block is announced as soon as every warp has stored its items of
-    // it, and may be overwritten as soon as the previous unit's P V has multiplied it.
+    // and stores are conflict-free.  Warp cw takes the row groups cw and cw + 4 of every slab, four slabs (two
+    // 128-feature blocks) at a time; a block is announced as soon as every warp has stored its items of it, and
+    // may be overwritten as soon as the previous unit's P V has multiplied it.  Every address is a per-lane base
+    // plus a compile-time offset.
     if constexpr (I8) {
       const int cw = warp - (12 + NG);
       const int r8 = lane & 7, cl = lane >> 3;
-      const int nitems = (p.Dv / 64) * 8;   // (fp16 slab, group of 8 rows), slab-major
+      const int nsl = p.Dv / 64;   // fp16 slabs of the value buffer
+      const uint32_t row_off = (uint32_t)(cw * 8 + r8) * 128;
+      const uint32_t src_lo = row_off + (uint32_t)((cl ^ r8) << 4), src_hi = src_lo ^ 64u;   // features 0-63 / 64-127 of an int8 slab
+      const uint32_t dst0 = row_off + (uint32_t)(((2 * cl) ^ r8) << 4), dst1 = dst0 ^ 16u;
       ptx::mbar_wait(&mi->q_ready, 0, abort_flag);   // q's scratch copy (in the value buffer) has been consumed
       for (int u = 0; u < nunits; ++u) {
         const int buf = u & 1;
         for (int sl = 0; sl < n_mt; ++sl) ptx::mbar_wait(&mi->full[buf][sl], sphase(u), abort_flag);   // the value features have landed
         if (cw == 0) TRS(13, u);
-        for (int it0 = 0; it0 < nitems; it0 += 32) {
+        const uint8_t* src = smem + (kb0 + buf * kb_st);
+        uint8_t* dst = smem + ub0;
+        for (int hb = 0; hb * 4 < nsl; ++hb) {
           uint4 v[8];
-          if (cw == 0) TRS(16 + (it0 >> 5) * 4, u);
+          if (cw == 0) TRS(16 + hb * 4, u);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int it = it0 + cw + 4 * j;
+          for (int j = 0; j < 8; ++j) {   // item j: slab 4 hb + j / 2, row group cw + 4 (j % 2)
+            const int i = hb * 4 + (j >> 1);
             v[j] = make_uint4(0, 0, 0, 0);
-            if (it < nitems) {
-              const int i = it >> 3, rr = (it & 7) * 8 + r8;
-              v[j] = *reinterpret_cast<const uint4*>(smem + L.kb_off[buf] + (size_t)(i >> 1) * WS_SLAB + (size_t)rr * 128 +
-                                                     ((((i & 1) * 4 + cl) ^ r8) << 4));
-            }
+            if (i < nsl) v[j] = *reinterpret_cast<const uint4*>(src + (i >> 1) * WS_SLAB + ((i & 1) ? src_hi : src_lo) + (j & 1) * 4096);
           }
-          if (it0 + 32 >= nitems) {
+          if ((hb + 1) * 4 >= nsl) {
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&mi->k_free[buf]);   // this warp has read what it needs of the row buffer
           }
-          if (cw == 0) TRS(17 + (it0 >> 5) * 4, u);
+          if (cw == 0) TRS(17 + hb * 4, u);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int it = it0 + cw + 4 * j;
-            if (it < nitems) {
-              const int i = it >> 3, rr = (it & 7) * 8 + r8, blk = i >> 1;
-              // once per block (this warp's items of a block are consecutive): the previous unit's P V has read it
-              if (u >= 1 && (it - 4 < 0 || ((it - 4) >> 4) != blk)) wait_pv_block(u - 1, blk);
-              uint4 lo, hi;
-              widen_i8x16_f16(v[j], lo, hi);   // zero rows (no data) widen to 0.0
-              uint8_t* d = smem + L.ub_off[0] + (size_t)i * WS_SLAB + (size_t)rr * 128;
-              *reinterpret_cast<uint4*>(d + (((2 * cl) ^ r8) << 4)) = lo;
-              *reinterpret_cast<uint4*>(d + (((2 * cl + 1) ^ r8) << 4)) = hi;
-              const int nxt = it + 4;
-              if (nxt >= nitems || (nxt >> 4) != blk) {   // this warp's last item of the block
-                if (cw == 0) TRS(24 + blk, u);
-                ptx::fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(&mi->v_full[blk]);
-                if (cw == 0) TRS(18 + (blk & 1) + (blk >> 1) * 4, u);
+          for (int jb = 0; jb < 2; ++jb) {
+            const int blk = hb * 2 + jb;
+            if (blk * 2 < nsl) {
+              if (u >= 1) wait_pv_block(u - 1, blk);   // the previous unit's P V has read this block
+#pragma unroll
+              for (int jj = 0; jj < 4; ++jj) {
+                const int j = jb * 4 + jj, i = hb * 4 + (j >> 1);
+                uint4 lo, hi;
+                widen_i8x16_f16(v[j], lo, hi);
+                uint8_t* d = dst + i * WS_SLAB + (j & 1) * 4096;
+                *reinterpret_cast<uint4*>(d + dst0) = lo;
+                *reinterpret_cast<uint4*>(d + dst1) = hi;
               }
+              if (cw == 0) TRS(24 + blk, u);
+              ptx::fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) ptx::mbar_arrive(&mi->v_full[blk]);
+              if (cw == 0) TRS(18 + (blk & 1) + (blk >> 1) * 4, u);
             }
           }
         }
@@ -560,7 +577,7 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
         // int8 x int8 -> int32, K = 32 per instruction, N = 128 = the hi and lo planes of q.  Issuer j takes the
         // units of parity j, whole.
         const uint32_t idesc_s = ptx::idesc_i8(WS_UNIT, 2 * WS_HEADS, 1, 1);
-        const uint32_t q_addr = ptx::smem_u32(q_s), k_addr = ptx::smem_u32(smem + L.kb_off[j]);
+        const uint32_t q_addr = ptx::smem_u32(q_s), k_addr = ptx::smem_u32(smem + (kb0 + (j) * kb_st));
         const uint32_t d = tmem_base + (uint32_t)(j * 128);
         for (int u = j; u < nunits; u += 2) {
           if (u >= 2) ptx::mbar_wait(&mi->s_free[j], sphase(u - 2), abort_flag);   // S^T(u - 2) has been read
@@ -587,7 +604,7 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
         const uint64_t q_desc = ptx::smem_desc_sw128(ptx::smem_u32(q_s), 16, 1024);
         for (int u = 0; u < nunits; ++u) {
           const int buf = sbuf(u);
-          const uint64_t k_desc = ptx::smem_desc_sw128(ptx::smem_u32(smem + L.ub_off[buf]), 16, 1024);
+          const uint64_t k_desc = ptx::smem_desc_sw128(ptx::smem_u32(smem + (ub0 + (buf) * ub_st)), 16, 1024);
           const uint32_t d = tmem_base + (uint32_t)(buf * 128 + j * WS_HEADS);
           if (u >= 2) ptx::mbar_wait(&mi->s_free[buf], sphase(u - 2), abort_flag);   // S^T(u - 2) has been read
           for (int kb = kb_lo; kb < kb_hi; ++kb) {
@@ -612,8 +629,8 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
       for (int u = 0; u < nunits; ++u) {
         const int buf = pbuf(u);
         // A, MN-major: 64-feature blocks 8 KB apart (LBO), 8-row groups 1 KB apart (SBO); 16 rows per K step
-        const uint64_t v_desc = ptx::smem_desc_sw128(ptx::smem_u32(smem + L.ub_off[buf]), WS_SLAB, 1024);
-        const uint64_t pt_desc = ptx::smem_desc_sw128(ptx::smem_u32(smem + L.pt_off[buf]), 16, 1024);
+        const uint64_t v_desc = ptx::smem_desc_sw128(ptx::smem_u32(smem + (ub0 + (buf) * ub_st)), WS_SLAB, 1024);
+        const uint64_t pt_desc = ptx::smem_desc_sw128(ptx::smem_u32(smem + (pt0 + (buf) * pt_st)), 16, 1024);
         ptx::mbar_wait(&mi->p_ready[buf], pphase(u), abort_flag);
         ptx::tc_fence_after_sync();
         if (warp == 10) TRS(9, u);
@@ -709,14 +726,11 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
     }
     ptx::fence_proxy_async_smem();
     ptx::mbar_arrive(&mi->q_ready);
-    float qs[16];   // int8 tables: the fixed-point steps of this thread's heads
-    if constexpr (I8) {
-      ptx::mbar_wait(&mi->q_ready, 0, abort_flag);   // every step has been written
-#pragma unroll
-      for (int c = 0; c < 16; ++c) qs[c] = mi->q_step[col0 + c];
-    }
+    if constexpr (I8) ptx::mbar_wait(&mi->q_ready, 0, abort_flag);   // every fixed-point step has been written
 
-    float l1 = 0.f;   // row sum of head col0 + li over this warp's rows of all units
+    // Sums of head col0 + li over this warp's rows of all units: l1 of the softmax weights (the denominator), w1
+    // (int8 tables) of the fp16 operand weights, which carry the row scale.
+    float l1 = 0.f, w1 = 0.f;
     for (int u = 0; u < nunits; ++u) {
       const int sb_i = sbuf(u), pb_i = pbuf(u), slot = u & (kRing - 1);
       ptx::mbar_wait(&mi->s_ready[sb_i], sphase(u), abort_flag);
@@ -731,9 +745,17 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
         ptx::tmem_ld_16x32bx2_x16(sa + (uint32_t)WS_HEADS, sb);
         ptx::tmem_ld_wait();
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          if constexpr (I8) sv[c] = __float_as_uint(fmaf((float)(int)sv[c], 256.f, (float)(int)sb[c]) * qs[c]);
-          else sv[c] = __float_as_uint(__uint_as_float(sv[c]) + __uint_as_float(sb[c]));
+        for (int c = 0; c < 16; c += 4) {
+          if constexpr (I8) {
+            const float4 qs = *reinterpret_cast<const float4*>(&mi->q_step[col0 + c]);   // the heads' fixed-point steps
+            sv[c] = __float_as_uint(fmaf((float)(int)sv[c], 256.f, (float)(int)sb[c]) * qs.x);
+            sv[c + 1] = __float_as_uint(fmaf((float)(int)sv[c + 1], 256.f, (float)(int)sb[c + 1]) * qs.y);
+            sv[c + 2] = __float_as_uint(fmaf((float)(int)sv[c + 2], 256.f, (float)(int)sb[c + 2]) * qs.z);
+            sv[c + 3] = __float_as_uint(fmaf((float)(int)sv[c + 3], 256.f, (float)(int)sb[c + 3]) * qs.w);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sv[c + e] = __float_as_uint(__uint_as_float(sv[c + e]) + __uint_as_float(sb[c + e]));
+          }
         }
       }
       ptx::tc_fence_before_sync();
@@ -744,16 +766,17 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
       const float mul = scale_log2 * rs;
       float gap = BF16 ? kRescaleGapBF16 : kRescaleGapF16;
       if (I8 && rs > 1.f) gap -= log2f(rs);
-      float mr[16];   // this thread's 16 reference maxima (they move only in the branch below)
-#pragma unroll
-      for (int c = 0; c < 16; c += 4)
-        *reinterpret_cast<float4*>(&mr[c]) = *reinterpret_cast<const float4*>(&mi->m_ref[col0 + c]);
       bool grow = false;
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        const float x = ok ? __uint_as_float(sv[c]) * mul : -INFINITY;
-        sv[c] = __float_as_uint(x);
-        grow |= x > mr[c] + gap;
+      for (int c = 0; c < 16; c += 4) {
+        const float4 mr = *reinterpret_cast<const float4*>(&mi->m_ref[col0 + c]);   // the heads' reference maxima
+        const float mrv[4] = {mr.x, mr.y, mr.z, mr.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float x = ok ? __uint_as_float(sv[c + e]) * mul : -INFINITY;
+          sv[c + e] = __float_as_uint(x);
+          grow |= x > mrv[e] + gap;
+        }
       }
       if (warp == 0) TRS(6, u);
       if (__syncthreads_or_256(grow)) {
@@ -780,6 +803,7 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
         group_sync(4, 256);
         ptx::tc_fence_after_sync();
         l1 *= mi->factor[col0 + li];
+        w1 *= mi->factor[col0 + li];
         if (u >= 1) {
           // warp -> (lane quarter of TMEM = 32 features, two of the four 128-feature blocks); columns = heads
           for (int m2 = 0; m2 < 2; ++m2) {
@@ -799,33 +823,36 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
           }
           ptx::tmem_st_wait();
         }
-#pragma unroll
-        for (int c = 0; c < 16; c += 4)
-          *reinterpret_cast<float4*>(&mr[c]) = *reinterpret_cast<const float4*>(&mi->m_ref[col0 + c]);
       }
-      if (warp == 0) TRS(7, u);
-      // ---- P^T (16-bit, K-major, swizzled) and the row sums
-      if (I8 && u >= 1) wait_pv_all(u - 1);   // the one P^T buffer has been read by the previous unit's P V
+      // ---- P^T (16-bit, K-major, swizzled); the weights join this thread's sums as the operand holds them
+      uint32_t prw[8];
       {
-        const float inv = I8 ? __frcp_rn(rs) : 1.f;
-        uint8_t* pbase = smem + L.pt_off[pb_i] + (row & 7) * 2;
-        const int cj = row >> 3;
 #pragma unroll
         for (int c = 0; c < 16; c += 2) {   // two heads per step: one packed conversion each way
-          const int h = col0 + c;
+          const float2 mr = *reinterpret_cast<const float2*>(&mi->m_ref[col0 + c]);   // (moves only in the branch above)
           const float s0 = __uint_as_float(sv[c]), s1 = __uint_as_float(sv[c + 1]);
-          float p0 = (s0 == -INFINITY) ? 0.f : fast_exp2(s0 - mr[c]);
-          float p1 = (s1 == -INFINITY) ? 0.f : fast_exp2(s1 - mr[c + 1]);
+          float p0 = (s0 == -INFINITY) ? 0.f : fast_exp2(s0 - mr.x);
+          float p1 = (s1 == -INFINITY) ? 0.f : fast_exp2(s1 - mr.y);
           if (I8) {
             p0 *= rs;
             p1 *= rs;
           }
           float b0, b1;
-          const uint32_t pr = pack_op16x2<BF16>(p0, p1, b0, b1);
-          sv[c] = __float_as_uint(I8 ? b0 * inv : b0);
-          sv[c + 1] = __float_as_uint(I8 ? b1 * inv : b1);
-          *reinterpret_cast<uint16_t*>(pbase + (size_t)h * 128 + ((cj ^ (h & 7)) << 4)) = (uint16_t)(pr & 0xffffu);
-          *reinterpret_cast<uint16_t*>(pbase + (size_t)(h + 1) * 128 + ((cj ^ ((h + 1) & 7)) << 4)) = (uint16_t)(pr >> 16);
+          prw[c >> 1] = pack_op16x2<BF16>(p0, p1, b0, b1);
+          sv[c] = __float_as_uint(b0);   // the weights as the operand holds them
+          sv[c + 1] = __float_as_uint(b1);
+        }
+      }
+      if (warp == 0) TRS(7, u);
+      if (I8 && u >= 1) wait_pv_all(u - 1);   // the one P^T buffer has been read by the previous unit's P V
+      {
+        uint8_t* pbase = smem + (pt0 + (pb_i) * pt_st) + (row & 7) * 2;
+        const int cj = row >> 3;
+#pragma unroll
+        for (int c = 0; c < 16; c += 2) {
+          const int h = col0 + c;
+          *reinterpret_cast<uint16_t*>(pbase + (size_t)h * 128 + ((cj ^ (h & 7)) << 4)) = (uint16_t)(prw[c >> 1] & 0xffffu);
+          *reinterpret_cast<uint16_t*>(pbase + (size_t)(h + 1) * 128 + ((cj ^ ((h + 1) & 7)) << 4)) = (uint16_t)(prw[c >> 1] >> 16);
         }
       }
       if (warp == 0) TRS(12, u);
@@ -833,25 +860,29 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(&mi->p_ready[pb_i]);
       if (warp == 0) TRS(8, u);
-      // Sum over the 16 rows of this half warp, behind the hand-off: at each step a lane keeps half of its
-      // columns and hands the other half to its partner, so 15 shuffles leave lane li with column li.
+      // the sums over the 16 rows of this half warp, behind the hand-off
+      {
+        float a[16];
+        if constexpr (I8) {
 #pragma unroll
-      for (int step = 8; step >= 1; step >>= 1) {
-        const bool upper = (li & step) != 0;
+          for (int c = 0; c < 16; ++c) a[c] = __uint_as_float(sv[c]);
+          w1 += half_warp_column_sum(a, li);
+          const float inv = __frcp_rn(rs);
 #pragma unroll
-        for (int c = 0; c < step; ++c) {
-          const float send = upper ? __uint_as_float(sv[c]) : __uint_as_float(sv[c + step]);
-          const float keep = upper ? __uint_as_float(sv[c + step]) : __uint_as_float(sv[c]);
-          sv[c] = __float_as_uint(keep + __shfl_xor_sync(0xffffffffu, send, step));
+          for (int c = 0; c < 16; ++c) a[c] = __uint_as_float(sv[c]) * inv;
+        } else {
+#pragma unroll
+          for (int c = 0; c < 16; ++c) a[c] = __uint_as_float(sv[c]);
         }
+        l1 += half_warp_column_sum(a, li);
       }
-      l1 += __uint_as_float(sv[0]);
     }
 
     // ------------------------------------------------------------------ row sums over all units
     if (tid == 0) TRS(11, 2);
-    group_sync(4, 256);   // nobody reads the column maxima any more
+    group_sync(4, 256);   // nobody reads the column maxima or the row ring any more
     mi->colmax[wq][col0 + li] = l1;
+    if constexpr (I8) mi->row_scale[wq][col0 + li] = w1;
     if (nunits >= 1) wait_pv_all(nunits - 1);
     if (!I8 && nunits >= 2) wait_pv_all(nunits - 2);
     ptx::tc_fence_after_sync();
@@ -866,6 +897,10 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
     if (tid < WS_HEADS) {
       const float l = (mi->colmax[0][tid] + mi->colmax[1][tid]) + (mi->colmax[2][tid] + mi->colmax[3][tid]);
       mi->l_tot[tid] = l;
+      float vb = 0.f;
+      if constexpr (I8)
+        vb = kValueBias * ((mi->row_scale[0][tid] + mi->row_scale[1][tid]) + (mi->row_scale[2][tid] + mi->row_scale[3][tid]));
+      mi->v_bias[tid] = vb;
       // per-head factor applied to O^T: 1 for partial output, exp(m - m') / denominator with the sink joined otherwise
       float fac = 1.f;
       if (finalize) {
@@ -903,7 +938,7 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
         for (int c = 0; c < 32; ++c) {
           const int h = hh * 32 + c;
           if (h >= p.H) continue;
-          const float o = __uint_as_float(ov[c]) * mi->factor[h];
+          const float o = (__uint_as_float(ov[c]) - mi->v_bias[h]) * mi->factor[h];
           if (finalize) store_elem<OT>(p.out, gbase + d + h * ostep, o);
           else if (direct) reinterpret_cast<float*>(p.out)[gbase + d + h * ostep] = o;
           else p.ws_o[gbase + d + h * ostep] = o;

@@ -31,8 +31,10 @@ def test_format_round_trip_is_bit_exact(kind):
     np.testing.assert_array_equal(p.cpu().numpy().view(np.uint32), rp)
     d = fa.dequantize_affine_q8(p, s, b, dtype=torch.float32)
     np.testing.assert_allclose(d.cpu().numpy(), qwen.affine_q8_dequantize(rp, rs, rb), rtol=0, atol=1e-6 * np.abs(x).max())
-    # error of the format itself: at most half a step per element
-    assert np.all(np.abs(d.cpu().numpy() - x) <= 0.5 * np.repeat(rs, 64, axis=-1) * 1.01 + 1e-7)
+    # error of the format itself: half a step per element, plus up to 255 x 2^-9 steps where the step was rounded
+    # to a 16-bit type (the top elements then land beyond 255 and clip)
+    steps = 0.5 * 1.01 if kind == "f32" else 1.0
+    assert np.all(np.abs(d.cpu().numpy() - x) <= steps * np.repeat(rs, 64, axis=-1) + 1e-7)
 
 
 @pytest.mark.parametrize("L,P", [(256, 2065), (135, 700), (64, 1)])

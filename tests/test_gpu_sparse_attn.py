@@ -313,7 +313,9 @@ def test_raw_buffer_that_is_not_full_yet(H, kvkind, pos0, T):
         rs = np.exp(rng.uniform(np.log(1e-3), np.log(1e-1), size=raw_cap)).astype(np.float16)
         comp_t, raw_t, cs_t, rs_t = dev(comp), dev(raw), dev(cs), dev(rs)
         comp, raw = ds4.dequant_rows(comp, cs), ds4.dequant_rows(raw, rs)
-        q, qt, scale, tol = bf16_round(rng.standard_normal((H, T, Dqk))), torch.bfloat16, Dqk ** -0.5 * 20.0, TOL_16
+        # values reach 127 x 0.1: the 16-bit bound is taken relative to them (2e-2 at values of magnitude <= 4)
+        q, qt, scale = bf16_round(rng.standard_normal((H, T, Dqk))), torch.bfloat16, Dqk ** -0.5 * 20.0
+        tol = TOL_16 * max(1.0, float(np.abs(raw).max()) / 4.0)
     elif kvkind == "bf16":
         comp, raw = bf16_round(rng.standard_normal((R, Dqk))), bf16_round(rng.standard_normal((raw_cap, Dqk)))
         comp_t, raw_t = dev(comp, torch.bfloat16), dev(raw, torch.bfloat16)
@@ -328,7 +330,7 @@ def test_raw_buffer_that_is_not_full_yet(H, kvkind, pos0, T):
     o = iak.sparse_attention(dev(q, qt)[None], comp_t, dev(ids)[None], dev(sinks), pos0=pos0, window=128, ratio=4,
                              raw_kv=raw_t[None], raw_start=5, scale=scale, d_v=Dv, kv_scales=cs_t, raw_scales=rs_t,
                              check=True)[0]
-    assert max_abs(o.permute(1, 0, 2), ref) <= tol
+    assert max_abs(o.permute(1, 0, 2), ref) <= tol, max_abs(o.permute(1, 0, 2), ref)
 
 
 def test_tensor_core_kernel_peaked_softmax_and_empty_tiles():
