@@ -566,7 +566,14 @@ def run_extras(torch, dev, tf_peak) -> dict:
                             row_count=torch.tensor([4096], dtype=torch.int32, device=dev), max_rows=4096)
         q, iq, iw = t(c["q"])[None], t(c["idx_q"])[None], t(c["idx_w"])[None]
         ms = timeit(lambda: sparse_decode_step(q, iq, iw, cache, k=c["k"], scale=c["scale"], d_v=c["d_v"]))
-        ex["c1_fp32_decode_step_us"] = ms * 1e3
+        ex["c1_fp32_decode_step_eager_us"] = ms * 1e3          # one Python call per operator: host-bound
+        from moespresso_b200.deepseek_v4.decode_step import SparseDecodePlan
+        plan = SparseDecodePlan(cache, heads=int(q.shape[1]), d_qk=int(q.shape[2]), idx_heads=int(iq.shape[1]),
+                                idx_dim=int(iq.shape[2]), k=int(c["k"]), scale=c["scale"], d_v=c["d_v"],
+                                q_dtype=torch.float32)
+        plan.load_inputs(q, iq, iw)
+        ms = timeit(plan.launch, iters=200)
+        ex["c1_fp32_decode_step_us"] = ms * 1e3                # the same step as one CUDA graph launch
     except Exception as e:  # report, do not hide
         ex["c1_error"] = repr(e)
     try:

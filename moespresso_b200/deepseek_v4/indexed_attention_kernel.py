@@ -43,7 +43,7 @@ def check_status(status: torch.Tensor, what: str) -> None:
 def sparse_attention(q4, comp_kv, topk3, sinks, *, pos0, window, ratio, raw_kv=None, raw_start=0,
                      scale=None, d_v=None, kv_scales=None, raw_scales=None, comp_row_start=None,
                      comp_row_count=None, n_comp=None, pos0_dev=None, out=None, out_dtype=torch.float32,
-                     out_layout="bhtd", partial=False, n_splits=0, exact_fp32=False, check=False):
+                     out_layout="bhtd", partial=False, n_splits=0, exact_fp32=False, check=False, status=None):
     """Launch the sparse attention kernel.
 
     q4 [B,H,T,Dqk] (any strides on the first three axes); comp_kv a flat
@@ -52,7 +52,9 @@ def sparse_attention(q4, comp_kv, topk3, sinks, *, pos0, window, ratio, raw_kv=N
     None.  Returns out [B,H,T,Dv] ("bhtd") or [B,T,H,Dv] ("bthd"); with
     ``partial=True`` returns (un-normalised fp32 out, ml [B,T,H,2]).  16-bit and int8
     tables with up to 64 heads run on the tensor-core kernel; ``exact_fp32=True`` forces
-    the fp32 CUDA-core kernel (always used for float32 tables).
+    the fp32 CUDA-core kernel (always used for float32 tables).  ``status``: a caller-owned int64 device
+    buffer to use in place of the library's status word (``moespresso_b200.cycle_trace`` passes a larger one:
+    an instrumented build writes its cycle stamps there).
     """
     dev = require_cuda(q4, comp_kv, topk3)
     lib = _abi.load()
@@ -100,10 +102,12 @@ def sparse_attention(q4, comp_kv, topk3, sinks, *, pos0, window, ratio, raw_kv=N
     a.flags = _abi.SPARSE_EXACT_FP32 if exact_fp32 else 0
     ws = workspace(lib.mxb_sparse_attn_workspace_bytes(C.byref(a)), dev)
     a.workspace = ptr(ws); a.workspace_bytes = 0 if ws is None else ws.numel()
-    status = status_word(dev) if check else None
+    own_status = status is None
+    if own_status:
+        status = status_word(dev) if check else None
     a.status = ptr(status)
     _abi.check(_t.launch("sparse_attn", lib.mxb_sparse_attn, a))
-    if check:
+    if check and own_status:
         check_status(status, "sparse attention")
     return (out, ml) if partial else out
 

@@ -5,6 +5,7 @@
 * With two or more GPUs the driver itself runs as NCCL ranks (one process per GPU, NVLS off).
 Both must reproduce the single-device result: bit-exact selection, output within the 16-bit tolerance.
 """
+import datetime
 import os
 import socket
 
@@ -47,7 +48,7 @@ def _check(c, scores_ref, ids, out):
     assert np.abs(out - ref).max() <= 2e-2
 
 
-@pytest.mark.parametrize("world,R", [(2, 70000), (4, 9000), (3, 2500)])
+@pytest.mark.parametrize("world,R", [(2, 70000), (4, 9000), (3, 2500), (8, 1048576)])   # the last: one 1 M-row sequence over 8 ranks
 def test_range_sharded_step_emulated_ranks(world, R):
     need_gpu()
     c, scores_ref = _case(R, seed=world)
@@ -84,7 +85,8 @@ def _nccl_worker(rank, world, port, R, out_dir):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    torch.distributed.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    torch.distributed.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                                         timeout=datetime.timedelta(seconds=120))
     try:
         c, _ = _case(R, seed=world)
         lo, hi = mdist.row_range(R, world, rank, align=128)
@@ -121,7 +123,8 @@ def _plan_worker(rank, world, port, R, out_dir):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    torch.distributed.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    torch.distributed.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                                         timeout=datetime.timedelta(seconds=120))
     try:
         c, _ = _case(R, seed=5)
         lo, hi = mdist.row_range(R, world, rank, align=128)

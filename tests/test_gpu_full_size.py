@@ -39,25 +39,35 @@ def test_batched_decode_step_at_full_size():
             tied_out = torch.nonzero(row == kth).reshape(-1)
             tied_in = ids[b][taken[b] == kth]
             assert tied_in.max() < tied_out.min()
-    # --- scores and attention of a sample of sequences against the oracle
-    keys = None
+    # --- scores of EVERY sequence against the oracle; the selection against the oracle's, swaps allowed only among
+    # near-ties of the k-th score (the two sides round the scores differently); attention of every fourth sequence
     sc = scores.cpu().numpy()
     idn = ids.cpu().numpy()
-    for b in (0, B // 2, B - 1):
+    margins = []
+    for b in range(B):
         s, n = int(c["row_start"][b]), int(c["lens"][b])
         kb = synth.e4m3_bits_to_f32(c["idx_key_bits"][s:s + n])
         ref_scores = ds4.indexer_scores(c["idx_q"][b][None], kb, c["idx_w"][b][None])[0]
         np.testing.assert_allclose(sc[s:s + n], ref_scores, rtol=2e-4, atol=2e-3)
+        order = np.sort(ref_scores)[::-1]
+        kth = order[k - 1]
+        margins.append(float(kth - order[k]) / max(1.0, abs(float(kth))))   # relative gap at the k-th boundary
+        diff = np.setxor1d(idn[b], ds4.topk_ids(ref_scores, k)[0])
+        if diff.size:
+            assert np.all(np.abs(ref_scores[diff] - kth) <= 1e-3 * max(1.0, abs(kth))), (b, diff)
+        if b % 4:
+            continue
         sel = idn[b].astype(np.int64)
         ref = ds4.indexed_mixed_attention_decode(c["q"][b], None, c["kv"][s:s + n][sel], np.arange(k), None, pos0=0,
                                                  window=0, ratio=0, scale=c["scale"], d_v=c["d_v"],
                                                  kv_scales=c["kv_scales"][s:s + n][sel])
         assert max_abs(out[b], ref) <= 2e-2
+    print(f"k-th boundary margins (relative): min {min(margins):.2e}, median {float(np.median(margins)):.2e}")
 
 
 def test_qwen_prefill_at_full_size():
-    """S = 8192, 16 query heads over 2 KV heads, head_dim 256, bf16: three query tiles of three heads against a
-    float64 evaluation of those rows."""
+    """S = 8192, 16 query heads over 2 KV heads, head_dim 256, bf16: every head of four query tiles (first, two in
+    the middle, last) against a float64 evaluation of those rows."""
     need_gpu()
     c = synth.config2()
     t = lambda x: torch.from_numpy(x).cuda().to(torch.bfloat16)  # noqa: E731
@@ -65,22 +75,24 @@ def test_qwen_prefill_at_full_size():
     out = sdpa_fa_prefill(q, k, v, c["scale"], gate=g, layout="lhd").float().cpu().numpy()
     S, Hq, D = c["q"].shape
     group = Hq // c["k"].shape[1]
-    for h in (0, 7, 15):
+    for h in range(Hq):
         kk = c["k"][:, h // group].astype(np.float64)
         vv = c["v"][:, h // group].astype(np.float64)
-        for r0 in (0, 4032, S - 128):
+        for r0 in (0, 2688, 4032, S - 128):
             rows = np.arange(r0, r0 + 128)
-            s = (c["q"][rows, h].astype(np.float64) @ kk.T) * c["scale"]
-            s[np.arange(S)[None, :] > rows[:, None]] = -np.inf
+            n_keys = r0 + 128                      # later keys are masked for every row of the tile
+            s = (c["q"][rows, h].astype(np.float64) @ kk[:n_keys].T) * c["scale"]
+            s[np.arange(n_keys)[None, :] > rows[:, None]] = -np.inf
             p = np.exp(s - s.max(axis=1, keepdims=True))
-            ref = (p @ vv) / p.sum(axis=1, keepdims=True)
+            ref = (p @ vv[:n_keys]) / p.sum(axis=1, keepdims=True)
             ref = ref / (1.0 + np.exp(-c["gate"][rows, h].astype(np.float64)))
             assert np.abs(out[rows, h] - ref).max() <= 2e-2
 
 
 def test_chunked_sparse_prefill_at_full_size():
     """One 4096-token chunk at the end of a 131072-token context over 32768 ratio-4 compressed rows, top-k 2048 per
-    token, bf16: a sample of tokens against the oracle (scores -> selection -> attention)."""
+    token, bf16: 64 tokens spread over the chunk (and its first and last) against the oracle (scores -> selection ->
+    attention)."""
     need_gpu()
     from moespresso_b200.deepseek_v4.prefill_step import sparse_prefill_step
     c = synth.config4()
@@ -94,7 +106,7 @@ def test_chunked_sparse_prefill_at_full_size():
     vis = (int(c["pos0"]) + torch.arange(T, device="cuda") + 1) // int(c["ratio"])
     assert torch.all(ids[:, 1:] > ids[:, :-1]) and torch.all(ids >= 0) and torch.all(ids < vis[:, None])
     ids_n = ids.cpu().numpy()
-    for t in (0, 1, T // 2 + 3, T - 1):
+    for t in sorted(set(range(0, T, 65)) | {1, T - 1}):
         v = int(vis[t])
         ref_scores = ds4.indexer_scores(c["idx_q"][t][None], c["idx_keys"][:v], c["idx_w"][t][None])[0]
         ref_ids = ds4.topk_ids(ref_scores, k)[0]

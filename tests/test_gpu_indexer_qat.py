@@ -127,3 +127,35 @@ def test_fused_score_tail_bitexact(n_heads, cap, valid, wdtype):
     np.testing.assert_array_equal(np.isnan(g), np.isnan(exp))                  # NaN scores pass through (payload free)
     ok = ~np.isnan(exp)
     np.testing.assert_array_equal(g[ok].view(np.uint32), exp[ok].view(np.uint32))
+
+
+def test_pooled_qat_appends_in_place_and_padded_scores_match_the_valid_prefix():
+    """The fixed-capacity derived cache of the indexer (reference: model.py:905-944 with
+    fixed_decode_state.aux_fixed_update): rows appended over several decode steps equal the QAT of the whole pool
+    bit for bit, the buffer never moves, and scoring the full capacity then masking past the valid count gives the
+    concat-layout scores bitwise and the same top-k (its tests/test_deepseek_v4_fixed_decode_state.py:337-375)."""
+    need_gpu()
+    from moespresso_b200.deepseek_v4 import fixed_decode_state as fds
+    from moespresso_b200.deepseek_v4.attention import topk_select
+    rng = np.random.default_rng(37)
+    n_rows, capacity, heads, topk = 961, 1024, 64, 512
+    pool = dev(rng.standard_normal((1, n_rows, 128)).astype(np.float32))
+    branch, state = fds.FixedBranch(pool_capacity=capacity), {}
+    addr = None
+    for rows in (1, 640, 641, 960, 961):
+        view, prior = fds.pooled_qat_update(branch, state, pool[:, :rows])
+        cap = fds.aux_capacity_buffer(branch, "pooled_qat")
+        addr = addr or cap.data_ptr()
+        assert cap.data_ptr() == addr and tuple(cap.shape) == (1, capacity, 128)
+    assert prior == 960 and state["pooled_qat_rows"] == n_rows
+    assert torch.equal(view, isk.indexer_qat_rows(pool))
+    np.testing.assert_array_equal(view[0].cpu().numpy(), ds4.indexer_qat(pool[0].cpu().numpy()))
+    assert torch.all(cap[:, n_rows:] == 0)
+    q = dev(rng.standard_normal((1, heads, 1, 128)).astype(np.float32))
+    w = dev(rng.standard_normal((1, 1, heads)).astype(np.float32))
+    scale = 128 ** -0.5
+    valid = isk.fused_qat_indexer_scores(q, view, w, scale)
+    params = fds.decode_step_params(offset=3844, pool_rows=n_rows)
+    padded = fds.pad_scores_to_capacity(isk.fused_qat_indexer_scores(q, cap, w, scale), params)
+    assert torch.equal(padded[:n_rows], valid) and torch.all(torch.isneginf(padded[n_rows:]))
+    assert torch.equal(topk_select(padded[None], topk), topk_select(valid[None], topk))
