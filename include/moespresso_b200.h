@@ -89,6 +89,12 @@ typedef struct {
   int32_t ratio;
   int32_t flags;            /* MXB_INDEXER_* */
   int32_t* status;
+  uint32_t* digit_hist;     /* NULL, or [B, 2048] counters, zero on entry: the decode scan (T == 1, ratio == 0, FP8
+                               keys, 16-bit q, 8 | 16 | 32 | 64 heads; MXB_ERR_UNSUPPORTED otherwise) adds, per
+                               sequence, the histogram of the top 11 bits of the selection keys of the scores it
+                               writes, so that mxb_topk_select can skip its first pass (the radix select of
+                               fused_decode_prep follows its scores in one launch the same way:
+                               decode_attention_kernel.py:295-375) */
 } mxb_indexer_scores_args;
 
 #define MXB_INDEXER_EXACT_FP32 1 /* CUDA-core fp32 path even for 16-bit / fp8 operands */
@@ -271,6 +277,9 @@ typedef struct {
   int32_t k;                /* 1 <= k <= 8192 */
   void* workspace;
   int64_t workspace_bytes;
+  uint32_t* digit_hist;     /* NULL, or [rows, 2048]: the first-digit histogram of exactly the scores of each row,
+                               as mxb_indexer_scores leaves it.  The selection then starts at its threshold step,
+                               and the counters are zero again when the call has run (ready for the next step). */
 } mxb_topk_args;
 
 int64_t mxb_topk_workspace_bytes(int32_t rows, int64_t n, int32_t k);

@@ -30,14 +30,14 @@ class IndexerScoresArgs(C.Structure):
         ("row_start", _p), ("row_count", _p),
         ("B", _i32), ("T", _i32), ("H", _i32), ("D", _i32),
         ("n_rows", _i64), ("rows_total", _i64), ("pos0", _i64),
-        ("ratio", _i32), ("flags", _i32), ("status", _p),
+        ("ratio", _i32), ("flags", _i32), ("status", _p), ("digit_hist", _p),
     ]
 
 
 class TopkArgs(C.Structure):
     _fields_ = [
         ("scores", _p), ("row_stride", _i64), ("row_start", _p), ("row_count", _p), ("out_ids", _p),
-        ("rows", _i32), ("n", _i64), ("k", _i32), ("workspace", _p), ("workspace_bytes", _i64),
+        ("rows", _i32), ("n", _i64), ("k", _i32), ("workspace", _p), ("workspace_bytes", _i64), ("digit_hist", _p),
     ]
 
 

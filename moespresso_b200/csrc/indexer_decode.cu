@@ -24,6 +24,7 @@
 // tensor work is tiny (32 flop per byte); this kernel is bound by HBM, which is why it uses
 // warp-level MMA rather than the tcgen05 pipeline the prefill form needs.
 #include "common.cuh"
+#include "topk_common.cuh"
 
 namespace mxb {
 
@@ -40,6 +41,7 @@ struct DecodeIdxParams {
   const int32_t* row_count;
   int32_t B, H;
   int64_t n_rows;
+  uint32_t* hist;         // [B, 2048] first-digit histogram of the selection keys, or null
 };
 
 constexpr int kDecWarps = 8;
@@ -64,15 +66,20 @@ __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint16_t v) {
 // 2^a as a float, a in [-126, 127]
 __device__ __forceinline__ float pow2i(int a) { return __int_as_float((127 + a) << 23); }
 
-// D = feature width (64 | 128), NT = heads / 8 (n-tiles of the MMA)
-template <int D, int NT>
+// D = feature width (64 | 128), NT = heads / 8 (n-tiles of the MMA).  HIST: the score is still in a register when
+// it is stored, so the first radix digit of the selection that follows is counted here (a shared-memory histogram
+// per CTA, flushed with one global add per non-empty bin at the end of each sequence's segment).
+template <int D, int NT, bool HIST>
 __global__ void __launch_bounds__(kDecWarps * 32, (D == 64 && NT <= 2) ? 3 : 1) indexer_decode_kernel(DecodeIdxParams p) {
   constexpr int EPL = D / 4;    // features (= key bytes) per lane per row
   constexpr int KS = D / 16;    // MMA k-steps
   constexpr int VPL = EPL / 16; // 16-byte loads per lane per row
   extern __shared__ int64_t pre_s[];   // [B + 1] exclusive prefix sums of the row counts
+  __shared__ uint32_t hist_s[HIST ? kBigBins : 1];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
+  if constexpr (HIST)
+    for (int i = threadIdx.x; i < kBigBins; i += kDecWarps * 32) hist_s[i] = 0;
 
   if (warp == 0) {
     int64_t carry = 0;
@@ -228,15 +235,33 @@ __global__ void __launch_bounds__(kDecWarps * 32, (D == 64 && NT <= 2) ? 3 : 1) 
         s_lo += __shfl_xor_sync(0xffffffffu, s_lo, 2);
         s_hi += __shfl_xor_sync(0xffffffffu, s_hi, 2);
         // lane t of the quad stores: t == 0 -> row g, t == 1 -> row g + 8
-        if (t < 2 && u * 16 + g + 8 * t < left) st[go + u * 16] = t == 0 ? s_lo : s_hi;
+        if (t < 2 && u * 16 + g + 8 * t < left) {
+          const float sc = t == 0 ? s_lo : s_hi;
+          st[go + u * 16] = sc;
+          if constexpr (HIST) {
+            const uint32_t key = score_key_full(sc);
+            if (key) atomicAdd(&hist_s[key >> 21], 1u);
+          }
+        }
       }
+    }
+    if constexpr (HIST) {   // b and the segment bounds are the same for every thread of the CTA
+      __syncthreads();
+      for (int i = threadIdx.x; i < kBigBins; i += kDecWarps * 32) {
+        const uint32_t v = hist_s[i];
+        if (v) {
+          atomicAdd(&p.hist[(int64_t)b * kBigBins + i], v);
+          hist_s[i] = 0;
+        }
+      }
+      __syncthreads();
     }
   }
 }
 
-template <int D, int NT>
+template <int D, int NT, bool HIST>
 static int launch_decode_nt(DecodeIdxParams& p, cudaStream_t st) {
-  auto kern = indexer_decode_kernel<D, NT>;
+  auto kern = indexer_decode_kernel<D, NT, HIST>;
   static int per_sm[64] = {0};   // resident CTAs per SM, per device
   int dev = 0;
   MXB_CUDA_OK(cudaGetDevice(&dev));
@@ -259,11 +284,19 @@ static int launch_decode_nt(DecodeIdxParams& p, cudaStream_t st) {
 
 template <int D>
 static int launch_decode_d(DecodeIdxParams& p, cudaStream_t st) {
+  if (p.hist) {
+    switch (p.H / 8) {
+      case 1: return launch_decode_nt<D, 1, true>(p, st);
+      case 2: return launch_decode_nt<D, 2, true>(p, st);
+      case 4: return launch_decode_nt<D, 4, true>(p, st);
+      case 8: return launch_decode_nt<D, 8, true>(p, st);
+    }
+  }
   switch (p.H / 8) {
-    case 1: return launch_decode_nt<D, 1>(p, st);
-    case 2: return launch_decode_nt<D, 2>(p, st);
-    case 4: return launch_decode_nt<D, 4>(p, st);
-    case 8: return launch_decode_nt<D, 8>(p, st);
+    case 1: return launch_decode_nt<D, 1, false>(p, st);
+    case 2: return launch_decode_nt<D, 2, false>(p, st);
+    case 4: return launch_decode_nt<D, 4, false>(p, st);
+    case 8: return launch_decode_nt<D, 8, false>(p, st);
   }
   return fail(MXB_ERR_UNSUPPORTED, "decode indexer: head count %d is not 8, 16, 32 or 64", p.H);
 }
@@ -284,6 +317,7 @@ int launch_indexer_decode(const mxb_indexer_scores_args* a, cudaStream_t st) {
   p.q_vec = (reinterpret_cast<uintptr_t>(a->q) & 15) == 0 && a->q_stride_b % 8 == 0 && a->q_stride_h % 8 == 0;
   p.weights = a->weights; p.scores = a->scores; p.s_sb = a->score_stride_b;
   p.row_start = a->row_start; p.row_count = a->row_count; p.B = a->B; p.H = a->H; p.n_rows = a->n_rows;
+  p.hist = a->digit_hist;
   if (a->D == 64) return launch_decode_d<64>(p, st);
   return launch_decode_d<128>(p, st);
 }

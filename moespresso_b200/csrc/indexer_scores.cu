@@ -157,6 +157,8 @@ extern "C" int mxb_indexer_scores(const mxb_indexer_scores_args* a, void* stream
   p.pos0 = a->pos0; p.ratio = a->ratio; p.status = a->status;
 
   if (indexer_decode_eligible(a)) return launch_indexer_decode(a, st);
+  MXB_REQUIRE(a->digit_hist == nullptr, MXB_ERR_UNSUPPORTED,
+              "indexer scores: digit_hist needs the decode scan (one token, ratio 0, FP8 keys, 16-bit q, 8/16/32/64 heads)");
   const bool q16 = a->q_dtype == MXB_F16 || a->q_dtype == MXB_BF16;
   const bool keys_match = a->key_dtype == a->q_dtype || a->key_dtype == MXB_F8E4M3;
   const bool q_vec_ok = (reinterpret_cast<uintptr_t>(a->q) & 15) == 0 && a->q_stride_b % 8 == 0 &&

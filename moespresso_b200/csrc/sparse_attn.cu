@@ -19,25 +19,44 @@ constexpr int kHeadsPerCta = 8;
 constexpr int kMaxDvRegs = 16;  // Dv <= 512
 
 
+// Two rows of a tile at once, four 16-byte chunks of each per trip: eight loads are in flight before the first
+// is unpacked (a decode step of one sequence is a latency problem, not a bandwidth one).  A null row is zeros.
 template <int KVT>
-__device__ __forceinline__ void stage_row(float* dst, const void* src_row, int Dqk, float row_scale, int lane) {
+__device__ __forceinline__ void stage_row_pair(float* dst0, float* dst1, const void* src0, const void* src1, int Dqk,
+                                               float rs0, float rs1, int lane) {
   constexpr int EPV = 16 / ElemBytes<KVT>::v;
   const int nchunks = Dqk / EPV;
-  const uint4* src = reinterpret_cast<const uint4*>(src_row);
-  for (int c = lane; c < nchunks; c += 32) {
-    uint4 v = __ldg(src + c);
-    float f[EPV];
-    unpack16<KVT>(v, f);
+  const uint4* s0 = reinterpret_cast<const uint4*>(src0);
+  const uint4* s1 = reinterpret_cast<const uint4*>(src1);
+  for (int c0 = lane; c0 < nchunks; c0 += 128) {
+    uint4 v[2][4];
 #pragma unroll
-    for (int j = 0; j < EPV; ++j) dst[c * EPV + j] = (KVT == MXB_I8) ? f[j] * row_scale : f[j];
+    for (int u = 0; u < 4; ++u) {
+      const int c = c0 + 32 * u;
+      v[0][u] = (s0 && c < nchunks) ? __ldg(s0 + c) : make_uint4(0, 0, 0, 0);
+      v[1][u] = (s1 && c < nchunks) ? __ldg(s1 + c) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int c = c0 + 32 * u;
+      if (c < nchunks) {
+        float f[EPV];
+        unpack16<KVT>(v[0][u], f);
+#pragma unroll
+        for (int j = 0; j < EPV; ++j) dst0[c * EPV + j] = (KVT == MXB_I8) ? f[j] * rs0 : f[j];
+        unpack16<KVT>(v[1][u], f);
+#pragma unroll
+        for (int j = 0; j < EPV; ++j) dst1[c * EPV + j] = (KVT == MXB_I8) ? f[j] * rs1 : f[j];
+      }
+    }
   }
 }
 
 template <int KVT, int QT, int OT>
 __global__ void __launch_bounds__(256) sparse_attn_kernel(SparseParams p) {
   extern __shared__ float smem_f[];
-  const int ld = p.Dqk + 1;
-  float* rows_s = smem_f;                                  // [32][Dqk+1]
+  const int ld = p.Dqk + 4;   // rows stay 16-byte aligned; a quarter warp of 16-byte reads covers all 32 banks
+  float* rows_s = smem_f;                                  // [32][Dqk+4]
   float* q_s = rows_s + kTileRows * ld;                    // [8][Dqk]
   float* p_s = q_s + kHeadsPerCta * p.Dqk;                 // [8][32]
   int* valid_s = reinterpret_cast<int*>(p_s + kHeadsPerCta * kTileRows);  // [32]
@@ -100,42 +119,51 @@ __global__ void __launch_bounds__(256) sparse_attn_kernel(SparseParams p) {
   const int nreg = (p.Dv + 31) / 32;
 
   for (int e0 = e_lo; e0 < e_hi; e0 += kTileRows) {
-    // stage up to 32 rows
-    for (int rr = warp; rr < kTileRows; rr += 8) {
-      const int e = e0 + rr;
-      const void* src = nullptr;
-      float rs = 1.f;
-      if (e < e_hi) {
-        if (e < n_raw) {
-          const int64_t pabs = first + e;
-          const int64_t phys = ((int64_t)p.raw_start + (pabs - first_raw_pos)) % p.raw_cap;
-          const int64_t ridx = (int64_t)b * p.raw_cap + phys;
-          src = reinterpret_cast<const char*>(p.raw_kv) + ridx * p.Dqk * ElemBytes<KVT>::v;
-          if (KVT == MXB_I8) rs = __half2float(p.raw_scales[ridx]);
-        } else {
-          const int32_t id = ids[e - n_raw];
-          if (id >= 0) {
-            const int64_t ridx = cbase + id;
-            src = reinterpret_cast<const char*>(p.comp_kv) + ridx * p.Dqk * ElemBytes<KVT>::v;
-            if (KVT == MXB_I8) rs = __half2float(p.comp_scales[ridx]);
+    // stage up to 32 rows: warp w takes rows w, w + 8 and w + 16, w + 24, a pair at a time
+    for (int pr = 0; pr < 2; ++pr) {
+      const void* src[2] = {nullptr, nullptr};
+      float rs[2] = {1.f, 1.f};
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int e = e0 + warp + 8 * (2 * pr + u);
+        if (e < e_hi) {
+          if (e < n_raw) {
+            const int64_t pabs = first + e;
+            const int64_t phys = ((int64_t)p.raw_start + (pabs - first_raw_pos)) % p.raw_cap;
+            const int64_t ridx = (int64_t)b * p.raw_cap + phys;
+            src[u] = reinterpret_cast<const char*>(p.raw_kv) + ridx * p.Dqk * ElemBytes<KVT>::v;
+            if (KVT == MXB_I8) rs[u] = __half2float(p.raw_scales[ridx]);
+          } else {
+            const int32_t id = ids[e - n_raw];
+            if (id >= 0) {
+              const int64_t ridx = cbase + id;
+              src[u] = reinterpret_cast<const char*>(p.comp_kv) + ridx * p.Dqk * ElemBytes<KVT>::v;
+              if (KVT == MXB_I8) rs[u] = __half2float(p.comp_scales[ridx]);
+            }
           }
         }
       }
-      float* dst = rows_s + rr * ld;
-      if (src) {
-        stage_row<KVT>(dst, src, p.Dqk, rs, lane);
-      } else {
-        for (int d = lane; d < p.Dqk; d += 32) dst[d] = 0.f;
+      const int r0 = warp + 8 * (2 * pr), r1 = r0 + 8;
+      stage_row_pair<KVT>(rows_s + r0 * ld, rows_s + r1 * ld, src[0], src[1], p.Dqk, rs[0], rs[1], lane);
+      if (lane == 0) {
+        valid_s[r0] = src[0] != nullptr;
+        valid_s[r1] = src[1] != nullptr;
       }
-      if (lane == 0) valid_s[rr] = src != nullptr;
     }
     __syncthreads();
 
     if (head_ok) {
-      const float* qh = q_s + warp * p.Dqk;
-      const float* rj = rows_s + lane * ld;
-      float dot = 0.f;
-      for (int d = 0; d < p.Dqk; ++d) dot = fmaf(qh[d], rj[d], dot);
+      const float4* qh = reinterpret_cast<const float4*>(q_s + warp * p.Dqk);
+      const float4* rj = reinterpret_cast<const float4*>(rows_s + lane * ld);
+      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;   // four partial sums, combined in a fixed order
+      for (int d = 0; d < p.Dqk / 4; ++d) {
+        const float4 a = qh[d], r = rj[d];
+        d0 = fmaf(a.x, r.x, d0);
+        d1 = fmaf(a.y, r.y, d1);
+        d2 = fmaf(a.z, r.z, d2);
+        d3 = fmaf(a.w, r.w, d3);
+      }
+      const float dot = (d0 + d1) + (d2 + d3);
       const bool ok = valid_s[lane] != 0;
       const float s = ok ? dot * p.scale : -INFINITY;
       const float tmax = warp_max(s);
@@ -329,7 +357,7 @@ static int choose_splits(const mxb_sparse_attn_args* a) {
   const int64_t base = (int64_t)a->B * a->T * ceil_div(a->H, kHeadsPerCta);
   const int64_t max_rows = (int64_t)a->k + a->raw_cap;
   int64_t want = ceil_div(2 * (int64_t)sm_count(), base);
-  int64_t cap = ceil_div(max_rows, 2 * kTileRows);
+  int64_t cap = ceil_div(max_rows, (int64_t)kTileRows);   // down to one 32-row tile per split
   if (cap < 1) cap = 1;
   if (want > cap) want = cap;
   if (want > 64) want = 64;
@@ -416,7 +444,7 @@ extern "C" int mxb_sparse_attn(const mxb_sparse_attn_args* a, void* stream) {
     p.ws_o = reinterpret_cast<float*>(a->workspace);
     p.ws_ml = p.ws_o + (int64_t)p.nsplit * N * a->Dv;
   }
-  const size_t smem = ((size_t)kTileRows * (a->Dqk + 1) + (size_t)kHeadsPerCta * a->Dqk +
+  const size_t smem = ((size_t)kTileRows * (a->Dqk + 4) + (size_t)kHeadsPerCta * a->Dqk +
                        (size_t)kHeadsPerCta * kTileRows + kTileRows) * 4;
   dim3 grid((unsigned)p.nsplit, (unsigned)ceil_div(a->H, kHeadsPerCta), (unsigned)(a->B * a->T));
 

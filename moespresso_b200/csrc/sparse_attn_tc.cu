@@ -311,6 +311,14 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
     mi->keff = p.k;
     ptx::mbar_fence_init();
   }
+  if (tid == 384) {   // the row tables' descriptors are on their way while the barriers and TMEM are set up
+    ptx::tma_prefetch_desc(&tm_comp);
+    if (p.raw_cap > 0) ptx::tma_prefetch_desc(&tm_raw);
+    if (I8 && (p.Dqk & 127) != 0) {   // the 64-feature tail slab has maps of its own
+      ptx::tma_prefetch_desc(&tm_comp_tail);
+      if (p.raw_cap > 0) ptx::tma_prefetch_desc(&tm_raw_tail);
+    }
+  }
   if (tid < WS_HEADS) {
     mi->m_ref[tid] = -INFINITY;
     mi->factor[tid] = 1.f;

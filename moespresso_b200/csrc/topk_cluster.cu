@@ -43,6 +43,7 @@ struct TopkClusterParams {
   int64_t n;
   int32_t k;
   int32_t part_cap;   // keys per CTA the launch reserved shared memory for
+  uint32_t* hist;     // [rows, 2048] digit-1 histogram of every row, counted by the producer of the scores, or null
 };
 
 #ifdef MXB_TRACE_TC
@@ -134,6 +135,11 @@ __global__ void __launch_bounds__(kCThreads) topk_cluster_kernel(TopkClusterPara
   const uint32_t* wkeys = keys + warp * wchunk;
   const uint32_t lt = (1u << lane) - 1u;
 
+  // With the row's digit-1 histogram already counted (by the kernel that wrote the scores), the load only fills
+  // shared memory and the threshold bin comes straight from that histogram: no counting, no push, one cluster
+  // barrier less.
+  const bool pre = p.hist != nullptr;
+  const uint32_t* row_hist = pre ? p.hist + (int64_t)row * kBigBins : ghist;
   TRC(1);
   // ---- digit 1 (top 11 bits) while loading
   for (int it0 = 0; it0 < iters; it0 += 2) {
@@ -161,7 +167,7 @@ __global__ void __launch_bounds__(kCThreads) topk_cluster_kernel(TopkClusterPara
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           k4[j] = score_key_full(x[u][j]);
-          if (k4[j]) atomicAdd(&lhist[k4[j] >> 21], 1u);
+          if (!pre && k4[j]) atomicAdd(&lhist[k4[j] >> 21], 1u);
         }
         *reinterpret_cast<uint4*>(&keys[wbase + (it0 + u) * 128]) = make_uint4(k4[0], k4[1], k4[2], k4[3]);
       }
@@ -171,11 +177,13 @@ __global__ void __launch_bounds__(kCThreads) topk_cluster_kernel(TopkClusterPara
   TRC(2);
   cluster.barrier_wait();
   TRC(3);
-  push_hist(cluster, lhist, ghist, cs);
-  TRC(4);
-  cluster.sync();
+  if (!pre) {
+    push_hist(cluster, lhist, ghist, cs);
+    TRC(4);
+    cluster.sync();
+  }
   TRC(5);
-  row_threshold(ghist, p.k, warp_sums, &s_total, s_thr);
+  row_threshold(row_hist, p.k, warp_sums, &s_total, s_thr);
   TRC(6);
   const uint32_t k_eff = s_thr[0];
   if (rank == 0)
@@ -231,6 +239,8 @@ __global__ void __launch_bounds__(kCThreads) topk_cluster_kernel(TopkClusterPara
   const bool listed = s_overflow == 0;   // per CTA: otherwise the later steps scan all keys of the part
   push_hist256(cluster, lhist, ghs[0], cs);
   cluster.sync();
+  if (pre && rank == 0)   // every CTA of the cluster has read the row's histogram: leave it clear for the next step
+    for (int i = tid; i < kBigBins; i += kCThreads) p.hist[(int64_t)row * kBigBins + i] = 0;
   TRC(8);
   if (tid < 32) pick_digit_256(ghs[0], want, &s_digit, &s_dabove);
   __syncthreads();
@@ -424,6 +434,7 @@ int launch_topk_cluster(const mxb_topk_args* a, int cs, cudaStream_t st) {
   TopkClusterParams p{};
   p.scores = a->scores; p.row_stride = a->row_stride; p.row_start = a->row_start; p.row_count = a->row_count;
   p.out_ids = a->out_ids; p.rows = a->rows; p.n = a->n; p.k = a->k;
+  p.hist = a->digit_hist;
   const int64_t part_cap = round_up(ceil_div(a->n, (int64_t)cs), (int64_t)kCPartUnit);
   MXB_REQUIRE(part_cap <= kCPartMax, MXB_ERR_INVALID, "topk: row length %lld exceeds the cluster kernel's capacity",
               (long long)a->n);

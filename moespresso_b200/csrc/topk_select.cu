@@ -331,6 +331,8 @@ extern "C" int mxb_topk_select(const mxb_topk_args* a, void* stream) {
   p.out_ids = a->out_ids; p.rows = a->rows; p.n = a->n; p.k = a->k;
 
   if (const int cs = topk_cluster_size(a->rows, a->n)) return launch_topk_cluster(a, cs, st);
+  // the other kernels count their own first digit: only keep the promise that the counters end up clear
+  if (a->digit_hist) MXB_CUDA_OK(cudaMemsetAsync(a->digit_hist, 0, (size_t)a->rows * kBigBins * sizeof(uint32_t), st));
   if (a->n <= kSmemRowMax) {
     int threads = a->n >= 8192 ? 1024 : (a->n >= 2048 ? 512 : 256);
     size_t smem = (size_t)a->n * 4 + (size_t)(threads / 32) * 256 * 4;   // keys + per-warp histograms
@@ -390,6 +392,7 @@ extern "C" int mxb_topk_select_static(const mxb_topk_args* a, void* stream) {
   MXB_REQUIRE(a->rows > 0 && a->n > 0, MXB_ERR_INVALID, "topk: scores must contain at least one row and column");
   MXB_REQUIRE(a->k >= 1 && a->k <= 8192, MXB_ERR_INVALID, "topk must be between 1 and 8192");
   MXB_REQUIRE(a->scores && a->out_ids, MXB_ERR_INVALID, "topk: null tensor");
+  MXB_REQUIRE(a->digit_hist == nullptr, MXB_ERR_INVALID, "topk (static): digit_hist is not taken by this entry point");
   MXB_REQUIRE((int64_t)a->rows * a->n <= kStaticCandEntries, MXB_ERR_INVALID,
               "topk (static scratch): rows * n = %lld exceeds the built-in scratch of %lld entries; "
               "use mxb_topk_select with a workspace",

@@ -16,7 +16,7 @@ from .. import _torchabi as _t
 from .._torchabi import ptr, require_cuda, stream_ptr, workspace
 
 
-def topk_select(scores, k: int, *, valid=None, row_start=None, n=None, order: str = "index"):
+def topk_select(scores, k: int, *, valid=None, row_start=None, n=None, order: str = "index", digit_hist=None):
     """Ids of the k largest finite scores of every row; ties to the lower id;
     -inf / NaN never selected; -1 in unused slots.
 
@@ -24,7 +24,9 @@ def topk_select(scores, k: int, *, valid=None, row_start=None, n=None, order: st
     (int64 ``[rows]``) and ``valid`` (int32 ``[rows]``), one flat vector holding ragged
     rows, ``n`` = the longest row.  ``order="index"``: ids ascending (what the
     attention kernels walk); ``order="score"``: descending score, ties by ascending id
-    (the order of the NumPy contract).  Returns int32 ``[..., k]``.
+    (the order of the NumPy contract).  Returns int32 ``[..., k]``.  ``digit_hist``: int32 ``[rows, 2048]`` as
+    ``indexer_scores(..., digit_hist=)`` left it for exactly these scores; the selection skips its first pass and
+    leaves the counters at zero for the next step.
     """
     dev = require_cuda(scores)
     if scores.dtype != torch.float32:
@@ -55,6 +57,10 @@ def topk_select(scores, k: int, *, valid=None, row_start=None, n=None, order: st
     a.out_ids = ptr(out); a.rows = rows; a.n = n_; a.k = int(k)
     ws = workspace(lib.mxb_topk_workspace_bytes(rows, n_, int(k)), dev)
     a.workspace = ptr(ws); a.workspace_bytes = 0 if ws is None else ws.numel()
+    if digit_hist is not None:
+        if digit_hist.dtype != torch.int32 or tuple(digit_hist.shape) != (rows, 2048) or not digit_hist.is_contiguous():
+            raise ValueError("digit_hist must be a contiguous int32 [rows, 2048] tensor")
+        a.digit_hist = ptr(digit_hist)
     _abi.check(_t.launch("topk_select", lib.mxb_topk_select, a))
     out = out.reshape(*lead, int(k))
     if order == "score":

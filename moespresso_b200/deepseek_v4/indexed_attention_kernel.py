@@ -326,13 +326,26 @@ def indexer_scores_tiled_live(q, weights, index_comp, *, pos0: int, ratio: int =
     return scores
 
 
+DIGIT_BINS = 2048   # first radix digit of the selection: the top 11 bits of the monotone score key
+
+
+def scan_counts_digits(q, keys_flat, *, n_tokens: int, ratio: int, exact_fp32: bool = False, fp8_mma: bool = False) -> bool:
+    """Does this call run on the decode scan, the kernel that can count the selection's first digit as it writes
+    the scores (``digit_hist``)?  One token, no causal mask, FP8 keys, 16-bit q, 8 / 16 / 32 / 64 heads."""
+    f8 = getattr(torch, "float8_e4m3fn", None)
+    return (n_tokens == 1 and ratio == 0 and keys_flat.dtype == f8 and q.dtype in (torch.float16, torch.bfloat16)
+            and int(q.shape[1]) in (8, 16, 32, 64) and int(q.shape[0]) <= 4096 and not exact_fp32 and not fp8_mma)
+
+
 def indexer_scores(q, weights, keys_flat, *, n_rows, pos0=0, ratio=0, row_start=None, row_count=None,
-                   exact_fp32=False, fp8_mma=False, out=None, check=False):
+                   exact_fp32=False, fp8_mma=False, out=None, check=False, digit_hist=None):
     """General launcher: q [B,H,T,D], weights [B,T,H] f32, keys_flat [rows_total, D].
 
     Uniform batches (row_start None): returns [B,T,n_rows].  Ragged batches (T == 1,
     row_start / row_count int64 / int32 device vectors): returns a flat [rows_total]
-    score vector laid out like the key table."""
+    score vector laid out like the key table.  ``digit_hist``: int32 ``[B, 2048]``, zero on entry — the decode
+    scan (see ``scan_counts_digits``) adds every sequence's first-digit histogram of the scores it writes, for
+    ``topk_select(..., digit_hist=)`` to start from."""
     dev = require_cuda(q, weights, keys_flat)
     lib = _abi.load()
     B, H, T, D = (int(x) for x in q.shape)
@@ -361,6 +374,10 @@ def indexer_scores(q, weights, keys_flat, *, n_rows, pos0=0, ratio=0, row_start=
     a.n_rows = int(n_rows); a.rows_total = rows_total; a.pos0 = int(pos0); a.ratio = int(ratio)
     a.flags = (_abi.INDEXER_EXACT_FP32 if exact_fp32 else 0) | (_abi.INDEXER_FP8_MMA if fp8_mma else 0)
     a.status = ptr(status)
+    if digit_hist is not None:
+        if digit_hist.dtype != torch.int32 or tuple(digit_hist.shape) != (B, DIGIT_BINS) or not digit_hist.is_contiguous():
+            raise ValueError("digit_hist must be a contiguous int32 [B, 2048] tensor")
+        a.digit_hist = ptr(digit_hist)
     _abi.check(_t.launch("indexer_scores", lib.mxb_indexer_scores, a))
     if check:
         check_status(status, "indexer scores")

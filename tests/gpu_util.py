@@ -33,3 +33,13 @@ def bf16_round(x):
 
 def f16_round(x):
     return np.asarray(x, np.float32).astype(np.float16).astype(np.float32)
+
+
+def first_digit_hist(scores):
+    """2048-bin histogram of the top 11 bits of the selection keys of finite scores (NumPy): the key of x is its
+    bit pattern with the sign bit set for x >= 0 (-0 counts as +0) and all bits flipped for x < 0."""
+    x = np.asarray(scores, dtype=np.float32)
+    x = x[np.isfinite(x)] + np.float32(0.0)
+    b = x.view(np.uint32)
+    key = np.where(b & np.uint32(0x80000000), ~b, b | np.uint32(0x80000000))
+    return np.bincount((key >> np.uint32(21)).astype(np.int64), minlength=2048).astype(np.int32)

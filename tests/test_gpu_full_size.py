@@ -21,9 +21,14 @@ def test_batched_decode_step_at_full_size():
     cache = LatentCache(kv=dev(c["kv"]), kv_scales=dev(c["kv_scales"]), idx_keys=fp8_from_bits(c["idx_key_bits"]),
                         row_start=dev(c["row_start"]), row_count=dev(c["lens"].astype(np.int32)),
                         max_rows=int(c["lens"].max()))
+    hist = torch.zeros((B, 2048), dtype=torch.int32, device="cuda")   # the scan counts the selection's first digit
     out, ids, scores = sparse_decode_step(dev(c["q"], torch.bfloat16), dev(c["idx_q"], torch.bfloat16),
                                           dev(c["idx_w"]), cache, k=k, scale=c["scale"], d_v=c["d_v"],
-                                          return_ids=True, return_scores=True)
+                                          return_ids=True, return_scores=True, digit_hist=hist)
+    assert int(hist.abs().sum()) == 0                                  # ... and the selection leaves it clear
+    out_b, ids_b = sparse_decode_step(dev(c["q"], torch.bfloat16), dev(c["idx_q"], torch.bfloat16), dev(c["idx_w"]),
+                                      cache, k=k, scale=c["scale"], d_v=c["d_v"], return_ids=True)
+    assert torch.equal(ids, ids_b) and torch.equal(out, out_b)        # same step without the fused counting
     # --- top-k over EVERY row, on the device: ascending distinct valid ids, and nothing left out beats anything taken
     rs, ln = dev(c["row_start"]), dev(c["lens"])
     assert ids.dtype == torch.int32 and tuple(ids.shape) == (B, k)

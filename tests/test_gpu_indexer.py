@@ -94,6 +94,37 @@ def test_ragged_batch_fp8_scores():
         np.testing.assert_allclose(got[s:s + n], ref, rtol=2e-4, atol=2e-3)
 
 
+def test_scan_counts_the_first_digit_of_the_selection():
+    """The decode scan leaves, per sequence, the histogram of the top 11 bits of the selection keys of exactly the
+    scores it wrote; a call the scan does not take refuses the histogram."""
+    need_gpu()
+    from tests.gpu_util import first_digit_hist
+    c = synth.config3(seed=4, lens=[70000, 129, 33000, 1, 2500, 5000])
+    B = int(c["lens"].size)
+    rs = dev(c["row_start"]); rc = dev(c["lens"].astype(np.int32))
+    q = dev(c["idx_q"], torch.bfloat16)[:, :, None, :]
+    w = dev(c["idx_w"])[:, None, :].contiguous()
+    keys = fp8_from_bits(c["idx_key_bits"])
+    assert iak.scan_counts_digits(q, keys, n_tokens=1, ratio=0)
+    hist = torch.zeros((B, iak.DIGIT_BINS), dtype=torch.int32, device="cuda")
+    got = iak.indexer_scores(q, w, keys, n_rows=int(c["lens"].max()), row_start=rs, row_count=rc, digit_hist=hist)
+    plain = iak.indexer_scores(q, w, keys, n_rows=int(c["lens"].max()), row_start=rs, row_count=rc)
+    assert torch.equal(got, plain)                         # the same score bits with and without the counting
+    sc, h = got.cpu().numpy(), hist.cpu().numpy()
+    for b, (s, n) in enumerate(zip(c["row_start"], c["lens"])):
+        np.testing.assert_array_equal(h[b], first_digit_hist(sc[s:s + n]))
+        assert int(h[b].sum()) == int(n)
+    # a second call adds on top (the selection is what clears the counters)
+    iak.indexer_scores(q, w, keys, n_rows=int(c["lens"].max()), row_start=rs, row_count=rc, digit_hist=hist)
+    np.testing.assert_array_equal(hist.cpu().numpy(), 2 * h)
+    with pytest.raises(ValueError):                        # wrong shape
+        iak.indexer_scores(q, w, keys, n_rows=int(c["lens"].max()), row_start=rs, row_count=rc, digit_hist=hist[:, :100])
+    from moespresso_b200 import _abi
+    with pytest.raises((_abi.MxbError, RuntimeError)):     # float32 keys: not the scan
+        iak.indexer_scores(q.float(), w, dev(synth.e4m3_bits_to_f32(c["idx_key_bits"])), n_rows=int(c["lens"].max()),
+                           row_start=rs, row_count=rc, digit_hist=hist)
+
+
 def test_score_is_independent_of_row_partition():
     """A row's score bits do not depend on where the row sits in the table
     (needed for bit-exact top-k under KV-range sharding)."""

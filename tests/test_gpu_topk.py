@@ -94,6 +94,40 @@ def test_ragged_flat_rows():
         np.testing.assert_array_equal(got[b], ds4.topk_ids(flat[s:s + n], 2048)[0])
 
 
+@pytest.mark.parametrize("kind", ["normal", "ties", "specials"])
+def test_selection_from_a_precounted_first_digit(kind):
+    """With the rows' first-digit histograms handed in (as the decode scan leaves them) the selection is the same,
+    bit for bit, and the counters are zero afterwards — on the cluster kernel, which uses them, and on the kernels
+    that only clear them."""
+    need_gpu()
+    from tests.gpu_util import first_digit_hist
+    rng = np.random.default_rng(11)
+    lens = np.array([70000, 129, 131072, 1, 46000, 0, 24000], np.int64)
+    start = np.concatenate([[0], np.cumsum(lens)[:-1]])
+    flat = rng.standard_normal(int(lens.sum())).astype(np.float32)
+    if kind == "ties":
+        flat = np.round(flat * 2).astype(np.float32)
+    if kind == "specials":
+        flat[::7] = -np.inf; flat[5] = np.nan; flat[70001] = np.inf; flat[3] = -0.0; flat[4] = 0.0
+        flat[200000:200100] = 1e-40
+    hist = np.stack([first_digit_hist(flat[s:s + n]) for s, n in zip(start, lens)])
+    for k in (2048, 16):
+        h = dev(hist.copy())
+        got = topk_select(dev(flat), k, valid=dev(lens.astype(np.int32)), row_start=dev(start), n=int(lens.max()),
+                          digit_hist=h).cpu().numpy()
+        for b, (s, n) in enumerate(zip(start, lens)):
+            ref = ds4.topk_ids(flat[s:s + n], k)[0] if n else np.full(k, -1)
+            np.testing.assert_array_equal(got[b], ref)
+        assert int(h.abs().sum()) == 0
+    # short rows go to the one-CTA kernel, very long ones to the multi-launch one: both ignore and clear the counters
+    for n in (5000, 400000):
+        s2 = rng.standard_normal((2, n)).astype(np.float32)
+        h = dev(np.stack([first_digit_hist(r) for r in s2]))
+        got = topk_select(dev(s2), 512, digit_hist=h).cpu().numpy()
+        np.testing.assert_array_equal(got, ds4.topk_ids(s2, 512))
+        assert int(h.abs().sum()) == 0
+
+
 def test_causal_indexer_topk_known_answers(golden):
     need_gpu()
     raw = np.array([[[1.0, 20.0, 1000.0, 1000.0], [2.0, 10.0, 1000.0, 1000.0]],
