@@ -52,14 +52,29 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   if (*abort_flag) return false;
   for (uint32_t i = 1; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-#ifdef MXB_MBAR_BACKOFF_NS
-    __nanosleep(MXB_MBAR_BACKOFF_NS);   // waiting warps leave the memory-instruction queue to the working ones
-#endif
     if ((i & 1023u) == 1023u && *abort_flag) return false;
   }
   *abort_flag = 1;
   return false;
 }
+
+// ---------------------------------------------------------------- clusters ---
+// Address of the same shared-memory location in CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+// The hardware barrier of the cluster: every thread of every CTA arrives; stores made before `arrive` (to any CTA's
+// shared memory) are visible after `wait`.  The CTAs of a cluster are co-scheduled, nothing spins on memory.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
 
 // ---------------------------------------------------------------- fences ----
 __device__ __forceinline__ void fence_proxy_async_smem() {

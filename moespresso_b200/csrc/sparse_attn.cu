@@ -466,7 +466,7 @@ extern "C" int mxb_sparse_attn(const mxb_sparse_attn_args* a, void* stream) {
 #undef MXB_PAIR
   if (rc != MXB_OK) return rc;
 
-  if (p.nsplit > 1) {
+  if (p.nsplit > 1 && !p.cluster_merge) {
     MergeParams mp{};
     mp.o_parts = p.ws_o; mp.ml_parts = p.ws_ml; mp.sinks = a->sinks;
     mp.out = a->out; mp.out_ml = a->partial_ml;

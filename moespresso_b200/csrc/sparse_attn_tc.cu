@@ -59,8 +59,9 @@ constexpr int WS_HEADS = 64;      // heads per CTA (MMA N; two planes of 64 for 
 constexpr int WS_MAX_SLABS = 9;   // Dqk <= 576
 constexpr int WS_SLAB = 8192;     // [64 rows or heads] x 128 B
 constexpr int WS_THREADS = 640;   // 20 warps
-constexpr int kWsMiscBytes = 7168;
+constexpr int kWsMiscBytes = 9216;
 constexpr int kRing = 8;          // units of row metadata kept in shared memory (a slot is rewritten six units later)
+constexpr int kMaxClusterMerge = 4;   // splits of a token that can merge through shared memory
 // P = 2^(s - m_ref) may be as large as 2^gap.  bf16 operands have fp32's range; fp16 operands top out at 65504,
 // and the int8 path folds the row's dequantisation scale into P, so its gap shrinks by log2(scale) when positive.
 constexpr float kRescaleGapF16 = 15.f;
@@ -123,6 +124,8 @@ struct WsMisc {
   float colmax[4][WS_HEADS];       // per row quarter; reused for the row sums at the end
   float q_step[WS_HEADS];          // int8 tables: q[h, :] = (256 hi + lo) * q_step[h]
   float v_bias[WS_HEADS];          // int8 tables: kValueBias x (sum of the fp16 weights), taken off O^T at the end
+  float xm[kMaxClusterMerge][WS_HEADS];   // cluster merge: every split's reference maximum (log2 units) and
+  float xl[kMaxClusterMerge][WS_HEADS];   //   denominator, written here by the splits themselves (remote stores)
   uint32_t q_amax[WS_HEADS];       // bits of max |q[h, :]|
   uint32_t row_ref[kRing][WS_UNIT];   // kNoRow, or row index within its table (< 2^31), bit 31 set for the raw table
   float row_scale[kRing][WS_UNIT];
@@ -897,11 +900,7 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
     group_sync(4, 256);
     if (tid == 0) TRS(11, 3);
 
-    // ------------------------------------------------------------------ output
-    const int64_t N = (int64_t)p.B * p.T * p.H;
-    const bool direct = p.nsplit == 1;
-    const bool finalize = direct && !p.partial_ml;
-    const bool have_o = nunits > 0;
+    // ------------------------------------------------------------------ per-head sums of this split
     if (tid < WS_HEADS) {
       const float l = (mi->colmax[0][tid] + mi->colmax[1][tid]) + (mi->colmax[2][tid] + mi->colmax[3][tid]);
       mi->l_tot[tid] = l;
@@ -909,16 +908,55 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
       if constexpr (I8)
         vb = kValueBias * ((mi->row_scale[0][tid] + mi->row_scale[1][tid]) + (mi->row_scale[2][tid] + mi->row_scale[3][tid]));
       mi->v_bias[tid] = vb;
-      // per-head factor applied to O^T: 1 for partial output, exp(m - m') / denominator with the sink joined otherwise
+      if (p.cluster_merge) {   // tell every split of this token (this one included) where this one stands
+        const uint32_t am = ptx::smem_u32(&mi->xm[split][tid]), al = ptx::smem_u32(&mi->xl[split][tid]);
+        for (int r = 0; r < p.nsplit; ++r) {
+          ptx::st_cluster_f32(ptx::cluster_map(am, (uint32_t)r), mi->m_ref[tid]);
+          ptx::st_cluster_f32(ptx::cluster_map(al, (uint32_t)r), l);
+        }
+      }
+    }
+  }
+
+  // ====================================================================== output
+  // Every role is done with this CTA's operand buffers (the softmax warps arrive here only after the last P V).
+  // Three ways out: one split -> final or external-partial output straight from TMEM; splits in a cluster ->
+  // merged through shared memory below; otherwise (o, m, l) partials for the merge kernel.
+  const bool cmerge = p.cluster_merge != 0;
+  if (cmerge) {
+    __syncwarp();
+    ptx::cluster_arrive();   // (1) every split's (m, l) is in place and every CTA's buffers are idle
+    ptx::cluster_wait();
+  }
+  const int n_slots = cmerge ? (n_mt + p.nsplit - 1) / p.nsplit : 0;   // value blocks a CTA merges: mt = rank + slot * nsplit
+  float* recv = reinterpret_cast<float*>(smem);   // cluster merge: [slot][source split][16 head groups][128 features][4 heads]
+  if (warp < 8) {
+    const int wq = warp & 3, cset = warp >> 2;
+    const uint32_t lane_off = (uint32_t)(wq * 32) << 16;
+    const int64_t N = (int64_t)p.B * p.T * p.H;
+    const bool direct = p.nsplit == 1;
+    const bool finalize = direct && !p.partial_ml;
+    const bool have_o = nunits > 0;
+    if (tid < WS_HEADS) {
+      // per-head factor applied to O^T: 1 for partial output; otherwise this split's weight over the denominator
+      // of the whole token, exp2(m - m*) / (sum over splits of l exp2(m_s - m*) + sink), the sink joining once
       float fac = 1.f;
-      if (finalize) {
+      if (finalize || cmerge) {
         const float m = mi->m_ref[tid];
         const float sink2 = (p.sinks && tid < p.H) ? p.sinks[tid] * 1.4426950408889634f : -INFINITY;
-        const float m2v = fmaxf(m, sink2);
+        float m2v = fmaxf(m, sink2);
+        if (cmerge)
+          for (int r = 0; r < p.nsplit; ++r) m2v = fmaxf(m2v, mi->xm[r][tid]);
         float w = 0.f, den = 0.f;
         if (m2v > -INFINITY) {
           w = (m == -INFINITY) ? 0.f : exp2f(m - m2v);
-          den = l * w + ((sink2 == -INFINITY) ? 0.f : exp2f(sink2 - m2v));
+          if (cmerge) {
+            for (int r = 0; r < p.nsplit; ++r)   // split order: the same sum in every CTA and on every run
+              if (mi->xm[r][tid] > -INFINITY) den = fmaf(mi->xl[r][tid], exp2f(mi->xm[r][tid] - m2v), den);
+          } else {
+            den = mi->l_tot[tid] * w;
+          }
+          den += (sink2 == -INFINITY) ? 0.f : exp2f(sink2 - m2v);
         }
         fac = den > 0.f ? w / den : 0.f;
       }
@@ -932,6 +970,10 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
       const int mt = cset * 2 + m2;
       if (mt >= n_mt) continue;
       const int d = mt * 128 + wq * 32 + lane;
+      // cluster merge: block mt belongs to split mt % nsplit; this thread's feature row of it goes there, four
+      // heads per 16-byte store, consecutive features in consecutive lanes
+      const uint32_t owner = (uint32_t)(mt % p.nsplit);
+      const uint32_t dst0 = cmerge ? ptx::cluster_map(ptx::smem_u32(recv) + (uint32_t)((((mt / p.nsplit) * p.nsplit + split) * 16) * 128 + wq * 32 + lane) * 16u, owner) : 0u;
 #pragma unroll 1
       for (int hh = 0; hh < 2; ++hh) {
         uint32_t ov[32];
@@ -941,6 +983,19 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
         } else {
 #pragma unroll
           for (int c = 0; c < 32; ++c) ov[c] = 0u;
+        }
+        if (cmerge) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 4) {
+            float o4[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int h = hh * 32 + c + e;
+              o4[e] = have_o ? (__uint_as_float(ov[c + e]) - mi->v_bias[h]) * mi->factor[h] : 0.f;
+            }
+            ptx::st_cluster_v4(dst0 + (uint32_t)((hh * 8 + (c >> 2)) * 128) * 16u, o4[0], o4[1], o4[2], o4[3]);
+          }
+          continue;
         }
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
@@ -953,13 +1008,43 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
         }
       }
     }
-    if (tid < p.H && (!direct || p.partial_ml)) {
+    if (!cmerge && tid < p.H && (!direct || p.partial_ml)) {
       // (m, l) in natural-log units for the merge kernel
       const float m_nat = mi->m_ref[tid] == -INFINITY ? -INFINITY : mi->m_ref[tid] * 0.6931471805599453f;
       float* ml = direct ? p.partial_ml + ((int64_t)bt * p.H + tid) * 2
                          : p.ws_ml + ((int64_t)split * N + (int64_t)bt * p.H + tid) * 2;
       ml[0] = m_nat;
       ml[1] = mi->l_tot[tid];
+    }
+  }
+  if (cmerge) {
+    __syncwarp();
+    ptx::cluster_arrive();   // (2) every split's weighted blocks have arrived; nothing remote is touched after this
+    ptx::cluster_wait();
+    if (warp < 8) {
+      // thread = (feature of the block, half of the head groups): sum the splits in split order, store the output
+      const int f = tid & 127, hg0 = (tid >> 7) * 8;
+      for (int slot = 0; slot < n_slots; ++slot) {
+        const int mt = split + slot * p.nsplit;
+        if (mt >= n_mt) break;
+        const int d = mt * 128 + f;
+        const float4* src = reinterpret_cast<const float4*>(recv) + (size_t)(slot * p.nsplit) * 16 * 128 + f;
+#pragma unroll 1
+        for (int hg = hg0; hg < hg0 + 8; ++hg) {
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int r = 0; r < p.nsplit; ++r) {
+            const float4 v = src[(size_t)(r * 16 + hg) * 128];
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+          }
+          const float o4[4] = {acc.x, acc.y, acc.z, acc.w};
+          const int64_t ob = (int64_t)b * p.o_sb + (int64_t)t * p.o_st + d;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int h = hg * 4 + e;
+            if (h < p.H) store_elem<OT>(p.out, ob + h * p.o_sh, o4[e]);
+          }
+        }
+      }
     }
   }
 
@@ -987,13 +1072,13 @@ bool sparse_tc_eligible(int kv_dtype, int q_dtype, int H, int Dqk, int Dv) {
 
 int sparse_tc_splits(int B, int T, int H, int k, int raw_cap, int requested) {
   const int64_t max_parts = ceil_div((int64_t)k + raw_cap, 2 * WS_UNIT);   // at least two units per split
-  int64_t want;
-  if (requested > 0) {
-    want = requested;
-  } else {
-    const int64_t base = (int64_t)B * T;
-    want = (int64_t)sm_count() / (base > 0 ? base : 1);  // one wave of CTAs
-  }
+  const int64_t base = (int64_t)B * T > 0 ? (int64_t)B * T : 1;
+  // Splits exist to fill idle SMs, so a split launch never has more CTAs than the device has SMs (one CTA per SM):
+  // a request beyond that is cut down.  (One launch of 40 tokens x 4 splits = 160 CTAs ended in "unspecified launch
+  // failure"; the cause was not found by reading and that shape is not launched again.)
+  const int64_t one_wave = (int64_t)sm_count() / base;
+  int64_t want = requested > 0 ? (int64_t)requested : one_wave;
+  if (want > one_wave) want = one_wave;
   if (want > max_parts) want = max_parts;
   if (want > 64) want = 64;
   if (want < 1) want = 1;
@@ -1087,15 +1172,77 @@ static int launch_tc_typed(SparseParams& p, int out_dtype, cudaStream_t st) {
   const int64_t ctas = (int64_t)p.B * p.T * p.nsplit;
   MXB_REQUIRE(ctas <= 0x7FFFFFFFll, MXB_ERR_INVALID, "sparse attention: too many (batch, token, split) items");
   dim3 grid((unsigned)ctas);
-#define MXB_TC(OT)                                                                                   \
+  // The splits of a token as one thread-block cluster that merges through shared memory: when a final output is
+  // wanted, the blocks to merge fit the (then idle) operand buffers, and every cluster is resident at once (a
+  // cluster needs nsplit whole SMs of one GPC; a second wave of clusters would cost more than the merge kernel).
+  p.cluster_merge = 0;
+  const int n_mt = p.Dv / 128;
+  const int n_slots = p.nsplit > 0 ? (n_mt + p.nsplit - 1) / p.nsplit : 0;
+  const bool merge_fits = (size_t)n_slots * p.nsplit * 32768 <= (size_t)L.misc_off;
+#define MXB_TC(OT, CLUSTER)                                                                          \
   {                                                                                                  \
     auto kern = sparse_attn_tc_kernel<KVT, QT, OT>;                                                  \
     MXB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));      \
-    kern<<<grid, WS_THREADS, smem, st>>>(p, tm_comp, tm_raw, tm_comp_tail, tm_raw_tail, tm_q);       \
+    cudaLaunchConfig_t cfg = {};                                                                     \
+    cfg.gridDim = grid;                                                                              \
+    cfg.blockDim = dim3(WS_THREADS);                                                                 \
+    cfg.dynamicSmemBytes = (size_t)smem;                                                             \
+    cfg.stream = st;                                                                                 \
+    cudaLaunchAttribute at[1];                                                                       \
+    at[0].id = cudaLaunchAttributeClusterDimension;                                                  \
+    at[0].val.clusterDim.x = (unsigned)p.nsplit;                                                     \
+    at[0].val.clusterDim.y = 1;                                                                      \
+    at[0].val.clusterDim.z = 1;                                                                      \
+    cfg.attrs = at;                                                                                  \
+    cfg.numAttrs = 1;                                                                                \
+    bool as_cluster = false;                                                                         \
+    if (CLUSTER) {                                                                                   \
+      static int resident_cache[16][kMaxClusterMerge + 1]; /* per device and cluster size; 0 = not asked yet */ \
+      int dev = 0;                                                                                   \
+      MXB_CUDA_OK(cudaGetDevice(&dev));                                                              \
+      int resident = (dev >= 0 && dev < 16) ? resident_cache[dev][p.nsplit] : 0;                     \
+      if (resident == 0) {                                                                           \
+        if (cudaOccupancyMaxActiveClusters(&resident, kern, &cfg) != cudaSuccess) {                  \
+          (void)cudaGetLastError();                                                                  \
+          resident = -1;                                                                             \
+        }                                                                                            \
+        if (resident == 0) resident = -1;                                                            \
+        if (dev >= 0 && dev < 16) resident_cache[dev][p.nsplit] = resident;                          \
+      }                                                                                              \
+      as_cluster = (int64_t)resident >= (int64_t)p.B * p.T;                                          \
+    }                                                                                                \
+    if (as_cluster) {                                                                                \
+      p.cluster_merge = 1;                                                                           \
+      MXB_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p, tm_comp, tm_raw, tm_comp_tail, tm_raw_tail, tm_q)); \
+    } else if (CLUSTER) {                                                                            \
+      return MXB_ERR_UNSUPPORTED; /* the caller retries with fp32 partials */                         \
+    } else {                                                                                         \
+      kern<<<grid, WS_THREADS, smem, st>>>(p, tm_comp, tm_raw, tm_comp_tail, tm_raw_tail, tm_q);     \
+    }                                                                                                \
   }
-  if (out_dtype == MXB_F32 || p.nsplit > 1 || p.partial_ml) MXB_TC(MXB_F32)
-  else if (out_dtype == MXB_BF16) MXB_TC(MXB_BF16)
-  else MXB_TC(MXB_F16)
+  const bool try_cluster = p.nsplit >= 2 && p.nsplit <= kMaxClusterMerge && !p.partial_ml && merge_fits;
+  int rc_cluster = MXB_ERR_UNSUPPORTED;
+  if (try_cluster) {
+    auto attempt = [&]() -> int {
+      if (out_dtype == MXB_F32) MXB_TC(MXB_F32, true)
+      else if (out_dtype == MXB_BF16) MXB_TC(MXB_BF16, true)
+      else MXB_TC(MXB_F16, true)
+      return MXB_OK;
+    };
+    rc_cluster = attempt();
+    if (rc_cluster != MXB_OK && rc_cluster != MXB_ERR_UNSUPPORTED) return rc_cluster;
+  }
+  if (rc_cluster != MXB_OK) {
+    p.cluster_merge = 0;
+    auto plain = [&]() -> int {
+      if (out_dtype == MXB_F32 || p.nsplit > 1 || p.partial_ml) MXB_TC(MXB_F32, false)
+      else if (out_dtype == MXB_BF16) MXB_TC(MXB_BF16, false)
+      else MXB_TC(MXB_F16, false)
+      return MXB_OK;
+    };
+    const int rc = plain();
+    if (rc != MXB_OK) return rc;
+  }
 #undef MXB_TC
   note_launch();
   MXB_CUDA_OK(cudaGetLastError());

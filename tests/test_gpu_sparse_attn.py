@@ -333,6 +333,52 @@ def test_raw_buffer_that_is_not_full_yet(H, kvkind, pos0, T):
     assert max_abs(o.permute(1, 0, 2), ref) <= tol, max_abs(o.permute(1, 0, 2), ref)
 
 
+@pytest.mark.parametrize("kvkind", ["bf16", "int8"])
+@pytest.mark.parametrize("B,ns,Dqk,Dv,H", [(3, 4, 576, 512, 64), (2, 3, 576, 512, 64), (5, 2, 576, 512, 40),
+                                            (2, 4, 256, 256, 16), (2, 2, 192, 128, 16), (8, 4, 576, 512, 64)])
+def test_tensor_core_kernel_splits_merged_inside_a_cluster(kvkind, B, ns, Dqk, Dv, H):
+    """Two to four splits of a token run as one thread-block cluster and merge through shared memory (no partials,
+    no merge kernel); shapes whose blocks do not fit the idle operand buffers keep the partials path.  The result
+    must be the oracle's, with a sink, ragged sequences, and an empty split."""
+    need_gpu()
+    rng = np.random.default_rng(B * 100 + ns * 10 + Dv)
+    k, R = 700, 3000
+    lens = rng.integers(900, R, size=B)
+    lens[0] = 70                                   # fewer visible rows than k: most splits of this sequence are empty
+    row_start = np.concatenate([[0], np.cumsum(lens)[:-1]]).astype(np.int64)
+    total = int(lens.sum())
+    q = bf16_round(rng.standard_normal((B, H, Dqk)))
+    sinks = rng.standard_normal(H).astype(np.float32)
+    ids = np.stack([np.sort(rng.choice(int(n), size=min(k, int(n)), replace=False)).tolist() + [-1] * (k - min(k, int(n)))
+                    for n in lens]).astype(np.int32)
+    if kvkind == "int8":
+        kv = rng.integers(-127, 128, size=(total, Dqk), dtype=np.int8)
+        sc = np.exp(rng.uniform(np.log(1e-3), np.log(3e-2), size=total)).astype(np.float16)
+        kv_t, sc_t, okw = dev(kv), dev(sc), dict(kv_scales=None)
+    else:
+        kv = bf16_round(rng.standard_normal((total, Dqk)))
+        kv_t, sc_t, okw = dev(kv, torch.bfloat16), None, {}
+    from moespresso_b200 import _abi
+    before = int(_abi.load().mxb_kernel_launches())
+    o = iak.sparse_attention(dev(q, torch.bfloat16)[:, :, None, :], kv_t, dev(ids)[:, None, :], dev(sinks), pos0=0,
+                             window=0, ratio=0, scale=Dqk ** -0.5, d_v=Dv, kv_scales=sc_t,
+                             comp_row_start=dev(row_start), comp_row_count=dev(lens.astype(np.int32)),
+                             n_comp=int(lens.max()), n_splits=ns, out_dtype=torch.bfloat16, check=True)[:, :, 0]
+    launches = int(_abi.load().mxb_kernel_launches()) - before
+    # one kernel when the cluster merges, kernel + merge kernel otherwise (more clusters than fit at once; blocks
+    # that do not fit the idle operand buffers of a narrow shape)
+    assert launches in (1, 2)
+    if Dqk == 576:
+        assert launches == 1
+    for b in range(B):
+        s, n = int(row_start[b]), int(lens[b])
+        rows = kv[s:s + n]
+        ref = ds4.indexed_mixed_attention_decode(q[b], None, rows, ids[b], sinks, pos0=0, window=0, ratio=0,
+                                                 scale=Dqk ** -0.5, d_v=Dv,
+                                                 **(dict(kv_scales=sc[s:s + n]) if kvkind == "int8" else {}))
+        assert max_abs(o[b], ref) <= TOL_16, (b, max_abs(o[b], ref))
+
+
 def test_tensor_core_kernel_peaked_softmax_and_empty_tiles():
     """Logits spread over hundreds of units force reference-maximum updates and O rescales;
     a list with long runs of skipped ids gives tiles without any valid row."""
