@@ -603,6 +603,47 @@ def run_extras(torch, dev, tf_peak) -> dict:
     except Exception as e:
         ex["c2_error"] = repr(e)
     try:
+        # Qwen q8 KV cache (the served form of configuration 2): one 4096-token chunk over a 28672-token affine-q8
+        # past (context 32768 after the chunk), and one decode token over 131072 cached keys.
+        from moespresso_b200.qwen.full_attention import (QuantizedKVCache, dequantize_affine_q8, quantize_affine_q8,
+                                                         sdpa_decode_q8, sdpa_fa_prefill_q8)
+        g8 = torch.Generator(device=dev).manual_seed(5)
+        rn8 = lambda *sh: (0.5 * torch.randn(*sh, generator=g8, device=dev, dtype=torch.float32)).to(torch.bfloat16)
+        Hq8, Hkv8, D8, L8, P8, PD8 = 16, 2, 256, 4096, 28672, 131072
+        cache8 = QuantizedKVCache(Hkv8, D8, PD8)
+        for lo in range(0, PD8, 16384):
+            cache8.update_and_fetch(rn8(1, Hkv8, 16384, D8), rn8(1, Hkv8, 16384, D8))
+        past_k = tuple(x[:, :, :P8] for x in cache8.keys)
+        past_v = tuple(x[:, :, :P8] for x in cache8.values)
+        q8, gate8 = rn8(1, Hq8, L8, D8), rn8(1, L8, Hq8 * D8)
+        sk = dequantize_affine_q8(*quantize_affine_q8(rn8(1, Hkv8, L8, D8)))
+        sv = dequantize_affine_q8(*quantize_affine_q8(rn8(1, Hkv8, L8, D8)))
+        ms = timeit(lambda: sdpa_fa_prefill_q8(q8, *past_k, *past_v, sk, sv, D8 ** -0.5, gate=gate8), iters=5)
+        flops = 4.0 * Hq8 * D8 * (L8 * P8 + L8 * (L8 + 1) / 2)
+        ex["qwen_q8_prefill_chunk_ms"] = ms
+        ex["qwen_q8_prefill_chunk_tflops"] = flops / (ms * 1e-3) / 1e12
+        ex["qwen_q8_prefill_chunk_frac_of_bf16_peak"] = ex["qwen_q8_prefill_chunk_tflops"] / tf_peak
+        qd = torch.randn((1, Hq8, 1, D8), generator=g8, device=dev, dtype=torch.float32)
+        dec = lambda: sdpa_decode_q8(qd, *cache8.keys, *cache8.values, D8 ** -0.5, splits=128)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                dec()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g_dec = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_dec):          # decode kernel + merge as one graph launch: device time, no host gaps
+            dec()
+        ms = timeit(g_dec.replay, iters=50)
+        q8_bytes = 2 * Hkv8 * PD8 * (D8 + 2 * (D8 // 64) * 2)     # packed words + bf16 scales and biases, keys and values
+        ex["qwen_q8_decode_us"] = ms * 1e3
+        ex["qwen_q8_decode_GBs"] = q8_bytes / (ms * 1e-3) / 1e9
+        ex["qwen_q8_decode_frac_of_measured_hbm"] = ex["qwen_q8_decode_GBs"] / measured_peaks()[0]
+        del cache8, past_k, past_v
+    except Exception as e:
+        ex["qwen_q8_error"] = repr(e)
+    try:
         # config 4: 4096-token chunk over 32768 ratio-4 compressed rows, top-k 2048 per token, bf16.
         # Inputs are generated on the device (same shapes and N(0,1) distributions as synth.config4).
         from moespresso_b200 import _torchabi

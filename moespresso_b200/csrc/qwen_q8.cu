@@ -11,10 +11,10 @@
 //  * affine_q8_quantize_kernel / affine_q8_dequantize_kernel — the format, one warp per row (any width that is
 //    a multiple of 64); the dequantiser writes with a caller-chosen row stride so that a past can be expanded
 //    straight into the front of a [past + chunk] operand of the flash prefill kernel.
-//  * q8_decode_kernel — one query token over a q8 cache, split over the keys: a CTA owns (split, KV head), its
-//    eight warps take keys four at a time, round-robin, and keep an online softmax for each of the KV head's query heads; the
-//    warps' states are merged in shared memory and every split writes (o, m, l) partials for the log-sum-exp
-//    merge kernel (mxb_merge_partials).  HBM-bound: 2 x (256 + 16) bytes per key and KV head are read once.
+//  * q8_decode_kernel — one query token over a q8 cache, split over the keys: a CTA owns (split, KV head), its four
+//    warps take 16 keys at a time and run both contractions on the warp-level tensor cores straight from the packed
+//    rows (see the comment at the kernel); every split writes (o, m, l) partials for the log-sum-exp merge kernel
+//    (mxb_merge_partials).  HBM-bound: 2 x (256 + 16) bytes per key and KV head are read once.
 #include "common.cuh"
 
 namespace mxb {
@@ -95,7 +95,23 @@ __global__ void __launch_bounds__(128) affine_q8_dequantize_kernel(const uint32_
 // ---------------------------------------------------------------------------------------------
 // decode: one query token, head_dim 256, GQA group of up to 8 query heads per KV head
 // ---------------------------------------------------------------------------------------------
-constexpr int QD_D = 256, QD_WARPS = 8, QD_MAXG = 8, QD_BATCH = 4;
+// Warp-level tensor-core flash decoding (mma.sync m16n8k16, fp16 operands, fp32 accumulation) straight from the
+// packed rows: a warp takes 16 keys at a time.
+//   S [16 keys x 8 heads]  = K . q^T : lane (g, t) loads the 64 contiguous bytes [64 t, 64 t + 64) of key rows g and
+//     g + 8 — exactly one quantisation group, so one (scale, bias) pair per row — and uses bytes 4 s .. 4 s + 3 as
+//     its A-fragment elements of k-step s; q is loaded under the same permutation of the feature axis, so the
+//     contraction is unchanged.  Bytes become fp16 exactly (0x6400 | u is 1024 + u), then u * scale + bias in one
+//     fused half2 operation.
+//   O^T [256 dims x 8 heads] += V^T . P : the dequantised value pairs of a lane are 8 x 8 blocks in the layout of
+//     `movmatrix`; transposed, they are A fragments whose 16 rows are the dims {64 c + 2 j + e}; P (fp16) goes from
+//     the accumulator layout of S to the B layout by two more transposes.
+// Online softmax per head with a lazy rescale of O^T (only when a maximum moved).  Measured on a B200 (131,072 keys,
+// 2 KV heads, 128 splits): 60 us, 0.3 of the HBM rate — the warp-level MMA path runs at an eighth of the tcgen05
+// rate and, more to the point, the three half2 operations per pair of bytes issue at ~0.25 instructions per clock
+// per warp; folding the group scales into per-group accumulators (bytes straight into the MMA) is the next step.  The CTA's four warps are merged
+// in shared memory and every split writes (o, m, l) partials for mxb_merge_partials.  HBM-bound: 2 x (256 + 16)
+// bytes per key and KV head are read once.
+constexpr int QD_D = 256, QD_WARPS = 4, QD_MAXG = 8, QD_TILE = 16;
 
 struct Q8DecodeParams {
   const void* q;           // [Hq, 256]
@@ -110,110 +126,163 @@ struct Q8DecodeParams {
   float* ml_parts;         // [nsplit, Hq, 2]
 };
 
+__device__ __forceinline__ void mma_f16_16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                              uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// Transpose of an 8 x 8 matrix of 16-bit elements held one row per four lanes (lane 4 r + c holds columns 2 c, 2 c + 1).
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+// bytes (2 which, 2 which + 1) of w, dequantised: (u * scale + bias) as two fp16 values in one register
+__device__ __forceinline__ uint32_t dequant_pair(uint32_t w, int which, __half2 scale, __half2 bias) {
+  uint32_t r = __byte_perm(w, 0x64646464u, which == 0 ? 0x4140 : 0x4342);   // 0x6400 | u = 1024 + u, exactly
+  const __half2 u = __hsub2(*reinterpret_cast<__half2*>(&r), __floats2half2_rn(1024.f, 1024.f));
+  const __half2 x = __hfma2(u, scale, bias);
+  return *reinterpret_cast<const uint32_t*>(&x);
+}
+
 template <int ST>
 __global__ void __launch_bounds__(QD_WARPS * 32) q8_decode_kernel(Q8DecodeParams p) {
-  extern __shared__ float q8_smem[];
-  float (*q_s)[QD_D] = reinterpret_cast<float (*)[QD_D]>(q8_smem);                                   // [QD_MAXG][QD_D]
-  float (*o_s)[QD_MAXG][QD_D] = reinterpret_cast<float (*)[QD_MAXG][QD_D]>(q8_smem + QD_MAXG * QD_D);   // the warps' accumulators at the end
+  __shared__ float o_s[QD_WARPS][QD_MAXG][QD_D];   // the warps' accumulators at the end
   __shared__ float m_s[QD_WARPS][QD_MAXG], l_s[QD_WARPS][QD_MAXG];
   const int split = blockIdx.x, kvh = blockIdx.y;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
   const int G = p.Hq / p.Hkv;
-  for (int i = tid; i < G * QD_D; i += QD_WARPS * 32) {
-    const int g = i / QD_D, d = i % QD_D;
-    const int64_t off = (int64_t)(kvh * G + g) * QD_D + d;
-    q_s[g][d] = p.q_dtype == MXB_F32 ? load_elem<MXB_F32>(p.q, off)
-                : p.q_dtype == MXB_F16 ? load_elem<MXB_F16>(p.q, off) : load_elem<MXB_BF16>(p.q, off);
+
+  // q as B fragments: head g, features 64 t + 4 s + {0, 1} and + {2, 3}, times scale * log2(e), fp16
+  uint32_t qb[16][2];
+#pragma unroll
+  for (int s = 0; s < 16; ++s) {
+    float f[4] = {0.f, 0.f, 0.f, 0.f};
+    if (g < G) {
+      const int64_t off = (int64_t)(kvh * G + g) * QD_D + 64 * t + 4 * s;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        f[e] = (p.q_dtype == MXB_F32   ? load_elem<MXB_F32>(p.q, off + e)
+                : p.q_dtype == MXB_F16 ? load_elem<MXB_F16>(p.q, off + e)
+                                       : load_elem<MXB_BF16>(p.q, off + e)) * p.scale_log2;
+    }
+    const __half2 lo = __floats2half2_rn(f[0], f[1]), hi = __floats2half2_rn(f[2], f[3]);
+    qb[s][0] = *reinterpret_cast<const uint32_t*>(&lo);
+    qb[s][1] = *reinterpret_cast<const uint32_t*>(&hi);
   }
-  __syncthreads();
+
+  float m_run[2] = {-INFINITY, -INFINITY};   // heads 2 t, 2 t + 1 (the same in the eight lanes that share t)
+  float l_run[2] = {0.f, 0.f};               // ... over this lane's keys only
+  float o[16][4];                            // o[i][c]: head 2 t + c % 2, dim 64 (g / 2) + 2 (2 i + c / 2) + g % 2
+#pragma unroll
+  for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
   const int per = (p.P + p.nsplit - 1) / p.nsplit;
   const int k_lo = min(split * per, p.P), k_hi = min(k_lo + per, p.P);
-  // lane l holds features 8 l .. 8 l + 7 of a row: one 8-byte word pair, group l / 8
-  float qv[QD_MAXG][8];
-#pragma unroll
-  for (int g = 0; g < QD_MAXG; ++g)
-#pragma unroll
-    for (int e = 0; e < 8; ++e) qv[g][e] = g < G ? q_s[g][lane * 8 + e] : 0.f;
-  float m[QD_MAXG], l[QD_MAXG], o[QD_MAXG][8];
-#pragma unroll
-  for (int g = 0; g < QD_MAXG; ++g) {
-    m[g] = -INFINITY;
-    l[g] = 0.f;
-#pragma unroll
-    for (int e = 0; e < 8; ++e) o[g][e] = 0.f;
-  }
+  const int ntiles = (k_hi - k_lo + QD_TILE - 1) / QD_TILE;
   const int64_t hb = (int64_t)kvh * p.head_stride_rows;
-  // a warp takes QD_BATCH keys per trip and issues all of their loads before the arithmetic (bytes in flight)
-  for (int key0 = k_lo + warp * QD_BATCH; key0 < k_hi; key0 += QD_WARPS * QD_BATCH) {
-    uint2 kw[QD_BATCH], vw[QD_BATCH];
-    float ksc[QD_BATCH], kbi[QD_BATCH], vsc[QD_BATCH], vbi[QD_BATCH];
+  for (int tile = warp; tile < ntiles; tile += QD_WARPS) {
+    const int key0 = k_lo + tile * QD_TILE;
+    const bool ok0 = key0 + g < k_hi, ok1 = key0 + g + 8 < k_hi;
+    const int64_t r0 = hb + min(key0 + g, k_hi - 1), r1 = hb + min(key0 + g + 8, k_hi - 1);   // clamped rows are masked below
+    uint32_t kr0[16], kr1[16], vr0[16], vr1[16];   // this lane's 64 bytes of the four rows
 #pragma unroll
-    for (int b = 0; b < QD_BATCH; ++b) {
-      const int64_t r = hb + min(key0 + b, k_hi - 1);
-      kw[b] = __ldg(reinterpret_cast<const uint2*>(p.kp + r * 64) + lane);
-      vw[b] = __ldg(reinterpret_cast<const uint2*>(p.vp + r * 64) + lane);
-      const int64_t gi = r * 4 + (lane >> 3);
-      ksc[b] = load_elem<ST>(p.ks, gi);
-      kbi[b] = load_elem<ST>(p.kb, gi);
-      vsc[b] = load_elem<ST>(p.vs, gi);
-      vbi[b] = load_elem<ST>(p.vb, gi);
+    for (int c = 0; c < 4; ++c) {
+      *reinterpret_cast<uint4*>(&kr0[4 * c]) = __ldg(reinterpret_cast<const uint4*>(p.kp + r0 * 64) + t * 4 + c);
+      *reinterpret_cast<uint4*>(&kr1[4 * c]) = __ldg(reinterpret_cast<const uint4*>(p.kp + r1 * 64) + t * 4 + c);
+      *reinterpret_cast<uint4*>(&vr0[4 * c]) = __ldg(reinterpret_cast<const uint4*>(p.vp + r0 * 64) + t * 4 + c);
+      *reinterpret_cast<uint4*>(&vr1[4 * c]) = __ldg(reinterpret_cast<const uint4*>(p.vp + r1 * 64) + t * 4 + c);
     }
+    const __half2 ks0 = __float2half2_rn(load_elem<ST>(p.ks, r0 * 4 + t)), kb0 = __float2half2_rn(load_elem<ST>(p.kb, r0 * 4 + t));
+    const __half2 ks1 = __float2half2_rn(load_elem<ST>(p.ks, r1 * 4 + t)), kb1 = __float2half2_rn(load_elem<ST>(p.kb, r1 * 4 + t));
+    const __half2 vs0 = __float2half2_rn(load_elem<ST>(p.vs, r0 * 4 + t)), vb0 = __float2half2_rn(load_elem<ST>(p.vb, r0 * 4 + t));
+    const __half2 vs1 = __float2half2_rn(load_elem<ST>(p.vs, r1 * 4 + t)), vb1 = __float2half2_rn(load_elem<ST>(p.vb, r1 * 4 + t));
+
+    // ---- S = K q^T (log2 units): c0, c1 = key g, heads 2 t, 2 t + 1; c2, c3 = key g + 8
+    float sc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int b = 0; b < QD_BATCH; ++b) {
-      if (key0 + b >= k_hi) break;
-      float kf[8], vf[8];
-      const uint32_t kww[2] = {kw[b].x, kw[b].y}, vww[2] = {vw[b].x, vw[b].y};
+    for (int s = 0; s < 16; ++s)
+      mma_f16_16816(sc, dequant_pair(kr0[s], 0, ks0, kb0), dequant_pair(kr1[s], 0, ks1, kb1),
+                    dequant_pair(kr0[s], 1, ks0, kb0), dequant_pair(kr1[s], 1, ks1, kb1), qb[s][0], qb[s][1]);
+    if (!ok0) sc[0] = sc[1] = -INFINITY;
+    if (!ok1) sc[2] = sc[3] = -INFINITY;
+    float mt0 = fmaxf(sc[0], sc[2]), mt1 = fmaxf(sc[1], sc[3]);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        kf[e] = fmaf((float)((kww[e >> 2] >> (8 * (e & 3))) & 0xffu), ksc[b], kbi[b]);
-        vf[e] = fmaf((float)((vww[e >> 2] >> (8 * (e & 3))) & 0xffu), vsc[b], vbi[b]);
+    for (int off = 4; off < 32; off <<= 1) {   // over the eight lanes (keys) that share t
+      mt0 = fmaxf(mt0, __shfl_xor_sync(0xffffffffu, mt0, off));
+      mt1 = fmaxf(mt1, __shfl_xor_sync(0xffffffffu, mt1, off));
+    }
+    const float mn0 = fmaxf(m_run[0], mt0), mn1 = fmaxf(m_run[1], mt1);
+    if (__any_sync(0xffffffffu, mn0 > m_run[0] || mn1 > m_run[1])) {   // a maximum moved: bring O^T and l along
+      const float c0 = m_run[0] == -INFINITY ? 0.f : exp2f(m_run[0] - mn0);
+      const float c1 = m_run[1] == -INFINITY ? 0.f : exp2f(m_run[1] - mn1);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        o[i][0] *= c0; o[i][2] *= c0;
+        o[i][1] *= c1; o[i][3] *= c1;
       }
+      l_run[0] *= c0;
+      l_run[1] *= c1;
+      m_run[0] = mn0;
+      m_run[1] = mn1;
+    }
+    // ---- P (fp16) and its sums; rows without a key weigh nothing
+    const float p00 = ok0 ? exp2f(sc[0] - m_run[0]) : 0.f, p01 = ok0 ? exp2f(sc[1] - m_run[1]) : 0.f;
+    const float p10 = ok1 ? exp2f(sc[2] - m_run[0]) : 0.f, p11 = ok1 ? exp2f(sc[3] - m_run[1]) : 0.f;
+    const __half2 plo = __floats2half2_rn(p00, p01), phi = __floats2half2_rn(p10, p11);
+    l_run[0] += __low2float(plo) + __low2float(phi);   // the weights as the MMA reads them
+    l_run[1] += __high2float(plo) + __high2float(phi);
+    const uint32_t pb0 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&plo));   // head g, keys 2 t, 2 t + 1
+    const uint32_t pb1 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&phi));   // head g, keys 2 t + 8, 2 t + 9
+
+    // ---- O^T += V^T P, 16 dims per MMA: rows 0-7 from value pair 2 i, rows 8-15 from pair 2 i + 1
 #pragma unroll
-      for (int g = 0; g < QD_MAXG; ++g) {
-        if (g < G) {
-          float s = 0.f;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) s = fmaf(qv[g][e], kf[e], s);
-          s = warp_sum(s) * p.scale_log2;
-          const float mn = fmaxf(m[g], s);
-          const float corr = exp2f(m[g] - mn), pw = exp2f(s - mn);   // m = -inf: corr = 0
-          l[g] = l[g] * corr + pw;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) o[g][e] = fmaf(o[g][e], corr, pw * vf[e]);
-          m[g] = mn;
-        }
-      }
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t a0 = movmatrix_trans(dequant_pair(vr0[i], 0, vs0, vb0));
+      const uint32_t a1 = movmatrix_trans(dequant_pair(vr0[i], 1, vs0, vb0));
+      const uint32_t a2 = movmatrix_trans(dequant_pair(vr1[i], 0, vs1, vb1));
+      const uint32_t a3 = movmatrix_trans(dequant_pair(vr1[i], 1, vs1, vb1));
+      mma_f16_16816(o[i], a0, a1, a2, a3, pb0, pb1);
     }
   }
-  // merge the eight warps in warp order
+
+  // ---- merge the warps in warp order
 #pragma unroll
-  for (int g = 0; g < QD_MAXG; ++g) {
-    if (g < G) {
-      if (lane == 0) {
-        m_s[warp][g] = m[g];
-        l_s[warp][g] = l[g];
-      }
-#pragma unroll
-      for (int e = 0; e < 8; ++e) o_s[warp][g][lane * 8 + e] = o[g][e];
-    }
+  for (int off = 4; off < 32; off <<= 1) {
+    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], off);
+    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], off);
   }
+  if (g == 0) {
+    m_s[warp][2 * t] = m_run[0];
+    m_s[warp][2 * t + 1] = m_run[1];
+    l_s[warp][2 * t] = l_run[0];
+    l_s[warp][2 * t + 1] = l_run[1];
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+      o_s[warp][2 * t + (c & 1)][64 * (g >> 1) + 2 * (2 * i + (c >> 1)) + (g & 1)] = o[i][c];
   __syncthreads();
   for (int i = tid; i < G * QD_D; i += QD_WARPS * 32) {
-    const int g = i / QD_D, d = i % QD_D;
+    const int h = i / QD_D, d = i % QD_D;
     float mm = -INFINITY;
-    for (int w = 0; w < QD_WARPS; ++w) mm = fmaxf(mm, m_s[w][g]);
+    for (int w = 0; w < QD_WARPS; ++w) mm = fmaxf(mm, m_s[w][h]);
     float acc = 0.f, ll = 0.f;
     for (int w = 0; w < QD_WARPS; ++w) {
-      const float f = m_s[w][g] == -INFINITY ? 0.f : exp2f(m_s[w][g] - mm);
-      acc = fmaf(o_s[w][g][d], f, acc);
-      ll = fmaf(l_s[w][g], f, ll);
+      const float f = m_s[w][h] == -INFINITY ? 0.f : exp2f(m_s[w][h] - mm);
+      acc = fmaf(o_s[w][h][d], f, acc);
+      ll = fmaf(l_s[w][h], f, ll);
     }
-    const int h = kvh * G + g;
-    p.o_parts[((int64_t)split * p.Hq + h) * QD_D + d] = acc;
+    const int hq = kvh * G + h;
+    p.o_parts[((int64_t)split * p.Hq + hq) * QD_D + d] = acc;
     if (d == 0) {
       // (m, l) in natural-log units for the merge kernel
-      p.ml_parts[((int64_t)split * p.Hq + h) * 2] = mm == -INFINITY ? -INFINITY : mm * 0.6931471805599453f;
-      p.ml_parts[((int64_t)split * p.Hq + h) * 2 + 1] = ll;
+      p.ml_parts[((int64_t)split * p.Hq + hq) * 2] = mm == -INFINITY ? -INFINITY : mm * 0.6931471805599453f;
+      p.ml_parts[((int64_t)split * p.Hq + hq) * 2 + 1] = ll;
     }
   }
 }
@@ -283,8 +352,8 @@ extern "C" int mxb_sdpa_decode_q8(const mxb_sdpa_decode_q8_args* a, void* stream
   MXB_REQUIRE(a->q && a->k_packed && a->k_scales && a->k_biases && a->v_packed && a->v_scales && a->v_biases &&
                   a->o_parts && a->ml_parts,
               MXB_ERR_INVALID, "q8 decode: null tensor");
-  MXB_REQUIRE(((reinterpret_cast<uintptr_t>(a->k_packed) | reinterpret_cast<uintptr_t>(a->v_packed)) & 7) == 0,
-              MXB_ERR_INVALID, "q8 decode: packed words must be 8-byte aligned");
+  MXB_REQUIRE(((reinterpret_cast<uintptr_t>(a->k_packed) | reinterpret_cast<uintptr_t>(a->v_packed)) & 15) == 0,
+              MXB_ERR_INVALID, "q8 decode: packed words must be 16-byte aligned");
   Q8DecodeParams p{};
   p.q = a->q; p.q_dtype = a->q_dtype;
   p.kp = reinterpret_cast<const uint32_t*>(a->k_packed); p.ks = a->k_scales; p.kb = a->k_biases;
@@ -295,12 +364,7 @@ extern "C" int mxb_sdpa_decode_q8(const mxb_sdpa_decode_q8_args* a, void* stream
   p.o_parts = a->o_parts; p.ml_parts = a->ml_parts;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   dim3 grid((unsigned)a->n_splits, (unsigned)a->Hkv);
-  const int smem = (QD_MAXG * QD_D + QD_WARPS * QD_MAXG * QD_D) * (int)sizeof(float);   // 72 KB
-#define MXB_QD(ST)                                                                                            \
-  {                                                                                                           \
-    MXB_CUDA_OK(cudaFuncSetAttribute(q8_decode_kernel<ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
-    q8_decode_kernel<ST><<<grid, QD_WARPS * 32, smem, st>>>(p);                                               \
-  }
+#define MXB_QD(ST) q8_decode_kernel<ST><<<grid, QD_WARPS * 32, 0, st>>>(p);
   if (a->sb_dtype == MXB_F32) MXB_QD(MXB_F32)
   else if (a->sb_dtype == MXB_F16) MXB_QD(MXB_F16)
   else if (a->sb_dtype == MXB_BF16) MXB_QD(MXB_BF16)

@@ -294,22 +294,44 @@ __global__ void __launch_bounds__(256) merge_kernel(MergeParams p) {
       if (sink > -INFINITY) l += expf(sink - m);
     }
   } else {
-    for (int s = 0; s < p.P; ++s) m = fmaxf(m, __ldg(p.ml_parts + ((int64_t)s * N + n) * 2));
+    // many splits: sixteen at a time, every load of a batch issued before anything depends on one (a thread's
+    // loads are otherwise a chain of L2 round trips: 128 splits took 80 us); the sum stays in split order
+    constexpr int kBatch = 16;
+    for (int s0 = 0; s0 < p.P; s0 += kBatch) {
+      float ms[kBatch];
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u)
+        ms[u] = s0 + u < p.P ? __ldg(p.ml_parts + ((int64_t)(s0 + u) * N + n) * 2) : -INFINITY;
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) m = fmaxf(m, ms[u]);
+    }
     m = fmaxf(m, sink);
     if (m > -INFINITY) {
-      for (int s = 0; s < p.P; ++s) {
-        const float ms = __ldg(p.ml_parts + ((int64_t)s * N + n) * 2);
-        const float ls = __ldg(p.ml_parts + ((int64_t)s * N + n) * 2 + 1);
-        if (ms > -INFINITY) {
-          const float w = expf(ms - m);
-          l = fmaf(ls, w, l);
-          const float* src = p.o_parts + ((int64_t)s * N + n) * p.Dv + d0;
-          if constexpr (VEC == 4) {
-            const float4 v = __ldg(reinterpret_cast<const float4*>(src));
-            acc[0] = fmaf(v.x, w, acc[0]); acc[1] = fmaf(v.y, w, acc[1]);
-            acc[2] = fmaf(v.z, w, acc[2]); acc[3] = fmaf(v.w, w, acc[3]);
-          } else {
-            acc[0] = fmaf(__ldg(src), w, acc[0]);
+      for (int s0 = 0; s0 < p.P; s0 += kBatch) {
+        float2 ml[kBatch];
+        float4 v[kBatch];
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+          ml[u] = make_float2(-INFINITY, 0.f);
+          v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (s0 + u < p.P) {
+            const int64_t row = (int64_t)(s0 + u) * N + n;
+            ml[u].x = __ldg(p.ml_parts + row * 2);
+            ml[u].y = __ldg(p.ml_parts + row * 2 + 1);
+            const float* src = p.o_parts + row * p.Dv + d0;
+            if constexpr (VEC == 4) v[u] = __ldg(reinterpret_cast<const float4*>(src));
+            else v[u].x = __ldg(src);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+          if (ml[u].x > -INFINITY) {
+            const float w = expf(ml[u].x - m);
+            l = fmaf(ml[u].y, w, l);
+            acc[0] = fmaf(v[u].x, w, acc[0]);
+            if constexpr (VEC == 4) {
+              acc[1] = fmaf(v[u].y, w, acc[1]); acc[2] = fmaf(v[u].z, w, acc[2]); acc[3] = fmaf(v[u].w, w, acc[3]);
+            }
           }
         }
       }
@@ -329,11 +351,110 @@ __global__ void __launch_bounds__(256) merge_kernel(MergeParams p) {
   }
 }
 
+// Many splits of few rows (a decode token split 128 ways): one CTA per row, the splits spread over the CTA so that a
+// thread's chain of dependent loads is P / lanes long instead of P.  Weights exp(m_s - m) are computed once into
+// shared memory; thread (lane, vec) sums the splits lane, lane + L, ... in ascending order and the L partial sums
+// are added in lane order: the same order on every run.
+constexpr int kMergeRowsMaxP = 1024;
+template <int OT>
+__global__ void __launch_bounds__(256) merge_rows_kernel(MergeParams p) {
+  __shared__ float w_s[kMergeRowsMaxP];
+  __shared__ float red[256];
+  __shared__ float4 part[256];
+  const int64_t N = (int64_t)p.B * p.T * p.H;
+  const int64_t n = blockIdx.x;
+  const int tid = threadIdx.x;
+  const int h = (int)(n % p.H);
+  const int t = (int)((n / p.H) % p.T);
+  const int b = (int)(n / ((int64_t)p.H * p.T));
+  const float sink = (p.finalize && p.sinks) ? p.sinks[h] : -INFINITY;
+  // global maximum
+  float m = -INFINITY;
+  for (int s = tid; s < p.P; s += 256) m = fmaxf(m, __ldg(p.ml_parts + ((int64_t)s * N + n) * 2));
+  red[tid] = m;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (tid < o) red[tid] = fmaxf(red[tid], red[tid + o]);
+    __syncthreads();
+  }
+  m = fmaxf(red[0], sink);
+  __syncthreads();
+  // weights and the denominator (fixed tree order)
+  float lp = 0.f;
+  for (int s = tid; s < p.P; s += 256) {
+    const float ms = __ldg(p.ml_parts + ((int64_t)s * N + n) * 2);
+    const float w = (ms > -INFINITY && m > -INFINITY) ? expf(ms - m) : 0.f;
+    w_s[s] = w;
+    lp = fmaf(__ldg(p.ml_parts + ((int64_t)s * N + n) * 2 + 1), w, lp);
+  }
+  red[tid] = lp;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (tid < o) red[tid] += red[tid + o];
+    __syncthreads();
+  }
+  float l = red[0];
+  if (m > -INFINITY && sink > -INFINITY) l += expf(sink - m);
+  // features: nvec = Dv / 4 vectors, L = 256 / nvec lanes of splits
+  const int nvec = p.Dv / 4, L = 256 / nvec;
+  const int vec = tid % nvec, lane = tid / nvec;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (lane < L) {
+    constexpr int kBatch = 8;
+    for (int s0 = lane; s0 < p.P; s0 += L * kBatch) {
+      float4 v[kBatch];
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const int s = s0 + u * L;
+        v[u] = s < p.P ? __ldg(reinterpret_cast<const float4*>(p.o_parts + ((int64_t)s * N + n) * p.Dv) + vec)
+                       : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const int s = s0 + u * L;
+        const float w = s < p.P ? w_s[s] : 0.f;
+        acc.x = fmaf(v[u].x, w, acc.x); acc.y = fmaf(v[u].y, w, acc.y);
+        acc.z = fmaf(v[u].z, w, acc.z); acc.w = fmaf(v[u].w, w, acc.w);
+      }
+    }
+  }
+  part[tid] = acc;
+  __syncthreads();
+  if (tid < nvec) {
+    float4 r = part[tid];
+    for (int q = 1; q < L; ++q) {
+      const float4 x = part[q * nvec + tid];
+      r.x += x.x; r.y += x.y; r.z += x.z; r.w += x.w;
+    }
+    const int64_t ob = (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)t * p.o_st + 4 * tid;
+    const float inv = (p.finalize ? (l > 0.f ? 1.f / l : 0.f) : 1.f);
+    const float o4[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (p.finalize) store_elem<OT>(p.out, ob + j, o4[j] * inv);
+      else reinterpret_cast<float*>(p.out)[ob + j] = o4[j];
+    }
+    if (!p.finalize && tid == 0) {
+      p.out_ml[n * 2 + 0] = m;
+      p.out_ml[n * 2 + 1] = l;
+    }
+  }
+}
+
 static int launch_merge(const MergeParams& mp, int out_dtype, cudaStream_t st) {
   const int64_t N = (int64_t)mp.B * mp.T * mp.H;
   const bool vec = (mp.Dv % 4 == 0) && ((reinterpret_cast<uintptr_t>(mp.o_parts) & 15) == 0) &&
                    ((reinterpret_cast<uintptr_t>(mp.ml_parts) & 7) == 0);
   const int64_t items = N * (vec ? mp.Dv / 4 : mp.Dv);
+  // few rows, many splits: spread the splits over a CTA per row instead of one thread walking them all
+  if (vec && mp.P > 16 && mp.P <= kMergeRowsMaxP && mp.Dv / 4 <= 256 && 256 % (mp.Dv / 4) == 0 && items < 148 * 2 * 256) {
+    if (out_dtype == MXB_F32) merge_rows_kernel<MXB_F32><<<(unsigned)N, 256, 0, st>>>(mp);
+    else if (out_dtype == MXB_BF16) merge_rows_kernel<MXB_BF16><<<(unsigned)N, 256, 0, st>>>(mp);
+    else merge_rows_kernel<MXB_F16><<<(unsigned)N, 256, 0, st>>>(mp);
+    note_launch();
+    MXB_CUDA_OK(cudaGetLastError());
+    return MXB_OK;
+  }
   dim3 grid((unsigned)ceil_div(items, 256));
 #define MXB_MG(OT)                                             \
   if (vec) merge_kernel<OT, 4><<<grid, 256, 0, st>>>(mp);      \

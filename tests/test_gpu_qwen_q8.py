@@ -91,7 +91,8 @@ def test_decode_q8_matches_composed_path(P, splits, qdt):
     s = np.einsum("hd,phd->hp", q.astype(np.float64), np.repeat(kd, Hq // Hkv, axis=1).astype(np.float64)) / 16.0
     p = np.exp(s - s.max(axis=1, keepdims=True))
     ref = np.einsum("hp,phd->hd", p / p.sum(axis=1, keepdims=True), np.repeat(vd, Hq // Hkv, axis=1).astype(np.float64))
-    assert max_abs(out[0, :, 0], ref) <= (1e-4 if qdt == "f32" else 2e-2)
+    # fp16 operands on the tensor cores (keys, values and P rounded to 11 bits), fp32 accumulation
+    assert max_abs(out[0, :, 0], ref) <= (2e-3 if qdt == "f32" else 2e-2)
 
 
 @torch.no_grad()
