@@ -101,10 +101,10 @@ __global__ void __launch_bounds__(256) sparse_attn_kernel(SparseParams p) {
     if (mine < p.k) atomicMin(&s_keff, mine);
   }
   // q -> smem (fp32)
-  for (int i = tid; i < kHeadsPerCta * p.Dqk; i += blockDim.x) {
-    const int hh = blockIdx.y * kHeadsPerCta + i / p.Dqk, d = i % p.Dqk;
-    q_s[i] = hh < p.H ? load_elem<QT>(p.q, (int64_t)b * p.q_sb + (int64_t)hh * p.q_sh + (int64_t)t * p.q_st + d)
-                      : 0.f;
+  for (int hl = 0; hl < kHeadsPerCta; ++hl) {
+    const int hh = blockIdx.y * kHeadsPerCta + hl;
+    const int64_t qbase = (int64_t)b * p.q_sb + (int64_t)hh * p.q_sh + (int64_t)t * p.q_st;
+    for (int d = tid; d < p.Dqk; d += blockDim.x) q_s[hl * p.Dqk + d] = hh < p.H ? load_elem<QT>(p.q, qbase + d) : 0.f;
   }
   __syncthreads();
   const int total = n_raw + s_keff;
@@ -113,10 +113,12 @@ __global__ void __launch_bounds__(256) sparse_attn_kernel(SparseParams p) {
   const int e_lo = min(split * per, total), e_hi = min(e_lo + per, total);
 
   float M = -INFINITY, S = 0.f;
+  // lane owns the features 4 (lane + 32 i) + e, i < 4, e < 4: one 16-byte shared-memory read per (row, i)
   float o[kMaxDvRegs];
 #pragma unroll
   for (int i = 0; i < kMaxDvRegs; ++i) o[i] = 0.f;
-  const int nreg = (p.Dv + 31) / 32;
+  const int nq4 = (p.Dv + 127) / 128;         // groups of 128 features in use
+  const bool dv4 = (p.Dv & 3) == 0;
 
   for (int e0 = e_lo; e0 < e_hi; e0 += kTileRows) {
     // stage up to 32 rows: warp w takes rows w, w + 8 and w + 16, w + 24, a pair at a time
@@ -179,10 +181,26 @@ __global__ void __launch_bounds__(256) sparse_attn_kernel(SparseParams p) {
         for (int i = 0; i < kMaxDvRegs; ++i) o[i] *= corr;
         for (int j = 0; j < kTileRows; ++j) {
           const float pw = p_s[warp * kTileRows + j];
-          const float* r = rows_s + j * ld + lane;
+          const float* r = rows_s + j * ld + 4 * lane;
 #pragma unroll
-          for (int i = 0; i < kMaxDvRegs; ++i)
-            if (i < nreg) o[i] = fmaf(pw, (lane + 32 * i < p.Dv) ? r[32 * i] : 0.f, o[i]);
+          for (int i = 0; i < kMaxDvRegs / 4; ++i) {
+            if (i < nq4) {
+              const int f0 = 4 * (lane + 32 * i);
+              float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (dv4) {
+                if (f0 < p.Dv) v = *reinterpret_cast<const float4*>(r + 128 * i);
+              } else {
+                if (f0 < p.Dv) v.x = r[128 * i];
+                if (f0 + 1 < p.Dv) v.y = r[128 * i + 1];
+                if (f0 + 2 < p.Dv) v.z = r[128 * i + 2];
+                if (f0 + 3 < p.Dv) v.w = r[128 * i + 3];
+              }
+              o[4 * i] = fmaf(pw, v.x, o[4 * i]);
+              o[4 * i + 1] = fmaf(pw, v.y, o[4 * i + 1]);
+              o[4 * i + 2] = fmaf(pw, v.z, o[4 * i + 2]);
+              o[4 * i + 3] = fmaf(pw, v.w, o[4 * i + 3]);
+            }
+          }
         }
         __syncwarp();
       }
@@ -196,8 +214,10 @@ __global__ void __launch_bounds__(256) sparse_attn_kernel(SparseParams p) {
     if (p.partial_ml) {
       float* outp = reinterpret_cast<float*>(p.out) + (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)t * p.o_st;
 #pragma unroll
-      for (int i = 0; i < kMaxDvRegs; ++i)
-        if (i < nreg && lane + 32 * i < p.Dv) outp[lane + 32 * i] = o[i];
+      for (int i = 0; i < kMaxDvRegs; ++i) {
+        const int f = 4 * (lane + 32 * (i >> 2)) + (i & 3);
+        if (f < p.Dv) outp[f] = o[i];
+      }
       if (lane == 0) {
         p.partial_ml[n_idx * 2 + 0] = M;
         p.partial_ml[n_idx * 2 + 1] = S;
@@ -213,15 +233,28 @@ __global__ void __launch_bounds__(256) sparse_attn_kernel(SparseParams p) {
       const float inv = den > 0.f ? w / den : 0.f;
       const int64_t ob = (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)t * p.o_st;
 #pragma unroll
-      for (int i = 0; i < kMaxDvRegs; ++i)
-        if (i < nreg && lane + 32 * i < p.Dv) store_elem<OT>(p.out, ob + lane + 32 * i, o[i] * inv);
+      for (int i = 0; i < kMaxDvRegs; ++i) {
+        const int f = 4 * (lane + 32 * (i >> 2)) + (i & 3);
+        if (f < p.Dv) store_elem<OT>(p.out, ob + f, o[i] * inv);
+      }
     }
   } else {
     const int64_t N = (int64_t)p.B * p.T * p.H;
     float* wo = p.ws_o + ((int64_t)split * N + n_idx) * p.Dv;
 #pragma unroll
-    for (int i = 0; i < kMaxDvRegs; ++i)
-      if (i < nreg && lane + 32 * i < p.Dv) wo[lane + 32 * i] = o[i];
+    if (dv4) {
+#pragma unroll
+      for (int i = 0; i < kMaxDvRegs / 4; ++i) {
+        const int f0 = 4 * (lane + 32 * i);
+        if (f0 < p.Dv) *reinterpret_cast<float4*>(wo + f0) = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < kMaxDvRegs; ++i) {
+        const int f = 4 * (lane + 32 * (i >> 2)) + (i & 3);
+        if (f < p.Dv) wo[f] = o[i];
+      }
+    }
     if (lane == 0) {
       p.ws_ml[((int64_t)split * N + n_idx) * 2 + 0] = M;
       p.ws_ml[((int64_t)split * N + n_idx) * 2 + 1] = S;
