@@ -207,7 +207,7 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=60))
     W = max(args.warmup, 3)
     K = max(args.steps, 1)
 
@@ -401,19 +401,54 @@ def main():
         line["config"]["workload"] = WORKLOAD + "_SMALL"
 
     extras = {"kernels": kernels}
+    failed = False
     if not args.no_extras and not args.small:
         del plan, cache
         torch.cuda.empty_cache()
         if rank == 0:
             extras.update(run_extras(torch, dev, tf))
-        try:
-            extras["c5a"] = run_c5a(torch, dist, dev, rank, world, hbm, barrier, max_over_ranks)
-        except Exception as e:   # report, do not hide
-            extras["c5a_error"] = repr(e)
-        try:
-            extras["c5b"] = run_c5b(torch, dist, dev, rank, world, barrier, max_over_ranks)
-        except Exception as e:
-            extras["c5b_error"] = repr(e)
+        # The secondary multi-GPU workloads synchronise the ranks through the rendezvous store (host side), not
+        # through NCCL: a rank that fails says so there, the others stop waiting at once and skip what is left,
+        # and the headline line is still printed (a CUDA error is sticky: nothing on the device can follow it).
+        store = dist.distributed_c10d._get_default_store() if world > 1 else None
+        tags = iter(range(1 << 20))
+
+        def soft_barrier():
+            torch.cuda.synchronize()
+            if store is None:
+                return
+            key = f"mxb/bar/{next(tags)}"
+            store.add(key, 1)
+            t0 = time.time()
+            while int(store.add(key, 0)) < world:
+                if store.check(["mxb/failed"]):
+                    raise RuntimeError("another rank failed in a secondary workload")
+                if time.time() - t0 > 300:
+                    raise RuntimeError("a rank did not reach the barrier within 300 s")
+                time.sleep(0.0005)
+
+        def soft_max(xs):
+            if store is None:
+                return [float(x) for x in xs]
+            key = f"mxb/max/{next(tags)}"
+            store.set(f"{key}/{rank}", json.dumps([float(x) for x in xs]))
+            soft_barrier()
+            cols = [json.loads(store.get(f"{key}/{r}")) for r in range(world)]
+            return [max(c[i] for c in cols) for i in range(len(cols[0]))]
+
+        for name, fn in (("c5a", lambda: run_c5a(torch, dist, dev, rank, world, hbm, soft_barrier, soft_max)),
+                         ("c5b", lambda: run_c5b(torch, dist, dev, rank, world, soft_barrier, soft_max))):
+            if failed:
+                extras[name + "_error"] = "skipped: an earlier secondary workload failed"
+                continue
+            try:
+                soft_barrier()                     # nobody starts a workload that a failed rank will never join
+                extras[name] = fn()
+            except Exception as e:   # report, do not hide
+                extras[name + "_error"] = repr(e)
+                failed = True
+                if store is not None:
+                    store.set("mxb/failed", str(rank))
     line["extras"] = extras
     if rank == 0 and not args.no_cpu:
         cores = len(os.sched_getaffinity(0))
@@ -422,7 +457,9 @@ def main():
         line["cpu_baseline"] = {"value": len(seqs) / t, "unit": UNIT, "cores": cores, "kind": "port",
                                 "sample": f"one pass over all {len(seqs)} sequences of the batch, NumPy float32"}
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
+    if failed:
+        os._exit(0)   # the device (or a peer) is in an error state: no orderly teardown of CUDA / NCCL is possible
     if world > 1:
         dist.destroy_process_group()
 
@@ -506,7 +543,7 @@ def run_c5b(torch, dist, dev, rank, world, barrier, max_over_ranks) -> dict:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29541")
         dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev,
-                                timeout=datetime.timedelta(seconds=180))
+                                timeout=datetime.timedelta(seconds=60))
         own_group = True
     else:
         own_group = False

@@ -297,6 +297,37 @@ int mxb_topk_select(const mxb_topk_args* a, void* stream);
 int mxb_topk_select_static(const mxb_topk_args* a, void* stream);
 
 /* ------------------------------------------------------------------------ *
+ * Index arithmetic of the KV-range-sharded decode step (no counterpart in the reference, which is one device):
+ * the two pieces between the local kernels and the collectives, each one launch instead of a chain of
+ * element-wise operations.
+ * mxb_range_candidates: a rank's local top-k as (score, global id) candidates:
+ *   out_scores[i] = ids[i] >= 0 ? scores[ids[i]] : -inf;  out_ids[i] = ids[i] >= 0 ? ids[i] + row_lo : -1.
+ * mxb_range_local_ids: after the global selection over every rank's candidates, the rows THIS rank attends:
+ *   g = pos[i] >= 0 ? cand_ids[(pos[i] / k) * cand_rank_stride + pos[i] % k] : -1;
+ *   out[i] = row_lo <= g < row_lo + rows_local ? g - row_lo : -1.
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  const float* scores;    /* [rows_local] */
+  const int32_t* ids;     /* [k] local ids, ascending, -1 padded */
+  float* out_scores;      /* [k] */
+  int32_t* out_ids;       /* [k] global ids */
+  int32_t k;
+  int64_t row_lo;
+} mxb_range_candidates_args;
+
+typedef struct {
+  const int32_t* pos;        /* [k] positions in the rank-major list of all candidates, -1 padded */
+  const int32_t* cand_ids;   /* global ids of rank r's candidates at cand_ids + r * cand_rank_stride */
+  int64_t cand_rank_stride;  /* elements */
+  int32_t* out;              /* [k] ids local to this rank, -1 where another rank owns the row */
+  int32_t k;
+  int64_t row_lo, rows_local;
+} mxb_range_local_ids_args;
+
+int mxb_range_candidates(const mxb_range_candidates_args* a, void* stream);
+int mxb_range_local_ids(const mxb_range_local_ids_args* a, void* stream);
+
+/* ------------------------------------------------------------------------ *
  * Indexed mixed (sparse) attention, decode and prefill forms.
  * Replaces  indexed_mixed_attention_decode(q, raw_kv, comp_kv, topk, sinks, *, pos0, window, ratio, raw_start)
  *           src/moespresso/runtime/deepseek_v4/indexed_attention_kernel.py:1496-1568

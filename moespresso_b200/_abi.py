@@ -114,6 +114,15 @@ class FlashPrefillArgs(C.Structure):
     ]
 
 
+class RangeCandidatesArgs(C.Structure):
+    _fields_ = [("scores", _p), ("ids", _p), ("out_scores", _p), ("out_ids", _p), ("k", _i32), ("row_lo", _i64)]
+
+
+class RangeLocalIdsArgs(C.Structure):
+    _fields_ = [("pos", _p), ("cand_ids", _p), ("cand_rank_stride", _i64), ("out", _p), ("k", _i32),
+                ("row_lo", _i64), ("rows_local", _i64)]
+
+
 EXPORTS = {
     "mxb_abi_version": (C.c_int, []),
     "mxb_last_error": (C.c_char_p, []),
@@ -128,6 +137,8 @@ EXPORTS = {
     "mxb_affine_q8_quantize": (C.c_int, [C.POINTER(AffineQ8Args), _p]),
     "mxb_affine_q8_dequantize": (C.c_int, [C.POINTER(AffineQ8Args), _p]),
     "mxb_sdpa_decode_q8": (C.c_int, [C.POINTER(SdpaDecodeQ8Args), _p]),
+    "mxb_range_candidates": (C.c_int, [C.POINTER(RangeCandidatesArgs), _p]),
+    "mxb_range_local_ids": (C.c_int, [C.POINTER(RangeLocalIdsArgs), _p]),
     "mxb_topk_workspace_bytes": (_i64, [_i32, _i64, _i32]),
     "mxb_topk_select": (C.c_int, [C.POINTER(TopkArgs), _p]),
     "mxb_topk_select_static": (C.c_int, [C.POINTER(TopkArgs), _p]),

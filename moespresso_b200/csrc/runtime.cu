@@ -93,5 +93,43 @@ extern "C" int mxb_copy_h2d_async(void* dst_device, const void* src_host, int64_
   return MXB_OK;
 }
 
+namespace mxb {
+__global__ void range_candidates_kernel(mxb_range_candidates_args a) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= a.k) return;
+  const int32_t id = a.ids[i];
+  a.out_scores[i] = id >= 0 ? a.scores[id] : -INFINITY;
+  a.out_ids[i] = id >= 0 ? (int32_t)(id + a.row_lo) : -1;
+}
+__global__ void range_local_ids_kernel(mxb_range_local_ids_args a) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= a.k) return;
+  const int32_t pos = a.pos[i];
+  int64_t g = -1;
+  if (pos >= 0) g = a.cand_ids[(int64_t)(pos / a.k) * a.cand_rank_stride + pos % a.k];
+  a.out[i] = (g >= a.row_lo && g < a.row_lo + a.rows_local) ? (int32_t)(g - a.row_lo) : -1;
+}
+}  // namespace mxb
+
+extern "C" int mxb_range_candidates(const mxb_range_candidates_args* a, void* stream) {
+  MXB_REQUIRE(a != nullptr && a->k > 0, MXB_ERR_INVALID, "range candidates: null args or empty list");
+  MXB_REQUIRE(a->scores && a->ids && a->out_scores && a->out_ids, MXB_ERR_INVALID, "range candidates: null tensor");
+  MXB_REQUIRE(a->row_lo >= 0 && a->row_lo < ((int64_t)1 << 31), MXB_ERR_INVALID, "range candidates: global ids must fit 31 bits");
+  mxb::range_candidates_kernel<<<(a->k + 255) / 256, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*a);
+  mxb::note_launch();
+  MXB_CUDA_OK(cudaGetLastError());
+  return MXB_OK;
+}
+
+extern "C" int mxb_range_local_ids(const mxb_range_local_ids_args* a, void* stream) {
+  MXB_REQUIRE(a != nullptr && a->k > 0, MXB_ERR_INVALID, "range local ids: null args or empty list");
+  MXB_REQUIRE(a->pos && a->cand_ids && a->out, MXB_ERR_INVALID, "range local ids: null tensor");
+  MXB_REQUIRE(a->rows_local >= 0 && a->row_lo >= 0, MXB_ERR_INVALID, "range local ids: negative row range");
+  mxb::range_local_ids_kernel<<<(a->k + 255) / 256, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*a);
+  mxb::note_launch();
+  MXB_CUDA_OK(cudaGetLastError());
+  return MXB_OK;
+}
+
 extern "C" int mxb_abi_version(void) { return MXB_ABI_VERSION; }
 extern "C" const char* mxb_last_error(void) { return mxb::g_err; }

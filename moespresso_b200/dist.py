@@ -81,6 +81,24 @@ class CudaOps:
         from .deepseek_v4.indexed_attention_kernel import merge_partials
         return merge_partials(o_parts[:, None, None], ml_parts[:, None, None], sinks)[0, 0]
 
+    # The index arithmetic between the kernels and the collectives, one launch each (the generic drivers below do
+    # the same with a chain of element-wise torch operations, which is what the NumPy stand-ins of the CPU tests get).
+    def candidates(self, scores, local_ids, row_lo, out_scores, out_ids):
+        """out_scores / out_ids [k] (float32 / int32): the local top-k as (score, global id) candidates."""
+        from . import _abi, _torchabi as _t
+        a = _abi.RangeCandidatesArgs()
+        a.scores, a.ids, a.out_scores, a.out_ids = _t.ptr(scores), _t.ptr(local_ids), _t.ptr(out_scores), _t.ptr(out_ids)
+        a.k, a.row_lo = int(local_ids.numel()), int(row_lo)
+        _abi.check(_t.launch("range_candidates", _abi.load().mxb_range_candidates, a))
+
+    def local_ids(self, pos, cand_ids, rank_stride, row_lo, rows_local, out):
+        """out [k] int32: the globally selected rows this rank owns, as local ids (-1 elsewhere)."""
+        from . import _abi, _torchabi as _t
+        a = _abi.RangeLocalIdsArgs()
+        a.pos, a.cand_ids, a.cand_rank_stride, a.out = _t.ptr(pos), _t.ptr(cand_ids), int(rank_stride), _t.ptr(out)
+        a.k, a.row_lo, a.rows_local = int(pos.numel()), int(row_lo), int(rows_local)
+        _abi.check(_t.launch("range_local_ids", _abi.load().mxb_range_local_ids, a))
+
 
 def _all_gather(t: torch.Tensor, group=None) -> torch.Tensor:
     world = dist.get_world_size(group)
@@ -171,6 +189,7 @@ class RangeDecodePlan:
         # partials travel as one tensor: [H, d_v] un-normalised output, then (m, l)
         self.part = torch.empty((heads, self.d_v + 2), dtype=torch.float32, device=dev)
         self.all_part = torch.empty((world, heads, self.d_v + 2), dtype=torch.float32, device=dev)
+        self.mine = torch.empty((self.k,), dtype=torch.int32, device=dev)   # the selected rows this rank owns
         self.out = None
         self._graphs = None
         if graph:
@@ -193,15 +212,29 @@ class RangeDecodePlan:
                 graphs.append(g)
             self._graphs = graphs
 
+    def _fused(self) -> bool:
+        return hasattr(self.ops, "candidates") and int(self.shard.idx_keys.shape[0]) > 0
+
     def _candidates(self):
+        if self._fused():    # scores -> local top-k -> candidates written straight into the send buffer
+            scores = self.ops.scores(self.idx_q, self.idx_w, self.shard.idx_keys)
+            self.ops.candidates(scores, self.ops.topk(scores, self.k), self.shard.row_lo,
+                                self.cand[0].view(torch.float32), self.cand[1])
+            return
         cs, ci = range_step_candidates(self.idx_q, self.idx_w, self.shard, k=self.k, ops=self.ops)
         self.cand[0].copy_(cs.contiguous().view(torch.int32))
         self.cand[1].copy_(ci)
 
     def _partial(self):
-        o, ml, _ = range_step_partial(self.q, self.shard, self.all_cand[:, 0].contiguous().view(torch.float32),
-                                      self.all_cand[:, 1].long(), k=self.k, scale=self.scale, d_v=self.d_v,
-                                      ops=self.ops, want_ids=False)
+        if self._fused():    # global selection over every rank's candidates -> the rows this rank owns -> attention
+            pos = self.ops.topk(self.all_cand[:, 0].contiguous().view(torch.float32).reshape(-1), self.k)
+            self.ops.local_ids(pos, self.all_cand[:, 1], self.all_cand.stride(0), self.shard.row_lo,
+                               int(self.shard.idx_keys.shape[0]), self.mine)
+            o, ml = self.ops.attend_partial(self.q, self.shard.kv, self.shard.kv_scales, self.mine, self.scale, self.d_v)
+        else:
+            o, ml, _ = range_step_partial(self.q, self.shard, self.all_cand[:, 0].contiguous().view(torch.float32),
+                                          self.all_cand[:, 1].long(), k=self.k, scale=self.scale, d_v=self.d_v,
+                                          ops=self.ops, want_ids=False)
         self.part[:, :self.d_v].copy_(o)
         self.part[:, self.d_v:].copy_(ml)
 
