@@ -59,13 +59,18 @@ constexpr int WS_HEADS = 64;      // heads per CTA (MMA N; two planes of 64 for 
 constexpr int WS_MAX_SLABS = 9;   // Dqk <= 576
 constexpr int WS_SLAB = 8192;     // [64 rows or heads] x 128 B
 constexpr int WS_THREADS = 640;   // 20 warps
-constexpr int kWsMiscBytes = 9216;
+constexpr int kWsMiscBytes = 10240;
 constexpr int kRing = 8;          // units of row metadata kept in shared memory (a slot is rewritten six units later)
 constexpr int kMaxClusterMerge = 4;   // splits of a token that can merge through shared memory
-// P = 2^(s - m_ref) may be as large as 2^gap.  bf16 operands have fp32's range; fp16 operands top out at 65504,
-// and the int8 path folds the row's dequantisation scale into P, so its gap shrinks by log2(scale) when positive.
+// An operand weight 2^(s - m_ref) may be as large as 2^gap.  bf16 operands have fp32's range; fp16 operands top out
+// at 65504.  (The int8 path folds the row's dequantisation scale into the weight: there s = logit + log2(scale).)
 constexpr float kRescaleGapF16 = 15.f;
 constexpr float kRescaleGapBF16 = 60.f;
+// A reference that moves is put this far above the unit's maximum (fp16 operands): moving it costs a wait for the
+// previous P V and a pass over O^T, and the maxima of the first units of a list are still far from the list's.  The
+// largest weight of a head is then at least 2^-kRescaleHeadroom, 10 bits above fp16's smallest normal number: weights
+// below a thousandth of the largest one are the first to lose precision.
+constexpr float kRescaleHeadroom = 4.f;
 constexpr uint32_t kNoRow = 0xFFFFFFFFu;
 
 struct WsLayout {
@@ -135,6 +140,9 @@ struct WsMisc {
   uint64_t k_free[2];              // int8 tables: the widening warps have read row buffer b
   uint64_t meta_ready;             // int8 tables: the scales of units 0 and 1 have been published
   uint64_t s_ready[2], s_free[2], p_ready[2];
+  uint64_t p_summed;               // int8 tables: the producer warps have added a unit's P^T to the row sums
+  float row_inv[2][WS_UNIT];       // int8 tables: 1 / row scale of the unit whose P^T is in the buffer (by unit parity)
+  int grew[2];                     // int8 tables: the reference maxima moved before this unit's P^T (by unit parity)
   uint64_t pv_blk[2][4];           // P V of one 128-feature block of the unit in buffer b has completed: its two slabs are free
   uint32_t tmem_slot;
   int abort_flag;
@@ -298,7 +306,7 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
 
   if (tid == 0) {
     ptx::mbar_init(&mi->q_full, 1);
-    ptx::mbar_init(&mi->q_ready, 256);
+    ptx::mbar_init(&mi->q_ready, I8 ? (uint32_t)(WS_THREADS - 128) : 256u);
     for (int i = 0; i < 2; ++i) {
       for (int kb = 0; kb < WS_MAX_SLABS; ++kb) ptx::mbar_init(&mi->full[i][kb], 1);
       ptx::mbar_init(&mi->s_ready[i], I8 ? 1u : 2u);
@@ -310,6 +318,7 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
     ptx::mbar_init(&mi->k_free[0], 4);
     ptx::mbar_init(&mi->k_free[1], 4);
     ptx::mbar_init(&mi->meta_ready, (uint32_t)WS_UNIT);
+    ptx::mbar_init(&mi->p_summed, 4);
     mi->abort_flag = 0;
     mi->keff = p.k;
     ptx::mbar_fence_init();
@@ -406,6 +415,63 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
   constexpr uint32_t fmt = BF16 ? ptx::kFmtBF16 : ptx::kFmtF16;
   const float scale_log2 = p.scale * 1.4426950408889634f;
 
+  if constexpr (I8) {
+    // ---- q as two int8 digit planes, by every warp but the four that are already gathering rows
+    // Per head h: step_h = 2^(e - 13) with 2^e <= max |q[h, :]| < 2^(e + 1); Q = round(q / step_h), |Q| <= 2^14;
+    // Q = 256 hi + lo with lo in [-128, 127]: lo is the low byte of Q and hi the second byte of Q + 128.  Rows h (hi)
+    // and 64 + h (lo) of the B operand: 128-feature slabs of [128 rows x 128 B] with the 128-byte swizzle, the 64
+    // tail features in [128 rows x 64 B] with the 64-byte one.
+    if (warp < 12 || warp >= 16) {
+      constexpr int NST = WS_THREADS - 128;
+      const int st = warp < 12 ? tid : tid - 128;
+      if (p.q_tma) ptx::mbar_wait(&mi->q_full, 0, abort_flag);
+      float amax = 0.f;
+      for (int i = st; i < n_items; i += NST) {   // i % 64 = st % 64: one head per thread
+        float f[8];
+        load_q_item(i, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+      }
+      atomicMax(&mi->q_amax[st & (WS_HEADS - 1)], __float_as_uint(amax));
+      group_sync(6, NST);
+      const uint32_t abits = mi->q_amax[st & (WS_HEADS - 1)];
+      const int ex = (int)(abits >> 23) - 127;   // floor(log2(max)); zeros and denormals: a harmless tiny step
+      const float step = abits == 0u ? 1.f : __uint_as_float((uint32_t)(max(ex - 13, -126) + 127) << 23);
+      const float inv_step = 1.f / step;
+      if (st < WS_HEADS) mi->q_step[st] = step;
+      for (int i = st; i < n_items; i += NST) {
+        const int h = i & (WS_HEADS - 1), c = i >> 6;
+        float f[8];
+        load_q_item(i, f);
+        uint32_t hi_w[2], lo_w[2];
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {
+          int Q[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) Q[e] = max(-16384, min(16384, __float2int_rn(f[4 * w + e] * inv_step)));
+          lo_w[w] = __byte_perm(__byte_perm(Q[0], Q[1], 0x0040), __byte_perm(Q[2], Q[3], 0x0040), 0x5410);
+          hi_w[w] = __byte_perm(__byte_perm(Q[0] + 128, Q[1] + 128, 0x0051), __byte_perm(Q[2] + 128, Q[3] + 128, 0x0051), 0x5410);
+        }
+        const int f0 = c * 8;
+        if (f0 < L.n128 * 128) {
+          uint8_t* base = q_s + (size_t)(f0 >> 7) * 2 * WS_SLAB + (f0 & 8);
+          const int ck = (f0 & 127) >> 4;
+          *reinterpret_cast<uint2*>(base + (size_t)h * 128 + ((ck ^ (h & 7)) << 4)) = make_uint2(hi_w[0], hi_w[1]);
+          *reinterpret_cast<uint2*>(base + (size_t)(64 + h) * 128 + ((ck ^ (h & 7)) << 4)) = make_uint2(lo_w[0], lo_w[1]);
+        } else {
+          const int bb = f0 - L.n128 * 128;
+          uint8_t* base = q_s + (size_t)L.n128 * 2 * WS_SLAB + (bb & 8);
+          const int ck = bb >> 4;
+          *reinterpret_cast<uint2*>(base + (size_t)h * 64 + ((ck ^ ((h >> 1) & 3)) << 4)) = make_uint2(hi_w[0], hi_w[1]);
+          *reinterpret_cast<uint2*>(base + (size_t)(64 + h) * 64 + ((ck ^ (((64 + h) >> 1) & 3)) << 4)) =
+              make_uint2(lo_w[0], lo_w[1]);
+        }
+      }
+      ptx::fence_proxy_async_smem();
+      ptx::mbar_arrive(&mi->q_ready);
+    }
+  }
+
   constexpr int NG = I8 ? 4 : 8;   // gather warps (int8 tables: the other four producer warps widen the values)
   if (warp >= 12 && warp < 12 + NG) {
     // ================================================================ row gathers
@@ -440,7 +506,8 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
         return;
       }
       ref = (uint32_t)ridx | (raw ? 0x80000000u : 0u);
-      if (I8) rs = __half2float(raw ? p.raw_scales[ridx] : p.comp_scales[ridx]);
+      // (a zero scale, i.e. an all-zero row, still counts in the denominator: it is taken as fp16's smallest number)
+      if (I8) rs = fmaxf(__half2float(raw ? p.raw_scales[ridx] : p.comp_scales[ridx]), 5.9604645e-8f);
     };
     auto publish_ref = [&](int U, uint32_t ref) {
       if (resolver && U < nunits) mi->row_ref[U & (kRing - 1)][pt] = ref;
@@ -533,9 +600,46 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
       const uint32_t row_off = (uint32_t)(cw * 8 + r8) * 128;
       const uint32_t src_lo = row_off + (uint32_t)((cl ^ r8) << 4), src_hi = src_lo ^ 64u;   // features 0-63 / 64-127 of an int8 slab
       const uint32_t dst0 = row_off + (uint32_t)(((2 * cl) ^ r8) << 4), dst1 = dst0 ^ 16u;
+      // These warps also keep the row sums of P^T, so that the softmax warps do not have to: thread = (head, half
+      // of the unit's rows) reads its 32 fp16 weights of a finished P^T from shared memory and adds them up, once
+      // as they are (for the value bias) and once divided by the row scale (the softmax denominator).  When the
+      // reference maxima moved before a unit, the sums so far are rescaled first, as O^T was.
+      const int sh = (cw * 32 + lane) & (WS_HEADS - 1), shalf = (cw * 32 + lane) >> 6;
+      float l_run = 0.f, w_run = 0.f;
+      auto add_unit = [&](int v) {
+        ptx::mbar_wait(&mi->p_ready[0], pphase(v), abort_flag);
+        if (mi->grew[v & 1]) {
+          const float f = mi->factor[sh];
+          l_run *= f;
+          w_run *= f;
+        }
+        const uint8_t* prow = smem + pt0 + (size_t)sh * 128;
+        float ls = 0.f, ws = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int c = 4 * shalf + i;   // rows 8 c .. 8 c + 7
+          const uint4 x = *reinterpret_cast<const uint4*>(prow + ((c ^ (sh & 7)) << 4));
+          const float4 i0 = *reinterpret_cast<const float4*>(&mi->row_inv[v & 1][8 * c]);
+          const float4 i1 = *reinterpret_cast<const float4*>(&mi->row_inv[v & 1][8 * c + 4]);
+          const __half2* hx = reinterpret_cast<const __half2*>(&x);
+          const float2 a = __half22float2(hx[0]), b2 = __half22float2(hx[1]), c2 = __half22float2(hx[2]), d = __half22float2(hx[3]);
+          ws += ((a.x + a.y) + (b2.x + b2.y)) + ((c2.x + c2.y) + (d.x + d.y));
+          ls = fmaf(a.x, i0.x, ls); ls = fmaf(a.y, i0.y, ls); ls = fmaf(b2.x, i0.z, ls); ls = fmaf(b2.y, i0.w, ls);
+          ls = fmaf(c2.x, i1.x, ls); ls = fmaf(c2.y, i1.y, ls); ls = fmaf(d.x, i1.z, ls); ls = fmaf(d.y, i1.w, ls);
+        }
+        l_run += ls;
+        w_run += ws;
+        if (v == nunits - 1) {   // the totals, for the epilogue (the column maxima are not needed any more)
+          mi->colmax[shalf][sh] = l_run;
+          mi->colmax[2 + shalf][sh] = w_run;
+        }
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&mi->p_summed);
+      };
       ptx::mbar_wait(&mi->q_ready, 0, abort_flag);   // q's scratch copy (in the value buffer) has been consumed
       for (int u = 0; u < nunits; ++u) {
         const int buf = u & 1;
+        if (u >= 1) add_unit(u - 1);
         for (int sl = 0; sl < n_mt; ++sl) ptx::mbar_wait(&mi->full[buf][sl], sphase(u), abort_flag);   // the value features have landed
         if (cw == 0) TRS(13, u);
         const uint8_t* src = smem + (kb0 + buf * kb_st);
@@ -578,6 +682,7 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
         }
         if (cw == 0) TRS(15, u);
       }
+      if (nunits >= 1) add_unit(nunits - 1);
     }
   } else if (warp == 8 || warp == 9) {
     // ================================================================ S^T = Kunit . Q^T issuers
@@ -673,52 +778,7 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
     // ---- q: finish the operand
     if (p.q_tma) ptx::mbar_wait(&mi->q_full, 0, abort_flag);
     if constexpr (I8) {
-      // Per head h: step_h = 2^(e - 13) with 2^e <= max |q[h, :]| < 2^(e + 1); Q = round(q / step_h), |Q| <= 2^14;
-      // Q = 256 hi + lo with lo in [-128, 127].  Rows h (hi) and 64 + h (lo) of the B operand: 128-feature slabs of
-      // [128 rows x 128 B] with the 128-byte swizzle, the 64 tail features in [128 rows x 64 B] with the 64-byte one.
-      float amax = 0.f;
-      for (int i = tid; i < n_items; i += 256) {   // i % 64 = tid % 64: one head per thread
-        float f[8];
-        load_q_item(i, f);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
-      }
-      atomicMax(&mi->q_amax[tid & (WS_HEADS - 1)], __float_as_uint(amax));
-      group_sync(4, 256);
-      const uint32_t abits = mi->q_amax[tid & (WS_HEADS - 1)];
-      const int ex = (int)(abits >> 23) - 127;   // floor(log2(max)); zeros and denormals: a harmless tiny step
-      const float step = abits == 0u ? 1.f : __uint_as_float((uint32_t)(max(ex - 13, -126) + 127) << 23);
-      const float inv_step = 1.f / step;
-      if (tid < WS_HEADS) mi->q_step[tid] = step;
-      for (int i = tid; i < n_items; i += 256) {
-        const int h = i & (WS_HEADS - 1), c = i >> 6;
-        float f[8];
-        load_q_item(i, f);
-        uint32_t hi_w[2] = {0u, 0u}, lo_w[2] = {0u, 0u};
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          int Q = __float2int_rn(f[e] * inv_step);
-          Q = max(-16384, min(16384, Q));
-          const int hi = (Q + 128) >> 8;
-          const int lo = Q - (hi << 8);
-          hi_w[e >> 2] |= (uint32_t)(hi & 0xff) << (8 * (e & 3));
-          lo_w[e >> 2] |= (uint32_t)(lo & 0xff) << (8 * (e & 3));
-        }
-        const int f0 = c * 8;
-        if (f0 < L.n128 * 128) {
-          uint8_t* base = q_s + (size_t)(f0 >> 7) * 2 * WS_SLAB + (f0 & 8);
-          const int ck = (f0 & 127) >> 4;
-          *reinterpret_cast<uint2*>(base + (size_t)h * 128 + ((ck ^ (h & 7)) << 4)) = make_uint2(hi_w[0], hi_w[1]);
-          *reinterpret_cast<uint2*>(base + (size_t)(64 + h) * 128 + ((ck ^ (h & 7)) << 4)) = make_uint2(lo_w[0], lo_w[1]);
-        } else {
-          const int bb = f0 - L.n128 * 128;
-          uint8_t* base = q_s + (size_t)L.n128 * 2 * WS_SLAB + (bb & 8);
-          const int ck = bb >> 4;
-          *reinterpret_cast<uint2*>(base + (size_t)h * 64 + ((ck ^ ((h >> 1) & 3)) << 4)) = make_uint2(hi_w[0], hi_w[1]);
-          *reinterpret_cast<uint2*>(base + (size_t)(64 + h) * 64 + ((ck ^ (((64 + h) >> 1) & 3)) << 4)) =
-              make_uint2(lo_w[0], lo_w[1]);
-        }
-      }
+      // the digit planes were written before the roles parted
     } else if (!p.q_tma) {
       // [64 heads x Dqk] K-major, 128-byte swizzle, rounded to the operand type; a warp writes 32 different rows
       for (int i = tid; i < n_items; i += 256) {
@@ -735,13 +795,16 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
             make_uint4(w[0], w[1], w[2], w[3]);
       }
     }
-    ptx::fence_proxy_async_smem();
-    ptx::mbar_arrive(&mi->q_ready);
-    if constexpr (I8) ptx::mbar_wait(&mi->q_ready, 0, abort_flag);   // every fixed-point step has been written
+    if constexpr (!I8) {
+      ptx::fence_proxy_async_smem();
+      ptx::mbar_arrive(&mi->q_ready);
+    } else {
+      ptx::mbar_wait(&mi->q_ready, 0, abort_flag);   // every fixed-point step has been written
+    }
 
-    // Sums of head col0 + li over this warp's rows of all units: l1 of the softmax weights (the denominator), w1
-    // (int8 tables) of the fp16 operand weights, which carry the row scale.
-    float l1 = 0.f, w1 = 0.f;
+    // 16-bit tables: l1 = the sum of the softmax weights of head col0 + li over this warp's rows of all units (the
+    // denominator).  Int8 tables: the producer warps keep both sums (see add_unit).
+    float l1 = 0.f;
     for (int u = 0; u < nunits; ++u) {
       const int sb_i = sbuf(u), pb_i = pbuf(u), slot = u & (kRing - 1);
       ptx::mbar_wait(&mi->s_ready[sb_i], sphase(u), abort_flag);
@@ -775,8 +838,11 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
       const bool ok = mi->row_ref[slot][row] != kNoRow;
       const float rs = I8 ? mi->row_scale[slot][row] : 1.f;
       const float mul = scale_log2 * rs;
-      float gap = BF16 ? kRescaleGapBF16 : kRescaleGapF16;
-      if (I8 && rs > 1.f) gap -= log2f(rs);
+      // Int8 tables: the operand weight of a row is its softmax weight times the row's dequantisation scale, and
+      // that product is what has to fit fp16.  So the references follow the maxima of logit + log2(scale): the
+      // largest operand weight of a head is 1 (2^-headroom) when its reference moves, whatever the scales are.
+      const float lrs = (I8 && ok) ? log2f(rs) : 0.f;
+      const float gap = BF16 ? kRescaleGapBF16 : kRescaleGapF16;
       bool grow = false;
 #pragma unroll
       for (int c = 0; c < 16; c += 4) {
@@ -784,12 +850,13 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
         const float mrv[4] = {mr.x, mr.y, mr.z, mr.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float x = ok ? __uint_as_float(sv[c + e]) * mul : -INFINITY;
+          const float x = ok ? fmaf(__uint_as_float(sv[c + e]), mul, lrs) : -INFINITY;
           sv[c + e] = __float_as_uint(x);
           grow |= x > mrv[e] + gap;
         }
       }
       if (warp == 0) TRS(6, u);
+      bool grown = false;
       if (__syncthreads_or_256(grow)) {
         // exact column maxima of this unit (xor shuffles of 8, 4, 2, 1 stay inside a half warp = one head range)
 #pragma unroll
@@ -801,20 +868,24 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
           o = max(o, __shfl_xor_sync(0xffffffffu, o, 1));
           if (li == c) mi->colmax[wq][col0 + c] = order_float(o);
         }
-        // O^T belongs to the old reference: it is final for the units so far once the previous P V is done
+        // O^T belongs to the old reference: it is final for the units so far once the previous P V is done (and
+        // the row sums have taken the previous factor, if any, before this one replaces it)
+        if (warp == 0) TRS(29, u);
         if (u >= 1) wait_pv_all(u - 1);
+        if (I8 && u >= 1) ptx::mbar_wait(&mi->p_summed, (uint32_t)((u - 1) & 1), abort_flag);
+        if (warp == 0) TRS(30, u);
         group_sync(4, 256);
         if (tid < WS_HEADS) {
           const float old = mi->m_ref[tid];
           float mx = fmaxf(fmaxf(mi->colmax[0][tid], mi->colmax[1][tid]), fmaxf(mi->colmax[2][tid], mi->colmax[3][tid]));
-          mx = fmaxf(mx, old);
+          mx = mx > old ? mx + (BF16 ? 0.f : kRescaleHeadroom) : old;
           mi->factor[tid] = (old == -INFINITY) ? 0.f : exp2f(old - mx);
           mi->m_ref[tid] = mx;
         }
         group_sync(4, 256);
         ptx::tc_fence_after_sync();
-        l1 *= mi->factor[col0 + li];
-        w1 *= mi->factor[col0 + li];
+        if constexpr (!I8) l1 *= mi->factor[col0 + li];
+        grown = true;
         if (u >= 1) {
           // warp -> (lane quarter of TMEM = 32 features, two of the four 128-feature blocks); columns = heads
           for (int m2 = 0; m2 < 2; ++m2) {
@@ -834,6 +905,7 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
           }
           ptx::tmem_st_wait();
         }
+        if (warp == 0) TRS(28, u);
       }
       // ---- P^T (16-bit, K-major, swizzled); the weights join this thread's sums as the operand holds them
       uint32_t prw[8];
@@ -844,10 +916,6 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
           const float s0 = __uint_as_float(sv[c]), s1 = __uint_as_float(sv[c + 1]);
           float p0 = (s0 == -INFINITY) ? 0.f : fast_exp2(s0 - mr.x);
           float p1 = (s1 == -INFINITY) ? 0.f : fast_exp2(s1 - mr.y);
-          if (I8) {
-            p0 *= rs;
-            p1 *= rs;
-          }
           float b0, b1;
           prw[c >> 1] = pack_op16x2<BF16>(p0, p1, b0, b1);
           sv[c] = __float_as_uint(b0);   // the weights as the operand holds them
@@ -855,7 +923,14 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
         }
       }
       if (warp == 0) TRS(7, u);
-      if (I8 && u >= 1) wait_pv_all(u - 1);   // the one P^T buffer has been read by the previous unit's P V
+      if (I8 && u >= 1) {   // the one P^T buffer has been read by the previous unit's P V and by the row sums
+        wait_pv_all(u - 1);
+        ptx::mbar_wait(&mi->p_summed, (uint32_t)((u - 1) & 1), abort_flag);
+      }
+      if constexpr (I8) {
+        if (cset == 0 && ch == 0) mi->row_inv[u & 1][row] = ok ? __frcp_rn(rs) : 0.f;
+        if (tid == 0) mi->grew[u & 1] = grown ? 1 : 0;
+      }
       {
         uint8_t* pbase = smem + (pt0 + (pb_i) * pt_st) + (row & 7) * 2;
         const int cj = row >> 3;
@@ -871,20 +946,12 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(&mi->p_ready[pb_i]);
       if (warp == 0) TRS(8, u);
-      // the sums over the 16 rows of this half warp, behind the hand-off
-      {
+      // 16-bit tables: the sums over the 16 rows of this half warp, behind the hand-off (int8 tables: the producer
+      // warps sum P^T from shared memory)
+      if constexpr (!I8) {
         float a[16];
-        if constexpr (I8) {
 #pragma unroll
-          for (int c = 0; c < 16; ++c) a[c] = __uint_as_float(sv[c]);
-          w1 += half_warp_column_sum(a, li);
-          const float inv = __frcp_rn(rs);
-#pragma unroll
-          for (int c = 0; c < 16; ++c) a[c] = __uint_as_float(sv[c]) * inv;
-        } else {
-#pragma unroll
-          for (int c = 0; c < 16; ++c) a[c] = __uint_as_float(sv[c]);
-        }
+        for (int c = 0; c < 16; ++c) a[c] = __uint_as_float(sv[c]);
         l1 += half_warp_column_sum(a, li);
       }
     }
@@ -892,8 +959,8 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
     // ------------------------------------------------------------------ row sums over all units
     if (tid == 0) TRS(11, 2);
     group_sync(4, 256);   // nobody reads the column maxima or the row ring any more
-    mi->colmax[wq][col0 + li] = l1;
-    if constexpr (I8) mi->row_scale[wq][col0 + li] = w1;
+    if constexpr (!I8) mi->colmax[wq][col0 + li] = l1;
+    if (I8 && nunits >= 1) ptx::mbar_wait(&mi->p_summed, (uint32_t)((nunits - 1) & 1), abort_flag);   // the totals are in
     if (nunits >= 1) wait_pv_all(nunits - 1);
     if (!I8 && nunits >= 2) wait_pv_all(nunits - 2);
     ptx::tc_fence_after_sync();
@@ -902,11 +969,14 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
 
     // ------------------------------------------------------------------ per-head sums of this split
     if (tid < WS_HEADS) {
-      const float l = (mi->colmax[0][tid] + mi->colmax[1][tid]) + (mi->colmax[2][tid] + mi->colmax[3][tid]);
+      float l, vb = 0.f;
+      if constexpr (I8) {   // rows 0-1: the denominator's two halves, rows 2-3: the operand weights' (producer warps)
+        l = nunits >= 1 ? mi->colmax[0][tid] + mi->colmax[1][tid] : 0.f;
+        vb = nunits >= 1 ? kValueBias * (mi->colmax[2][tid] + mi->colmax[3][tid]) : 0.f;
+      } else {
+        l = (mi->colmax[0][tid] + mi->colmax[1][tid]) + (mi->colmax[2][tid] + mi->colmax[3][tid]);
+      }
       mi->l_tot[tid] = l;
-      float vb = 0.f;
-      if constexpr (I8)
-        vb = kValueBias * ((mi->row_scale[0][tid] + mi->row_scale[1][tid]) + (mi->row_scale[2][tid] + mi->row_scale[3][tid]));
       mi->v_bias[tid] = vb;
       if (p.cluster_merge) {   // tell every split of this token (this one included) where this one stands
         const uint32_t am = ptx::smem_u32(&mi->xm[split][tid]), al = ptx::smem_u32(&mi->xl[split][tid]);
@@ -927,6 +997,7 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
     __syncwarp();
     ptx::cluster_arrive();   // (1) every split's (m, l) is in place and every CTA's buffers are idle
     ptx::cluster_wait();
+    if (tid == 0) TRS(11, 5);
   }
   const int n_slots = cmerge ? (n_mt + p.nsplit - 1) / p.nsplit : 0;   // value blocks a CTA merges: mt = rank + slot * nsplit
   float* recv = reinterpret_cast<float*>(smem);   // cluster merge: [slot][source split][16 head groups][128 features][4 heads]
@@ -1018,9 +1089,11 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
     }
   }
   if (cmerge) {
+    if (tid == 0) TRS(11, 6);
     __syncwarp();
     ptx::cluster_arrive();   // (2) every split's weighted blocks have arrived; nothing remote is touched after this
     ptx::cluster_wait();
+    if (tid == 0) TRS(11, 7);
     if (warp < 8) {
       // thread = (feature of the block, half of the head groups): sum the splits in split order, store the output
       const int f = tid & 127, hg0 = (tid >> 7) * 8;

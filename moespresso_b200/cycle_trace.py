@@ -112,10 +112,17 @@ def main(argv) -> int:
     t, units, ms = trace(argv[1])
     print(f"{argv[1]}: kernel (+ merge) {ms * 1e3:.1f} us with the stamps; cycles of CTA 0 relative to its start")
     print("prologue done %d | softmax loop done %d | last P V done %d | CTA end %d" % tuple(int(t[11, i]) for i in (1, 2, 3, 4)))
+    if t[11, 5:8].any():
+        print("cluster merge: (m, l) exchanged %d | blocks pushed %d | blocks arrived %d" % tuple(int(t[11, i]) for i in (5, 6, 7)))
     order = [0, 1, 2, 3, 4, 5, 6, 7, 12, 8, 9, 10, 13, 15]
     print("unit " + " ".join(f"{EVENTS[r]:>15s}" for r in order))
     for u in range(units):
         print(f"{u:4d} " + " ".join(f"{int(t[r, u]):15d}" for r in order))
+    if t[28:31].any():
+        print("units whose reference maxima moved: column maxima done, previous P V and sums done, O^T rescaled")
+        for u in range(units):
+            if t[28, u]:
+                print(f"{u:4d} {int(t[29, u]):10d} {int(t[30, u]):10d} {int(t[28, u]):10d}")
     if t[16:28].any():
         print("widening warp 0, per unit: rows 16-27 (half starts, preloads done, block stores done)")
         for u in range(min(units, 8)):

@@ -402,6 +402,35 @@ def test_tensor_core_kernel_peaked_softmax_and_empty_tiles():
     assert float(o.abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("ns", [1, 2, 4])
+def test_tensor_core_kernel_int8_scales_that_rise_and_rows_of_zeros(ns):
+    """Int8 rows whose dequantisation scales rise through the list by three decades (the reference maxima, which
+    follow logit + log2(scale), keep moving, and O is rescaled each time), with all-zero rows (scale 0) in between:
+    those carry no value but count in the denominator with logit 0."""
+    need_gpu()
+    rng = np.random.default_rng(5)
+    H, Dqk, Dv, R, k = 64, 576, 512, 3000, 1024
+    q = bf16_round(rng.standard_normal((H, Dqk)) * 0.5)
+    kv = rng.integers(-127, 128, size=(R, Dqk), dtype=np.int8)
+    sc = (np.exp(np.linspace(np.log(2e-4), np.log(0.2), R)) * rng.uniform(0.5, 1.0, R)).astype(np.float16)
+    zero = rng.choice(R, size=300, replace=False)
+    sc[zero] = 0
+    kv[zero[:150]] = 0                      # a quantiser writes zeros there; the other half keeps stale bytes
+    rows = kv.astype(np.float64) * sc.astype(np.float64)[:, None]
+    ids = np.sort(rng.choice(R, size=k, replace=False)).astype(np.int32)
+    ref = ds4.indexed_mixed_attention_decode(q, None, rows, ids, None, pos0=0, window=0, ratio=0, scale=Dqk ** -0.5,
+                                             d_v=Dv)
+    o = iak.sparse_attention(dev(q, torch.bfloat16)[None, :, None, :], dev(kv), dev(ids)[None, None], None, pos0=0,
+                             window=0, ratio=0, scale=Dqk ** -0.5, d_v=Dv, kv_scales=dev(sc), n_splits=ns,
+                             check=True)[0, :, 0]
+    assert max_abs(o, ref) <= TOL_16 * max(1.0, float(np.abs(ref).max()) / 4), max_abs(o, ref)
+    # a list of nothing but zero rows: uniform weights over zero values
+    only = np.sort(zero[:150])[:128].astype(np.int32)
+    o = iak.sparse_attention(dev(q, torch.bfloat16)[None, :, None, :], dev(kv), dev(only)[None, None], None, pos0=0,
+                             window=0, ratio=0, scale=Dqk ** -0.5, d_v=Dv, kv_scales=dev(sc), check=True)
+    assert float(o.abs().max()) == 0.0 and bool(torch.isfinite(o).all())
+
+
 def test_tensor_core_kernel_prefill_form():
     need_gpu()
     rng = np.random.default_rng(8)
