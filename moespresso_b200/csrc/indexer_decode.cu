@@ -28,6 +28,21 @@
 
 namespace mxb {
 
+// 16 bytes of read-only global memory that nobody reads again soon: past L1, first in line for eviction from L2.
+__device__ __forceinline__ uint64_t make_stream_policy() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint4 ld_stream(const uint4* src, uint64_t policy) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(src), "l"(policy));
+  return v;
+}
+
+
 struct DecodeIdxParams {
   const uint8_t* keys;
   const void* q;
@@ -181,6 +196,9 @@ __global__ void __launch_bounds__(kDecWarps * 32, (D == 64 && NT <= 2) ? 3 : 1) 
     float* st = p.scores + (p.row_start ? p.row_start[b] : 0) + (int64_t)b * p.s_sb + seg_lo + g + 8 * t;
     const int64_t n_here = seg_hi - seg_lo;
 
+    // The keys are read once per step and are larger than L2: they are marked to be evicted first, so that they do
+    // not push out what the next kernels of the step come back to (their code, the scores, the lists, the queries).
+    const uint64_t stream_policy = make_stream_policy();
     // warps interleave groups of kDecUnroll tiles so that the CTA reads one contiguous stream
     for (int64_t go = (int64_t)warp * kDecGroup; go < n_here; go += kDecCtaRows) {
       const int64_t left64 = n_here - go;
@@ -193,7 +211,7 @@ __global__ void __launch_bounds__(kDecWarps * 32, (D == 64 && NT <= 2) ? 3 : 1) 
 #pragma unroll
           for (int hrow = 0; hrow < 2; ++hrow)
 #pragma unroll
-            for (int v = 0; v < VPL; ++v) raw[u][hrow][v] = __ldg(src + (u * 16 + hrow * 8) * (D / 16) + v);
+            for (int v = 0; v < VPL; ++v) raw[u][hrow][v] = ld_stream(src + (u * 16 + hrow * 8) * (D / 16) + v, stream_policy);
       } else {
 #pragma unroll
         for (int u = 0; u < kDecUnroll; ++u)
@@ -202,7 +220,7 @@ __global__ void __launch_bounds__(kDecWarps * 32, (D == 64 && NT <= 2) ? 3 : 1) 
             const int rr = min(u * 16 + hrow * 8 + g, left - 1);   // clamped rows are computed and discarded
             const uint4* src = reinterpret_cast<const uint4*>(kt + (go + rr) * D);
 #pragma unroll
-            for (int v = 0; v < VPL; ++v) raw[u][hrow][v] = __ldg(src + v);
+            for (int v = 0; v < VPL; ++v) raw[u][hrow][v] = ld_stream(src + v, stream_policy);
           }
       }
 #pragma unroll

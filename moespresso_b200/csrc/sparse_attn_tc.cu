@@ -1102,12 +1102,15 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
         if (mt >= n_mt) break;
         const int d = mt * 128 + f;
         const float4* src = reinterpret_cast<const float4*>(recv) + (size_t)(slot * p.nsplit) * 16 * 128 + f;
-#pragma unroll 1
-        for (int hg = hg0; hg < hg0 + 8; ++hg) {
+#pragma unroll 4
+        for (int hg = hg0; hg < hg0 + 8; ++hg) {   // (several head groups' loads in flight)
           float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (int r = 0; r < p.nsplit; ++r) {
-            const float4 v = src[(size_t)(r * 16 + hg) * 128];
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+#pragma unroll
+          for (int r = 0; r < kMaxClusterMerge; ++r) {
+            if (r < p.nsplit) {
+              const float4 v = src[(size_t)(r * 16 + hg) * 128];
+              acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
           }
           const float o4[4] = {acc.x, acc.y, acc.z, acc.w};
           const int64_t ob = (int64_t)b * p.o_sb + (int64_t)t * p.o_st + d;
