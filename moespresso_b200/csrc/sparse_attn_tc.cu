@@ -446,11 +446,13 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
         uint32_t hi_w[2], lo_w[2];
 #pragma unroll
         for (int w = 0; w < 2; ++w) {
-          int Q[4];
+          // round(q / step) by one fused multiply-add: adding 1.5 * 2^23 leaves the integer (|Q| <= 2^14 by the choice
+          // of the step, rounded to nearest even like a conversion) in the low mantissa bits, in two's complement
+          uint32_t Q[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) Q[e] = max(-16384, min(16384, __float2int_rn(f[4 * w + e] * inv_step)));
+          for (int e = 0; e < 4; ++e) Q[e] = __float_as_uint(fmaf(f[4 * w + e], inv_step, 12582912.f));
           lo_w[w] = __byte_perm(__byte_perm(Q[0], Q[1], 0x0040), __byte_perm(Q[2], Q[3], 0x0040), 0x5410);
-          hi_w[w] = __byte_perm(__byte_perm(Q[0] + 128, Q[1] + 128, 0x0051), __byte_perm(Q[2] + 128, Q[3] + 128, 0x0051), 0x5410);
+          hi_w[w] = __byte_perm(__byte_perm(Q[0] + 128u, Q[1] + 128u, 0x0051), __byte_perm(Q[2] + 128u, Q[3] + 128u, 0x0051), 0x5410);
         }
         const int f0 = c * 8;
         if (f0 < L.n128 * 128) {
