@@ -354,7 +354,8 @@ typedef struct {
   int64_t q_stride_b, q_stride_h, q_stride_t;
   const void* comp_kv;    /* flat [comp_rows_total, Dqk] */
   int32_t kv_dtype;       /* F32 | F16 | BF16 | I8 */
-  const void* comp_scales;          /* fp16 [comp_rows_total], I8 only */
+  const void* comp_scales;          /* fp16 [comp_rows_total], I8 only; a row of scale 0 is a row of zeros: it adds
+                                       exp(0 - m) to the denominator and nothing to the output */
   const int64_t* comp_row_start;    /* [B] or NULL: b*n_comp */
   const int32_t* comp_row_count;    /* [B] or NULL: n_comp */
   int64_t n_comp;
