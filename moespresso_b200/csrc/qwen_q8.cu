@@ -96,19 +96,26 @@ __global__ void __launch_bounds__(128) affine_q8_dequantize_kernel(const uint32_
 // decode: one query token, head_dim 256, GQA group of up to 8 query heads per KV head
 // ---------------------------------------------------------------------------------------------
 // Warp-level tensor-core flash decoding (mma.sync m16n8k16, fp16 operands, fp32 accumulation) straight from the
-// packed rows: a warp takes 16 keys at a time.
-//   S [16 keys x 8 heads]  = K . q^T : lane (g, t) loads the 64 contiguous bytes [64 t, 64 t + 64) of key rows g and
-//     g + 8 — exactly one quantisation group, so one (scale, bias) pair per row — and uses bytes 4 s .. 4 s + 3 as
-//     its A-fragment elements of k-step s; q is loaded under the same permutation of the feature axis, so the
-//     contraction is unchanged.  Bytes become fp16 exactly (0x6400 | u is 1024 + u), then u * scale + bias in one
-//     fused half2 operation.
-//   O^T [256 dims x 8 heads] += V^T . P : the dequantised value pairs of a lane are 8 x 8 blocks in the layout of
-//     `movmatrix`; transposed, they are A fragments whose 16 rows are the dims {64 c + 2 j + e}; P (fp16) goes from
-//     the accumulator layout of S to the B layout by two more transposes.
+// packed rows: a warp takes 16 keys at a time, and the bytes enter both contractions as they are stored.
+// A byte becomes an fp16 operand exactly by one byte-permute (0x6400 | u is 1024 + u); since
+// w = u * scale + bias = (1024 + u) * scale + (bias - 1024 scale) and scale and bias are constant over a group of 64
+// features, the affine part is applied per GROUP, outside the MMAs: every k-step (keys) and every 16-dim block (values)
+// lies inside one quantisation group.  Lane (g, t) loads the bytes [16 t, 16 t + 16) of each of the four groups of
+// key rows g and g + 8.
+//   S [16 keys x 8 heads] = K . q^T : k-step i = 4 grp + w takes bytes 4 w .. 4 w + 3 of the lane's piece of group
+//     grp (q is loaded under the same permutation of the feature axis); after the four k-steps of a group,
+//     S += scale[key, grp] * (bytes . q) + (bias - 1024 scale)[key, grp] * (sum of q over the group), the sums of q
+//     coming from four MMAs against a matrix of ones in the prologue (already in the accumulator layout).
+//   O^T [256 dims x 8 heads] += V^T . P : the byte pairs of a lane are 8 x 8 blocks in the layout of `movmatrix`;
+//     transposed, they are A fragments whose 16 rows are dims of one group.  The key's scale for that group is
+//     multiplied into P (rounded to fp16, two more transposes bring it to the B layout), and
+//     sum over keys of P * bias - 1024 * (P * scale as rounded) is kept per group and head beside the accumulators
+//     and added to every dim of the group at the end: the 1024s cancel against exactly the weights the MMA used.
 // Online softmax per head with a lazy rescale of O^T (only when a maximum moved).  Measured on a B200 (131,072 keys,
-// 2 KV heads, 128 splits): 60 us, 0.3 of the HBM rate — the warp-level MMA path runs at an eighth of the tcgen05
-// rate and, more to the point, the three half2 operations per pair of bytes issue at ~0.25 instructions per clock
-// per warp; folding the group scales into per-group accumulators (bytes straight into the MMA) is the next step.  The CTA's four warps are merged
+// 2 KV heads, 128 splits): 55 us with the merge, 0.40 of the HBM rate (69 us when every byte pair was dequantised
+// by three half2 operations before the MMA; 433 us as a scalar kernel).  What is left: 72 `movmatrix` and 36 MMAs
+// per 16 keys on the warp-level tensor path, and a warp's loads are not overlapped with its own arithmetic (the
+// next tile's 64 registers do not fit beside the accumulators).  The CTA's four warps are merged
 // in shared memory and every split writes (o, m, l) partials for mxb_merge_partials.  HBM-bound: 2 x (256 + 16)
 // bytes per key and KV head are read once.
 constexpr int QD_D = 256, QD_WARPS = 4, QD_MAXG = 8, QD_TILE = 16;
@@ -139,12 +146,26 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
   asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
   return d;
 }
-// bytes (2 which, 2 which + 1) of w, dequantised: (u * scale + bias) as two fp16 values in one register
-__device__ __forceinline__ uint32_t dequant_pair(uint32_t w, int which, __half2 scale, __half2 bias) {
-  uint32_t r = __byte_perm(w, 0x64646464u, which == 0 ? 0x4140 : 0x4342);   // 0x6400 | u = 1024 + u, exactly
-  const __half2 u = __hsub2(*reinterpret_cast<__half2*>(&r), __floats2half2_rn(1024.f, 1024.f));
-  const __half2 x = __hfma2(u, scale, bias);
-  return *reinterpret_cast<const uint32_t*>(&x);
+// four consecutive scales or biases (the four groups of one row) as floats
+template <int ST>
+__device__ __forceinline__ void load_group4(const void* base, int64_t idx, float (&f)[4]) {
+  if constexpr (ST == MXB_F32) {
+    const float4 v = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + idx));
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+  } else {
+    const uint2 v = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(base) + idx));
+    if constexpr (ST == MXB_F16) {
+      const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x)), c = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+      f[0] = a.x; f[1] = a.y; f[2] = c.x; f[3] = c.y;
+    } else {
+      f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xFFFF0000u);
+      f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xFFFF0000u);
+    }
+  }
+}
+// bytes (2 which, 2 which + 1) of w as the fp16 pair (1024 + u0, 1024 + u1), exactly: 0x6400 | u
+__device__ __forceinline__ uint32_t byte_pair_f16(uint32_t w, int which) {
+  return __byte_perm(w, 0x64646464u, which == 0 ? 0x4140 : 0x4342);
 }
 
 template <int ST>
@@ -156,13 +177,14 @@ __global__ void __launch_bounds__(QD_WARPS * 32) q8_decode_kernel(Q8DecodeParams
   const int g = lane >> 2, t = lane & 3;
   const int G = p.Hq / p.Hkv;
 
-  // q as B fragments: head g, features 64 t + 4 s + {0, 1} and + {2, 3}, times scale * log2(e), fp16
+  // q as B fragments of k-step i = 4 grp + w: head g, features 64 grp + 16 t + 4 w + {0, 1} and + {2, 3}, times
+  // scale * log2(e), fp16.  The sixteen features of a k-step lie in ONE quantisation group.
   uint32_t qb[16][2];
 #pragma unroll
-  for (int s = 0; s < 16; ++s) {
+  for (int i = 0; i < 16; ++i) {
     float f[4] = {0.f, 0.f, 0.f, 0.f};
     if (g < G) {
-      const int64_t off = (int64_t)(kvh * G + g) * QD_D + 64 * t + 4 * s;
+      const int64_t off = (int64_t)(kvh * G + g) * QD_D + 64 * (i >> 2) + 16 * t + 4 * (i & 3);
 #pragma unroll
       for (int e = 0; e < 4; ++e)
         f[e] = (p.q_dtype == MXB_F32   ? load_elem<MXB_F32>(p.q, off + e)
@@ -170,15 +192,31 @@ __global__ void __launch_bounds__(QD_WARPS * 32) q8_decode_kernel(Q8DecodeParams
                                        : load_elem<MXB_BF16>(p.q, off + e)) * p.scale_log2;
     }
     const __half2 lo = __floats2half2_rn(f[0], f[1]), hi = __floats2half2_rn(f[2], f[3]);
-    qb[s][0] = *reinterpret_cast<const uint32_t*>(&lo);
-    qb[s][1] = *reinterpret_cast<const uint32_t*>(&hi);
+    qb[i][0] = *reinterpret_cast<const uint32_t*>(&lo);
+    qb[i][1] = *reinterpret_cast<const uint32_t*>(&hi);
+  }
+  // sums of q (as the MMA reads it) over each group, in the accumulator layout: qsum[grp][e] = head 2 t + e
+  float qsum[4][2];
+#pragma unroll
+  for (int grp = 0; grp < 4; ++grp) {
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int w = 0; w < 4; ++w)
+      mma_f16_16816(c, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, qb[4 * grp + w][0], qb[4 * grp + w][1]);
+    qsum[grp][0] = c[0];
+    qsum[grp][1] = c[1];
   }
 
   float m_run[2] = {-INFINITY, -INFINITY};   // heads 2 t, 2 t + 1 (the same in the eight lanes that share t)
   float l_run[2] = {0.f, 0.f};               // ... over this lane's keys only
-  float o[16][4];                            // o[i][c]: head 2 t + c % 2, dim 64 (g / 2) + 2 (2 i + c / 2) + g % 2
+  float o[16][4];   // o[i][c]: head 2 t + c % 2, dim 64 (i / 4) + 16 (g / 2) + 4 (i % 4) + 2 (c / 2) + g % 2
 #pragma unroll
   for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  // what the byte operands leave out, per group and head 2 t + e, over this lane's keys only:
+  // sum of P * (bias - 1024 scale)  (P as the value MMA reads it: rounded, times the rounded scale)
+  float ofix[4][2];
+#pragma unroll
+  for (int grp = 0; grp < 4; ++grp) ofix[grp][0] = ofix[grp][1] = 0.f;
 
   const int per = (p.P + p.nsplit - 1) / p.nsplit;
   const int k_lo = min(split * per, p.P), k_hi = min(k_lo + per, p.P);
@@ -188,25 +226,39 @@ __global__ void __launch_bounds__(QD_WARPS * 32) q8_decode_kernel(Q8DecodeParams
     const int key0 = k_lo + tile * QD_TILE;
     const bool ok0 = key0 + g < k_hi, ok1 = key0 + g + 8 < k_hi;
     const int64_t r0 = hb + min(key0 + g, k_hi - 1), r1 = hb + min(key0 + g + 8, k_hi - 1);   // clamped rows are masked below
-    uint32_t kr0[16], kr1[16], vr0[16], vr1[16];   // this lane's 64 bytes of the four rows
+    uint32_t kr0[16], kr1[16], vr0[16], vr1[16];   // bytes [16 t, 16 t + 16) of every group of the four rows
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-      *reinterpret_cast<uint4*>(&kr0[4 * c]) = __ldg(reinterpret_cast<const uint4*>(p.kp + r0 * 64) + t * 4 + c);
-      *reinterpret_cast<uint4*>(&kr1[4 * c]) = __ldg(reinterpret_cast<const uint4*>(p.kp + r1 * 64) + t * 4 + c);
-      *reinterpret_cast<uint4*>(&vr0[4 * c]) = __ldg(reinterpret_cast<const uint4*>(p.vp + r0 * 64) + t * 4 + c);
-      *reinterpret_cast<uint4*>(&vr1[4 * c]) = __ldg(reinterpret_cast<const uint4*>(p.vp + r1 * 64) + t * 4 + c);
+      *reinterpret_cast<uint4*>(&kr0[4 * c]) = __ldg(reinterpret_cast<const uint4*>(p.kp + r0 * 64) + c * 4 + t);
+      *reinterpret_cast<uint4*>(&kr1[4 * c]) = __ldg(reinterpret_cast<const uint4*>(p.kp + r1 * 64) + c * 4 + t);
+      *reinterpret_cast<uint4*>(&vr0[4 * c]) = __ldg(reinterpret_cast<const uint4*>(p.vp + r0 * 64) + c * 4 + t);
+      *reinterpret_cast<uint4*>(&vr1[4 * c]) = __ldg(reinterpret_cast<const uint4*>(p.vp + r1 * 64) + c * 4 + t);
     }
-    const __half2 ks0 = __float2half2_rn(load_elem<ST>(p.ks, r0 * 4 + t)), kb0 = __float2half2_rn(load_elem<ST>(p.kb, r0 * 4 + t));
-    const __half2 ks1 = __float2half2_rn(load_elem<ST>(p.ks, r1 * 4 + t)), kb1 = __float2half2_rn(load_elem<ST>(p.kb, r1 * 4 + t));
-    const __half2 vs0 = __float2half2_rn(load_elem<ST>(p.vs, r0 * 4 + t)), vb0 = __float2half2_rn(load_elem<ST>(p.vb, r0 * 4 + t));
-    const __half2 vs1 = __float2half2_rn(load_elem<ST>(p.vs, r1 * 4 + t)), vb1 = __float2half2_rn(load_elem<ST>(p.vb, r1 * 4 + t));
+    float ks0[4], kb0[4], ks1[4], kb1[4], vs0[4], vb0[4], vs1[4], vb1[4];
+    load_group4<ST>(p.ks, r0 * 4, ks0); load_group4<ST>(p.kb, r0 * 4, kb0);
+    load_group4<ST>(p.ks, r1 * 4, ks1); load_group4<ST>(p.kb, r1 * 4, kb1);
+    load_group4<ST>(p.vs, r0 * 4, vs0); load_group4<ST>(p.vb, r0 * 4, vb0);
+    load_group4<ST>(p.vs, r1 * 4, vs1); load_group4<ST>(p.vb, r1 * 4, vb1);
 
-    // ---- S = K q^T (log2 units): c0, c1 = key g, heads 2 t, 2 t + 1; c2, c3 = key g + 8
+    // ---- S = K q^T (log2 units): c0, c1 = key g, heads 2 t, 2 t + 1; c2, c3 = key g + 8.  The bytes go into the
+    // MMA as 1024 + u; per group, w = u * scale + bias = (1024 + u) * scale + (bias - 1024 scale), so
+    // S += scale * (bytes . q) + (bias - 1024 scale) * (sum of q over the group).
     float sc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int s = 0; s < 16; ++s)
-      mma_f16_16816(sc, dequant_pair(kr0[s], 0, ks0, kb0), dequant_pair(kr1[s], 0, ks1, kb1),
-                    dequant_pair(kr0[s], 1, ks0, kb0), dequant_pair(kr1[s], 1, ks1, kb1), qb[s][0], qb[s][1]);
+    for (int grp = 0; grp < 4; ++grp) {
+      float a[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const int i = 4 * grp + w;
+        mma_f16_16816(a, byte_pair_f16(kr0[i], 0), byte_pair_f16(kr1[i], 0), byte_pair_f16(kr0[i], 1),
+                      byte_pair_f16(kr1[i], 1), qb[i][0], qb[i][1]);
+      }
+      const float o0 = fmaf(-1024.f, ks0[grp], kb0[grp]), o1 = fmaf(-1024.f, ks1[grp], kb1[grp]);
+      sc[0] += fmaf(ks0[grp], a[0], o0 * qsum[grp][0]);
+      sc[1] += fmaf(ks0[grp], a[1], o0 * qsum[grp][1]);
+      sc[2] += fmaf(ks1[grp], a[2], o1 * qsum[grp][0]);
+      sc[3] += fmaf(ks1[grp], a[3], o1 * qsum[grp][1]);
+    }
     if (!ok0) sc[0] = sc[1] = -INFINITY;
     if (!ok1) sc[2] = sc[3] = -INFINITY;
     float mt0 = fmaxf(sc[0], sc[2]), mt1 = fmaxf(sc[1], sc[3]);
@@ -224,6 +276,11 @@ __global__ void __launch_bounds__(QD_WARPS * 32) q8_decode_kernel(Q8DecodeParams
         o[i][0] *= c0; o[i][2] *= c0;
         o[i][1] *= c1; o[i][3] *= c1;
       }
+#pragma unroll
+      for (int grp = 0; grp < 4; ++grp) {
+        ofix[grp][0] *= c0;
+        ofix[grp][1] *= c1;
+      }
       l_run[0] *= c0;
       l_run[1] *= c1;
       m_run[0] = mn0;
@@ -235,17 +292,41 @@ __global__ void __launch_bounds__(QD_WARPS * 32) q8_decode_kernel(Q8DecodeParams
     const __half2 plo = __floats2half2_rn(p00, p01), phi = __floats2half2_rn(p10, p11);
     l_run[0] += __low2float(plo) + __low2float(phi);   // the weights as the MMA reads them
     l_run[1] += __high2float(plo) + __high2float(phi);
-    const uint32_t pb0 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&plo));   // head g, keys 2 t, 2 t + 1
-    const uint32_t pb1 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&phi));   // head g, keys 2 t + 8, 2 t + 9
 
-    // ---- O^T += V^T P, 16 dims per MMA: rows 0-7 from value pair 2 i, rows 8-15 from pair 2 i + 1
+    // ---- O^T += V^T P, 16 dims of ONE group per MMA: the value bytes go in as 1024 + u, the key's scale for that
+    // group goes into P (rounded to fp16: what the MMA reads), and the rest, sum of P * scale * (bias / scale - 1024),
+    // is kept beside the accumulators with the same rounded weights
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const uint32_t a0 = movmatrix_trans(dequant_pair(vr0[i], 0, vs0, vb0));
-      const uint32_t a1 = movmatrix_trans(dequant_pair(vr0[i], 1, vs0, vb0));
-      const uint32_t a2 = movmatrix_trans(dequant_pair(vr1[i], 0, vs1, vb1));
-      const uint32_t a3 = movmatrix_trans(dequant_pair(vr1[i], 1, vs1, vb1));
-      mma_f16_16816(o[i], a0, a1, a2, a3, pb0, pb1);
+    for (int grp = 0; grp < 4; ++grp) {
+      const __half2 w0 = __hmul2(plo, __float2half2_rn(vs0[grp])), w1 = __hmul2(phi, __float2half2_rn(vs1[grp]));
+      const uint32_t pb0 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&w0));   // head g, keys 2 t, 2 t + 1
+      const uint32_t pb1 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&w1));   // head g, keys 2 t + 8, 2 t + 9
+      // bias * P - 1024 * (P * scale as rounded)
+      ofix[grp][0] += fmaf(__low2float(plo), vb0[grp], fmaf(__low2float(phi), vb1[grp], -1024.f * (__low2float(w0) + __low2float(w1))));
+      ofix[grp][1] += fmaf(__high2float(plo), vb0[grp], fmaf(__high2float(phi), vb1[grp], -1024.f * (__high2float(w0) + __high2float(w1))));
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const int i = 4 * grp + w;
+        const uint32_t a0 = movmatrix_trans(byte_pair_f16(vr0[i], 0));
+        const uint32_t a1 = movmatrix_trans(byte_pair_f16(vr0[i], 1));
+        const uint32_t a2 = movmatrix_trans(byte_pair_f16(vr1[i], 0));
+        const uint32_t a3 = movmatrix_trans(byte_pair_f16(vr1[i], 1));
+        mma_f16_16816(o[i], a0, a1, a2, a3, pb0, pb1);
+      }
+    }
+  }
+  // the left-out terms, summed over the eight lanes (keys) that share t, join every dim of their group
+#pragma unroll
+  for (int grp = 0; grp < 4; ++grp) {
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {
+      ofix[grp][0] += __shfl_xor_sync(0xffffffffu, ofix[grp][0], off);
+      ofix[grp][1] += __shfl_xor_sync(0xffffffffu, ofix[grp][1], off);
+    }
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      o[4 * grp + w][0] += ofix[grp][0]; o[4 * grp + w][2] += ofix[grp][0];
+      o[4 * grp + w][1] += ofix[grp][1]; o[4 * grp + w][3] += ofix[grp][1];
     }
   }
 
@@ -265,7 +346,7 @@ __global__ void __launch_bounds__(QD_WARPS * 32) q8_decode_kernel(Q8DecodeParams
   for (int i = 0; i < 16; ++i)
 #pragma unroll
     for (int c = 0; c < 4; ++c)
-      o_s[warp][2 * t + (c & 1)][64 * (g >> 1) + 2 * (2 * i + (c >> 1)) + (g & 1)] = o[i][c];
+      o_s[warp][2 * t + (c & 1)][64 * (i >> 2) + 16 * (g >> 1) + 4 * (i & 3) + 2 * (c >> 1) + (g & 1)] = o[i][c];
   __syncthreads();
   for (int i = tid; i < G * QD_D; i += QD_WARPS * 32) {
     const int h = i / QD_D, d = i % QD_D;
