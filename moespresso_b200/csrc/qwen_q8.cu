@@ -111,14 +111,17 @@ __global__ void __launch_bounds__(128) affine_q8_dequantize_kernel(const uint32_
 //     multiplied into P (rounded to fp16, two more transposes bring it to the B layout), and
 //     sum over keys of P * bias - 1024 * (P * scale as rounded) is kept per group and head beside the accumulators
 //     and added to every dim of the group at the end: the 1024s cancel against exactly the weights the MMA used.
-// Online softmax per head with a lazy rescale of O^T (only when a maximum moved).  Measured on a B200 (131,072 keys,
-// 2 KV heads, 128 splits): 55 us with the merge, 0.40 of the HBM rate (69 us when every byte pair was dequantised
-// by three half2 operations before the MMA; 433 us as a scalar kernel).  What is left: 72 `movmatrix` and 36 MMAs
-// per 16 keys on the warp-level tensor path, and a warp's loads are not overlapped with its own arithmetic (the
-// next tile's 64 registers do not fit beside the accumulators).  The CTA's four warps are merged
-// in shared memory and every split writes (o, m, l) partials for mxb_merge_partials.  HBM-bound: 2 x (256 + 16)
-// bytes per key and KV head are read once.
+// Online softmax per head with a lazy rescale of O^T (only when a maximum moved).  A warp's loads run one tile ahead
+// of its arithmetic through shared memory (`cp.async`, see the kernel), the q fragments live in shared memory too,
+// and three CTAs fit an SM.  Measured on a B200 (131,072 keys, 2 KV heads, 128 splits): 51 us with the merge
+// (~41 us for this kernel = 3.6 TB/s of DRAM traffic, 0.43 of the HBM rate over the algorithmic bytes with the merge;
+// 55 us before the staging; 69 us when every byte pair was dequantised by three half2 operations before the MMA;
+// 433 us as a scalar kernel).  What is left: 72 `movmatrix` and 36 MMAs per 16 keys on the warp-level tensor path
+// (0.36 instructions per clock per scheduler; stalls spread over long scoreboard, short scoreboard and fixed
+// latency).  The CTA's four warps are merged in shared memory and every split writes (o, m, l) partials for
+// mxb_merge_partials.  HBM-bound: 2 x (256 + 16) bytes per key and KV head are read once.
 constexpr int QD_D = 256, QD_WARPS = 4, QD_MAXG = 8, QD_TILE = 16;
+constexpr int QD_STAGES = 2;   // tiles of a warp in shared memory: one in use, one on its way
 
 struct Q8DecodeParams {
   const void* q;           // [Hq, 256]
@@ -146,14 +149,21 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
   asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
   return d;
 }
-// four consecutive scales or biases (the four groups of one row) as floats
+// Asynchronous copies of 16 or 8 bytes from global to shared memory; groups of them are waited for in order.
+__device__ __forceinline__ void stage16(void* smem_dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void stage8(void* smem_dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
+}
+// four consecutive scales or biases out of a lane's staging slot
 template <int ST>
-__device__ __forceinline__ void load_group4(const void* base, int64_t idx, float (&f)[4]) {
+__device__ __forceinline__ void staged_group4(const uint8_t* slot, float (&f)[4]) {
   if constexpr (ST == MXB_F32) {
-    const float4 v = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + idx));
+    const float4 v = *reinterpret_cast<const float4*>(slot);
     f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
   } else {
-    const uint2 v = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(base) + idx));
+    const uint2 v = *reinterpret_cast<const uint2*>(slot);
     if constexpr (ST == MXB_F16) {
       const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x)), c = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
       f[0] = a.x; f[1] = a.y; f[2] = c.x; f[3] = c.y;
@@ -169,18 +179,30 @@ __device__ __forceinline__ uint32_t byte_pair_f16(uint32_t w, int which) {
 }
 
 template <int ST>
-__global__ void __launch_bounds__(QD_WARPS * 32) q8_decode_kernel(Q8DecodeParams p) {
-  __shared__ float o_s[QD_WARPS][QD_MAXG][QD_D];   // the warps' accumulators at the end
+__global__ void __launch_bounds__(QD_WARPS * 32, 3) q8_decode_kernel(Q8DecodeParams p) {
+  // Every lane stages its own pieces of the next tile in shared memory (16 x 16 bytes of packed rows, piece j of
+  // lane l at (j * 32 + l): it reads back only what it copied itself) and two of the eight (scales | biases) x
+  // (keys | values) x (row g | row g + 8) slots of its key rows, which the four lanes of a quad share (hence the
+  // warp-wide wait below).  Loads run a tile ahead of the arithmetic without holding registers, which together
+  // with the q fragments in shared memory leaves room for three CTAs per SM.  The staging memory takes the warps'
+  // accumulators at the end.
+  extern __shared__ __align__(16) uint8_t q8_smem[];
+  float (*o_s)[QD_MAXG][QD_D] = reinterpret_cast<float (*)[QD_MAXG][QD_D]>(q8_smem);
   __shared__ float m_s[QD_WARPS][QD_MAXG], l_s[QD_WARPS][QD_MAXG];
+  constexpr int SB = ST == MXB_F32 ? 16 : 8;               // bytes of four scales
+  constexpr int STAGE_BYTES = 16 * 512 + 8 * 8 * SB;        // per warp and tile: packed pieces, then [slot][g]
+  uint32_t* qb_s = reinterpret_cast<uint32_t*>(q8_smem + (size_t)QD_WARPS * QD_STAGES * STAGE_BYTES);   // [16][2][32 lanes]
+
   const int split = blockIdx.x, kvh = blockIdx.y;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int G = p.Hq / p.Hkv;
+  uint8_t* my_stage = q8_smem + (size_t)warp * QD_STAGES * STAGE_BYTES;
 
   // q as B fragments of k-step i = 4 grp + w: head g, features 64 grp + 16 t + 4 w + {0, 1} and + {2, 3}, times
   // scale * log2(e), fp16.  The sixteen features of a k-step lie in ONE quantisation group.
-  uint32_t qb[16][2];
-#pragma unroll
+  if (warp == 0) {
+#pragma unroll 1
   for (int i = 0; i < 16; ++i) {
     float f[4] = {0.f, 0.f, 0.f, 0.f};
     if (g < G) {
@@ -192,9 +214,11 @@ __global__ void __launch_bounds__(QD_WARPS * 32) q8_decode_kernel(Q8DecodeParams
                                        : load_elem<MXB_BF16>(p.q, off + e)) * p.scale_log2;
     }
     const __half2 lo = __floats2half2_rn(f[0], f[1]), hi = __floats2half2_rn(f[2], f[3]);
-    qb[i][0] = *reinterpret_cast<const uint32_t*>(&lo);
-    qb[i][1] = *reinterpret_cast<const uint32_t*>(&hi);
+    qb_s[(i * 2 + 0) * 32 + lane] = *reinterpret_cast<const uint32_t*>(&lo);
+    qb_s[(i * 2 + 1) * 32 + lane] = *reinterpret_cast<const uint32_t*>(&hi);
   }
+  }
+  __syncthreads();
   // sums of q (as the MMA reads it) over each group, in the accumulator layout: qsum[grp][e] = head 2 t + e
   float qsum[4][2];
 #pragma unroll
@@ -202,7 +226,8 @@ __global__ void __launch_bounds__(QD_WARPS * 32) q8_decode_kernel(Q8DecodeParams
     float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int w = 0; w < 4; ++w)
-      mma_f16_16816(c, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, qb[4 * grp + w][0], qb[4 * grp + w][1]);
+      mma_f16_16816(c, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, qb_s[((4 * grp + w) * 2 + 0) * 32 + lane],
+                    qb_s[((4 * grp + w) * 2 + 1) * 32 + lane]);
     qsum[grp][0] = c[0];
     qsum[grp][1] = c[1];
   }
@@ -222,23 +247,59 @@ __global__ void __launch_bounds__(QD_WARPS * 32) q8_decode_kernel(Q8DecodeParams
   const int k_lo = min(split * per, p.P), k_hi = min(k_lo + per, p.P);
   const int ntiles = (k_hi - k_lo + QD_TILE - 1) / QD_TILE;
   const int64_t hb = (int64_t)kvh * p.head_stride_rows;
+  const int esz = ST == MXB_F32 ? 4 : 2;
+  auto issue_tile = [&](int tile, int stage) {   // this lane's pieces of a tile, on their way into its staging slots
+    if (tile < ntiles) {
+      const int key0 = k_lo + tile * QD_TILE;
+      const int64_t r0 = hb + min(key0 + g, k_hi - 1), r1 = hb + min(key0 + g + 8, k_hi - 1);   // clamped rows are masked later
+      uint8_t* st = my_stage + (size_t)stage * STAGE_BYTES;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        stage16(st + ((0 + c) * 32 + lane) * 16, reinterpret_cast<const uint4*>(p.kp + r0 * 64) + c * 4 + t);
+        stage16(st + ((4 + c) * 32 + lane) * 16, reinterpret_cast<const uint4*>(p.kp + r1 * 64) + c * 4 + t);
+        stage16(st + ((8 + c) * 32 + lane) * 16, reinterpret_cast<const uint4*>(p.vp + r0 * 64) + c * 4 + t);
+        stage16(st + ((12 + c) * 32 + lane) * 16, reinterpret_cast<const uint4*>(p.vp + r1 * 64) + c * 4 + t);
+      }
+      uint8_t* ss = st + 16 * 512;
+      // slots: 0 ks(r0) 1 kb(r0) 2 ks(r1) 3 kb(r1) 4 vs(r0) 5 vb(r0) 6 vs(r1) 7 vb(r1); lane t copies slots t, t + 4
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int j = t + 4 * half;
+        const void* base = half == 0 ? ((j & 1) ? p.kb : p.ks) : ((j & 1) ? p.vb : p.vs);
+        const int64_t r = (j & 2) ? r1 : r0;
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(base) + r * 4 * esz;
+        if constexpr (ST == MXB_F32) stage16(ss + (j * 8 + g) * SB, src);
+        else stage8(ss + (j * 8 + g) * SB, src);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");   // (an empty group past the last tile keeps the count uniform)
+  };
+#pragma unroll
+  for (int s0 = 0; s0 < QD_STAGES - 1; ++s0) issue_tile(warp + s0 * QD_WARPS, s0);
+  int stage = 0;
   for (int tile = warp; tile < ntiles; tile += QD_WARPS) {
     const int key0 = k_lo + tile * QD_TILE;
     const bool ok0 = key0 + g < k_hi, ok1 = key0 + g + 8 < k_hi;
-    const int64_t r0 = hb + min(key0 + g, k_hi - 1), r1 = hb + min(key0 + g + 8, k_hi - 1);   // clamped rows are masked below
-    uint32_t kr0[16], kr1[16], vr0[16], vr1[16];   // bytes [16 t, 16 t + 16) of every group of the four rows
+    __syncwarp();   // every lane is done with the slots that the next copies overwrite
+    {
+      int ahead = stage + QD_STAGES - 1;
+      if (ahead >= QD_STAGES) ahead -= QD_STAGES;
+      issue_tile(tile + (QD_STAGES - 1) * QD_WARPS, ahead);
+    }
+    asm volatile("cp.async.wait_group %0;" ::"n"(QD_STAGES - 1) : "memory");   // this tile's pieces have landed
+    __syncwarp();                                                                // ... those of the other lanes of the quad too
+    const uint8_t* st = my_stage + (size_t)stage * STAGE_BYTES;
+    const uint8_t* ss = st + 16 * 512;
+    stage = stage + 1 == QD_STAGES ? 0 : stage + 1;
+    uint32_t kr0[16], kr1[16];   // bytes [16 t, 16 t + 16) of every group of key rows g and g + 8
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-      *reinterpret_cast<uint4*>(&kr0[4 * c]) = __ldg(reinterpret_cast<const uint4*>(p.kp + r0 * 64) + c * 4 + t);
-      *reinterpret_cast<uint4*>(&kr1[4 * c]) = __ldg(reinterpret_cast<const uint4*>(p.kp + r1 * 64) + c * 4 + t);
-      *reinterpret_cast<uint4*>(&vr0[4 * c]) = __ldg(reinterpret_cast<const uint4*>(p.vp + r0 * 64) + c * 4 + t);
-      *reinterpret_cast<uint4*>(&vr1[4 * c]) = __ldg(reinterpret_cast<const uint4*>(p.vp + r1 * 64) + c * 4 + t);
+      *reinterpret_cast<uint4*>(&kr0[4 * c]) = *reinterpret_cast<const uint4*>(st + ((0 + c) * 32 + lane) * 16);
+      *reinterpret_cast<uint4*>(&kr1[4 * c]) = *reinterpret_cast<const uint4*>(st + ((4 + c) * 32 + lane) * 16);
     }
-    float ks0[4], kb0[4], ks1[4], kb1[4], vs0[4], vb0[4], vs1[4], vb1[4];
-    load_group4<ST>(p.ks, r0 * 4, ks0); load_group4<ST>(p.kb, r0 * 4, kb0);
-    load_group4<ST>(p.ks, r1 * 4, ks1); load_group4<ST>(p.kb, r1 * 4, kb1);
-    load_group4<ST>(p.vs, r0 * 4, vs0); load_group4<ST>(p.vb, r0 * 4, vb0);
-    load_group4<ST>(p.vs, r1 * 4, vs1); load_group4<ST>(p.vb, r1 * 4, vb1);
+    float ks0[4], kb0[4], ks1[4], kb1[4];
+    staged_group4<ST>(ss + (0 * 8 + g) * SB, ks0); staged_group4<ST>(ss + (1 * 8 + g) * SB, kb0);
+    staged_group4<ST>(ss + (2 * 8 + g) * SB, ks1); staged_group4<ST>(ss + (3 * 8 + g) * SB, kb1);
 
     // ---- S = K q^T (log2 units): c0, c1 = key g, heads 2 t, 2 t + 1; c2, c3 = key g + 8.  The bytes go into the
     // MMA as 1024 + u; per group, w = u * scale + bias = (1024 + u) * scale + (bias - 1024 scale), so
@@ -251,7 +312,7 @@ __global__ void __launch_bounds__(QD_WARPS * 32) q8_decode_kernel(Q8DecodeParams
       for (int w = 0; w < 4; ++w) {
         const int i = 4 * grp + w;
         mma_f16_16816(a, byte_pair_f16(kr0[i], 0), byte_pair_f16(kr1[i], 0), byte_pair_f16(kr0[i], 1),
-                      byte_pair_f16(kr1[i], 1), qb[i][0], qb[i][1]);
+                      byte_pair_f16(kr1[i], 1), qb_s[(i * 2 + 0) * 32 + lane], qb_s[(i * 2 + 1) * 32 + lane]);
       }
       const float o0 = fmaf(-1024.f, ks0[grp], kb0[grp]), o1 = fmaf(-1024.f, ks1[grp], kb1[grp]);
       sc[0] += fmaf(ks0[grp], a[0], o0 * qsum[grp][0]);
@@ -293,6 +354,15 @@ __global__ void __launch_bounds__(QD_WARPS * 32) q8_decode_kernel(Q8DecodeParams
     l_run[0] += __low2float(plo) + __low2float(phi);   // the weights as the MMA reads them
     l_run[1] += __high2float(plo) + __high2float(phi);
 
+    uint32_t vr0[16], vr1[16];   // the value rows, read from the staging slots only now
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      *reinterpret_cast<uint4*>(&vr0[4 * c]) = *reinterpret_cast<const uint4*>(st + ((8 + c) * 32 + lane) * 16);
+      *reinterpret_cast<uint4*>(&vr1[4 * c]) = *reinterpret_cast<const uint4*>(st + ((12 + c) * 32 + lane) * 16);
+    }
+    float vs0[4], vb0[4], vs1[4], vb1[4];
+    staged_group4<ST>(ss + (4 * 8 + g) * SB, vs0); staged_group4<ST>(ss + (5 * 8 + g) * SB, vb0);
+    staged_group4<ST>(ss + (6 * 8 + g) * SB, vs1); staged_group4<ST>(ss + (7 * 8 + g) * SB, vb1);
     // ---- O^T += V^T P, 16 dims of ONE group per MMA: the value bytes go in as 1024 + u, the key's scale for that
     // group goes into P (rounded to fp16: what the MMA reads), and the rest, sum of P * scale * (bias / scale - 1024),
     // is kept beside the accumulators with the same rounded weights
@@ -336,6 +406,8 @@ __global__ void __launch_bounds__(QD_WARPS * 32) q8_decode_kernel(Q8DecodeParams
     l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], off);
     l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], off);
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();   // the staging memory becomes the accumulator exchange
   if (g == 0) {
     m_s[warp][2 * t] = m_run[0];
     m_s[warp][2 * t + 1] = m_run[1];
@@ -435,6 +507,12 @@ extern "C" int mxb_sdpa_decode_q8(const mxb_sdpa_decode_q8_args* a, void* stream
               MXB_ERR_INVALID, "q8 decode: null tensor");
   MXB_REQUIRE(((reinterpret_cast<uintptr_t>(a->k_packed) | reinterpret_cast<uintptr_t>(a->v_packed)) & 15) == 0,
               MXB_ERR_INVALID, "q8 decode: packed words must be 16-byte aligned");
+  {
+    const uintptr_t sb = reinterpret_cast<uintptr_t>(a->k_scales) | reinterpret_cast<uintptr_t>(a->k_biases) |
+                         reinterpret_cast<uintptr_t>(a->v_scales) | reinterpret_cast<uintptr_t>(a->v_biases);
+    MXB_REQUIRE((sb & (a->sb_dtype == MXB_F32 ? 15u : 7u)) == 0, MXB_ERR_INVALID,
+                "q8 decode: scales and biases must be aligned to the four values of a row");
+  }
   Q8DecodeParams p{};
   p.q = a->q; p.q_dtype = a->q_dtype;
   p.kp = reinterpret_cast<const uint32_t*>(a->k_packed); p.ks = a->k_scales; p.kb = a->k_biases;
@@ -445,7 +523,14 @@ extern "C" int mxb_sdpa_decode_q8(const mxb_sdpa_decode_q8_args* a, void* stream
   p.o_parts = a->o_parts; p.ml_parts = a->ml_parts;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   dim3 grid((unsigned)a->n_splits, (unsigned)a->Hkv);
-#define MXB_QD(ST) q8_decode_kernel<ST><<<grid, QD_WARPS * 32, 0, st>>>(p);
+#define MXB_QD(ST)                                                                                              \
+  {                                                                                                             \
+    const int stage_bytes = QD_WARPS * QD_STAGES * (16 * 512 + 8 * 8 * ((ST) == MXB_F32 ? 16 : 8)) + 16 * 2 * 32 * 4; \
+    const int out_bytes = QD_WARPS * QD_MAXG * QD_D * 4;                                                         \
+    const int smem = stage_bytes > out_bytes ? stage_bytes : out_bytes;                                          \
+    MXB_CUDA_OK(cudaFuncSetAttribute(q8_decode_kernel<ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
+    q8_decode_kernel<ST><<<grid, QD_WARPS * 32, smem, st>>>(p);                                                 \
+  }
   if (a->sb_dtype == MXB_F32) MXB_QD(MXB_F32)
   else if (a->sb_dtype == MXB_F16) MXB_QD(MXB_F16)
   else if (a->sb_dtype == MXB_BF16) MXB_QD(MXB_BF16)
