@@ -113,9 +113,9 @@ __global__ void __launch_bounds__(128) affine_q8_dequantize_kernel(const uint32_
 //     and added to every dim of the group at the end: the 1024s cancel against exactly the weights the MMA used.
 // Online softmax per head with a lazy rescale of O^T (only when a maximum moved).  A warp's loads run one tile ahead
 // of its arithmetic through shared memory (`cp.async`, see the kernel), the q fragments live in shared memory too,
-// and three CTAs fit an SM.  Measured on a B200 (131,072 keys, 2 KV heads, 128 splits): 51 us with the merge
-// (~41 us for this kernel = 3.6 TB/s of DRAM traffic, 0.43 of the HBM rate over the algorithmic bytes with the merge;
-// 55 us before the staging; 69 us when every byte pair was dequantised by three half2 operations before the MMA;
+// and three CTAs fit an SM.  Measured on a B200 (131,072 keys, 2 KV heads, 128 splits): 45 us with the merge
+// (~41 us for this kernel = 3.6 TB/s of DRAM traffic, 0.49 of the HBM rate over the algorithmic bytes with the merge;
+// 55 us before the staging and with a slower merge; 69 us when every byte pair was dequantised by three half2 operations before the MMA;
 // 433 us as a scalar kernel).  What is left: 72 `movmatrix` and 36 MMAs per 16 keys on the warp-level tensor path
 // (0.36 instructions per clock per scheduler; stalls spread over long scoreboard, short scoreboard and fixed
 // latency).  The CTA's four warps are merged in shared memory and every split writes (o, m, l) partials for

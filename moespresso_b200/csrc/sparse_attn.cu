@@ -433,7 +433,7 @@ __global__ void __launch_bounds__(256) merge_rows_kernel(MergeParams p) {
   const int vec = tid % nvec, lane = tid / nvec;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   if (lane < L) {
-    constexpr int kBatch = 8;
+    constexpr int kBatch = 16;   // loads in flight per thread: the splits' rows come from L2, one round trip per batch
     for (int s0 = lane; s0 < p.P; s0 += L * kBatch) {
       float4 v[kBatch];
 #pragma unroll
