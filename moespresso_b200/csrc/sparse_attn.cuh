@@ -33,6 +33,7 @@ struct SparseParams {
   int32_t* status;
   int32_t q_tma;      // q reaches shared memory by TMA (tensor map beside these parameters) instead of registers
   int32_t q_axis[3];  // which of (0 = head, 1 = token, 2 = batch) lies on dimensions 1..3 of that map
+  int32_t cta_base;        // set by the tensor-core launcher: (token, split) index of this launch's CTA 0
   int32_t cluster_merge;   // set by the tensor-core launcher: the splits of a token ran as one thread-block cluster
                            // and merged through shared memory (no partials in the workspace, no merge kernel)
 };

@@ -248,8 +248,9 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
   volatile int* abort_flag = &mi->abort_flag;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int bt = (int)(blockIdx.x / (unsigned)p.nsplit);
-  const int split = (int)(blockIdx.x - (unsigned)bt * (unsigned)p.nsplit);
+  const unsigned cta = blockIdx.x + (unsigned)p.cta_base;
+  const int bt = (int)(cta / (unsigned)p.nsplit);
+  const int split = (int)(cta - (unsigned)bt * (unsigned)p.nsplit);
   const int b = bt / p.T, t = bt % p.T;
   const int nslab = L.nslab;
   const int n_mt = p.Dv / 128;
@@ -1291,11 +1292,21 @@ static int launch_tc_typed(SparseParams& p, int out_dtype, cudaStream_t st) {
     }                                                                                                \
     if (as_cluster) {                                                                                \
       p.cluster_merge = 1;                                                                           \
+      p.cta_base = 0;                                                                                \
       MXB_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p, tm_comp, tm_raw, tm_comp_tail, tm_raw_tail, tm_q)); \
     } else if (CLUSTER) {                                                                            \
       return MXB_ERR_UNSUPPORTED; /* the caller retries with fp32 partials */                         \
     } else {                                                                                         \
-      kern<<<grid, WS_THREADS, smem, st>>>(p, tm_comp, tm_raw, tm_comp_tail, tm_raw_tail, tm_q);     \
+      /* One wave per launch: a CTA never starts on an SM that another CTA of the same launch has   \
+         just left (see the note on launch failures in the kernel's description). */                  \
+      const int64_t wave = (int64_t)(sm_count() / p.nsplit) * p.nsplit > 0                           \
+                               ? (int64_t)(sm_count() / p.nsplit) * p.nsplit : p.nsplit;             \
+      for (int64_t base = 0; base < ctas; base += wave) {                                            \
+        p.cta_base = (int32_t)base;                                                                  \
+        const unsigned n = (unsigned)(ctas - base < wave ? ctas - base : wave);                      \
+        kern<<<dim3(n), WS_THREADS, smem, st>>>(p, tm_comp, tm_raw, tm_comp_tail, tm_raw_tail, tm_q); \
+      }                                                                                              \
+      p.cta_base = 0;                                                                                \
     }                                                                                                \
   }
   const bool try_cluster = p.nsplit >= 2 && p.nsplit <= kMaxClusterMerge && !p.partial_ml && merge_fits;
