@@ -1305,6 +1305,7 @@ static int launch_tc_typed(SparseParams& p, int out_dtype, cudaStream_t st) {
         p.cta_base = (int32_t)base;                                                                  \
         const unsigned n = (unsigned)(ctas - base < wave ? ctas - base : wave);                      \
         kern<<<dim3(n), WS_THREADS, smem, st>>>(p, tm_comp, tm_raw, tm_comp_tail, tm_raw_tail, tm_q); \
+        if (base > 0) note_launch(); /* the first launch is counted below */                          \
       }                                                                                              \
       p.cta_base = 0;                                                                                \
     }                                                                                                \
