@@ -1297,8 +1297,10 @@ static int launch_tc_typed(SparseParams& p, int out_dtype, cudaStream_t st) {
     } else if (CLUSTER) {                                                                            \
       return MXB_ERR_UNSUPPORTED; /* the caller retries with fp32 partials */                         \
     } else {                                                                                         \
-      /* One wave per launch: a CTA never starts on an SM that another CTA of the same launch has   \
-         just left (see the note on launch failures in the kernel's description). */                  \
+      /* One wave per launch.  Launches of this kernel that put a second CTA on an SM which a CTA of  \
+         the same launch had just left have failed ("unspecified launch failure": always for 160    \
+         split CTAs, rarely for 4,096 one-split CTAs) and launches of at most one CTA per SM never   \
+         have; the cause is not known.  Between launches nothing of the previous wave is in flight. */ \
       const int64_t wave = (int64_t)(sm_count() / p.nsplit) * p.nsplit > 0                           \
                                ? (int64_t)(sm_count() / p.nsplit) * p.nsplit : p.nsplit;             \
       for (int64_t base = 0; base < ctas; base += wave) {                                            \
