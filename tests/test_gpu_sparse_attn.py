@@ -431,6 +431,43 @@ def test_tensor_core_kernel_int8_scales_that_rise_and_rows_of_zeros(ns):
     assert float(o.abs().max()) == 0.0 and bool(torch.isfinite(o).all())
 
 
+@pytest.mark.parametrize("kvkind", ["bf16", "int8"])
+def test_tensor_core_kernel_more_tokens_than_sms(kvkind):
+    """More (sequence, token) items than the device has SMs: the tensor-core kernel is issued one wave at a time
+    (at most one CTA per SM per launch), and every item comes out the same as on its own."""
+    need_gpu()
+    from moespresso_b200 import _abi
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    B = sms + 37
+    rng = np.random.default_rng(11)
+    H, Dqk, Dv, R, k = 64, 576, 512, 700, 192
+    q = bf16_round(rng.standard_normal((B, H, Dqk)))
+    if kvkind == "int8":
+        kv = rng.integers(-127, 128, size=(R, Dqk), dtype=np.int8)
+        sc = np.exp(rng.uniform(np.log(1e-3), np.log(1e-1), size=R)).astype(np.float16)
+        rows = kv.astype(np.float64) * sc.astype(np.float64)[:, None]
+        kv_t, sc_t = dev(kv), dev(sc)
+    else:
+        rows32 = bf16_round(rng.standard_normal((R, Dqk)))
+        rows, kv_t, sc_t = rows32.astype(np.float64), dev(rows32, torch.bfloat16), None
+    ids = np.stack([np.sort(rng.choice(R, size=k, replace=False)) for _ in range(B)]).astype(np.int32)
+    zero = torch.zeros(B, dtype=torch.int64, device="cuda")      # every sequence reads the same table
+    count = torch.full((B,), R, dtype=torch.int32, device="cuda")
+    before = int(_abi.load().mxb_kernel_launches())
+    out = iak.sparse_attention(dev(q, torch.bfloat16)[:, :, None, :], kv_t, dev(ids)[:, None, :], None, pos0=0, window=0,
+                               ratio=0, scale=Dqk ** -0.5, d_v=Dv, kv_scales=sc_t, comp_row_start=zero,
+                               comp_row_count=count, n_comp=R, n_splits=1, check=True)
+    assert int(_abi.load().mxb_kernel_launches()) - before == 2      # two waves
+    for b in (0, 1, sms - 1, sms, sms + 1, B - 1):
+        ref = ds4.indexed_mixed_attention_decode(q[b], None, rows, ids[b], None, pos0=0, window=0, ratio=0,
+                                                 scale=Dqk ** -0.5, d_v=Dv)
+        assert max_abs(out[b, :, 0], ref) <= TOL_16 * max(1.0, float(np.abs(ref).max()) / 4), (b, max_abs(out[b, :, 0], ref))
+    alone = iak.sparse_attention(dev(q[sms:sms + 1], torch.bfloat16)[:, :, None, :], kv_t, dev(ids[sms:sms + 1])[:, None, :],
+                                 None, pos0=0, window=0, ratio=0, scale=Dqk ** -0.5, d_v=Dv, kv_scales=sc_t,
+                                 comp_row_start=zero[:1], comp_row_count=count[:1], n_comp=R, n_splits=1)
+    assert torch.equal(alone[0], out[sms])
+
+
 def test_tensor_core_kernel_prefill_form():
     need_gpu()
     rng = np.random.default_rng(8)
