@@ -140,7 +140,7 @@ struct WsMisc {
   uint64_t k_free[2];              // int8 tables: the widening warps have read row buffer b
   uint64_t meta_ready;             // int8 tables: the scales of units 0 and 1 have been published
   uint64_t s_ready[2], s_free[2], p_ready[2];
-  uint64_t p_summed;               // int8 tables: the producer warps have added a unit's P^T to the row sums
+  uint64_t p_summed;               // int8 tables: the widening warps have added a unit's P^T to the row sums
   float row_inv[2][WS_UNIT];       // int8 tables: 1 / row scale of the unit whose P^T is in the buffer (by unit parity)
   int grew[2];                     // int8 tables: the reference maxima moved before this unit's P^T (by unit parity)
   uint64_t pv_blk[2][4];           // P V of one 128-feature block of the unit in buffer b has completed: its two slabs are free
@@ -806,7 +806,7 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
     }
 
     // 16-bit tables: l1 = the sum of the softmax weights of head col0 + li over this warp's rows of all units (the
-    // denominator).  Int8 tables: the producer warps keep both sums (see add_unit).
+    // denominator).  Int8 tables: the widening warps keep both sums (see add_unit).
     float l1 = 0.f;
     for (int u = 0; u < nunits; ++u) {
       const int sb_i = sbuf(u), pb_i = pbuf(u), slot = u & (kRing - 1);
@@ -949,7 +949,7 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(&mi->p_ready[pb_i]);
       if (warp == 0) TRS(8, u);
-      // 16-bit tables: the sums over the 16 rows of this half warp, behind the hand-off (int8 tables: the producer
+      // 16-bit tables: the sums over the 16 rows of this half warp, behind the hand-off (int8 tables: the widening
       // warps sum P^T from shared memory)
       if constexpr (!I8) {
         float a[16];
@@ -973,7 +973,7 @@ sparse_attn_tc_kernel(SparseParams p, const __grid_constant__ CUtensorMap tm_com
     // ------------------------------------------------------------------ per-head sums of this split
     if (tid < WS_HEADS) {
       float l, vb = 0.f;
-      if constexpr (I8) {   // rows 0-1: the denominator's two halves, rows 2-3: the operand weights' (producer warps)
+      if constexpr (I8) {   // rows 0-1: the denominator's two halves, rows 2-3: the operand weights' (widening warps)
         l = nunits >= 1 ? mi->colmax[0][tid] + mi->colmax[1][tid] : 0.f;
         vb = nunits >= 1 ? kValueBias * (mi->colmax[2][tid] + mi->colmax[3][tid]) : 0.f;
       } else {
