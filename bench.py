@@ -428,7 +428,7 @@ def main():
                for name in stage}
     dominant = max(stage, key=stage.get)
     kernel_names = {"indexer_scores": "indexer_decode_kernel<64, 16 heads>", "topk_select": "topk_cluster_kernel",
-                    "sparse_attn": "sparse_attn_tc_kernel<int8 kv, bf16 q> + merge_kernel"}
+                    "sparse_attn": "sparse_attn_tc_kernel<int8 kv, bf16 q> (splits merged inside a cluster)"}
     # DRAM traffic from ncu captures on the --small case (profiles/), scaled by the units each launch processes:
     # the key scan reads 65.0 B and writes 4.8 B per key row; the attention kernel reads 787 B per gathered row
     # (576-byte rows start at any 64-byte offset: sector rounding) plus q; the selection re-reads the scores
